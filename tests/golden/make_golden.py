@@ -1,0 +1,150 @@
+"""Generate tests/golden/*.npz by RUNNING the reference's own pure-torch functions.
+
+The reference package cannot be imported as a whole in this environment
+(`import sglang` needs IPython, `sgl_kernel` is not installed), but the oracle
+functions its tests define are plain torch.  This script parses the reference
+test files, extracts exactly those function definitions with `ast`, executes
+them unmodified in a namespace that only provides torch, and stores their
+inputs and outputs.  Nothing from the reference is copied into the repository;
+only the numeric vectors are committed.
+
+Sources executed (paths inside the reference checkout):
+  python/sglang/test/test_block_fp8.py      native_per_token_group_quant_fp8,
+                                            native_w8a8_block_fp8_matmul,
+                                            torch_w8a8_block_fp8_moe
+  sgl-kernel/tests/test_fp8_blockwise_gemm.py   baseline_scaled_mm
+  sgl-kernel/tests/test_fp8_blockwise_moe.py    calc_diff, per_token_cast_to_fp8,
+                                                per_block_cast_to_fp8
+  test/srt/quant/test_fp8_kernel.py         TestFP8Base._make_A / _make_B (known-answer generators)
+
+Usage:  python tests/golden/make_golden.py [--reference /root/reference]
+"""
+from __future__ import annotations
+
+import argparse
+import ast
+import os
+from typing import Optional, Tuple, Type
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+FP8 = torch.float8_e4m3fn
+
+
+def _extract(path: str, names, ns: dict, inside_class: str | None = None):
+    with open(path) as f:
+        src = f.read()
+    tree = ast.parse(src)
+    body = tree.body
+    if inside_class is not None:
+        body = next(n for n in tree.body if isinstance(n, ast.ClassDef) and n.name == inside_class).body
+    for node in body:
+        if isinstance(node, ast.FunctionDef) and node.name in names:
+            node.decorator_list = []  # drop @staticmethod
+            mod = ast.Module(body=[node], type_ignores=[])
+            exec(compile(mod, path, "exec"), ns)
+    missing = [n for n in names if n not in ns]
+    assert not missing, f"{path}: not found: {missing}"
+
+
+def _np(t: torch.Tensor) -> np.ndarray:
+    t = t.detach().cpu().contiguous()
+    if t.dtype == FP8:
+        return t.view(torch.uint8).numpy()
+    if t.dtype in (torch.bfloat16, torch.float16):
+        return t.view(torch.int16).numpy()
+    return t.numpy()
+
+
+class _SiluAndMul:
+    """Stand-in with the arithmetic of SiluAndMul.forward_native (activation.py:60-62)."""
+    def forward_native(self, x):
+        d = x.shape[-1] // 2
+        return F.silu(x[..., :d]) * x[..., d:]
+
+
+def main(reference: str):
+    ns = {"torch": torch, "Optional": Optional, "Tuple": Tuple, "Type": Type, "SiluAndMul": _SiluAndMul}
+    _extract(os.path.join(reference, "python/sglang/test/test_block_fp8.py"),
+             ["native_per_token_group_quant_fp8", "native_w8a8_block_fp8_matmul", "torch_w8a8_block_fp8_moe"], ns)
+    _extract(os.path.join(reference, "sgl-kernel/tests/test_fp8_blockwise_gemm.py"), ["baseline_scaled_mm"], ns)
+    _extract(os.path.join(reference, "sgl-kernel/tests/test_fp8_blockwise_moe.py"),
+             ["calc_diff", "ceil_div", "per_token_cast_to_fp8", "per_block_cast_to_fp8"], ns)
+    ka = {"torch": torch}
+    _extract(os.path.join(reference, "test/srt/quant/test_fp8_kernel.py"), ["_make_A", "_make_B"], ka,
+             inside_class="TestFP8Base")
+
+    # ---------------- quant: reference torch twin on its own test distribution (torch.rand, seed 0)
+    out = {}
+    for name, dtype in (("bf16", torch.bfloat16), ("f16", torch.float16), ("f32", torch.float32)):
+        torch.manual_seed(0)
+        x = torch.rand(7, 512, dtype=dtype)
+        q, s = ns["native_per_token_group_quant_fp8"](x, 128)
+        out[f"rand_{name}_x"] = _np(x); out[f"rand_{name}_q"] = _np(q); out[f"rand_{name}_s"] = _np(s)
+    torch.manual_seed(1)
+    x = (torch.randn(83, 1024) * torch.where(torch.rand(83, 1024) < 1e-2, 100.0, 1.0)).to(torch.bfloat16)
+    q, s = ns["native_per_token_group_quant_fp8"](x, 128)
+    out["randn_bf16_x"] = _np(x); out["randn_bf16_q"] = _np(q); out["randn_bf16_s"] = _np(s)
+    np.savez_compressed(os.path.join(HERE, "quant_native.npz"), **out)
+
+    # ---------------- quant: known-answer generator of test_fp8_kernel.py (device kw patched to cpu)
+    _rand, _randn = torch.rand, torch.randn
+    torch.rand = lambda *a, **k: _rand(*a, **{**k, "device": "cpu"})
+    try:
+        torch.manual_seed(0)
+        A, A_q, A_s = ka["_make_A"](64, 512, 128, FP8)
+        B, B_q, B_s = ka["_make_B"](512, 256 + 64, 128, FP8)
+    finally:
+        torch.rand = _rand
+    np.savez_compressed(os.path.join(HERE, "known_answer.npz"),
+                        A=_np(A), A_q=_np(A_q), A_s=_np(A_s), B=_np(B), B_q=_np(B_q), B_s=_np(B_s))
+
+    # ---------------- matmul: reference native matmul + sgl-kernel baseline on the same inputs
+    torch.manual_seed(0)
+    M, N, K = 33, 384, 512
+    a = ((torch.rand(M, K) - 0.5) * 2 * 448).to(FP8)
+    b = ((torch.rand(N, K) - 0.5) * 2 * 448).to(FP8)
+    As = torch.rand(M, K // 128) * 1e-2
+    Bs = torch.rand(N // 128, K // 128) * 1e-2
+    c32 = ns["native_w8a8_block_fp8_matmul"](a, b, As, Bs, [128, 128], torch.float32)
+    cbf = ns["native_w8a8_block_fp8_matmul"](a, b, As, Bs, [128, 128], torch.bfloat16)
+    base = ns["baseline_scaled_mm"](a, b.t(), As, Bs.t(), torch.bfloat16)
+    np.savez_compressed(os.path.join(HERE, "matmul_native.npz"), a=_np(a), b=_np(b), As=_np(As), Bs=_np(Bs),
+                        c_f32=_np(c32), c_bf16=_np(cbf), baseline_bf16=_np(base))
+
+    # ---------------- weight / token casts
+    torch.manual_seed(2)
+    w = torch.randn(200, 384) * 0.02
+    wq, ws = ns["per_block_cast_to_fp8"](w)
+    t = torch.randn(5, 256)
+    tq, ts = ns["per_token_cast_to_fp8"](t)
+    d = ns["calc_diff"](torch.randn(64, 64, generator=torch.Generator().manual_seed(3)),
+                        torch.randn(64, 64, generator=torch.Generator().manual_seed(4)))
+    np.savez_compressed(os.path.join(HERE, "casts.npz"), w=_np(w), wq=_np(wq), ws=_np(ws),
+                        t=_np(t), tq=_np(tq), ts=_np(ts), calc_diff=np.float64(d))
+
+    # ---------------- MoE: reference torch_w8a8_block_fp8_moe
+    torch.manual_seed(5)
+    Mt, D, I, E, topk = 17, 256, 128, 4, 2
+    a = (torch.randn(Mt, D) / 10).to(torch.bfloat16)
+    w1 = torch.randn(E, 2 * I, D) * 0.05
+    w2 = torch.randn(E, D, I) * 0.05
+    w1q, w1s, w2q, w2s = [], [], [], []
+    for e in range(E):
+        q_, s_ = ns["per_block_cast_to_fp8"](w1[e]); w1q.append(q_); w1s.append(s_)
+        q_, s_ = ns["per_block_cast_to_fp8"](w2[e]); w2q.append(q_); w2s.append(s_)
+    w1q, w1s, w2q, w2s = torch.stack(w1q), torch.stack(w1s), torch.stack(w2q), torch.stack(w2s)
+    score = torch.randn(Mt, E)
+    o = ns["torch_w8a8_block_fp8_moe"](a, w1q, w2q, w1s, w2s, score, topk, [128, 128])
+    np.savez_compressed(os.path.join(HERE, "moe_native.npz"), a=_np(a), w1q=_np(w1q), w1s=_np(w1s),
+                        w2q=_np(w2q), w2s=_np(w2s), score=_np(score), topk=np.int64(topk), out=_np(o))
+    print("golden vectors written to", HERE)
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    main(ap.parse_args().reference)
