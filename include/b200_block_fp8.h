@@ -1,0 +1,102 @@
+/*
+ * C ABI of libb200_block_fp8.so -- the W8A8 block-FP8 linear path for NVIDIA B200 (sm_100a).
+ *
+ * Every entry point takes plain device pointers, sizes and element strides; none
+ * allocates, synchronises or reads device data on the host unless stated.  Kernels are
+ * enqueued on `stream` (a cudaStream_t passed as void*; NULL = legacy default stream) of
+ * the CURRENT device.  Return value: 0 on success, a negative B200_ERR_* code otherwise
+ * (nothing is launched when an argument check fails); b200_strerror() names it.
+ *
+ * Each declaration cites the interface of the reference project (walker-ai/sglang,
+ * paths relative to its checkout) that it stands in for.
+ */
+#ifndef B200_BLOCK_FP8_H_
+#define B200_BLOCK_FP8_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types of activations / outputs */
+#define B200_DT_F32 0
+#define B200_DT_F16 1
+#define B200_DT_BF16 2
+
+/* error codes */
+#define B200_OK 0
+#define B200_ERR_NULL_PTR (-1)
+#define B200_ERR_BAD_DTYPE (-2)
+#define B200_ERR_BAD_SHAPE (-3)      /* negative size, K % group != 0, ... */
+#define B200_ERR_BAD_STRIDE (-4)     /* stride not allowed by the layout contract */
+#define B200_ERR_MISALIGNED (-5)     /* pointer or leading dimension not 16-byte aligned */
+#define B200_ERR_UNSUPPORTED (-6)    /* valid in the reference, not built here (see message) */
+#define B200_ERR_CUDA (-7)           /* a CUDA runtime/driver call failed; see b200_last_cuda_error() */
+#define B200_ERR_NOT_SM100 (-8)      /* current device is not compute capability 10.x */
+#define B200_ERR_TOO_LARGE (-9)      /* size beyond a stated maximum */
+#define B200_ERR_DEVICE_TIMEOUT (-10) /* a bounded device-side wait gave up (status word set) */
+
+const char* b200_strerror(int code);
+/* cudaError_t of the last failing CUDA call made by this library on this thread (0 if none). */
+int b200_last_cuda_error(void);
+/* Library ABI version (bumped on any signature change). */
+int b200_abi_version(void);
+
+/*
+ * Per-token-group FP8 quantisation (e4m3, saturating, round-to-nearest-even).
+ * Replaces: sgl_per_token_group_quant_fp8
+ *   (sgl-kernel/csrc/gemm/per_token_group_quant_8bit.cu:116-240, schema
+ *    sgl-kernel/csrc/common_extension.cc:116-119).
+ * x   [M,K] contiguous, x_dtype one of B200_DT_*; K % group_size == 0; group_size in {64,128,256,512}
+ * q   [M,K] contiguous e4m3 codes (1 byte each)
+ * s   fp32 scales; element (row r, group g) is written at s[r*s_stride_row + g*s_stride_grp].
+ *     Row-major [M,G]: (G,1).  Column-major [G,M]: (1,M).  Column-major padded to 4 rows
+ *     (TMA-aligned): (1, align4(M)); padding rows are not written.
+ * Arithmetic (bit-exact with the reference kernel): amax = max(eps, max|float(x)|);
+ * scale = amax / fp8_max (IEEE); code = e4m3_rne_sat(min(max(float(x)/scale, fp8_min), fp8_max)).
+ * M == 0 is a no-op.
+ */
+int b200_per_token_group_quant_fp8(const void* x, int x_dtype, void* q, float* s,
+                                   int64_t M, int64_t K, int64_t group_size,
+                                   int64_t s_stride_row, int64_t s_stride_grp,
+                                   float eps, float fp8_min, float fp8_max, void* stream);
+
+/* Same contract; divides with the IEEE division instruction sequence per element instead of
+ * the reciprocal + exact-residual form.  Used by the tests to cross-check the fast form.
+ * No counterpart in the reference. */
+int b200_per_token_group_quant_fp8_ieee_div(const void* x, int x_dtype, void* q, float* s,
+                                            int64_t M, int64_t K, int64_t group_size,
+                                            int64_t s_stride_row, int64_t s_stride_grp,
+                                            float eps, float fp8_min, float fp8_max, void* stream);
+
+/*
+ * Dense block-scaled FP8 GEMM:  out[m,n] = cast( sum_kb ( sum_{k in kb} a[m,k]*b[n,k] )
+ *                                               * sa[m,kb] * sb[n/128,kb] ),  fp32 accumulation.
+ * Replaces: fp8_blockwise_scaled_mm
+ *   (sgl-kernel/csrc/gemm/fp8_blockwise_gemm_kernel.cu:345-423, schema common_extension.cc:111-114)
+ *   and w8a8_block_fp8_matmul (python/sglang/srt/layers/quantization/fp8_kernel.py:849-966).
+ * a    [M,K] e4m3, row-major, leading dimension lda (elements) -- lda % 16 == 0, 16-byte aligned
+ * b    [N,K] e4m3, row-major (= the reference's column-major [K,N] mat_b), ldb % 16 == 0
+ * sa   fp32, element (m,kb) at sa[m*sa_stride_m + kb*sa_stride_g]   (M-major: (1, M) or (1, align4(M)))
+ * sb   fp32, element (nb,kb) at sb[nb*sb_stride_n + kb*sb_stride_g]
+ * out  [M,N] out_dtype (B200_DT_BF16 or B200_DT_F16; B200_DT_F32 is accepted for accuracy checks),
+ *      leading dimension ldo elements, 16-byte aligned rows
+ * K need not be a multiple of 128 (the last k-block is zero-filled); N need not be a multiple of 128.
+ * M == 0 is a no-op.
+ */
+int b200_fp8_blockwise_scaled_mm(const void* a, int64_t lda, const void* b, int64_t ldb,
+                                 const float* sa, int64_t sa_stride_m, int64_t sa_stride_g,
+                                 const float* sb, int64_t sb_stride_n, int64_t sb_stride_g,
+                                 void* out, int64_t ldo, int out_dtype,
+                                 int64_t M, int64_t N, int64_t K, void* stream);
+
+/* Reads and clears this device's GEMM status word (0 = ok; non-zero = a bounded device-side
+ * wait gave up, value encodes which).  Synchronises the device.  No reference counterpart. */
+int b200_gemm_device_status(int* status_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_BLOCK_FP8_H_ */

@@ -1,0 +1,72 @@
+"""ctypes binding of libb200_block_fp8.so (the C ABI declared in include/b200_block_fp8.h).
+
+There is no CPU or PyTorch fallback: if the library is missing or a call fails, this raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_float, c_int, c_int64, c_void_p
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libb200_block_fp8.so")
+
+DT_F32, DT_F16, DT_BF16 = 0, 1, 2
+
+_lib = None
+
+
+class B200Error(RuntimeError):
+    """A C-ABI call returned a negative status."""
+
+    def __init__(self, fn: str, code: int, detail: str):
+        super().__init__(f"{fn}: {detail} (code {code})")
+        self.code = code
+
+
+_SIGNATURES = {
+    "b200_strerror": (ctypes.c_char_p, [c_int]),
+    "b200_last_cuda_error": (c_int, []),
+    "b200_abi_version": (c_int, []),
+    "b200_per_token_group_quant_fp8": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                                               c_int64, c_int64, c_float, c_float, c_float, c_void_p]),
+    "b200_per_token_group_quant_fp8_ieee_div": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64,
+                                                        c_int64, c_int64, c_int64, c_float, c_float, c_float,
+                                                        c_void_p]),
+    "b200_fp8_blockwise_scaled_mm": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64,
+                                             c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int, c_int64, c_int64,
+                                             c_int64, c_void_p]),
+    "b200_gemm_device_status": (c_int, [ctypes.POINTER(c_int)]),
+    "b200_debug_force_block_n": (c_int, [c_int]),
+    "b200_debug_force_quant_passes": (c_int, [c_int]),
+}
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.isfile(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -m sglang_b200.build` "
+                "(nvcc, sm_100a). There is no fallback implementation.")
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in _SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def check(fn_name: str, code: int) -> None:
+    if code == 0:
+        return
+    L = lib()
+    detail = L.b200_strerror(code).decode()
+    if code == -7:
+        detail += f" [cudaError {L.b200_last_cuda_error()}]"
+    raise B200Error(fn_name, code, detail)
+
+
+def exported_symbols():
+    return list(_SIGNATURES.keys())

@@ -1,0 +1,277 @@
+// Per-token-group FP8 (e4m3) quantisation for sm_100a, single pass over the input.
+//
+// Stands in for the reference kernel per_token_group_quant_8bit_kernel
+// (sgl-kernel/csrc/gemm/per_token_group_quant_8bit.cu:19-114) and must reproduce its codes
+// and scales bit for bit:
+//     amax  = max(eps, max_i |float(x_i)|)            (fmaxf drops NaNs)
+//     scale = amax / fp8_max                          (IEEE fp32 division)
+//     code  = e4m3_rne_satfinite(fminf(fmaxf(float(x_i) / scale, fp8_min), fp8_max))
+//
+// Layout of the work: a block of 256 threads owns a tile of ROWS x 1024 elements.  Each thread
+// keeps 16 consecutive elements per row-pass in registers (two 128-bit loads for 2-byte
+// inputs), so the input is read once; a warp reads 1 KB contiguous and writes 512 B
+// contiguous.  GROUP/16 neighbouring lanes reduce the group's amax with xor shuffles.
+// Scales of the tile are staged in shared memory and written out along whichever of the two
+// scale strides is the contiguous one, so row-major and column-major scale layouts both
+// produce full-sector stores.
+//
+// Division: x/scale is needed correctly rounded.  The default form computes the correctly
+// rounded reciprocal r once per group and then, per element, q0 = x*r, rem = fma(-q0, scale, x),
+// q = fma(rem, r, q0) -- correctly rounded for every scale whose significand is not all ones
+// (Markstein); groups with such a scale, or a non-finite scale, take the plain IEEE division.
+// The *_ieee_div entry point always uses the IEEE division and exists for cross-checking.
+#include "common.cuh"
+
+namespace b200 {
+int g_force_quant_passes = 0;  // experiments: 1, 2, 4 or 8 rows-of-4 per tile; 0 = automatic
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kTileW = 1024;  // elements per tile row
+constexpr int kVec = 16;      // elements per thread per pass
+
+template <typename T>
+struct Vec16;
+template <>
+struct Vec16<__nv_bfloat16> {
+  uint4 v[2];
+  __device__ __forceinline__ void load(const __nv_bfloat16* p) {
+    const uint4* p4 = reinterpret_cast<const uint4*>(p);
+    v[0] = __ldcs(p4);
+    v[1] = __ldcs(p4 + 1);
+  }
+  __device__ __forceinline__ void zero() { v[0] = v[1] = make_uint4(0, 0, 0, 0); }
+  __device__ __forceinline__ float get(int i) const {
+    const uint32_t* w = reinterpret_cast<const uint32_t*>(v);
+    const uint32_t word = w[i >> 1];
+    return __uint_as_float((i & 1) ? (word & 0xffff0000u) : (word << 16));
+  }
+};
+template <>
+struct Vec16<__half> {
+  uint4 v[2];
+  __device__ __forceinline__ void load(const __half* p) {
+    const uint4* p4 = reinterpret_cast<const uint4*>(p);
+    v[0] = __ldcs(p4);
+    v[1] = __ldcs(p4 + 1);
+  }
+  __device__ __forceinline__ void zero() { v[0] = v[1] = make_uint4(0, 0, 0, 0); }
+  __device__ __forceinline__ float get(int i) const {
+    const __half2* h = reinterpret_cast<const __half2*>(v);
+    const float2 f = __half22float2(h[i >> 1]);
+    return (i & 1) ? f.y : f.x;
+  }
+};
+template <>
+struct Vec16<float> {
+  uint4 v[4];
+  __device__ __forceinline__ void load(const float* p) {
+    const uint4* p4 = reinterpret_cast<const uint4*>(p);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = __ldcs(p4 + i);
+  }
+  __device__ __forceinline__ void zero() {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = make_uint4(0, 0, 0, 0);
+  }
+  __device__ __forceinline__ float get(int i) const { return reinterpret_cast<const float*>(v)[i]; }
+};
+
+__device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float d) {
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return lo | (hi << 16);
+}
+
+template <typename T, int GROUP, int PASSES, bool IEEE_DIV>
+__global__ void __launch_bounds__(kThreads)
+quant_group_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ s, int64_t M, int64_t K,
+                   int64_t s_stride_row, int64_t s_stride_grp, float eps, float fp8_min, float fp8_max,
+                   int tiles_k) {
+  constexpr int TPG = GROUP / kVec;              // lanes cooperating on one group
+  constexpr int GPT = kTileW / GROUP;            // groups per tile row
+  constexpr int SLOTS_PER_ROW = kTileW / kVec;   // 64 threads per tile row
+  constexpr int ROWS_PER_PASS = kThreads / SLOTS_PER_ROW;  // 4
+  constexpr int ROWS = ROWS_PER_PASS * PASSES;
+  static_assert(TPG >= 1 && TPG <= 32, "group size");
+
+  __shared__ float s_tile[ROWS * GPT];
+
+  const int tid = threadIdx.x;
+  const int64_t tile_m = blockIdx.x / tiles_k;
+  const int tile_k = blockIdx.x % tiles_k;
+  const int row_in_pass = tid / SLOTS_PER_ROW;
+  const int slot = tid % SLOTS_PER_ROW;
+  const int64_t col = static_cast<int64_t>(tile_k) * kTileW + slot * kVec;
+  const int64_t row0 = tile_m * ROWS + row_in_pass;
+  const bool col_ok = col < K;  // K % GROUP == 0 and GROUP % 16 == 0: a thread's 16 elements never straddle K
+
+  Vec16<T> data[PASSES];
+#pragma unroll
+  for (int p = 0; p < PASSES; ++p) {
+    const int64_t row = row0 + p * ROWS_PER_PASS;
+    if (col_ok && row < M) {
+      data[p].load(x + row * K + col);
+    } else {
+      data[p].zero();
+    }
+  }
+
+#pragma unroll
+  for (int p = 0; p < PASSES; ++p) {
+    const int64_t row = row0 + p * ROWS_PER_PASS;
+    float amax = eps;
+#pragma unroll
+    for (int i = 0; i < kVec; ++i) amax = fmaxf(amax, fabsf(data[p].get(i)));
+#pragma unroll
+    for (int off = TPG / 2; off >= 1; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+
+    const float scale = __fdiv_rn(amax, fp8_max);
+    float y[kVec];
+    bool fast = !IEEE_DIV;
+    if (!IEEE_DIV) {
+      const uint32_t bits = __float_as_uint(scale);
+      // all-ones significand or Inf/NaN scale: leave the fast form
+      fast = ((bits & 0x007fffffu) != 0x007fffffu) && ((bits & 0x7f800000u) != 0x7f800000u);
+    }
+    if (fast) {
+      const float r = __frcp_rn(scale);
+#pragma unroll
+      for (int i = 0; i < kVec; ++i) {
+        const float v = data[p].get(i);
+        const float q0 = __fmul_rn(v, r);
+        const float rem = __fmaf_rn(-q0, scale, v);
+        // the quotient carries the sign of v (scale > 0); this also restores -0 when q0 is -0
+        y[i] = copysignf(__fmaf_rn(rem, r, q0), v);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < kVec; ++i) y[i] = __fdiv_rn(data[p].get(i), scale);
+    }
+    // fmaxf maps NaN to fp8_min as the reference's fmaxf/fminf pair does.  The upper clamp is
+    // what the saturating conversion does anyway when fp8_max is the e4m3 maximum.
+#pragma unroll
+    for (int i = 0; i < kVec; ++i) y[i] = fmaxf(y[i], fp8_min);
+    if (fp8_max != 448.0f) {
+#pragma unroll
+      for (int i = 0; i < kVec; ++i) y[i] = fminf(y[i], fp8_max);
+    }
+
+    if (col_ok && row < M) {
+      uint4 out;
+      out.x = pack4_e4m3(y[0], y[1], y[2], y[3]);
+      out.y = pack4_e4m3(y[4], y[5], y[6], y[7]);
+      out.z = pack4_e4m3(y[8], y[9], y[10], y[11]);
+      out.w = pack4_e4m3(y[12], y[13], y[14], y[15]);
+      *reinterpret_cast<uint4*>(q + row * K + col) = out;
+    }
+    if ((slot % TPG) == 0) s_tile[(p * ROWS_PER_PASS + row_in_pass) * GPT + slot / TPG] = scale;
+  }
+  __syncthreads();
+
+  // Write the tile's scales along the contiguous scale dimension.
+  const int64_t g0 = static_cast<int64_t>(tile_k) * GPT;
+  const int64_t G = K / GROUP;
+  const int64_t r0 = tile_m * ROWS;
+  const bool rows_contig = s_stride_row <= s_stride_grp;
+  for (int idx = tid; idx < ROWS * GPT; idx += kThreads) {
+    int r, g;
+    if (rows_contig) {
+      g = idx / ROWS;
+      r = idx % ROWS;
+    } else {
+      r = idx / GPT;
+      g = idx % GPT;
+    }
+    if (r0 + r < M && g0 + g < G) s[(r0 + r) * s_stride_row + (g0 + g) * s_stride_grp] = s_tile[r * GPT + g];
+  }
+}
+
+template <typename T, int GROUP, bool IEEE_DIV>
+int launch_group(const void* x, void* q, float* s, int64_t M, int64_t K, int64_t ssr, int64_t ssg, float eps,
+                 float fmin_, float fmax_, cudaStream_t stream) {
+  const int tiles_k = static_cast<int>((K + kTileW - 1) / kTileW);
+  const int sms = sm_count();
+  if (sms <= 0) return B200_ERR_CUDA;
+  constexpr int kMaxPasses = sizeof(T) == 4 ? 4 : 8;
+  auto tiles_for = [&](int passes) { return ((M + 4 * passes - 1) / (4 * passes)) * tiles_k; };
+  int passes = kMaxPasses;
+  while (passes > 1 && tiles_for(passes) < 4LL * sms) passes >>= 1;
+  if (g_force_quant_passes > 0 && g_force_quant_passes <= kMaxPasses) passes = g_force_quant_passes;
+  const int64_t tiles = tiles_for(passes);
+  if (tiles > 0x7fffffffLL) return B200_ERR_TOO_LARGE;
+  const dim3 grid(static_cast<unsigned>(tiles));
+  const T* xp = static_cast<const T*>(x);
+  uint8_t* qp = static_cast<uint8_t*>(q);
+#define B200_LAUNCH_Q(P)                                                                                       \
+  quant_group_kernel<T, GROUP, P, IEEE_DIV><<<grid, kThreads, 0, stream>>>(xp, qp, s, M, K, ssr, ssg, eps, fmin_, \
+                                                                           fmax_, tiles_k)
+  switch (passes) {
+    case 8:
+      if constexpr (kMaxPasses >= 8) { B200_LAUNCH_Q(8); }
+      break;
+    case 4: B200_LAUNCH_Q(4); break;
+    case 2: B200_LAUNCH_Q(2); break;
+    default: B200_LAUNCH_Q(1); break;
+  }
+#undef B200_LAUNCH_Q
+  B200_CUDA_TRY(cudaGetLastError());
+  return B200_OK;
+}
+
+template <typename T, bool IEEE_DIV>
+int dispatch_group(int64_t group, const void* x, void* q, float* s, int64_t M, int64_t K, int64_t ssr, int64_t ssg,
+                   float eps, float fmin_, float fmax_, cudaStream_t st) {
+  switch (group) {
+    case 64: return launch_group<T, 64, IEEE_DIV>(x, q, s, M, K, ssr, ssg, eps, fmin_, fmax_, st);
+    case 128: return launch_group<T, 128, IEEE_DIV>(x, q, s, M, K, ssr, ssg, eps, fmin_, fmax_, st);
+    case 256: return launch_group<T, 256, IEEE_DIV>(x, q, s, M, K, ssr, ssg, eps, fmin_, fmax_, st);
+    case 512: return launch_group<T, 512, IEEE_DIV>(x, q, s, M, K, ssr, ssg, eps, fmin_, fmax_, st);
+    default: return B200_ERR_UNSUPPORTED;
+  }
+}
+
+template <bool IEEE_DIV>
+int quant_entry(const void* x, int x_dtype, void* q, float* s, int64_t M, int64_t K, int64_t group, int64_t ssr,
+                int64_t ssg, float eps, float fmin_, float fmax_, void* stream) {
+  if (M < 0 || K < 0 || group <= 0) return B200_ERR_BAD_SHAPE;
+  if (K % group != 0) return B200_ERR_BAD_SHAPE;
+  if (M == 0 || K == 0) return B200_OK;
+  if (!x || !q || !s) return B200_ERR_NULL_PTR;
+  if (!aligned16(x) || !aligned16(q)) return B200_ERR_MISALIGNED;
+  if (ssr < 0 || ssg < 0 || (ssr == 0 && M > 1) || (ssg == 0 && K / group > 1)) return B200_ERR_BAD_STRIDE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (x_dtype) {
+    case B200_DT_BF16:
+      return dispatch_group<__nv_bfloat16, IEEE_DIV>(group, x, q, s, M, K, ssr, ssg, eps, fmin_, fmax_, st);
+    case B200_DT_F16:
+      return dispatch_group<__half, IEEE_DIV>(group, x, q, s, M, K, ssr, ssg, eps, fmin_, fmax_, st);
+    case B200_DT_F32:
+      return dispatch_group<float, IEEE_DIV>(group, x, q, s, M, K, ssr, ssg, eps, fmin_, fmax_, st);
+    default:
+      return B200_ERR_BAD_DTYPE;
+  }
+}
+
+}  // namespace
+}  // namespace b200
+
+extern "C" int b200_per_token_group_quant_fp8(const void* x, int x_dtype, void* q, float* s, int64_t M, int64_t K,
+                                              int64_t group_size, int64_t s_stride_row, int64_t s_stride_grp,
+                                              float eps, float fp8_min, float fp8_max, void* stream) {
+  return b200::quant_entry<false>(x, x_dtype, q, s, M, K, group_size, s_stride_row, s_stride_grp, eps, fp8_min,
+                                  fp8_max, stream);
+}
+
+extern "C" int b200_per_token_group_quant_fp8_ieee_div(const void* x, int x_dtype, void* q, float* s, int64_t M,
+                                                       int64_t K, int64_t group_size, int64_t s_stride_row,
+                                                       int64_t s_stride_grp, float eps, float fp8_min, float fp8_max,
+                                                       void* stream) {
+  return b200::quant_entry<true>(x, x_dtype, q, s, M, K, group_size, s_stride_row, s_stride_grp, eps, fp8_min,
+                                 fp8_max, stream);
+}
+
+extern "C" int b200_debug_force_quant_passes(int passes) {
+  b200::g_force_quant_passes = passes;
+  return B200_OK;
+}

@@ -1,0 +1,87 @@
+"""sglang-level functions of the block-FP8 path, same names and signatures as
+python/sglang/srt/layers/quantization/fp8_kernel.py in the reference:
+
+  create_per_token_group_quant_fp8_output_scale   :300-341
+  sglang_per_token_group_quant_fp8                :344-372
+  per_token_group_quant_fp8                       :209-297 (the Triton twin; same results here)
+  w8a8_block_fp8_matmul                           :849-966 (prepare_block_fp8_matmul_inputs :801-846)
+"""
+from __future__ import annotations
+
+from typing import List, Tuple
+
+import torch
+
+from ...sgl_kernel import fp8_blockwise_scaled_mm, sgl_per_token_group_quant_fp8
+from ... import _lib
+
+fp8_dtype = torch.float8_e4m3fn
+fp8_max = torch.finfo(fp8_dtype).max
+fp8_min = -fp8_max
+
+
+def create_per_token_group_quant_fp8_output_scale(x_shape, device, group_size, column_major_scales: bool,
+                                                  scale_tma_aligned: bool, scale_ue8m0: bool):
+    if scale_ue8m0:
+        raise NotImplementedError("UE8M0-packed scales are not built; use fp32 scales")
+    if column_major_scales:
+        if scale_tma_aligned:
+            aligned_size = (x_shape[-2] + 3) // 4 * 4
+            return torch.empty(x_shape[:-2] + (x_shape[-1] // group_size, aligned_size), device=device,
+                               dtype=torch.float32).permute(-1, -2)[: x_shape[-2], :]
+        return torch.empty((x_shape[-1] // group_size,) + x_shape[:-1], device=device,
+                           dtype=torch.float32).permute(-1, -2)
+    return torch.empty(x_shape[:-1] + (x_shape[-1] // group_size,), device=device, dtype=torch.float32)
+
+
+def sglang_per_token_group_quant_fp8(x: torch.Tensor, group_size: int, eps: float = 1e-10,
+                                     column_major_scales: bool = False, scale_tma_aligned: bool = False,
+                                     scale_ue8m0: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    assert x.shape[-1] % group_size == 0, "the last dimension of `x` cannot be divisible by `group_size`"
+    assert x.is_contiguous(), "`x` is not contiguous"
+    x_q = torch.empty_like(x, device=x.device, dtype=fp8_dtype)
+    x_s = create_per_token_group_quant_fp8_output_scale(
+        x_shape=x.shape, device=x.device, group_size=group_size, column_major_scales=column_major_scales,
+        scale_tma_aligned=scale_tma_aligned, scale_ue8m0=scale_ue8m0)
+    if x.shape[0] > 0:
+        sgl_per_token_group_quant_fp8(x, x_q, x_s, group_size, eps, fp8_min, fp8_max, scale_ue8m0)
+    return x_q, x_s
+
+
+def per_token_group_quant_fp8(x: torch.Tensor, group_size: int, eps: float = 1e-10,
+                              column_major_scales: bool = False, scale_tma_aligned: bool = False,
+                              scale_ue8m0: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Same contract as the reference's Triton entry; one kernel serves both names here."""
+    return sglang_per_token_group_quant_fp8(x, group_size, eps, column_major_scales, scale_tma_aligned, scale_ue8m0)
+
+
+def w8a8_block_fp8_matmul(A: torch.Tensor, B: torch.Tensor, As: torch.Tensor, Bs: torch.Tensor,
+                          block_size: List[int], output_dtype: torch.dtype = torch.float16) -> torch.Tensor:
+    """A [...,K] e4m3 contiguous; B [N,K] e4m3 contiguous; As [...,ceil(K/128)] fp32 (any strides);
+    Bs [ceil(N/128), ceil(K/128)] fp32; returns [...,N] in output_dtype."""
+    assert len(block_size) == 2
+    block_n, block_k = block_size
+    assert block_n == 128 and block_k == 128, "only 128x128 weight blocks are built"
+    assert A.shape[-1] == B.shape[-1]
+    assert A.shape[:-1] == As.shape[:-1]
+    assert A.is_contiguous()
+    assert (A.shape[-1] + block_k - 1) // block_k == As.shape[-1]
+    M = A.numel() // A.shape[-1]
+    assert B.ndim == 2 and B.is_contiguous() and Bs.ndim == 2
+    N, K = B.shape
+    assert (N + block_n - 1) // block_n == Bs.shape[0]
+    assert (K + block_k - 1) // block_k == Bs.shape[1]
+    assert A.dtype == fp8_dtype and B.dtype == fp8_dtype
+    C = A.new_empty(A.shape[:-1] + (N,), dtype=output_dtype)
+    if M == 0:
+        return C
+    As2 = As.reshape(M, As.shape[-1]) if As.dim() != 2 else As
+    dt = {torch.float32: _lib.DT_F32, torch.float16: _lib.DT_F16, torch.bfloat16: _lib.DT_BF16}[output_dtype]
+    with torch.cuda.device(A.device):
+        rc = _lib.lib().b200_fp8_blockwise_scaled_mm(
+            A.data_ptr(), K, B.data_ptr(), K,
+            As2.data_ptr(), As2.stride(0), As2.stride(1),
+            Bs.data_ptr(), Bs.stride(0), Bs.stride(1),
+            C.data_ptr(), N, dt, M, N, K, torch.cuda.current_stream(A.device).cuda_stream)
+    _lib.check("w8a8_block_fp8_matmul", rc)
+    return C
