@@ -1,0 +1,430 @@
+"""Benchmark of the W8A8 block-FP8 linear path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+Workload (config.workload): the DeepSeek-V3-shaped dense MLP as two block-FP8 linears at
+M = 4096 tokens -- gate_up (K=7168, N=36864) then down (K=18432, N=7168).  One step =
+group-quantise x, GEMM, group-quantise h, GEMM (4 kernels).  Inputs are seeded synthetic
+tensors (activations N(0,1), weights N(0,0.02) block-quantised); weights (396 MB of e4m3) and
+activations (210 MB of bf16) exceed the 126 MB L2, so no explicit flush is needed.
+
+N > 1 (launched by torchrun, one rank per GPU, NCCL): the same MLP tensor-parallel as in the
+reference -- gate_up column-parallel (N/p per rank, no communication), down row-parallel
+(K/p per rank) followed by one bf16 all-reduce of [4096,7168].  Total work is fixed: strong scaling.
+
+The JSON line carries: value = whole-job TFLOP/s with inputs resident in HBM; e2e = the same
+through the public linear call with HOST activations (pinned) copied in and the bf16 results
+copied out inside the timed region; roofline for the dominant kernel (the gate_up GEMM) from
+CUDA events placed around its launches inside the timed region; cpu_baseline = the reference's
+own CPU block-FP8 matmul (oracle/_ref, built from the reference sources) or, where the host
+lacks AMX, the torch restatement, timed on the host cores on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+M_TOKENS = 4096
+HIDDEN = 7168
+INTER2 = 36864      # gate_up output (2 x 18432)
+INTER = 18432
+WORKLOAD = "deepseek_v3_dense_mlp_block_fp8_M4096(gate_up K7168 N36864 + down K18432 N7168)"
+FLOPS_PER_STEP = 2.0 * M_TOKENS * (INTER2 * HIDDEN + HIDDEN * INTER)
+NOMINAL_FP8_TFLOPS = 4500.0
+# dram bytes per launch of the gate_up GEMM from the committed ncu capture (profiles/), or None
+GEMM_TRAFFIC_BYTES = None
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_sustained": p["bf16_tflops_sustained"],
+                "bf16_burst": p["bf16_tflops"], "src": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_sustained": 1400.0, "bf16_burst": 1590.0, "src": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi SM clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.idx)], stdout=subprocess.PIPE, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        clocks, maxc, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                clocks.append(float(f[1])); maxc.append(float(f[2])); power.append(float(f[3]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not clocks:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        # samples under load = upper half of the power readings
+        order = sorted(range(len(clocks)), key=lambda i: power[i])
+        load = [clocks[i] for i in order[len(order) // 2:]]
+        load.sort()
+        return {"sm_mhz": load[len(load) // 2], "sm_max_mhz": max(maxc), "power_w_max": max(power),
+                "samples": len(clocks), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------------
+# CPU reference arm / baseline
+# ------------------------------------------------------------------------------------------
+def cpu_reference_run(steps: int, warmup: int, sample_rows: int = 64):
+    """Times the reference CPU block-FP8 matmul on `sample_rows` tokens of the workload (both
+    layers).  Returns (tflops, info dict)."""
+    import torch
+
+    from oracle import block_fp8_oracle as O
+    from oracle import build_ref
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    g = torch.Generator().manual_seed(0)
+    layers = []
+    for (n, k) in ((INTER2, HIDDEN), (HIDDEN, INTER)):
+        # codes/scales drawn directly (quantising 264 MB on the host would dominate start-up);
+        # distribution does not affect CPU matmul time
+        wq = torch.randint(0, 120, (n, k), dtype=torch.uint8, generator=g).view(torch.float8_e4m3fn)
+        ws = torch.rand((n // 128, k // 128), generator=g) * 1e-3 + 1e-4
+        x = torch.randn((sample_rows, k), generator=g).to(torch.bfloat16)
+        layers.append((x, wq, ws))
+    kind = "port"
+    if build_ref.load():
+        kind = "reference"
+        ops = torch.ops.sgl_kernel_ref
+        packed = [(x, ops.convert_weight_packed(wq), ws) for (x, wq, ws) in layers]
+
+        def step():
+            for (x, wp, ws) in packed:
+                ops.fp8_scaled_mm_cpu(x, wp, ws, [128, 128], None, torch.bfloat16, True)
+    else:
+        quant = [(O.quant_group_fp8_cuda_semantics(x, 128), wq, ws) for (x, wq, ws) in layers]
+
+        def step():
+            for ((q, s), wq, ws) in quant:
+                O.block_fp8_matmul_fp32(q, wq, s, ws).to(torch.bfloat16)
+    for _ in range(max(1, warmup)):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    flops = 2.0 * sample_rows * (INTER2 * HIDDEN + HIDDEN * INTER)
+    tflops = flops / dt / 1e12
+    info = {"value": tflops, "unit": "TFLOP/s", "cores": cores, "kind": kind,
+            "sample": f"{sample_rows} of {M_TOKENS} tokens through both layers, {steps} timed passes "
+                      f"({dt * 1e3:.1f} ms each); "
+                      + ("reference fp8_scaled_mm_cpu (W8A16, AMX), weights pre-packed" if kind == "reference"
+                         else "torch restatement of native_w8a8_block_fp8_matmul")}
+    return tflops, dt, info
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, args.steps)
+    # the full 4096-token workload takes about 1.6 s per pass on 8 AMX cores; shrink the sample
+    # for long runs so the arm still ends within a few minutes
+    rows = M_TOKENS if steps <= 30 else 512
+    tflops, dt, info = cpu_reference_run(steps, min(args.warmup, 2), rows)
+    line = {"impl": "reference", "metric": "block_fp8_linear_tflops", "value": tflops, "unit": "TFLOP/s",
+            "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 x e4m3 (W8A16)",
+            "data": "synthetic", "config": {"workload": WORKLOAD, "sample": info["sample"]},
+            "cpu_baseline": info,
+            "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------
+def gen_weight_device(n, k, seed, device):
+    """N(0,0.02^2) weight block-quantised on the device (amax.clamp(1e-4)/448 per 128x128 block,
+    the per_block_cast_to_fp8 recipe of sgl-kernel/tests/test_fp8_blockwise_moe.py:51-64)."""
+    import torch
+    g = torch.Generator(device=device).manual_seed(seed)
+    q = torch.empty((n, k), dtype=torch.float8_e4m3fn, device=device)
+    s = torch.empty((n // 128, k // 128), dtype=torch.float32, device=device)
+    rows = 2048
+    for r0 in range(0, n, rows):
+        r1 = min(n, r0 + rows)
+        w = torch.randn((r1 - r0, k), generator=g, device=device) * 0.02
+        wv = w.view((r1 - r0) // 128, 128, k // 128, 128)
+        amax = wv.abs().amax(dim=(1, 3), keepdim=True).clamp(1e-4)
+        q[r0:r1] = (wv * (448.0 / amax)).to(torch.float8_e4m3fn).view(r1 - r0, k)
+        s[r0 // 128:r1 // 128] = (amax / 448.0).view((r1 - r0) // 128, k // 128)
+    return q, s
+
+
+def run_gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+
+    from sglang_b200 import _lib
+    from sglang_b200.layers.quantization.fp8_kernel import sglang_per_token_group_quant_fp8
+    from sglang_b200.layers.quantization.fp8_utils import w8a8_block_fp8_linear
+    from sglang_b200.sgl_kernel import fp8_blockwise_scaled_mm
+
+    _lib.lib()  # fail loudly if the CUDA library is missing
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world} (launch with torchrun for N>1)"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    p = world
+    n1, k2 = INTER2 // p, INTER // p        # column-parallel gate_up, row-parallel down
+
+    w1q, w1s = gen_weight_device(n1, HIDDEN, 100 + rank, dev)
+    w2q, w2s = gen_weight_device(HIDDEN, k2, 200 + rank, dev)
+    w1_t, w1s_t, w2_t, w2s_t = w1q.T, w1s.T, w2q.T, w2s.T
+    g = torch.Generator(device=dev).manual_seed(7)           # x is replicated: same seed on all ranks
+    x = torch.randn((M_TOKENS, HIDDEN), generator=g, device=dev).to(torch.bfloat16)
+    gh = torch.Generator(device=dev).manual_seed(300 + rank)
+    h = torch.randn((M_TOKENS, k2), generator=gh, device=dev).to(torch.bfloat16)
+
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    kernel_events = []   # (name, start, stop) inside the timed region
+
+    def step(record=False):
+        def timed(name, fn):
+            if not record:
+                return fn()
+            a, b = ev(), ev()
+            a.record(); r = fn(); b.record()
+            kernel_events.append((name, a, b))
+            return r
+        xq, xs = timed("quant_x", lambda: sglang_per_token_group_quant_fp8(x, 128, column_major_scales=True))
+        y1 = timed("gemm_gate_up", lambda: fp8_blockwise_scaled_mm(xq, w1_t, xs, w1s_t, torch.bfloat16))
+        hq, hs = timed("quant_h", lambda: sglang_per_token_group_quant_fp8(h, 128, column_major_scales=True))
+        y2 = timed("gemm_down", lambda: fp8_blockwise_scaled_mm(hq, w2_t, hs, w2s_t, torch.bfloat16))
+        if world > 1:
+            timed("allreduce", lambda: dist.all_reduce(y2))
+        return y1, y2
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    # ---- timed region 1: device-resident inputs
+    t0, t1 = ev(), ev()
+    barrier()
+    t0.record()
+    for _ in range(args.steps):
+        step(record=True)
+    t1.record()
+    barrier()
+    ms = t0.elapsed_time(t1) / args.steps
+    per_kernel = {}
+    for name, a, b in kernel_events:
+        per_kernel.setdefault(name, []).append(a.elapsed_time(b))
+    per_kernel = {k: sum(v) / len(v) for k, v in per_kernel.items()}
+
+    # ---- timed region 2: end to end through the public linear call with host buffers
+    x_host = x.cpu().pin_memory()
+    h_host = h.cpu().pin_memory()
+    y1_host = torch.empty((M_TOKENS, n1), dtype=torch.bfloat16).pin_memory()
+    y2_host = torch.empty((M_TOKENS, HIDDEN), dtype=torch.bfloat16).pin_memory()
+    x_dev, h_dev = torch.empty_like(x), torch.empty_like(h)
+
+    def e2e_step():
+        x_dev.copy_(x_host, non_blocking=True)
+        y1 = w8a8_block_fp8_linear(x_dev, w1q, [128, 128], w1s)
+        y1_host.copy_(y1, non_blocking=True)
+        h_dev.copy_(h_host, non_blocking=True)
+        y2 = w8a8_block_fp8_linear(h_dev, w2q, [128, 128], w2s)
+        if world > 1:
+            dist.all_reduce(y2)
+        y2_host.copy_(y2, non_blocking=True)
+
+    e2e_steps = max(2, min(args.steps, 10))
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    t2, t3 = ev(), ev()
+    t2.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    t3.record()
+    barrier()
+    e2e_ms = t2.elapsed_time(t3) / e2e_steps
+    clocks = sampler.stop() if rank == 0 else None
+
+    times = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = float(times[0]), float(times[1])
+
+    import ctypes
+    st = ctypes.c_int(0)
+    _lib.check("status", _lib.lib().b200_gemm_device_status(ctypes.byref(st)))
+    assert st.value == 0, f"GEMM device status word {st.value}"
+
+    if rank == 0:
+        pk = _peaks()
+        gemm_ms = per_kernel["gemm_gate_up"]
+        gemm_flops = 2.0 * M_TOKENS * n1 * HIDDEN
+        achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12
+        peak = 2.0 * pk["bf16_sustained"]
+        quant_bytes = 3.03125 * M_TOKENS * HIDDEN
+        quant_gbs = quant_bytes / (per_kernel["quant_x"] * 1e-3) / 1e9
+        h2d = x.numel() * 2 + h.numel() * 2
+        d2h = y1_host.numel() * 2 + y2_host.numel() * 2
+        line = {
+            "metric": "block_fp8_linear_tflops", "value": FLOPS_PER_STEP / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "e4m3 x e4m3 -> f32 -> bf16",
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD, "parallelism": f"tp{world}" if world > 1 else "single",
+                       "l2": "inputs larger than L2 (weights 396 MB e4m3 + activations 210 MB bf16 per step)",
+                       "kernels_ms": per_kernel},
+            "e2e": {"value": FLOPS_PER_STEP / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
+                    "note": "activations from pinned host memory, bf16 results back to pinned host memory; "
+                            "weights stay resident (they are layer parameters)"},
+            "gpu_launches": args.steps * 4,
+            "roofline": {"bound": "tensor", "kernel": "gemm_block_fp8_kernel<256,bf16> (gate_up)",
+                         "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                         "peak_source": f"2 x bf16_tflops_sustained of {pk['src']} (the fp8 pipe does twice the "
+                                        "bf16 MACs per clock; the file holds no fp8 entry)",
+                         "frac_of_nominal_4500": achieved / NOMINAL_FP8_TFLOPS,
+                         "traffic": GEMM_TRAFFIC_BYTES, "algorithmic_flops_per_launch": gemm_flops},
+            "quant": {"bound": "hbm", "kernel": "quant_group_kernel<bf16,128> on [4096,7168]",
+                      "achieved": quant_gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": quant_gbs / pk["hbm_gbs"],
+                      "algorithmic_bytes_per_launch": quant_bytes},
+            "clocks": clocks,
+        }
+        if world == 1:
+            _, _, info = cpu_reference_run(steps=5, warmup=1, sample_rows=M_TOKENS)
+            line["cpu_baseline"] = info
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_kernel_case(args):
+    """One kernel alone on one GPU (used for the M sweeps and as the small case for ncu captures):
+    --kernel gemm_gate_up|gemm_down|quant --m M.  Prints one JSON line per case."""
+    import torch
+
+    from sglang_b200.layers.quantization.fp8_kernel import sglang_per_token_group_quant_fp8
+    from sglang_b200.sgl_kernel import fp8_blockwise_scaled_mm
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    pk = _peaks()
+    ms_list = [int(v) for v in str(args.m).split(",")]
+    for m in ms_list:
+        g = torch.Generator(device=dev).manual_seed(m)
+        if args.kernel == "quant":
+            nbuf = max(2, min(8, int(300e6 // (m * HIDDEN * 2)) + 1))   # rotate buffers: > L2 in total
+            xs = []
+            for _ in range(nbuf):
+                x = torch.randn((m, HIDDEN), generator=g, device=dev)
+                x = torch.where(torch.rand((m, HIDDEN), generator=g, device=dev) < 1e-3, x * 100, x)
+                xs.append(x.to(torch.bfloat16))
+            it = [0]
+
+            def fn():
+                it[0] += 1
+                return sglang_per_token_group_quant_fp8(xs[it[0] % nbuf], 128, column_major_scales=True,
+                                                        scale_tma_aligned=True)
+            work, unit, peak = 3.03125 * m * HIDDEN / 1e9, "GB/s", pk["hbm_gbs"]
+        else:
+            n, k = (INTER2, HIDDEN) if args.kernel == "gemm_gate_up" else (HIDDEN, INTER)
+            wq, ws = gen_weight_device(n, k, 1, dev)
+            x = torch.randn((m, k), generator=g, device=dev).to(torch.bfloat16)
+            xq, xs_ = sglang_per_token_group_quant_fp8(x, 128, column_major_scales=True)
+            w_t, ws_t = wq.T, ws.T
+
+            def fn():
+                return fp8_blockwise_scaled_mm(xq, w_t, xs_, ws_t, torch.bfloat16)
+            work, unit, peak = 2.0 * m * n * k / 1e12, "TFLOP/s", 2.0 * pk["bf16_sustained"]
+        for _ in range(max(3, args.warmup)):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        sec = a.elapsed_time(b) / args.steps * 1e-3
+        print(json.dumps({"kernel": args.kernel, "M": m, "us": sec * 1e6, "achieved": work / sec, "unit": unit,
+                          "frac_of_measured_peak": work / sec / peak}))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel", default=None, choices=["gemm_gate_up", "gemm_down", "quant"],
+                    help="time one kernel alone instead of the whole step")
+    ap.add_argument("--m", default="4096", help="token count(s) for --kernel, comma separated")
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    args = ap.parse_args()
+    if args.kernel is not None:
+        run_kernel_case(args)
+    elif args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

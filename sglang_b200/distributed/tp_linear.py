@@ -1,0 +1,87 @@
+"""Tensor-parallel block-FP8 linears, following the reference's sharding rules:
+
+* column-parallel (python/sglang/srt/layers/linear.py:242-413): weight rows N split p ways, every
+  rank sees the full activation, no collective (gather_output=False);
+* row-parallel (linear.py:1123-1304): weight columns K split p ways, each rank holds x[:, K/p],
+  partial outputs are summed with one bf16 all-reduce (linear.py:1294-1300,
+  python/sglang/srt/distributed/communication_op.py:11-13); bias only on rank 0 (linear.py:1293).
+* block-quant divisibility (python/sglang/srt/layers/quantization/fp8.py:239-262): every shard
+  boundary must fall on a 128-block boundary.
+
+The local linear is injectable so the sharding/collective logic can be exercised with CPU
+ranks (gloo); the default is the CUDA path and there is no CPU fallback in the product.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+BLOCK = 128
+
+
+def shard_block_fp8_weight(weight: torch.Tensor, weight_scale: torch.Tensor, dim: int, rank: int,
+                           world: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Slice weight [N,K] (e4m3) and its [N/128,K/128] block scales for `rank` along dim 0 (N,
+    column-parallel) or dim 1 (K, row-parallel)."""
+    size = weight.shape[dim]
+    if size % world != 0:
+        raise ValueError(f"dimension {dim} of size {size} is not divisible by tp size {world}")
+    part = size // world
+    if part % BLOCK != 0:
+        # fp8.py:245-262: "Weight input/output_size_per_partition ... is not divisible by weight quantization block"
+        raise ValueError(f"partition size {part} is not divisible by the weight quantization block {BLOCK}")
+    lo = rank * part
+    w = weight.narrow(dim, lo, part).contiguous()
+    s = weight_scale.narrow(dim, lo // BLOCK, part // BLOCK).contiguous()
+    return w, s
+
+
+def _default_linear(x, w, ws, bias):
+    from ..layers.quantization.fp8_utils import w8a8_block_fp8_linear
+    return w8a8_block_fp8_linear(x, w, [BLOCK, BLOCK], ws, bias=bias)
+
+
+class ColumnParallelBlockFp8Linear:
+    def __init__(self, weight, weight_scale, bias: Optional[torch.Tensor] = None, group=None,
+                 linear_fn: Callable = _default_linear, already_sharded: bool = False):
+        self.group = group
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+        rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if already_sharded or world == 1:
+            self.weight, self.weight_scale, self.bias = weight, weight_scale, bias
+        else:
+            self.weight, self.weight_scale = shard_block_fp8_weight(weight, weight_scale, 0, rank, world)
+            part = weight.shape[0] // world
+            self.bias = None if bias is None else bias.narrow(0, rank * part, part).contiguous()
+        self._linear = linear_fn
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self._linear(x, self.weight, self.weight_scale, self.bias)
+
+    __call__ = forward
+
+
+class RowParallelBlockFp8Linear:
+    def __init__(self, weight, weight_scale, bias: Optional[torch.Tensor] = None, group=None,
+                 linear_fn: Callable = _default_linear, reduce_results: bool = True, already_sharded: bool = False):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if already_sharded or self.world == 1:
+            self.weight, self.weight_scale = weight, weight_scale
+        else:
+            self.weight, self.weight_scale = shard_block_fp8_weight(weight, weight_scale, 1, self.rank, self.world)
+        self.bias = bias
+        self.reduce_results = reduce_results
+        self._linear = linear_fn
+
+    def forward(self, x_shard: torch.Tensor) -> torch.Tensor:
+        bias = self.bias if self.rank == 0 else None   # added once, before the sum
+        out = self._linear(x_shard, self.weight, self.weight_scale, bias)
+        if self.reduce_results and self.world > 1:
+            dist.all_reduce(out, op=dist.ReduceOp.SUM, group=self.group)
+        return out
+
+    __call__ = forward

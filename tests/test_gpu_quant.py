@@ -140,4 +140,4 @@ def test_full_size_checksum_property():
     # size-independent property: |dequant - x| <= scale * 2^-4 * 448 / 2 ... i.e. half an e4m3 ulp at amax
     deq = q.float().view(M, K // 128, 128) * s.unsqueeze(-1)
     err = (deq - x.float().view(M, K // 128, 128)).abs().amax(-1)
-    assert bool(torch.all(err <= s * 16.0 + 1e-30))
+    assert bool(torch.all(err <= s * 16.001 + 1e-30))   # 16 = half the e4m3 step at the top binade
