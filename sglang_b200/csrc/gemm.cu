@@ -17,7 +17,7 @@
 //               registers; after the last k-block it converts and stores the output row segment.
 // All mbarrier waits are bounded; a wait that gives up records a code in a device status word
 // and every role drains to a common exit where tensor memory is released.
-#include "common.cuh"
+#include "gemm_common.cuh"
 
 namespace b200 {
 namespace {
@@ -40,16 +40,6 @@ struct Cfg {
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
-struct GemmParams {
-  const float* sa;
-  const float* sb;
-  void* out;
-  int64_t sa_stride_m, sa_stride_g, sb_stride_n, sb_stride_g, ldo;
-  int M, N, K;
-  int out_dtype;
-  int* status;
-};
-
 __device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks, int& m_blk, int& n_blk) {
   const int group_size = kGroupM * n_blocks;
   const int group = tile / group_size;
@@ -58,49 +48,6 @@ __device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks
   const int in_group = tile - group * group_size;
   m_blk = first_m + in_group % rows;
   n_blk = in_group / rows;
-}
-
-__device__ __forceinline__ uint32_t pack2(__nv_bfloat16*, float a, float b) {
-  __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&t);
-}
-__device__ __forceinline__ uint32_t pack2(__half*, float a, float b) {
-  __half2 t = __floats2half2_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&t);
-}
-__device__ __forceinline__ __nv_bfloat16 cvt1(__nv_bfloat16*, float a) { return __float2bfloat16_rn(a); }
-__device__ __forceinline__ __half cvt1(__half*, float a) { return __float2half_rn(a); }
-
-// Store NCOLS consecutive outputs of one row; `valid` = columns left before N.
-template <int NCOLS, typename OutT>
-__device__ __forceinline__ void store_row(OutT* dst, const float (&acc)[NCOLS], int valid, bool vec_ok) {
-  if (vec_ok && valid >= NCOLS) {
-#pragma unroll
-    for (int c = 0; c < NCOLS; c += 8) {
-      uint4 v;
-      v.x = pack2(dst, acc[c + 0], acc[c + 1]);
-      v.y = pack2(dst, acc[c + 2], acc[c + 3]);
-      v.z = pack2(dst, acc[c + 4], acc[c + 5]);
-      v.w = pack2(dst, acc[c + 6], acc[c + 7]);
-      *reinterpret_cast<uint4*>(dst + c) = v;
-    }
-  } else {
-#pragma unroll
-    for (int c = 0; c < NCOLS; ++c)
-      if (c < valid) dst[c] = cvt1(dst, acc[c]);
-  }
-}
-template <int NCOLS>
-__device__ __forceinline__ void store_row(float* dst, const float (&acc)[NCOLS], int valid, bool vec_ok) {
-  if (vec_ok && valid >= NCOLS) {
-#pragma unroll
-    for (int c = 0; c < NCOLS; c += 4)
-      *reinterpret_cast<float4*>(dst + c) = make_float4(acc[c], acc[c + 1], acc[c + 2], acc[c + 3]);
-  } else {
-#pragma unroll
-    for (int c = 0; c < NCOLS; ++c)
-      if (c < valid) dst[c] = acc[c];
-  }
 }
 
 template <int BLOCK_N, typename OutT>
@@ -273,55 +220,6 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 }
 
 // ------------------------------------------------------------------------------------ host
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn) return fn;
-  void* ptr = nullptr;
-  cudaDriverEntryPointQueryResult qres;
-  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
-      qres != cudaDriverEntryPointSuccess) {
-    return nullptr;
-  }
-  fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  return fn;
-}
-
-// 2-D map over a row-major [rows, cols] matrix of bytes, box = box_rows x 128 bytes, 128-byte swizzle.
-int make_map_u8_2d(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
-  EncodeTiledFn fn = get_encode_fn();
-  if (!fn) return B200_ERR_CUDA;
-  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
-  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld)};
-  cuuint32_t box[2] = {128u, static_cast<cuuint32_t>(box_rows)};
-  cuuint32_t estr[2] = {1u, 1u};
-  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) {
-    g_last_cuda_error = static_cast<int>(r);
-    return B200_ERR_CUDA;
-  }
-  return B200_OK;
-}
-
-__device__ int g_gemm_status = 0;
-
-int* status_ptr() {
-  static int* ptrs[64] = {nullptr};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-  if (!ptrs[dev]) {
-    void* ptr = nullptr;
-    if (cudaGetSymbolAddress(&ptr, g_gemm_status) != cudaSuccess) return nullptr;
-    ptrs[dev] = static_cast<int*>(ptr);
-  }
-  return ptrs[dev];
-}
-
 template <int BLOCK_N, typename OutT>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t stream) {
   using C = Cfg<BLOCK_N>;
@@ -354,8 +252,11 @@ int launch_dtype(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams&
 
 }  // namespace
 
-// Tile-shape override for experiments and tests (0 = automatic).
+// Kernel override for experiments and tests: 0 = automatic, 128 / 256 = single-CTA kernel with that
+// BLOCK_N, 2 = CTA-pair kernel.
 int g_force_block_n = 0;
+
+int launch_gemm_pair(const void* a, int64_t lda, const void* b, int64_t ldb, const GemmParams& p, cudaStream_t stream);
 
 }  // namespace b200
 
@@ -382,10 +283,13 @@ extern "C" int b200_fp8_blockwise_scaled_mm(const void* a, int64_t lda, const vo
   p.ldo = ldo;
   p.M = static_cast<int>(M); p.N = static_cast<int>(N); p.K = static_cast<int>(K);
   p.out_dtype = out_dtype;
-  p.status = status_ptr();
+  p.status = gemm_status_ptr();
   if (!p.status) return B200_ERR_CUDA;
 
-  // Tile choice: 128 x 256 when that still gives every SM a tile, else 128 x 128.
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // M > 128: CTA-pair kernel (256 x 128 tiles).  Otherwise one CTA per tile:
+  // 128 x 256 when that still gives every SM a tile, else 128 x 128.
+  if ((M > 128 && g_force_block_n == 0) || g_force_block_n == 2) return launch_gemm_pair(a, lda, b, ldb, p, st);
   const int64_t m_blocks = (M + BLOCK_M - 1) / BLOCK_M;
   int block_n = 256;
   if (m_blocks * ((N + 255) / 256) < sm_count()) block_n = 128;
@@ -396,19 +300,7 @@ extern "C" int b200_fp8_blockwise_scaled_mm(const void* a, int64_t lda, const vo
   if (rc != B200_OK) return rc;
   rc = make_map_u8_2d(&mb, b, N, K, ldb, block_n);
   if (rc != B200_OK) return rc;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
   return block_n == 256 ? launch_dtype<256>(ma, mb, p, st) : launch_dtype<128>(ma, mb, p, st);
-}
-
-extern "C" int b200_gemm_device_status(int* status_out) {
-  using namespace b200;
-  if (!status_out) return B200_ERR_NULL_PTR;
-  int* ptr = status_ptr();
-  if (!ptr) return B200_ERR_CUDA;
-  B200_CUDA_TRY(cudaDeviceSynchronize());
-  B200_CUDA_TRY(cudaMemcpy(status_out, ptr, sizeof(int), cudaMemcpyDeviceToHost));
-  if (*status_out != 0) B200_CUDA_TRY(cudaMemset(ptr, 0, sizeof(int)));
-  return B200_OK;
 }
 
 extern "C" int b200_debug_force_block_n(int block_n) {

@@ -1,0 +1,71 @@
+// Pieces shared by the block-FP8 GEMM kernels: parameter block, output-row stores, tensor-map
+// construction and the device status word.
+#pragma once
+#include "common.cuh"
+
+namespace b200 {
+
+struct GemmParams {
+  const float* sa;
+  const float* sb;
+  void* out;
+  int64_t sa_stride_m, sa_stride_g, sb_stride_n, sb_stride_g, ldo;
+  int M, N, K;
+  int out_dtype;
+  int* status;
+};
+
+
+// Device status word of the GEMM kernels on the current device (0 = ok), or nullptr on error.
+int* gemm_status_ptr();
+// 2-D tensor map over a row-major [rows, cols] byte matrix with leading dimension ld, box =
+// box_rows x 128 bytes, 128-byte swizzle, zero fill outside the matrix.
+int make_map_u8_2d(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows);
+
+#if defined(__CUDACC__)
+__device__ __forceinline__ uint32_t pack2(__nv_bfloat16*, float a, float b) {
+  __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&t);
+}
+__device__ __forceinline__ uint32_t pack2(__half*, float a, float b) {
+  __half2 t = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&t);
+}
+__device__ __forceinline__ __nv_bfloat16 cvt1(__nv_bfloat16*, float a) { return __float2bfloat16_rn(a); }
+__device__ __forceinline__ __half cvt1(__half*, float a) { return __float2half_rn(a); }
+
+// Store NCOLS consecutive outputs of one row; `valid` = columns left before N.
+template <int NCOLS, typename OutT>
+__device__ __forceinline__ void store_row(OutT* dst, const float (&acc)[NCOLS], int valid, bool vec_ok) {
+  if (vec_ok && valid >= NCOLS) {
+#pragma unroll
+    for (int c = 0; c < NCOLS; c += 8) {
+      uint4 v;
+      v.x = pack2(dst, acc[c + 0], acc[c + 1]);
+      v.y = pack2(dst, acc[c + 2], acc[c + 3]);
+      v.z = pack2(dst, acc[c + 4], acc[c + 5]);
+      v.w = pack2(dst, acc[c + 6], acc[c + 7]);
+      *reinterpret_cast<uint4*>(dst + c) = v;
+    }
+  } else {
+#pragma unroll
+    for (int c = 0; c < NCOLS; ++c)
+      if (c < valid) dst[c] = cvt1(dst, acc[c]);
+  }
+}
+template <int NCOLS>
+__device__ __forceinline__ void store_row(float* dst, const float (&acc)[NCOLS], int valid, bool vec_ok) {
+  if (vec_ok && valid >= NCOLS) {
+#pragma unroll
+    for (int c = 0; c < NCOLS; c += 4)
+      *reinterpret_cast<float4*>(dst + c) = make_float4(acc[c], acc[c + 1], acc[c + 2], acc[c + 3]);
+  } else {
+#pragma unroll
+    for (int c = 0; c < NCOLS; ++c)
+      if (c < valid) dst[c] = acc[c];
+  }
+}
+
+#endif  // __CUDACC__
+
+}  // namespace b200

@@ -68,7 +68,7 @@ def _assert_parity(a, b, sa, sb, force_block_n=0):
     return c32, cbf
 
 
-@pytest.mark.parametrize("block_n", [128, 256])
+@pytest.mark.parametrize("block_n", [128, 256, 2])   # 2 = CTA-pair kernel
 @pytest.mark.parametrize("K", [128, 256, 512, 1024])
 @pytest.mark.parametrize("N", [128, 256, 512, 1152])
 @pytest.mark.parametrize("M", [1, 3, 5, 127, 128, 129, 512])
