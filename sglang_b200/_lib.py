@@ -39,6 +39,10 @@ _SIGNATURES = {
     "b200_gemm_device_status": (c_int, [ctypes.POINTER(c_int)]),
     "b200_debug_force_block_n": (c_int, [c_int]),
     "b200_debug_force_quant_passes": (c_int, [c_int]),
+    "b200_debug_pair_kernel_max_clusters": (c_int, []),
+    "b200_debug_gemm_mode": (c_int, [c_int]),
+    "b200_debug_wait_hint_ns": (c_int, [c_int]),
+    "b200_debug_set_timing_buffer": (c_int, [c_void_p]),
 }
 
 

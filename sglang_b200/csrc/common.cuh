@@ -68,15 +68,27 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+// try_wait with an optional suspend-time hint (ns): with a hint a failed try may keep the thread
+// suspended in hardware for up to that long; hint 0 uses the plain form.
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity, uint32_t hint_ns = 0) {
   uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred P;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
-      "selp.b32 %0, 1, 0, P;\n\t}\n"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
+  if (hint_ns != 0) {
+    asm volatile(
+        "{\n\t.reg .pred P;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
+        "selp.b32 %0, 1, 0, P;\n\t}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred P;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, P;\n\t}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+  }
   return ok != 0;
 }
 
@@ -84,11 +96,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // in *status (first failure wins) and returns false.  Callers leave their loops on false.
 constexpr long long kWaitLimitCycles = 2000000000LL;
 
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code,
+                                          uint32_t hint_ns = 0) {
+  if (mbar_try_wait(bar, parity, hint_ns)) return true;
   const long long t0 = clock64();
   uint32_t spins = 0;
-  while (!mbar_try_wait(bar, parity)) {
+  while (!mbar_try_wait(bar, parity, hint_ns)) {
     if ((++spins & 0xffu) == 0) {
       if (*reinterpret_cast<volatile int*>(status) != 0) return false;  // someone else gave up
       if (clock64() - t0 > kWaitLimitCycles) {
@@ -98,6 +111,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
     }
   }
   return true;
+}
+
+// The same wait for a whole converged warp; the outcome is made warp-uniform so that all lanes
+// leave their loop together when a wait gives up.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, int* status, int code,
+                                               uint32_t hint_ns = 0) {
+  const bool ok = mbar_wait(bar, parity, status, code, hint_ns);
+  return __all_sync(0xffffffffu, ok);
 }
 
 // ---- TMA (tiled bulk tensor copy global -> shared, completion on an mbarrier; no multicast)
@@ -152,7 +173,7 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
                : "memory");
 }
 // 32 lanes x 32 consecutive fp32 columns: thread t of the warp gets lane (base_lane + t).
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
   uint32_t* r = reinterpret_cast<uint32_t*>(v);
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -186,12 +207,15 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
 __device__ __forceinline__ void cluster_sync_all() {  // every thread of every CTA in the cluster
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// Arrive on the same-named mbarrier in CTA `cta` of the cluster.
+// Arrive on the same-named mbarrier in CTA `cta` of the cluster.  Default (.release.cta) semantics on
+// purpose: a cluster-scope release makes the warp wait for all its outstanding global loads
+// (measured as the dominant "membar" stall), and the only thing ordered here is tensor-memory
+// reads, which tcgen05.wait::ld + fence::before_thread_sync already cover.
 __device__ __forceinline__ void mbar_arrive_cluster(uint64_t* bar, uint32_t cta) {
   asm volatile(
       "{\n\t.reg .b32 remote;\n\t"
       "mapa.shared::cluster.u32 remote, %0, %1;\n\t"
-      "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [remote];\n\t}\n"
+      "mbarrier.arrive.shared::cluster.b64 _, [remote];\n\t}\n"
       ::"r"(smem_u32(bar)), "r"(cta)
       : "memory");
 }
@@ -232,6 +256,43 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t cta_mas
   asm volatile(
       "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
       ::"r"(smem_u32(bar)), "h"(cta_mask)
+      : "memory");
+}
+
+// One k-block of pair MMAs (four K=32 steps, fresh accumulator) plus its completion commit, issued
+// by the elected lane, bracketed by the barrier tests for the NEXT k-block: the two try_waits are
+// started first and their results are only read after the MMAs have been issued, so their latency
+// overlaps the issue instead of preceding it.  All lanes execute the tests (warp-uniform flow).
+__device__ __forceinline__ void umma_f8_pair_kblock_with_peek(
+    uint32_t elected, uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint64_t* done_bar,
+    uint16_t cta_mask, uint64_t* next_acc_bar, uint32_t next_acc_parity, uint64_t* next_full_bar,
+    uint32_t next_full_parity, uint32_t& acc_ready, uint32_t& ops_ready) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred PE, PA, PF, PT, PZ;\n\t"
+      ".reg .b64 ad, bd;\n\t"
+      "setp.ne.b32 PE, %2, 0;\n\t"
+      "setp.eq.b32 PT, 0, 0;\n\t"
+      "setp.ne.b32 PZ, 0, 0;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 PA, [%9], %10;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 PF, [%11], %12;\n\t"
+      "@PE tcgen05.mma.cta_group::2.kind::f8f6f4 [%3], %4, %5, %6, PZ;\n\t"
+      "add.s64 ad, %4, 2;\n\t"
+      "add.s64 bd, %5, 2;\n\t"
+      "@PE tcgen05.mma.cta_group::2.kind::f8f6f4 [%3], ad, bd, %6, PT;\n\t"
+      "add.s64 ad, %4, 4;\n\t"
+      "add.s64 bd, %5, 4;\n\t"
+      "@PE tcgen05.mma.cta_group::2.kind::f8f6f4 [%3], ad, bd, %6, PT;\n\t"
+      "add.s64 ad, %4, 6;\n\t"
+      "add.s64 bd, %5, 6;\n\t"
+      "@PE tcgen05.mma.cta_group::2.kind::f8f6f4 [%3], ad, bd, %6, PT;\n\t"
+      "@PE tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%7], %8;\n\t"
+      "selp.b32 %0, 1, 0, PA;\n\t"
+      "selp.b32 %1, 1, 0, PF;\n\t"
+      "}\n"
+      : "=r"(acc_ready), "=r"(ops_ready)
+      : "r"(elected), "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(smem_u32(done_bar)), "h"(cta_mask),
+        "r"(smem_u32(next_acc_bar)), "r"(next_acc_parity), "r"(smem_u32(next_full_bar)), "r"(next_full_parity)
       : "memory");
 }
 

@@ -4,19 +4,23 @@
 // (sgl-kernel/csrc/gemm/fp8_blockwise_gemm_kernel.cu:165-423) and the Triton kernel
 // _w8a8_block_fp8_matmul (python/sglang/srt/layers/quantization/fp8_kernel.py:493-575).
 //
-// One persistent CTA per SM, 18 warps, warp-specialised:
+// One persistent CTA per SM, warp-specialised:
 //   warp 0      TMA producer: per 128-wide k-block one A box (128 rows x 128 B) and one B box
 //               (BLOCK_N rows x 128 B) into a ring of shared-memory stages (128-byte swizzle).
 //   warp 1      MMA issuer: 4 x tcgen05.mma kind::f8f6f4 (M128 x N BLOCK_N x K32) per k-block into
 //               a tensor-memory accumulator that is started fresh for every k-block (the fp32
 //               scales differ per k-block, so partial sums cannot be chained inside the tensor
-//               core); accumulators rotate through 512/BLOCK_N tensor-memory buffers.
-//   warps 2..17 promotion + epilogue: each warp owns 32 rows (its tensor-memory lane quadrant)
-//               x BLOCK_N/4 columns; per k-block it reads the partial sums with tcgen05.ld,
-//               releases the buffer, and does acc += partial * (sa[m,kb] * sb[nb,kb]) in fp32
-//               registers; after the last k-block it converts and stores the output row segment.
-// All mbarrier waits are bounded; a wait that gives up records a code in a device status word
-// and every role drains to a common exit where tensor memory is released.
+//               core); accumulators rotate through 512/BLOCK_N tensor-memory buffers.  One
+//               tcgen05.commit per k-block signals both "stage reusable" and "partial sums ready".
+//   warps 2..   promotion + epilogue: each warp owns 32 rows (its tensor-memory lane quadrant)
+//               x CPW columns; per k-block it reads the partial sums with tcgen05.ld in chunks,
+//               releases the buffer after the last chunk has landed, and does
+//               acc += partial * (sa[m,kb] * sb[nb,kb]) with packed fp32 FMAs; after the last
+//               k-block it converts and stores its output row segment.
+// The TMA and MMA warps walk their loops with all 32 lanes (warp-uniform addresses and
+// descriptors) and one elected lane issues.  All mbarrier waits are bounded; a wait that gives up
+// records a code in a device status word and every role drains to a common exit where tensor
+// memory is released.
 #include "gemm_common.cuh"
 
 namespace b200 {
@@ -24,20 +28,26 @@ namespace {
 
 constexpr int BLOCK_M = 128;
 constexpr int BLOCK_K = 128;
-constexpr int kEpiWarps = 16;
-constexpr int kThreads = 32 * (2 + kEpiWarps);
 constexpr int kTmemCols = 512;
-constexpr int kGroupM = 16;  // m-blocks per rasterisation group (keeps A and B tiles of a wave in L2)
+constexpr int kGroupM = 16;     // m-blocks per rasterisation group (keeps A and B tiles of a wave in L2)
+constexpr int kScaleGroup = 4;   // k-blocks per scale-ring slot
+constexpr int kScaleSlots = 4;   // slots in the ring (the stager runs up to 16 k-blocks ahead)
 
-template <int BLOCK_N>
+template <int BLOCK_N, int EPI_WARPS, int ISSUERS = 1>
 struct Cfg {
   static constexpr int kStages = BLOCK_N == 256 ? 4 : 6;
   static constexpr int kABytes = BLOCK_M * BLOCK_K;
   static constexpr int kBBytes = BLOCK_N * BLOCK_K;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kNumAcc = kTmemCols / BLOCK_N;
-  static constexpr int kColsPerWarp = BLOCK_N / 4;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int kColsPerWarp = BLOCK_N / (EPI_WARPS / 4);
+  static constexpr int kStagerWarp = 2 + EPI_WARPS;             // stages the scale products in shared memory
+  static constexpr int kMmaWarpB = 3 + EPI_WARPS;               // second MMA-issuing warp when ISSUERS == 2
+  static constexpr int kThreads = 32 * (2 + ISSUERS + EPI_WARPS);
+  static constexpr int kHalves = BLOCK_N / 128;                 // weight-scale blocks per tile row
+  static constexpr int kSlotFloats = kScaleGroup * kHalves * BLOCK_M;
+  static constexpr int kScaleBytes = kScaleSlots * kSlotFloats * 4;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kScaleBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks, int& m_blk, int& n_blk) {
@@ -50,22 +60,24 @@ __device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks
   n_blk = in_group / rows;
 }
 
-template <int BLOCK_N, typename OutT>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int BLOCK_N, int EPI_WARPS, int CHUNK, int ISSUERS, typename OutT>
+__global__ void __launch_bounds__(Cfg<BLOCK_N, EPI_WARPS, ISSUERS>::kThreads, 1)
 gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                       const GemmParams p) {
-  using C = Cfg<BLOCK_N>;
+  using C = Cfg<BLOCK_N, EPI_WARPS, ISSUERS>;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: the 128-byte swizzle pattern is a function of address bits [4,10).
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_a = smem;
   uint8_t* smem_b = smem + C::kStages * C::kABytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes);
-  uint64_t* full_bar = bars;
-  uint64_t* empty_bar = bars + C::kStages;
-  uint64_t* acc_full = bars + 2 * C::kStages;
-  uint64_t* acc_empty = acc_full + C::kNumAcc;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + C::kNumAcc);
+  float* smem_scale = reinterpret_cast<float*>(smem + C::kStages * C::kStageBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes + C::kScaleBytes);
+  uint64_t* full_bar = bars;                    // operands of the stage have landed
+  uint64_t* done_bar = bars + C::kStages;       // the k-block's MMAs completed
+  uint64_t* acc_empty = bars + 2 * C::kStages;  // accumulator buffer has been read out
+  uint64_t* scale_full = acc_empty + C::kNumAcc;     // scale-ring slot written
+  uint64_t* scale_empty = scale_full + kScaleSlots;  // scale-ring slot consumed by every epilogue warp
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(scale_empty + kScaleSlots);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -77,11 +89,12 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   if (threadIdx.x == 0) {
     for (int i = 0; i < C::kStages; ++i) {
       mbar_init(&full_bar[i], 1);
-      mbar_init(&empty_bar[i], 1);
+      mbar_init(&done_bar[i], 1);
     }
-    for (int i = 0; i < C::kNumAcc; ++i) {
-      mbar_init(&acc_full[i], 1);
-      mbar_init(&acc_empty[i], kEpiWarps);
+    for (int i = 0; i < C::kNumAcc; ++i) mbar_init(&acc_empty[i], EPI_WARPS);
+    for (int i = 0; i < kScaleSlots; ++i) {
+      mbar_init(&scale_full[i], 1);
+      mbar_init(&scale_empty[i], EPI_WARPS);
     }
     fence_mbar_init();
     fence_proxy_async_smem();
@@ -101,106 +114,191 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-        int m_blk, n_blk;
-        tile_coords(tile, m_blocks, n_blocks, m_blk, n_blk);
-        for (int kb = 0; kb < nkb; ++kb) {
-          ok = mbar_wait(&empty_bar[stage], phase ^ 1u, p.status, 1);
-          if (!ok) break;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+      int m_blk, n_blk;
+      tile_coords(tile, m_blocks, n_blocks, m_blk, n_blk);
+      for (int kb = 0; kb < nkb; ++kb) {
+        ok = mbar_wait_warp(&done_bar[stage], phase ^ 1u, p.status, 1);
+        if (!ok) break;
+        if (elect_one()) {
           mbar_expect_tx(&full_bar[stage], C::kStageBytes);
           tma_load_2d(smem_a + stage * C::kABytes, &map_a, &full_bar[stage], kb * BLOCK_K, m_blk * BLOCK_M);
           tma_load_2d(smem_b + stage * C::kBBytes, &map_b, &full_bar[stage], kb * BLOCK_K, n_blk * BLOCK_N);
-          if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
         }
+        __syncwarp();
+        if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
       }
     }
     __syncwarp();
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_e4m3(BLOCK_M, BLOCK_N);
-      int stage = 0, acc = 0;
-      uint32_t phase = 0, acc_phase = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-        for (int kb = 0; kb < nkb; ++kb) {
-          ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1u, p.status, 2);
-          if (!ok) break;
-          ok = mbar_wait(&full_bar[stage], phase, p.status, 3);
-          if (!ok) break;
-          tc_fence_after();
-          const uint64_t a_desc = umma_desc_k128(smem_u32(smem_a + stage * C::kABytes));
-          const uint64_t b_desc = umma_desc_k128(smem_u32(smem_b + stage * C::kBBytes));
-          const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BLOCK_N);
+  } else if (warp == 1 || (ISSUERS == 2 && warp == C::kMmaWarpB)) {
+    // ------------------------------------------------------------------ MMA issuer(s)
+    // With ISSUERS == 2 (experimental), warp 1 takes the even k-blocks of this CTA's k-block
+    // sequence and the second warp the odd ones; k-blocks are independent (own stage, own
+    // accumulator buffer), so the two issue streams may interleave freely.
+    constexpr uint32_t idesc = umma_idesc_e4m3(BLOCK_M, BLOCK_N);
+    const uint64_t a_desc0 = umma_desc_k128(smem_u32(smem_a));
+    const uint64_t b_desc0 = umma_desc_k128(smem_u32(smem_b));
+    const int first = (warp == 1) ? 0 : 1;
+    const int my_tiles = (num_tiles > static_cast<int>(blockIdx.x))
+                             ? (num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
+                                   static_cast<int>(gridDim.x)
+                             : 0;
+    const long long total_kb = static_cast<long long>(my_tiles) * nkb;
+    int stage = first % C::kStages, acc = first % C::kNumAcc;
+    uint32_t phase = 0, acc_phase = 0;
+    bool ok = true;
+    for (long long g = first; ok && g < total_kb; g += ISSUERS) {
+      ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1u, p.status, 2);
+      if (ok) ok = mbar_wait(&full_bar[stage], phase, p.status, 3);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(stage * (C::kABytes >> 4));
+      const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(stage * (C::kBBytes >> 4));
+      const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BLOCK_N);
+      if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < BLOCK_K / 32; ++k) {
-            // advance 32 bytes along K inside the 128-byte swizzle row: +2 in the (addr >> 4) field
-            umma_f8(d_tmem, a_desc + static_cast<uint64_t>(2 * k), b_desc + static_cast<uint64_t>(2 * k), idesc,
-                    k > 0 ? 1u : 0u);
-          }
-          umma_commit(&empty_bar[stage]);  // stage reusable once these MMAs have read it
-          umma_commit(&acc_full[acc]);     // partial sums of this k-block are in tensor memory
-          if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
-          if (++acc == C::kNumAcc) { acc = 0; acc_phase ^= 1u; }
+        for (int k = 0; k < BLOCK_K / 32; ++k) {
+          // advance 32 bytes along K inside the 128-byte swizzle row: +2 in the (addr >> 4) field
+          umma_f8(d_tmem, a_desc + static_cast<uint64_t>(2 * k), b_desc + static_cast<uint64_t>(2 * k), idesc,
+                  k > 0 ? 1u : 0u);
         }
+        umma_commit(&done_bar[stage]);  // stage reusable and partial sums readable once these MMAs finish
+      }
+      __syncwarp();
+      stage += ISSUERS;
+      if (stage >= C::kStages) { stage -= C::kStages; phase ^= 1u; }
+      acc += ISSUERS;
+      if (acc >= C::kNumAcc) { acc -= C::kNumAcc; acc_phase ^= 1u; }
+    }
+    __syncwarp();
+  } else if (warp == C::kStagerWarp) {
+    // ------------------------------------------------------------------ scale stager
+    // Global loads of the scales take far longer than a k-block under TMA load (they were the
+    // dominant stall when the epilogue warps fetched them a few k-blocks ahead), so one warp
+    // runs up to kScaleSlots*kScaleGroup k-blocks ahead and leaves the products
+    // sa[m,kb] * sb[nb,kb] in a shared-memory ring: slot layout [kScaleGroup][halves][128 rows].
+    int slot = 0;
+    uint32_t sphase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+      int m_blk, n_blk;
+      tile_coords(tile, m_blocks, n_blocks, m_blk, n_blk);
+      const int m0 = m_blk * BLOCK_M;
+      for (int kb0 = 0; kb0 < nkb; kb0 += kScaleGroup) {
+        ok = mbar_wait_warp(&scale_empty[slot], sphase ^ 1u, p.status, 5);
+        if (!ok) break;
+        float* dst = smem_scale + slot * C::kSlotFloats;
+        float a[kScaleGroup][4];
+        float bsc[kScaleGroup][C::kHalves];
+#pragma unroll
+        for (int j = 0; j < kScaleGroup; ++j) {
+          const int kb = kb0 + j;
+          const bool kin = kb < nkb;
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            const int m = m0 + r * 32 + lane;
+            a[j][r] = (kin && m < p.M)
+                          ? __ldg(p.sa + static_cast<int64_t>(m) * p.sa_stride_m + static_cast<int64_t>(kb) * p.sa_stride_g)
+                          : 0.f;
+          }
+#pragma unroll
+          for (int h = 0; h < C::kHalves; ++h) {
+            const int nb = min(n_blk * BLOCK_N + h * 128, p.N - 1) / 128;
+            bsc[j][h] = kin ? __ldg(p.sb + static_cast<int64_t>(nb) * p.sb_stride_n +
+                                    static_cast<int64_t>(kb) * p.sb_stride_g)
+                            : 0.f;
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < kScaleGroup; ++j)
+#pragma unroll
+          for (int h = 0; h < C::kHalves; ++h)
+#pragma unroll
+            for (int r = 0; r < 4; ++r) dst[(j * C::kHalves + h) * BLOCK_M + r * 32 + lane] = a[j][r] * bsc[j][h];
+        __threadfence_block();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&scale_full[slot]);
+        if (++slot == kScaleSlots) { slot = 0; sphase ^= 1u; }
       }
     }
     __syncwarp();
   } else {
     // ------------------------------------------------------------------ promotion + epilogue
     constexpr int CPW = C::kColsPerWarp;
-    const int quad = warp & 3;          // tensor-memory lane quadrant this warp may read
-    const int part = (warp - 2) >> 2;   // which BLOCK_N/4 column slice
+    static_assert(CPW % CHUNK == 0 && (CHUNK == 16 || CHUNK == 32 || CHUNK == 64), "chunking");
+    static_assert(CPW <= 128, "a warp's columns lie in one weight-scale block");
+    const int quad = warp & 3;         // tensor-memory lane quadrant this warp may read
+    const int part = (warp - 2) >> 2;  // which CPW-wide column slice
+    const int half = (part * CPW) / 128;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     OutT* out = static_cast<OutT*>(p.out);
     const bool vec_ok = (p.ldo % (16 / (int)sizeof(OutT)) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15u) == 0);
-    int acc_i = 0;
-    uint32_t acc_phase = 0;
+    int acc_i = 0, stage = 0, slot = 0;
+    uint32_t phase = 0, sphase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
       int m_blk, n_blk;
       tile_coords(tile, m_blocks, n_blocks, m_blk, n_blk);
       const int m = m_blk * BLOCK_M + quad * 32 + lane;
       const int n0 = n_blk * BLOCK_N + part * CPW;
-      const bool row_ok = m < p.M;
-      const float* sa_ptr = p.sa + static_cast<int64_t>(row_ok ? m : 0) * p.sa_stride_m;
-      const int nb = min(n0, p.N - 1) / 128;
-      const float* sb_ptr = p.sb + static_cast<int64_t>(nb) * p.sb_stride_n;
       float acc[CPW];
 #pragma unroll
       for (int c = 0; c < CPW; ++c) acc[c] = 0.f;
-      float s_next = row_ok ? __ldg(sa_ptr) * __ldg(sb_ptr) : 0.f;
-      for (int kb = 0; kb < nkb; ++kb) {
-        const float s = s_next;
-        if (kb + 1 < nkb) {
-          const float a_s = row_ok ? __ldg(sa_ptr + static_cast<int64_t>(kb + 1) * p.sa_stride_g) : 0.f;
-          s_next = a_s * __ldg(sb_ptr + static_cast<int64_t>(kb + 1) * p.sb_stride_g);
-        }
-        ok = mbar_wait(&acc_full[acc_i], acc_phase, p.status, 4);
+      for (int kb0 = 0; ok && kb0 < nkb; kb0 += kScaleGroup) {
+        // the four scale products of this group, then the slot goes straight back to the stager
+        ok = mbar_wait(&scale_full[slot], sphase, p.status, 6);
         if (!ok) break;
-        tc_fence_after();
-        const uint32_t taddr = tmem_base + lane_addr + static_cast<uint32_t>(acc_i * BLOCK_N + part * CPW);
+        float sc[kScaleGroup];
+        const float* src = smem_scale + slot * C::kSlotFloats + half * BLOCK_M + quad * 32 + lane;
 #pragma unroll
-        for (int ch = 0; ch < CPW / 16; ++ch) {
-          float v[16];
-          tmem_ld16(taddr + ch * 16, v);
-          tmem_ld_wait();
-          if (ch == CPW / 16 - 1) {
-            // all of this warp's reads of the buffer are complete: hand it back to the MMA warp
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[acc_i]);
+        for (int j = 0; j < kScaleGroup; ++j) sc[j] = src[j * C::kHalves * BLOCK_M];
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&scale_empty[slot]);
+        if (++slot == kScaleSlots) { slot = 0; sphase ^= 1u; }
+#pragma unroll
+        for (int j = 0; j < kScaleGroup; ++j) {
+          const int kb = kb0 + j;
+          if (kb < nkb) {
+            ok = mbar_wait(&done_bar[stage], phase, p.status, 4);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + lane_addr + static_cast<uint32_t>(acc_i * BLOCK_N + part * CPW);
+            const float2 s2 = make_float2(sc[j], sc[j]);
+#pragma unroll
+            for (int ch = 0; ch < CPW / CHUNK; ++ch) {
+              float v[CHUNK];
+              if constexpr (CHUNK == 16) {
+                tmem_ld16(taddr + ch * CHUNK, v);
+              } else {
+#pragma unroll
+                for (int q = 0; q < CHUNK / 32; ++q) tmem_ld32(taddr + ch * CHUNK + q * 32, v + q * 32);
+              }
+              tmem_ld_wait();
+              if (ch == CPW / CHUNK - 1) {
+                // all of this warp's reads of the buffer are complete: hand it back to the MMA warp
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[acc_i]);
+              }
+              // two fp32 FMAs per instruction (fma.rn.f32x2); the promotion is issue-bound otherwise
+#pragma unroll
+              for (int c = 0; c < CHUNK; c += 2) {
+                const float2 r = __ffma2_rn(make_float2(v[c], v[c + 1]), s2,
+                                            make_float2(acc[ch * CHUNK + c], acc[ch * CHUNK + c + 1]));
+                acc[ch * CHUNK + c] = r.x;
+                acc[ch * CHUNK + c + 1] = r.y;
+              }
+            }
+            if (++acc_i == C::kNumAcc) acc_i = 0;
+            if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
           }
-#pragma unroll
-          for (int c = 0; c < 16; ++c) acc[ch * 16 + c] = fmaf(v[c], s, acc[ch * 16 + c]);
         }
-        if (++acc_i == C::kNumAcc) { acc_i = 0; acc_phase ^= 1u; }
       }
-      if (ok && row_ok && n0 < p.N) {
+      if (ok && m < p.M && n0 < p.N) {
         store_row<CPW>(out + static_cast<int64_t>(m) * p.ldo + n0, acc, p.N - n0, vec_ok);
       }
     }
@@ -220,10 +318,10 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 }
 
 // ------------------------------------------------------------------------------------ host
-template <int BLOCK_N, typename OutT>
+template <int BLOCK_N, int EPI_WARPS, int CHUNK, int ISSUERS, typename OutT>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t stream) {
-  using C = Cfg<BLOCK_N>;
-  auto kern = gemm_block_fp8_kernel<BLOCK_N, OutT>;
+  using C = Cfg<BLOCK_N, EPI_WARPS, ISSUERS>;
+  auto kern = gemm_block_fp8_kernel<BLOCK_N, EPI_WARPS, CHUNK, ISSUERS, OutT>;
   static bool attr_set[64] = {false};
   int dev = 0;
   B200_CUDA_TRY(cudaGetDevice(&dev));
@@ -235,26 +333,47 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cu
   const int n_blocks = (p.N + BLOCK_N - 1) / BLOCK_N;
   const int tiles = m_blocks * n_blocks;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  kern<<<grid, kThreads, C::kSmemBytes, stream>>>(ma, mb, p);
+  kern<<<grid, C::kThreads, C::kSmemBytes, stream>>>(ma, mb, p);
   B200_CUDA_TRY(cudaGetLastError());
   return B200_OK;
 }
 
-template <int BLOCK_N>
+template <int BLOCK_N, int EPI_WARPS, int CHUNK, int ISSUERS = 1>
 int launch_dtype(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t stream) {
   switch (p.out_dtype) {
-    case B200_DT_BF16: return launch<BLOCK_N, __nv_bfloat16>(ma, mb, p, stream);
-    case B200_DT_F16: return launch<BLOCK_N, __half>(ma, mb, p, stream);
-    case B200_DT_F32: return launch<BLOCK_N, float>(ma, mb, p, stream);
+    case B200_DT_BF16: return launch<BLOCK_N, EPI_WARPS, CHUNK, ISSUERS, __nv_bfloat16>(ma, mb, p, stream);
+    case B200_DT_F16: return launch<BLOCK_N, EPI_WARPS, CHUNK, ISSUERS, __half>(ma, mb, p, stream);
+    case B200_DT_F32: return launch<BLOCK_N, EPI_WARPS, CHUNK, ISSUERS, float>(ma, mb, p, stream);
     default: return B200_ERR_BAD_DTYPE;
+  }
+}
+
+// Experimental variants selectable through b200_debug_force_block_n (values >= 1000).
+int launch_variant(int id, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t st) {
+  switch (id) {
+    case 1001: return launch_dtype<128, 16, 32>(ma, mb, p, st);
+    case 1002: return launch_dtype<128, 8, 64>(ma, mb, p, st);
+    case 1003: return launch_dtype<128, 8, 32>(ma, mb, p, st);
+    case 1004: return launch_dtype<256, 16, 32>(ma, mb, p, st);
+    case 1005: return launch_dtype<256, 16, 16>(ma, mb, p, st);
+    case 1006: return launch_dtype<256, 8, 32>(ma, mb, p, st);
+    case 1007: return launch_dtype<128, 8, 64, 2>(ma, mb, p, st);
+    case 1008: return launch_dtype<128, 16, 32, 2>(ma, mb, p, st);
+    case 1009: return launch_dtype<256, 16, 16, 2>(ma, mb, p, st);
+    default: return B200_ERR_UNSUPPORTED;
   }
 }
 
 }  // namespace
 
 // Kernel override for experiments and tests: 0 = automatic, 128 / 256 = single-CTA kernel with that
-// BLOCK_N, 2 = CTA-pair kernel.
+// BLOCK_N, 2 = CTA-pair kernel, 1001.. = single-CTA variants (see launch_variant).
 int g_force_block_n = 0;
+// Pair-kernel timing experiments (bit mask): 1 = epilogue skips tensor-memory reads and FMAs,
+// 2 = no TMA and the MMA does not wait for operands, 16 = epilogue skips only the FMAs.
+int g_gemm_debug_mode = 0;
+int g_gemm_wait_hint_ns = 0;
+long long* g_gemm_debug_buf = nullptr;
 
 int launch_gemm_pair(const void* a, int64_t lda, const void* b, int64_t ldb, const GemmParams& p, cudaStream_t stream);
 
@@ -284,6 +403,9 @@ extern "C" int b200_fp8_blockwise_scaled_mm(const void* a, int64_t lda, const vo
   p.M = static_cast<int>(M); p.N = static_cast<int>(N); p.K = static_cast<int>(K);
   p.out_dtype = out_dtype;
   p.status = gemm_status_ptr();
+  p.debug_mode = g_gemm_debug_mode;
+  p.debug_buf = g_gemm_debug_buf;
+  p.wait_hint_ns = static_cast<uint32_t>(g_gemm_wait_hint_ns);
   if (!p.status) return B200_ERR_CUDA;
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -294,13 +416,30 @@ extern "C" int b200_fp8_blockwise_scaled_mm(const void* a, int64_t lda, const vo
   int block_n = 256;
   if (m_blocks * ((N + 255) / 256) < sm_count()) block_n = 128;
   if (g_force_block_n == 128 || g_force_block_n == 256) block_n = g_force_block_n;
+  if (g_force_block_n >= 1000) block_n = (g_force_block_n <= 1003 || g_force_block_n == 1007 || g_force_block_n == 1008) ? 128 : 256;
 
   CUtensorMap ma, mb;
   rc = make_map_u8_2d(&ma, a, M, K, lda, BLOCK_M);
   if (rc != B200_OK) return rc;
   rc = make_map_u8_2d(&mb, b, N, K, ldb, block_n);
   if (rc != B200_OK) return rc;
-  return block_n == 256 ? launch_dtype<256>(ma, mb, p, st) : launch_dtype<128>(ma, mb, p, st);
+  if (g_force_block_n >= 1000) return launch_variant(g_force_block_n, ma, mb, p, st);
+  return block_n == 256 ? launch_dtype<256, 16, 16>(ma, mb, p, st) : launch_dtype<128, 8, 64>(ma, mb, p, st);
+}
+
+extern "C" int b200_debug_set_timing_buffer(void* device_buf_5x64_i64) {
+  b200::g_gemm_debug_buf = static_cast<long long*>(device_buf_5x64_i64);
+  return B200_OK;
+}
+
+extern "C" int b200_debug_wait_hint_ns(int ns) {
+  b200::g_gemm_wait_hint_ns = ns;
+  return B200_OK;
+}
+
+extern "C" int b200_debug_gemm_mode(int mode) {
+  b200::g_gemm_debug_mode = mode;
+  return B200_OK;
 }
 
 extern "C" int b200_debug_force_block_n(int block_n) {

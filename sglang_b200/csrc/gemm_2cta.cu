@@ -6,12 +6,13 @@
 // both halves), the leader CTA issues tcgen05.mma.cta_group::2 (M256 x N128 x K32, four per
 // k-block) and each CTA receives its 128 x 128 fp32 partial sums in its own tensor memory.
 // Tensor memory holds four such buffers, so the MMA of k-block i+1..i+3 overlaps the promotion
-// of k-block i: 16 epilogue warps per CTA read their 32 x 32 slice with one tcgen05.ld, hand the
+// of k-block i: 8 epilogue warps per CTA read their 32 x 64 slice with tcgen05.ld, hand the
 // buffer back at once, and accumulate acc += partial * (sa[m,kb] * sb[nb,kb]) in registers.
 // Scales are fetched four k-blocks ahead.  Every wait is bounded (see common.cuh).
 #include "gemm_common.cuh"
 
 namespace b200 {
+int g_last_max_pairs = 0;  // what the cluster occupancy query returned (diagnostics)
 namespace {
 
 constexpr int kPairM = 256;     // rows per CTA pair
@@ -25,9 +26,10 @@ constexpr int kBBytes = kCtaBRows * kBlockK;
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kNumAcc = 4;
 constexpr int kTmemCols = 512;
-constexpr int kEpiWarps = 16;
-constexpr int kThreads = 32 * (2 + kEpiWarps);
-constexpr int kColsPerWarp = kTileN / 4;
+constexpr int kEpiWarps = 8;   // 2 per SM sub-partition: fewer, fatter warps amortise the per-k-block handshake
+constexpr int kMmaWarpB = 2 + kEpiWarps;   // second MMA-issuing warp (the first is warp 1)
+constexpr int kThreads = 32 * (3 + kEpiWarps);
+constexpr int kColsPerWarp = kTileN / (kEpiWarps / 4);
 constexpr int kGroupM = 8;      // pair-m-blocks per rasterisation group
 constexpr int kScaleAhead = 4;  // k-blocks of scale prefetch
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
@@ -51,10 +53,10 @@ gemm_block_fp8_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
   uint8_t* smem_a = smem;
   uint8_t* smem_b = smem + kStages * kABytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
-  uint64_t* full_bar = bars;                 // leader's copy is the live one
-  uint64_t* empty_bar = bars + kStages;      // one per CTA
-  uint64_t* acc_full = bars + 2 * kStages;   // one per CTA
-  uint64_t* acc_empty = acc_full + kNumAcc;  // leader's copy is the live one
+  uint64_t* full_bar = bars;                  // operands landed (leader's copy is the live one)
+  uint64_t* done_bar = bars + kStages;        // the k-block's MMAs completed: its stage may be refilled
+                                              // and its partial sums read (one per CTA)
+  uint64_t* acc_empty = bars + 2 * kStages;   // accumulator buffer read out (leader's copy is live)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + kNumAcc);
 
   const int warp = threadIdx.x >> 5;
@@ -72,12 +74,9 @@ gemm_block_fp8_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; ++i) {
       mbar_init(&full_bar[i], 2);   // one arrival per CTA's producer (+ both CTAs' bytes)
-      mbar_init(&empty_bar[i], 1);  // the leader's commit, delivered to both CTAs
+      mbar_init(&done_bar[i], 1);   // the leader's commit, delivered to both CTAs
     }
-    for (int i = 0; i < kNumAcc; ++i) {
-      mbar_init(&acc_full[i], 1);
-      mbar_init(&acc_empty[i], 2 * kEpiWarps);  // epilogue warps of both CTAs
-    }
+    for (int i = 0; i < kNumAcc; ++i) mbar_init(&acc_empty[i], 2 * kEpiWarps);  // epilogue warps of both CTAs
     fence_mbar_init();
     fence_proxy_async_smem();
   }
@@ -96,7 +95,7 @@ gemm_block_fp8_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (each CTA)
-    if (lane == 0) {
+    if (!(p.debug_mode & 2)) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -106,44 +105,63 @@ gemm_block_fp8_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
         const int row_a = m_blk * kPairM + static_cast<int>(rank) * kCtaM;
         const int row_b = n_blk * kTileN + static_cast<int>(rank) * kCtaBRows;
         for (int kb = 0; kb < nkb; ++kb) {
-          ok = mbar_wait(&empty_bar[stage], phase ^ 1u, p.status, 11);
+          ok = mbar_wait_warp(&done_bar[stage], phase ^ 1u, p.status, 11, p.wait_hint_ns);
           if (!ok) break;
-          if (leader) mbar_expect_tx(&full_bar[stage], 2 * kStageBytes);
-          tma_load_2d_pair(smem_a + stage * kABytes, &map_a, &full_bar[stage], kb * kBlockK, row_a);
-          tma_load_2d_pair(smem_b + stage * kBBytes, &map_b, &full_bar[stage], kb * kBlockK, row_b);
-          if (!leader) mbar_arrive_cluster(&full_bar[stage], 0);
+          if (elect_one()) {
+            if (leader) mbar_expect_tx(&full_bar[stage], 2 * kStageBytes);
+            tma_load_2d_pair(smem_a + stage * kABytes, &map_a, &full_bar[stage], kb * kBlockK, row_a);
+            tma_load_2d_pair(smem_b + stage * kBBytes, &map_b, &full_bar[stage], kb * kBlockK, row_b);
+            if (!leader) mbar_arrive_cluster(&full_bar[stage], 0);
+          }
+          __syncwarp();
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
     }
     __syncwarp();
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
-    if (leader && lane == 0) {
+  } else if (warp == 1 || warp == kMmaWarpB) {
+    // ------------------------------------------------------------------ MMA issuers (leader CTA only)
+    // Two warps share the issue: warp 1 takes the even k-blocks of the CTA pair's k-block sequence,
+    // warp kMmaWarpB the odd ones.  One warp alone spends ~700 cycles per k-block on its two barrier
+    // waits plus the issue (measured), which starves the tensor pipe; k-blocks are independent
+    // (own stage, own accumulator buffer), so the two issue streams may interleave freely.
+    if (leader) {
       constexpr uint32_t idesc = umma_idesc_e4m3(kPairM, kTileN);
-      int stage = 0, acc = 0;
-      uint32_t phase = 0, acc_phase = 0;
+      // the whole warp walks the loop so that addresses and descriptors stay warp-uniform; one
+      // elected lane issues the MMAs and the commit
+      const uint64_t a_desc0 = umma_desc_k128(smem_u32(smem_a));
+      const uint64_t b_desc0 = umma_desc_k128(smem_u32(smem_b));
+      const int issuer = (warp == 1) ? 0 : 1;
+      const bool wait_operands = !(p.debug_mode & 2);
+      const long long my_tiles = (num_tiles > pair_id) ? (num_tiles - pair_id + num_pairs - 1) / num_pairs : 0;
+      const long long total_kb = my_tiles * nkb;
       bool ok = true;
-      for (int tile = pair_id; ok && tile < num_tiles; tile += num_pairs) {
-        for (int kb = 0; kb < nkb; ++kb) {
-          ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1u, p.status, 12);
-          if (!ok) break;
-          ok = mbar_wait(&full_bar[stage], phase, p.status, 13);
-          if (!ok) break;
-          tc_fence_after();
-          const uint64_t a_desc = umma_desc_k128(smem_u32(smem_a + stage * kABytes));
-          const uint64_t b_desc = umma_desc_k128(smem_u32(smem_b + stage * kBBytes));
-          const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kTileN);
+      for (long long g = issuer; ok && g < total_kb; g += 2) {
+        const int stage = static_cast<int>(g % kStages);
+        const uint32_t phase = static_cast<uint32_t>((g / kStages) & 1);
+        const int acc = static_cast<int>(g % kNumAcc);
+        const uint32_t acc_phase = static_cast<uint32_t>((g / kNumAcc) & 1);
+        const bool rec = p.debug_buf != nullptr && pair_id == 0 && g < 64;
+        if (rec && lane == 0) p.debug_buf[0 * 64 + g] = clock64();   // before the waits
+        ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1u, p.status, 12, p.wait_hint_ns);
+        if (rec && lane == 0) p.debug_buf[1 * 64 + g] = clock64();   // accumulator free
+        if (ok && wait_operands) ok = mbar_wait(&full_bar[stage], phase, p.status, 13, p.wait_hint_ns);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        if (rec && lane == 0) p.debug_buf[2 * 64 + g] = clock64();   // operands landed, about to issue
+        const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(stage * (kABytes >> 4));
+        const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(stage * (kBBytes >> 4));
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kTileN);
+        if (elect_one()) {
 #pragma unroll
           for (int k = 0; k < kBlockK / 32; ++k) {
             umma_f8_pair(d_tmem, a_desc + static_cast<uint64_t>(2 * k), b_desc + static_cast<uint64_t>(2 * k), idesc,
                          k > 0 ? 1u : 0u);
           }
-          umma_commit_pair(&empty_bar[stage], 3);  // both CTAs' stages are reusable
-          umma_commit_pair(&acc_full[acc], 3);     // both CTAs' partial sums are ready
-          if (++stage == kStages) { stage = 0; phase ^= 1u; }
-          if (++acc == kNumAcc) { acc = 0; acc_phase ^= 1u; }
+          umma_commit_pair(&done_bar[stage], 3);  // one completion signal, delivered to both CTAs
         }
+        __syncwarp();
       }
     }
     __syncwarp();
@@ -155,8 +173,8 @@ gemm_block_fp8_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     OutT* out = static_cast<OutT*>(p.out);
     const bool vec_ok = (p.ldo % (16 / (int)sizeof(OutT)) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15u) == 0);
-    int acc_i = 0;
-    uint32_t acc_phase = 0;
+    int acc_i = 0, stage = 0;
+    uint32_t phase = 0;
     bool ok = true;
     for (int tile = pair_id; ok && tile < num_tiles; tile += num_pairs) {
       int m_blk, n_blk;
@@ -187,18 +205,40 @@ gemm_block_fp8_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
               fa[j] = __ldg(sa_ptr + static_cast<int64_t>(kn) * p.sa_stride_g);
               fb[j] = __ldg(sb_ptr + static_cast<int64_t>(kn) * p.sb_stride_g);
             }
-            ok = mbar_wait(&acc_full[acc_i], acc_phase, p.status, 14);
+            ok = mbar_wait(&done_bar[stage], phase, p.status, 14, p.wait_hint_ns);
             if (!ok) break;
+            const bool rec = p.debug_buf != nullptr && pair_id == 0 && leader && tile == pair_id && kb < 64 &&
+                             warp == 2 && lane == 0;
+            if (rec) p.debug_buf[3 * 64 + kb] = clock64();   // partial sums visible to the epilogue
             tc_fence_after();
             float v[CPW];
-            tmem_ld32(tmem_base + lane_addr + static_cast<uint32_t>(acc_i * kTileN + part * CPW), v);
-            tmem_ld_wait();
+            const uint32_t taddr = tmem_base + lane_addr + static_cast<uint32_t>(acc_i * kTileN + part * CPW);
+            if (!(p.debug_mode & 1)) {
+#pragma unroll
+              for (int ch = 0; ch < CPW / 32; ++ch) tmem_ld32(taddr + ch * 32, v + ch * 32);
+              tmem_ld_wait();
+            } else {
+#pragma unroll
+              for (int c = 0; c < CPW; ++c) v[c] = 0.f;
+            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(&acc_empty[acc_i], 0);
+            if (rec) p.debug_buf[4 * 64 + kb] = clock64();   // accumulator handed back
+            // two fp32 FMAs per instruction (fma.rn.f32x2): the promotion is issue-bound otherwise
+            const float2 s2 = make_float2(s, s);
+            if (!(p.debug_mode & 17)) {
 #pragma unroll
-            for (int c = 0; c < CPW; ++c) acc[c] = fmaf(v[c], s, acc[c]);
-            if (++acc_i == kNumAcc) { acc_i = 0; acc_phase ^= 1u; }
+              for (int c = 0; c < CPW; c += 2) {
+                const float2 r = __ffma2_rn(make_float2(v[c], v[c + 1]), s2, make_float2(acc[c], acc[c + 1]));
+                acc[c] = r.x;
+                acc[c + 1] = r.y;
+              }
+            } else {
+              acc[0] += v[0] * s;
+            }
+            if (++acc_i == kNumAcc) acc_i = 0;
+            if (++stage == kStages) { stage = 0; phase ^= 1u; }
           }
         }
       }
@@ -245,6 +285,7 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& 
     B200_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, kern, &cfg));
     if (n <= 0) return B200_ERR_UNSUPPORTED;
     max_pairs[dev] = n;
+    g_last_max_pairs = n;
   }
   const int m_blocks = (p.M + kPairM - 1) / kPairM;
   const int n_blocks = (p.N + kTileN - 1) / kTileN;
@@ -273,3 +314,5 @@ int launch_gemm_pair(const void* a, int64_t lda, const void* b, int64_t ldb, con
 }
 
 }  // namespace b200
+
+extern "C" int b200_debug_pair_kernel_max_clusters(void) { return b200::g_last_max_pairs; }

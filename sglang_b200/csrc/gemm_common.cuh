@@ -13,9 +13,15 @@ struct GemmParams {
   int M, N, K;
   int out_dtype;
   int* status;
+  uint32_t wait_hint_ns;  // suspend-time hint for mbarrier waits (0 = none)
+  long long* debug_buf;  // timing experiments: clock64 samples [5][64] of pair 0's leader CTA, or null
+  int debug_mode;  // timing experiments only (results are wrong when non-zero); 0 in normal use
 };
 
 
+extern int g_gemm_debug_mode;
+extern int g_gemm_wait_hint_ns;
+extern long long* g_gemm_debug_buf;
 // Device status word of the GEMM kernels on the current device (0 = ok), or nullptr on error.
 int* gemm_status_ptr();
 // 2-D tensor map over a row-major [rows, cols] byte matrix with leading dimension ld, box =
