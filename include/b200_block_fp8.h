@@ -92,6 +92,62 @@ int b200_fp8_blockwise_scaled_mm(const void* a, int64_t lda, const void* b, int6
                                  void* out, int64_t ldo, int out_dtype,
                                  int64_t M, int64_t N, int64_t K, void* stream);
 
+/*
+ * Grouped (per-expert) block-scaled FP8 GEMM: for every expert e,
+ *   out[off_e : off_e + m_e, :] = blockscaled( a[off_e : off_e + m_e, :], b[e] )   (same math as above)
+ * with off_e = expert_offsets[e], m_e = problem_sizes[3*e] read ON THE DEVICE (no host sync).
+ * Replaces: fp8_blockwise_scaled_grouped_mm
+ *   (sgl-kernel/csrc/moe/fp8_blockwise_moe_kernel.cu:587-743, schema common_extension.cc:192-197) and its
+ *   helper get_group_gemm_starts (sgl-kernel/csrc/moe/cutlass_moe_helper.cu:10-142).
+ * a    [total_rows, K] e4m3 row-major (rows grouped by expert), lda % 16 == 0
+ * b    [E, N, K] e4m3, each expert row-major with leading dimension ldb, experts N*ldb apart
+ * sa   fp32, element (row, kb) at sa[row*sa_stride_m + kb*sa_stride_g]  (row-major [rows, K/128]: (K/128, 1))
+ * sb   fp32, element (e, nb, kb) at sb[e*sb_stride_e + nb*sb_stride_n + kb*sb_stride_g]
+ * out  [total_rows, N]; rows not covered by any expert are left untouched
+ * num_experts <= 1024.
+ */
+int b200_fp8_blockwise_scaled_grouped_mm(const void* a, int64_t lda, const void* b, int64_t ldb,
+                                         const float* sa, int64_t sa_stride_m, int64_t sa_stride_g,
+                                         const float* sb, int64_t sb_stride_e, int64_t sb_stride_n,
+                                         int64_t sb_stride_g, void* out, int64_t ldo, int out_dtype,
+                                         const int32_t* expert_offsets, const int32_t* problem_sizes,
+                                         int num_experts, int64_t total_rows, int64_t N, int64_t K, void* stream);
+
+/*
+ * Routing tables for the grouped GEMMs, from topk_ids [num_tokens, topk] (int32; ids outside
+ * [0, num_experts) get no slot -- expert-parallel masking):
+ *   problem_sizes1[e] = (count_e, 2n, k), problem_sizes2[e] = (count_e, k, n),
+ *   expert_offsets[0..E] exclusive prefix of count_e, blockscale_offsets (optional, may be NULL)
+ *   prefix of count_e rounded up to 128, input_permutation[slot] = token, output_permutation[flat] = slot.
+ * Slots inside an expert follow ascending flat index (deterministic; the reference uses atomics).
+ * Replaces: prepare_moe_input (sgl-kernel/csrc/moe/prepare_moe_input.cu:13-167, schema
+ *   common_extension.cc:198-202).
+ * scratch: device memory of at least b200_moe_prepare_scratch_bytes(num_tokens*topk, num_experts) bytes,
+ *   overwritten by the call (the reference allocates its own atomic buffer per call).
+ */
+size_t b200_moe_prepare_scratch_bytes(int64_t num_ids, int num_experts);
+int b200_moe_prepare(const int32_t* topk_ids, int64_t num_tokens, int topk, int num_experts, int n, int k,
+                     int32_t* expert_offsets, int32_t* blockscale_offsets, int32_t* problem_sizes1,
+                     int32_t* problem_sizes2, int32_t* input_permutation, int32_t* output_permutation,
+                     void* scratch, size_t scratch_bytes, void* stream);
+
+/* output[d, :] = input[dst2src_map[d], :] for rows of row_bytes bytes (128-bit copies when rows and
+ * bases are 16-byte aligned, narrower ones otherwise).
+ * Replaces: shuffle_rows (sgl-kernel/csrc/moe/prepare_moe_input.cu:169-256, schema :204-205). */
+int b200_shuffle_rows(const void* input, const int32_t* dst2src_map, void* output, int64_t num_dst_rows,
+                      int64_t row_bytes, void* stream);
+
+/* out[r, :d] = silu(x[r, :d]) * x[r, d:2d] (fp32 math, one rounding); dtype B200_DT_BF16 / B200_DT_F16, d % 8 == 0.
+ * Replaces: silu_and_mul (sgl-kernel/csrc/elementwise/activation.cu), as used between the two grouped
+ * GEMMs at python/sglang/srt/layers/moe/cutlass_moe.py:191-192. */
+int b200_silu_and_mul(const void* x, void* out, int64_t rows, int64_t d, int dtype, void* stream);
+
+/* output[i, :] = sum_j factors[i*topk+j] * input[permutation[i*topk+j], :], j ascending, fp32 accumulation,
+ * one rounding; factors may be NULL (all ones); permutation entries < 0 are skipped.
+ * Replaces: apply_shuffle_mul_sum (sgl-kernel/csrc/moe/prepare_moe_input.cu:258-392, schema :206-207). */
+int b200_apply_shuffle_mul_sum(const void* input, void* output, const int32_t* permutation, const void* factors,
+                               int64_t m, int64_t topk, int64_t row_len, int dtype, void* stream);
+
 /* Reads and clears this device's GEMM status word (0 = ok; non-zero = a bounded device-side
  * wait gave up, value encodes which).  Synchronises the device.  No reference counterpart. */
 int b200_gemm_device_status(int* status_out);

@@ -37,6 +37,16 @@ _SIGNATURES = {
                                              c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int, c_int64, c_int64,
                                              c_int64, c_void_p]),
     "b200_gemm_device_status": (c_int, [ctypes.POINTER(c_int)]),
+    "b200_fp8_blockwise_scaled_grouped_mm": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64,
+                                                     c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int,
+                                                     c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p]),
+    "b200_moe_prepare_scratch_bytes": (ctypes.c_size_t, [c_int64, c_int]),
+    "b200_moe_prepare": (c_int, [c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                 c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_void_p]),
+    "b200_shuffle_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
+    "b200_silu_and_mul": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
+    "b200_apply_shuffle_mul_sum": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,
+                                           c_void_p]),
     "b200_debug_force_block_n": (c_int, [c_int]),
     "b200_debug_force_quant_passes": (c_int, [c_int]),
     "b200_debug_pair_kernel_max_clusters": (c_int, []),

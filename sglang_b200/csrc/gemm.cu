@@ -47,7 +47,9 @@ struct Cfg {
   static constexpr int kHalves = BLOCK_N / 128;                 // weight-scale blocks per tile row
   static constexpr int kSlotFloats = kScaleGroup * kHalves * BLOCK_M;
   static constexpr int kScaleBytes = kScaleSlots * kSlotFloats * 4;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kScaleBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int kMaxExperts = 1024;  // grouped form: m-tile prefix table in shared memory
+  static constexpr int kSmemBytes = kStages * kStageBytes + kScaleBytes + 1024 /*alignment slack*/ +
+                                    256 /*barriers*/ + (kMaxExperts + 1) * 4;
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks, int& m_blk, int& n_blk) {
@@ -60,7 +62,48 @@ __device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks
   n_blk = in_group / rows;
 }
 
-template <int BLOCK_N, int EPI_WARPS, int CHUNK, int ISSUERS, typename OutT>
+// Where a tile lives.  Dense: tiles of the [M, N] output, rasterised in groups of kGroupM m-blocks.
+// Grouped: the m-tiles of all experts laid end to end (tile_m_start[e] = first m-tile of expert e,
+// in shared memory), n-blocks fastest so that neighbouring CTAs stream different slices of the same
+// expert's weights while sharing its few activation rows through L2.
+struct TileInfo {
+  int row0;        // first row of A / out
+  int valid_rows;  // rows of this tile that belong to the problem (<= BLOCK_M)
+  int n_blk;       // column block
+  int b_row0;      // first row of the [E*N, K] weight matrix
+  int expert;
+};
+
+template <bool GROUPED, int BLOCK_N>
+__device__ __forceinline__ TileInfo get_tile(int tile, const GemmParams& p, int m_blocks, int n_blocks,
+                                             const int* tile_m_start) {
+  TileInfo t;
+  if constexpr (!GROUPED) {
+    int m_blk;
+    tile_coords(tile, m_blocks, n_blocks, m_blk, t.n_blk);
+    t.row0 = m_blk * BLOCK_M;
+    t.valid_rows = min(BLOCK_M, p.M - t.row0);
+    t.b_row0 = t.n_blk * BLOCK_N;
+    t.expert = 0;
+  } else {
+    const int mt = tile / n_blocks;
+    t.n_blk = tile - mt * n_blocks;
+    int lo = 0, hi = p.num_experts;   // last e with tile_m_start[e] <= mt
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (tile_m_start[mid] <= mt) lo = mid; else hi = mid;
+    }
+    t.expert = lo;
+    const int m_blk = mt - tile_m_start[lo];
+    const int m_e = p.problem_sizes[lo * 3];
+    t.row0 = p.expert_offsets[lo] + m_blk * BLOCK_M;
+    t.valid_rows = min(BLOCK_M, m_e - m_blk * BLOCK_M);
+    t.b_row0 = lo * p.N + t.n_blk * BLOCK_N;
+  }
+  return t;
+}
+
+template <int BLOCK_N, int EPI_WARPS, int CHUNK, int ISSUERS, bool GROUPED, typename OutT>
 __global__ void __launch_bounds__(Cfg<BLOCK_N, EPI_WARPS, ISSUERS>::kThreads, 1)
 gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                       const GemmParams p) {
@@ -79,12 +122,27 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   uint64_t* scale_empty = scale_full + kScaleSlots;  // scale-ring slot consumed by every epilogue warp
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(scale_empty + kScaleSlots);
 
+  int* tile_m_start = reinterpret_cast<int*>(tmem_slot + 2);   // [num_experts + 1], grouped form only
+
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int m_blocks = (p.M + BLOCK_M - 1) / BLOCK_M;
   const int n_blocks = (p.N + BLOCK_N - 1) / BLOCK_N;
-  const int num_tiles = m_blocks * n_blocks;
   const int nkb = (p.K + BLOCK_K - 1) / BLOCK_K;
+
+  if constexpr (GROUPED) {
+    for (int e = threadIdx.x; e < p.num_experts; e += blockDim.x)
+      tile_m_start[e + 1] = (max(p.problem_sizes[e * 3], 0) + BLOCK_M - 1) / BLOCK_M;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int run = 0;
+      tile_m_start[0] = 0;
+      for (int e = 1; e <= p.num_experts; ++e) {
+        run += tile_m_start[e];
+        tile_m_start[e] = run;
+      }
+    }
+  }
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < C::kStages; ++i) {
@@ -111,6 +169,7 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+  const int num_tiles = GROUPED ? tile_m_start[p.num_experts] * n_blocks : m_blocks * n_blocks;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -118,15 +177,14 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     uint32_t phase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-      int m_blk, n_blk;
-      tile_coords(tile, m_blocks, n_blocks, m_blk, n_blk);
+      const TileInfo t = get_tile<GROUPED, BLOCK_N>(tile, p, m_blocks, n_blocks, tile_m_start);
       for (int kb = 0; kb < nkb; ++kb) {
         ok = mbar_wait_warp(&done_bar[stage], phase ^ 1u, p.status, 1);
         if (!ok) break;
         if (elect_one()) {
           mbar_expect_tx(&full_bar[stage], C::kStageBytes);
-          tma_load_2d(smem_a + stage * C::kABytes, &map_a, &full_bar[stage], kb * BLOCK_K, m_blk * BLOCK_M);
-          tma_load_2d(smem_b + stage * C::kBBytes, &map_b, &full_bar[stage], kb * BLOCK_K, n_blk * BLOCK_N);
+          tma_load_2d(smem_a + stage * C::kABytes, &map_a, &full_bar[stage], kb * BLOCK_K, t.row0);
+          tma_load_2d(smem_b + stage * C::kBBytes, &map_b, &full_bar[stage], kb * BLOCK_K, t.b_row0);
         }
         __syncwarp();
         if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
@@ -185,9 +243,8 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     uint32_t sphase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-      int m_blk, n_blk;
-      tile_coords(tile, m_blocks, n_blocks, m_blk, n_blk);
-      const int m0 = m_blk * BLOCK_M;
+      const TileInfo t = get_tile<GROUPED, BLOCK_N>(tile, p, m_blocks, n_blocks, tile_m_start);
+      const float* sb_base = p.sb + static_cast<int64_t>(t.expert) * p.sb_stride_e;
       for (int kb0 = 0; kb0 < nkb; kb0 += kScaleGroup) {
         ok = mbar_wait_warp(&scale_empty[slot], sphase ^ 1u, p.status, 5);
         if (!ok) break;
@@ -200,15 +257,16 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           const bool kin = kb < nkb;
 #pragma unroll
           for (int r = 0; r < 4; ++r) {
-            const int m = m0 + r * 32 + lane;
-            a[j][r] = (kin && m < p.M)
-                          ? __ldg(p.sa + static_cast<int64_t>(m) * p.sa_stride_m + static_cast<int64_t>(kb) * p.sa_stride_g)
+            const int rr = r * 32 + lane;
+            a[j][r] = (kin && rr < t.valid_rows)
+                          ? __ldg(p.sa + static_cast<int64_t>(t.row0 + rr) * p.sa_stride_m +
+                                  static_cast<int64_t>(kb) * p.sa_stride_g)
                           : 0.f;
           }
 #pragma unroll
           for (int h = 0; h < C::kHalves; ++h) {
-            const int nb = min(n_blk * BLOCK_N + h * 128, p.N - 1) / 128;
-            bsc[j][h] = kin ? __ldg(p.sb + static_cast<int64_t>(nb) * p.sb_stride_n +
+            const int nb = min(t.n_blk * BLOCK_N + h * 128, p.N - 1) / 128;
+            bsc[j][h] = kin ? __ldg(sb_base + static_cast<int64_t>(nb) * p.sb_stride_n +
                                     static_cast<int64_t>(kb) * p.sb_stride_g)
                             : 0.f;
           }
@@ -241,10 +299,10 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     uint32_t phase = 0, sphase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-      int m_blk, n_blk;
-      tile_coords(tile, m_blocks, n_blocks, m_blk, n_blk);
-      const int m = m_blk * BLOCK_M + quad * 32 + lane;
-      const int n0 = n_blk * BLOCK_N + part * CPW;
+      const TileInfo t = get_tile<GROUPED, BLOCK_N>(tile, p, m_blocks, n_blocks, tile_m_start);
+      const int row_in_tile = quad * 32 + lane;
+      const int m = t.row0 + row_in_tile;
+      const int n0 = t.n_blk * BLOCK_N + part * CPW;
       float acc[CPW];
 #pragma unroll
       for (int c = 0; c < CPW; ++c) acc[c] = 0.f;
@@ -298,7 +356,7 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           }
         }
       }
-      if (ok && m < p.M && n0 < p.N) {
+      if (ok && row_in_tile < t.valid_rows && n0 < p.N) {
         store_row<CPW>(out + static_cast<int64_t>(m) * p.ldo + n0, acc, p.N - n0, vec_ok);
       }
     }
@@ -318,10 +376,10 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 }
 
 // ------------------------------------------------------------------------------------ host
-template <int BLOCK_N, int EPI_WARPS, int CHUNK, int ISSUERS, typename OutT>
+template <int BLOCK_N, int EPI_WARPS, int CHUNK, int ISSUERS, bool GROUPED, typename OutT>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t stream) {
   using C = Cfg<BLOCK_N, EPI_WARPS, ISSUERS>;
-  auto kern = gemm_block_fp8_kernel<BLOCK_N, EPI_WARPS, CHUNK, ISSUERS, OutT>;
+  auto kern = gemm_block_fp8_kernel<BLOCK_N, EPI_WARPS, CHUNK, ISSUERS, GROUPED, OutT>;
   static bool attr_set[64] = {false};
   int dev = 0;
   B200_CUDA_TRY(cudaGetDevice(&dev));
@@ -331,19 +389,21 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cu
   }
   const int m_blocks = (p.M + BLOCK_M - 1) / BLOCK_M;
   const int n_blocks = (p.N + BLOCK_N - 1) / BLOCK_N;
-  const int tiles = m_blocks * n_blocks;
-  const int grid = tiles < sm_count() ? tiles : sm_count();
+  // grouped: the tile count lives on the device; m-tiles <= ceil(rows/128) + experts bounds the grid
+  const long long tiles = GROUPED ? static_cast<long long>(m_blocks + p.num_experts) * n_blocks
+                                  : static_cast<long long>(m_blocks) * n_blocks;
+  const int grid = tiles < sm_count() ? static_cast<int>(tiles) : sm_count();
   kern<<<grid, C::kThreads, C::kSmemBytes, stream>>>(ma, mb, p);
   B200_CUDA_TRY(cudaGetLastError());
   return B200_OK;
 }
 
-template <int BLOCK_N, int EPI_WARPS, int CHUNK, int ISSUERS = 1>
+template <int BLOCK_N, int EPI_WARPS, int CHUNK, int ISSUERS = 1, bool GROUPED = false>
 int launch_dtype(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t stream) {
   switch (p.out_dtype) {
-    case B200_DT_BF16: return launch<BLOCK_N, EPI_WARPS, CHUNK, ISSUERS, __nv_bfloat16>(ma, mb, p, stream);
-    case B200_DT_F16: return launch<BLOCK_N, EPI_WARPS, CHUNK, ISSUERS, __half>(ma, mb, p, stream);
-    case B200_DT_F32: return launch<BLOCK_N, EPI_WARPS, CHUNK, ISSUERS, float>(ma, mb, p, stream);
+    case B200_DT_BF16: return launch<BLOCK_N, EPI_WARPS, CHUNK, ISSUERS, GROUPED, __nv_bfloat16>(ma, mb, p, stream);
+    case B200_DT_F16: return launch<BLOCK_N, EPI_WARPS, CHUNK, ISSUERS, GROUPED, __half>(ma, mb, p, stream);
+    case B200_DT_F32: return launch<BLOCK_N, EPI_WARPS, CHUNK, ISSUERS, GROUPED, float>(ma, mb, p, stream);
     default: return B200_ERR_BAD_DTYPE;
   }
 }
@@ -404,6 +464,7 @@ extern "C" int b200_fp8_blockwise_scaled_mm(const void* a, int64_t lda, const vo
   p.M = static_cast<int>(M); p.N = static_cast<int>(N); p.K = static_cast<int>(K);
   p.out_dtype = out_dtype;
   p.status = gemm_status_ptr();
+  p.expert_offsets = nullptr; p.problem_sizes = nullptr; p.sb_stride_e = 0; p.num_experts = 0;
   p.debug_mode = g_gemm_debug_mode;
   p.debug_buf = g_gemm_debug_buf;
   p.wait_hint_ns = static_cast<uint32_t>(g_gemm_wait_hint_ns);
@@ -427,6 +488,52 @@ extern "C" int b200_fp8_blockwise_scaled_mm(const void* a, int64_t lda, const vo
   if (rc != B200_OK) return rc;
   if (g_force_block_n >= 1000) return launch_variant(g_force_block_n, ma, mb, p, st);
   return block_n == 256 ? launch_dtype<256, 16, 16>(ma, mb, p, st) : launch_dtype<128, 8, 64>(ma, mb, p, st);
+}
+
+extern "C" int b200_fp8_blockwise_scaled_grouped_mm(const void* a, int64_t lda, const void* b, int64_t ldb,
+                                                    const float* sa, int64_t sa_stride_m, int64_t sa_stride_g,
+                                                    const float* sb, int64_t sb_stride_e, int64_t sb_stride_n,
+                                                    int64_t sb_stride_g, void* out, int64_t ldo, int out_dtype,
+                                                    const int32_t* expert_offsets, const int32_t* problem_sizes,
+                                                    int num_experts, int64_t total_rows, int64_t N, int64_t K,
+                                                    void* stream) {
+  using namespace b200;
+  if (total_rows < 0 || N < 0 || K <= 0 || num_experts <= 0) return B200_ERR_BAD_SHAPE;
+  if (total_rows == 0 || N == 0) return B200_OK;
+  if (num_experts > Cfg<256, 16, 1>::kMaxExperts) return B200_ERR_TOO_LARGE;
+  if (total_rows > 0x7fffff00LL || K > 0x7fffff00LL || N * num_experts > 0x7fffff00LL) return B200_ERR_TOO_LARGE;
+  if (!a || !b || !sa || !sb || !out || !expert_offsets || !problem_sizes) return B200_ERR_NULL_PTR;
+  if (out_dtype != B200_DT_BF16 && out_dtype != B200_DT_F16 && out_dtype != B200_DT_F32) return B200_ERR_BAD_DTYPE;
+  if (lda < K || ldb < K || ldo < N) return B200_ERR_BAD_STRIDE;
+  if ((lda % 16) != 0 || (ldb % 16) != 0 || !aligned16(a) || !aligned16(b)) return B200_ERR_MISALIGNED;
+  if (sa_stride_m < 0 || sa_stride_g < 0 || sb_stride_e < 0 || sb_stride_n < 0 || sb_stride_g < 0)
+    return B200_ERR_BAD_STRIDE;
+  int rc = require_sm100();
+  if (rc != B200_OK) return rc;
+
+  GemmParams p;
+  p.sa = sa; p.sb = sb; p.out = out;
+  p.sa_stride_m = sa_stride_m; p.sa_stride_g = sa_stride_g;
+  p.sb_stride_n = sb_stride_n; p.sb_stride_g = sb_stride_g; p.sb_stride_e = sb_stride_e;
+  p.ldo = ldo;
+  p.M = static_cast<int>(total_rows); p.N = static_cast<int>(N); p.K = static_cast<int>(K);
+  p.out_dtype = out_dtype;
+  p.status = gemm_status_ptr();
+  p.expert_offsets = expert_offsets; p.problem_sizes = problem_sizes; p.num_experts = num_experts;
+  p.debug_mode = 0; p.debug_buf = nullptr; p.wait_hint_ns = 0;
+  if (!p.status) return B200_ERR_CUDA;
+
+  // An expert's weights are rows [e*N, (e+1)*N) of one [E*N, K] matrix; a 128 x 256 tile must not
+  // straddle two experts' rows, so the wide tile needs N % 256 == 0.
+  const int block_n = (N % 256 == 0 && g_force_block_n != 128) ? 256 : 128;
+  CUtensorMap ma, mb;
+  rc = make_map_u8_2d(&ma, a, total_rows, K, lda, BLOCK_M);
+  if (rc != B200_OK) return rc;
+  rc = make_map_u8_2d(&mb, b, N * num_experts, K, ldb, block_n);
+  if (rc != B200_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return block_n == 256 ? launch_dtype<256, 16, 16, 1, true>(ma, mb, p, st)
+                        : launch_dtype<128, 8, 64, 1, true>(ma, mb, p, st);
 }
 
 extern "C" int b200_debug_set_timing_buffer(void* device_buf_5x64_i64) {

@@ -13,6 +13,12 @@ struct GemmParams {
   int M, N, K;
   int out_dtype;
   int* status;
+  // grouped (per-expert) form only: rows [expert_offsets[e], +problem_sizes[3e]) of A/out belong to
+  // expert e, whose weights are rows [e*N, (e+1)*N) of B and whose weight scales start at sb + e*sb_stride_e
+  const int32_t* expert_offsets;
+  const int32_t* problem_sizes;
+  int64_t sb_stride_e;
+  int num_experts;
   uint32_t wait_hint_ns;  // suspend-time hint for mbarrier waits (0 = none)
   long long* debug_buf;  // timing experiments: clock64 samples [5][64] of pair 0's leader CTA, or null
   int debug_mode;  // timing experiments only (results are wrong when non-zero); 0 in normal use

@@ -1,0 +1,354 @@
+// MoE glue kernels around the grouped block-FP8 GEMM: routing tables, row gather, SiLU*mul,
+// weighted un-permute sum.  All HBM-bound integer/byte work: 128-bit coalesced accesses, no
+// tensor cores.
+//
+// Stand in for (paths in the reference checkout):
+//   prepare_moe_input      sgl-kernel/csrc/moe/prepare_moe_input.cu:13-167
+//   shuffle_rows           sgl-kernel/csrc/moe/prepare_moe_input.cu:169-256
+//   apply_shuffle_mul_sum  sgl-kernel/csrc/moe/prepare_moe_input.cu:258-392
+//   silu_and_mul           sgl-kernel/csrc/elementwise/activation.cu (used at
+//                          python/sglang/srt/layers/moe/cutlass_moe.py:191-192)
+//
+// prepare: the reference hands out slots inside an expert with atomics, so its order inside an
+// expert changes from run to run; here the order is the ascending flat index of topk_ids
+// (a stable counting sort), one of the orders the reference can produce, and reproducible.
+// It runs as three launches over chunks of the flat id list and needs a scratch table of
+// per-chunk, per-expert counts in global memory.
+#include "common.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int kPrepThreads = 256;
+constexpr int kPrepChunk = 2048;   // ids per chunk
+
+// ---- phase 1: per-chunk histogram -> scratch[chunk][E]
+__global__ void __launch_bounds__(kPrepThreads)
+prep_count_kernel(const int32_t* __restrict__ topk_ids, int64_t n_ids, int num_experts, int32_t* __restrict__ scratch) {
+  extern __shared__ int32_t s_cnt[];
+  for (int e = threadIdx.x; e < num_experts; e += kPrepThreads) s_cnt[e] = 0;
+  __syncthreads();
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * kPrepChunk;
+  for (int i = threadIdx.x; i < kPrepChunk; i += kPrepThreads) {
+    const int64_t idx = base + i;
+    if (idx < n_ids) {
+      const int e = topk_ids[idx];
+      if (e >= 0 && e < num_experts) atomicAdd(&s_cnt[e], 1);   // integer adds commute: deterministic totals
+    }
+  }
+  __syncthreads();
+  int32_t* out = scratch + static_cast<int64_t>(blockIdx.x) * num_experts;
+  for (int e = threadIdx.x; e < num_experts; e += kPrepThreads) out[e] = s_cnt[e];
+}
+
+// ---- phase 2 (one block): per expert, exclusive scan over chunks; expert totals -> offsets, sizes.
+// After it, scratch[chunk][e] = first slot (global) of expert e's ids that live in `chunk`.
+__global__ void __launch_bounds__(1024)
+prep_scan_kernel(int32_t* __restrict__ scratch, int num_chunks, int num_experts, int32_t* __restrict__ expert_offsets,
+                 int32_t* __restrict__ blockscale_offsets, int32_t* __restrict__ problem_sizes1,
+                 int32_t* __restrict__ problem_sizes2, int n, int k) {
+  extern __shared__ int32_t s_tot[];   // [num_experts] totals, then exclusive offsets
+  for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
+    int run = 0;
+    for (int c = 0; c < num_chunks; ++c) {
+      const int v = scratch[static_cast<int64_t>(c) * num_experts + e];
+      scratch[static_cast<int64_t>(c) * num_experts + e] = run;   // offset inside the expert for now
+      run += v;
+    }
+    s_tot[e] = run;
+    problem_sizes1[e * 3 + 0] = run;
+    problem_sizes1[e * 3 + 1] = 2 * n;
+    problem_sizes1[e * 3 + 2] = k;
+    problem_sizes2[e * 3 + 0] = run;
+    problem_sizes2[e * 3 + 1] = k;
+    problem_sizes2[e * 3 + 2] = n;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {   // E is a few hundred at most: a serial prefix is a few microseconds
+    int run = 0, run_rounded = 0;
+    expert_offsets[0] = 0;
+    if (blockscale_offsets) blockscale_offsets[0] = 0;
+    for (int e = 0; e < num_experts; ++e) {
+      const int c = s_tot[e];
+      s_tot[e] = run;
+      run += c;
+      run_rounded += (c + 127) / 128 * 128;
+      expert_offsets[e + 1] = run;
+      if (blockscale_offsets) blockscale_offsets[e + 1] = run_rounded;
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
+    const int off = s_tot[e];
+    for (int c = 0; c < num_chunks; ++c) scratch[static_cast<int64_t>(c) * num_experts + e] += off;
+  }
+}
+
+// ---- phase 3: stable slot assignment inside each chunk.
+__global__ void __launch_bounds__(kPrepThreads)
+prep_scatter_kernel(const int32_t* __restrict__ topk_ids, int64_t n_ids, int topk, int num_experts,
+                    const int32_t* __restrict__ scratch, int32_t* __restrict__ input_permutation,
+                    int32_t* __restrict__ output_permutation) {
+  extern __shared__ int32_t s_mem[];
+  int32_t* s_next = s_mem;                 // [E] next free slot of each expert inside this chunk
+  int32_t* s_ids = s_mem + num_experts;    // [kPrepChunk]
+  const int32_t* chunk_base = scratch + static_cast<int64_t>(blockIdx.x) * num_experts;
+  for (int e = threadIdx.x; e < num_experts; e += kPrepThreads) s_next[e] = chunk_base[e];
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * kPrepChunk;
+  for (int i = threadIdx.x; i < kPrepChunk; i += kPrepThreads) {
+    const int64_t idx = base + i;
+    s_ids[i] = idx < n_ids ? topk_ids[idx] : -1;
+  }
+  __syncthreads();
+  // One warp walks the chunk in order, 32 ids at a time; equal experts inside the 32 are ranked
+  // with a match mask, so slots follow ascending flat index exactly.
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    for (int i0 = 0; i0 < kPrepChunk; i0 += 32) {
+      const int64_t idx = base + i0 + lane;
+      const int e = s_ids[i0 + lane];
+      const bool valid = e >= 0 && e < num_experts;
+      const unsigned peers = __match_any_sync(0xffffffffu, valid ? e : -1 - lane);
+      if (valid) {
+        const int rank = __popc(peers & ((1u << lane) - 1u));
+        const int slot = s_next[e] + rank;
+        input_permutation[slot] = static_cast<int32_t>(idx / topk);
+        output_permutation[idx] = slot;
+      } else if (idx < n_ids) {
+        output_permutation[idx] = -1;   // no slot: masked expert (the weighted sum skips it)
+      }
+      __syncwarp();
+      if (valid && (peers >> lane) <= 1u) s_next[e] += __popc(peers);   // highest lane of each group
+      __syncwarp();
+    }
+  }
+}
+
+// ---- row gather: out[d] = in[map[d]], rows of row_bytes bytes (multiple of 16)
+template <typename V>
+__global__ void __launch_bounds__(256)
+rows_gather_kernel(const V* __restrict__ in, const int32_t* __restrict__ map, V* __restrict__ out,
+                   int64_t num_dst_rows, int vec_per_row) {
+  const int rows_per_block = 256 / 32;   // one warp per row
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * rows_per_block + (threadIdx.x >> 5);
+  if (row >= num_dst_rows) return;
+  const int64_t src = map[row];
+  const V* s = in + src * vec_per_row;
+  V* d = out + row * vec_per_row;
+  for (int v = threadIdx.x & 31; v < vec_per_row; v += 32) d[v] = __ldg(s + v);
+}
+
+template <typename T>
+struct Pack8;   // 8 elements of T in one uint4
+template <>
+struct Pack8<__nv_bfloat16> {
+  static __device__ __forceinline__ void unpack(const uint4& u, float (&f)[8]) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 t = __bfloat1622float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+  }
+  static __device__ __forceinline__ uint4 pack(const float (&f)[8]) {
+    uint4 u;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    return u;
+  }
+  static __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+};
+template <>
+struct Pack8<__half> {
+  static __device__ __forceinline__ void unpack(const uint4& u, float (&f)[8]) {
+    const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 t = __half22float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+  }
+  static __device__ __forceinline__ uint4 pack(const float (&f)[8]) {
+    uint4 u;
+    __half2* h = reinterpret_cast<__half2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+    return u;
+  }
+  static __device__ __forceinline__ float to_float(__half v) { return __half2float(v); }
+};
+
+// ---- out[r, :d] = silu(x[r, :d]) * x[r, d:2d], fp32 math, one rounding
+template <typename T>
+__global__ void __launch_bounds__(256)
+silu_and_mul_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t rows, int d) {
+  const int vec_per_row = d / 8;
+  const int64_t total = rows * vec_per_row;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * 256) {
+    const int64_t r = i / vec_per_row;
+    const int v = static_cast<int>(i - r * vec_per_row);
+    const uint4 g = __ldg(reinterpret_cast<const uint4*>(x + r * 2 * d) + v);
+    const uint4 u = __ldg(reinterpret_cast<const uint4*>(x + r * 2 * d + d) + v);
+    float fg[8], fu[8], fo[8];
+    Pack8<T>::unpack(g, fg);
+    Pack8<T>::unpack(u, fu);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) fo[k] = (fg[k] / (1.0f + __expf(-fg[k]))) * fu[k];
+    reinterpret_cast<uint4*>(out + r * d)[v] = Pack8<T>::pack(fo);
+  }
+}
+
+// ---- out[i] = sum_j factors[i*topk+j] * in[perm[i*topk+j]], j ascending, fp32 accumulate
+template <typename T>
+__global__ void __launch_bounds__(256)
+unpermute_sum_kernel(const T* __restrict__ in, T* __restrict__ out, const int32_t* __restrict__ perm,
+                     const T* __restrict__ factors, int m, int topk, int row_len) {
+  const int i = blockIdx.x;
+  if (i >= m) return;
+  const int vec_per_row = row_len / 8;
+  for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+    for (int j = 0; j < topk; ++j) {
+      const int src = perm[i * topk + j];
+      if (src < 0) continue;   // masked expert (expert parallel): contributes nothing
+      const float w = factors ? Pack8<T>::to_float(factors[i * topk + j]) : 1.0f;
+      float f[8];
+      Pack8<T>::unpack(__ldg(reinterpret_cast<const uint4*>(in + static_cast<int64_t>(src) * row_len) + v), f);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] += w * f[k];   // contracted to an fma by nvcc, as the reference's `sum += factor * val` is
+    }
+    reinterpret_cast<uint4*>(out + static_cast<int64_t>(i) * row_len)[v] = Pack8<T>::pack(acc);
+  }
+}
+
+}  // namespace
+
+size_t moe_prepare_scratch_bytes(int64_t n_ids, int num_experts) {
+  const int64_t chunks = (n_ids + kPrepChunk - 1) / kPrepChunk;
+  return static_cast<size_t>(chunks < 1 ? 1 : chunks) * num_experts * sizeof(int32_t);
+}
+
+int moe_prepare_launch(const int32_t* topk_ids, int64_t n_ids, int topk, int num_experts, int n, int k,
+                       int32_t* expert_offsets, int32_t* blockscale_offsets, int32_t* problem_sizes1,
+                       int32_t* problem_sizes2, int32_t* input_permutation, int32_t* output_permutation,
+                       int32_t* scratch, cudaStream_t st) {
+  const int chunks = static_cast<int>((n_ids + kPrepChunk - 1) / kPrepChunk);
+  const int nch = chunks < 1 ? 1 : chunks;
+  prep_count_kernel<<<nch, kPrepThreads, num_experts * sizeof(int32_t), st>>>(topk_ids, n_ids, num_experts, scratch);
+  prep_scan_kernel<<<1, 1024, num_experts * sizeof(int32_t), st>>>(scratch, nch, num_experts, expert_offsets,
+                                                                   blockscale_offsets, problem_sizes1,
+                                                                   problem_sizes2, n, k);
+  prep_scatter_kernel<<<nch, kPrepThreads, (num_experts + kPrepChunk) * sizeof(int32_t), st>>>(
+      topk_ids, n_ids, topk, num_experts, scratch, input_permutation, output_permutation);
+  B200_CUDA_TRY(cudaGetLastError());
+  return B200_OK;
+}
+
+}  // namespace b200
+
+extern "C" size_t b200_moe_prepare_scratch_bytes(int64_t num_ids, int num_experts) {
+  if (num_ids < 0 || num_experts <= 0) return 0;
+  return b200::moe_prepare_scratch_bytes(num_ids, num_experts);
+}
+
+extern "C" int b200_moe_prepare(const int32_t* topk_ids, int64_t num_tokens, int topk, int num_experts, int n, int k,
+                                int32_t* expert_offsets, int32_t* blockscale_offsets, int32_t* problem_sizes1,
+                                int32_t* problem_sizes2, int32_t* input_permutation, int32_t* output_permutation,
+                                void* scratch, size_t scratch_bytes, void* stream) {
+  using namespace b200;
+  if (num_tokens < 0 || topk <= 0 || num_experts <= 0 || n < 0 || k < 0) return B200_ERR_BAD_SHAPE;
+  if (num_experts > 8192) return B200_ERR_TOO_LARGE;   // shared-memory tables are sized by the expert count
+  if (!expert_offsets || !problem_sizes1 || !problem_sizes2) return B200_ERR_NULL_PTR;
+  const int64_t n_ids = num_tokens * topk;
+  if (n_ids > 0x7fffffffLL) return B200_ERR_TOO_LARGE;
+  if (n_ids > 0 && (!topk_ids || !input_permutation || !output_permutation)) return B200_ERR_NULL_PTR;
+  if (!scratch || scratch_bytes < moe_prepare_scratch_bytes(n_ids, num_experts)) return B200_ERR_NULL_PTR;
+  return moe_prepare_launch(topk_ids, n_ids, topk, num_experts, n, k, expert_offsets, blockscale_offsets,
+                            problem_sizes1, problem_sizes2, input_permutation, output_permutation,
+                            static_cast<int32_t*>(scratch), static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200_shuffle_rows(const void* input, const int32_t* dst2src_map, void* output, int64_t num_dst_rows,
+                                 int64_t row_bytes, void* stream) {
+  using namespace b200;
+  if (num_dst_rows < 0 || row_bytes < 0) return B200_ERR_BAD_SHAPE;
+  if (num_dst_rows == 0 || row_bytes == 0) return B200_OK;
+  if (!input || !dst2src_map || !output) return B200_ERR_NULL_PTR;
+  const int64_t blocks = (num_dst_rows + 7) / 8;
+  if (blocks > 0x7fffffffLL) return B200_ERR_TOO_LARGE;
+  // widest vector that divides the row and both base addresses: 16 bytes for the shapes of the
+  // hot path (rows of K codes or K/128 scales with K % 512 == 0), narrower ones otherwise
+  const uintptr_t bits = static_cast<uintptr_t>(row_bytes) | reinterpret_cast<uintptr_t>(input) |
+                         reinterpret_cast<uintptr_t>(output);
+  const unsigned grid = static_cast<unsigned>(blocks);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if ((bits & 15u) == 0) {
+    rows_gather_kernel<uint4><<<grid, 256, 0, st>>>(static_cast<const uint4*>(input), dst2src_map,
+                                                    static_cast<uint4*>(output), num_dst_rows,
+                                                    static_cast<int>(row_bytes / 16));
+  } else if ((bits & 7u) == 0) {
+    rows_gather_kernel<uint2><<<grid, 256, 0, st>>>(static_cast<const uint2*>(input), dst2src_map,
+                                                    static_cast<uint2*>(output), num_dst_rows,
+                                                    static_cast<int>(row_bytes / 8));
+  } else if ((bits & 3u) == 0) {
+    rows_gather_kernel<uint32_t><<<grid, 256, 0, st>>>(static_cast<const uint32_t*>(input), dst2src_map,
+                                                       static_cast<uint32_t*>(output), num_dst_rows,
+                                                       static_cast<int>(row_bytes / 4));
+  } else {
+    rows_gather_kernel<uint8_t><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(input), dst2src_map,
+                                                      static_cast<uint8_t*>(output), num_dst_rows,
+                                                      static_cast<int>(row_bytes));
+  }
+  B200_CUDA_TRY(cudaGetLastError());
+  return B200_OK;
+}
+
+extern "C" int b200_silu_and_mul(const void* x, void* out, int64_t rows, int64_t d, int dtype, void* stream) {
+  using namespace b200;
+  if (rows < 0 || d < 0) return B200_ERR_BAD_SHAPE;
+  if (rows == 0 || d == 0) return B200_OK;
+  if (!x || !out) return B200_ERR_NULL_PTR;
+  if ((d % 8) != 0 || !aligned16(x) || !aligned16(out)) return B200_ERR_MISALIGNED;
+  const int64_t total = rows * (d / 8);
+  int64_t blocks = (total + 255) / 256;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+  if (blocks > cap) blocks = cap;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == B200_DT_BF16) {
+    silu_and_mul_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(out), rows, static_cast<int>(d));
+  } else if (dtype == B200_DT_F16) {
+    silu_and_mul_kernel<__half><<<static_cast<unsigned>(blocks), 256, 0, st>>>(
+        static_cast<const __half*>(x), static_cast<__half*>(out), rows, static_cast<int>(d));
+  } else {
+    return B200_ERR_BAD_DTYPE;
+  }
+  B200_CUDA_TRY(cudaGetLastError());
+  return B200_OK;
+}
+
+extern "C" int b200_apply_shuffle_mul_sum(const void* input, void* output, const int32_t* permutation,
+                                          const void* factors, int64_t m, int64_t topk, int64_t row_len, int dtype,
+                                          void* stream) {
+  using namespace b200;
+  if (m < 0 || topk <= 0 || row_len < 0) return B200_ERR_BAD_SHAPE;
+  if (m == 0 || row_len == 0) return B200_OK;
+  if (!input || !output || !permutation) return B200_ERR_NULL_PTR;
+  if ((row_len % 8) != 0 || !aligned16(input) || !aligned16(output)) return B200_ERR_MISALIGNED;
+  if (m > 0x7fffffffLL) return B200_ERR_TOO_LARGE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int threads = static_cast<int>(row_len / 8);
+  threads = threads > 256 ? 256 : (threads < 32 ? 32 : (threads + 31) / 32 * 32);
+  if (dtype == B200_DT_BF16) {
+    unpermute_sum_kernel<__nv_bfloat16><<<static_cast<unsigned>(m), threads, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(input), static_cast<__nv_bfloat16*>(output), permutation,
+        static_cast<const __nv_bfloat16*>(factors), static_cast<int>(m), static_cast<int>(topk),
+        static_cast<int>(row_len));
+  } else if (dtype == B200_DT_F16) {
+    unpermute_sum_kernel<__half><<<static_cast<unsigned>(m), threads, 0, st>>>(
+        static_cast<const __half*>(input), static_cast<__half*>(output), permutation,
+        static_cast<const __half*>(factors), static_cast<int>(m), static_cast<int>(topk), static_cast<int>(row_len));
+  } else {
+    return B200_ERR_BAD_DTYPE;
+  }
+  B200_CUDA_TRY(cudaGetLastError());
+  return B200_OK;
+}

@@ -1,0 +1,105 @@
+"""Fused MoE with block-FP8 experts: the op sequence of the reference's
+`cutlass_fused_experts_fp8` (python/sglang/srt/layers/moe/cutlass_moe.py:29-222), same signature.
+
+prepare_moe_input -> group quant -> row gather -> grouped GEMM 1 -> SiLU*mul -> group quant ->
+grouped GEMM 2 -> weighted un-permute sum.  Nothing on the host looks at device data (routing
+counts stay on the device), so the whole sequence is stream-ordered.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ...sgl_kernel import (apply_shuffle_mul_sum, fp8_blockwise_scaled_grouped_mm, prepare_moe_input, shuffle_rows,
+                           silu_and_mul)
+from ..quantization.fp8_kernel import sglang_per_token_group_quant_fp8
+
+
+def cutlass_fused_experts_fp8(
+    a: torch.Tensor,
+    w1_q: torch.Tensor,
+    w2_q: torch.Tensor,
+    w1_scale: torch.Tensor,
+    w2_scale: torch.Tensor,
+    topk_weights: torch.Tensor,
+    topk_ids: torch.Tensor,
+    a1_strides: Optional[torch.Tensor] = None,
+    c1_strides: Optional[torch.Tensor] = None,
+    a2_strides: Optional[torch.Tensor] = None,
+    c2_strides: Optional[torch.Tensor] = None,
+    workspace: Optional[torch.Tensor] = None,
+    a_ptrs: Optional[torch.Tensor] = None,
+    b_ptrs: Optional[torch.Tensor] = None,
+    out_ptrs: Optional[torch.Tensor] = None,
+    a_scales_ptrs: Optional[torch.Tensor] = None,
+    b_scales_ptrs: Optional[torch.Tensor] = None,
+    expert_offsets: Optional[torch.Tensor] = None,
+    problem_sizes1: Optional[torch.Tensor] = None,
+    problem_sizes2: Optional[torch.Tensor] = None,
+    use_fp8_blockscale: bool = True,
+) -> torch.Tensor:
+    """a [m, k] bf16/fp16; w1_q [E, k, 2n] and w2_q [E, n, k] e4m3 (transposed views of the
+    [E, N, K] weights, as the reference passes them); w1_scale / w2_scale: block scales whose memory
+    order is [E][N/128][K/128]; topk_weights / topk_ids [m, topk] (ids int32).  The stride, pointer
+    and workspace tensors are scratch of the reference kernels: accepted, not needed.  The three
+    routing tensors are allocated here when not supplied.  Returns [m, k] in a.dtype."""
+    assert use_fp8_blockscale, "Only support fp8 blockscale for now"
+    assert topk_weights.shape == topk_ids.shape, "topk shape mismatch"
+    assert w1_q.dtype == torch.float8_e4m3fn
+    assert w2_q.dtype == torch.float8_e4m3fn
+    assert a.shape[1] == w1_q.shape[1], "Hidden size mismatch w1"
+    assert w1_q.shape[2] == w2_q.shape[1] * 2, "Hidden size mismatch w2"
+    assert w1_q.shape[0] == w2_q.shape[0], "Expert number mismatch"
+    assert w1_q.shape[0] == w1_scale.shape[0], "w1 scales expert number mismatch"
+    assert w1_q.shape[0] == w2_scale.shape[0], "w2 scales expert number mismatch"
+    assert a.dtype in [torch.half, torch.bfloat16], "Invalid output dtype"
+
+    out_dtype = a.dtype
+    num_experts = w1_q.size(0)
+    m = a.size(0)
+    k = w1_q.size(1)
+    n = w2_q.size(1)
+    topk = topk_ids.size(1)
+    device = a.device
+    i32 = dict(dtype=torch.int32, device=device)
+    if expert_offsets is None:
+        expert_offsets = torch.empty(num_experts + 1, **i32)
+    if problem_sizes1 is None:
+        problem_sizes1 = torch.empty((num_experts, 3), **i32)
+    if problem_sizes2 is None:
+        problem_sizes2 = torch.empty((num_experts, 3), **i32)
+    topk_ids = topk_ids.to(torch.int32).contiguous()
+
+    a_map = torch.zeros((topk_ids.numel()), **i32)   # unrouted slots gather row 0 (in bounds, never used)
+    c_map = torch.empty((topk_ids.numel()), **i32)
+    prepare_moe_input(topk_ids, expert_offsets, problem_sizes1, problem_sizes2, a_map, c_map, num_experts, n, k)
+
+    a_q, a1_scale = sglang_per_token_group_quant_fp8(a, 128)
+    rep_a_q = shuffle_rows(a_q, a_map, (m * topk, k))
+    rep_a1_scales = shuffle_rows(a1_scale, a_map, (m * topk, int(k / 128)))
+
+    c1 = torch.empty((m * topk, n * 2), device=device, dtype=out_dtype)
+    c2 = torch.empty((m * topk, k), device=device, dtype=out_dtype)
+    fp8_blockwise_scaled_grouped_mm(c1, a_ptrs, b_ptrs, out_ptrs, a_scales_ptrs, b_scales_ptrs, rep_a_q, w1_q,
+                                    rep_a1_scales, w1_scale, a1_strides, a1_strides, c1_strides, None, None,
+                                    problem_sizes1, expert_offsets[:-1], workspace)
+
+    intermediate = torch.empty((m * topk, n), device=device, dtype=out_dtype)
+    silu_and_mul(c1, intermediate)
+    intermediate_q, a2_scale = sglang_per_token_group_quant_fp8(intermediate, 128)
+    fp8_blockwise_scaled_grouped_mm(c2, a_ptrs, b_ptrs, out_ptrs, a_scales_ptrs, b_scales_ptrs, intermediate_q, w2_q,
+                                    a2_scale, w2_scale, a2_strides, a2_strides, c2_strides, None, None,
+                                    problem_sizes2, expert_offsets[:-1], workspace)
+
+    result = torch.empty((m, k), device=device, dtype=out_dtype)
+    apply_shuffle_mul_sum(c2, result, c_map, topk_weights.to(out_dtype))
+    return result
+
+
+def fused_experts_block_fp8(a, w13, w2, w13_scale, w2_scale, topk_weights, topk_ids):
+    """Convenience form with natural weight layouts: w13 [E, 2n, k], w2 [E, k, n] e4m3 contiguous,
+    scales [E, 2n/128, k/128] and [E, k/128, n/128] -- what Fp8MoEMethod holds
+    (python/sglang/srt/layers/quantization/fp8.py:1030-1065 passes the transposed views)."""
+    return cutlass_fused_experts_fp8(a, w13.transpose(1, 2), w2.transpose(1, 2), w13_scale.transpose(1, 2),
+                                     w2_scale.transpose(1, 2), topk_weights, topk_ids)

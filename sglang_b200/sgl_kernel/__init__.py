@@ -8,6 +8,8 @@ CUDA dispatch key by the B200 C-ABI library, and exposes the same-named Python w
 import torch
 
 from .gemm import fp8_blockwise_scaled_mm, sgl_per_token_group_quant_fp8
+from .moe import (apply_shuffle_mul_sum, fp8_blockwise_scaled_grouped_mm, prepare_moe_input, shuffle_rows,
+                  shuffle_rows_into, silu_and_mul)
 
 _SCHEMAS = {
     "fp8_blockwise_scaled_mm":
@@ -15,10 +17,37 @@ _SCHEMAS = {
     "sgl_per_token_group_quant_fp8":
         "(Tensor input, Tensor output_q, Tensor output_s, int group_size, float eps, float fp8_min, "
         "float fp8_max, bool scale_ue8m0) -> ()",
+    "fp8_blockwise_scaled_grouped_mm":
+        "(Tensor output, Tensor a_ptrs, Tensor b_ptrs, Tensor out_ptrs, Tensor a_scales_ptrs, Tensor b_scales_ptrs, "
+        "Tensor a, Tensor b, Tensor scales_a, Tensor scales_b, Tensor stride_a, Tensor stride_b, Tensor stride_c, "
+        "Tensor layout_sfa, Tensor layout_sfb, Tensor problem_sizes, Tensor expert_offsets, Tensor workspace) -> ()",
+    "prepare_moe_input":
+        "(Tensor topk_ids, Tensor expert_offsets, Tensor? blockscale_offsets, Tensor problem_sizes1, "
+        "Tensor problem_sizes2, Tensor input_permutation, Tensor output_permutation, int num_experts, int n, int k) -> ()",
+    "shuffle_rows": "(Tensor input, Tensor dst2src_map, Tensor output) -> ()",
+    "apply_shuffle_mul_sum": "(Tensor input, Tensor output, Tensor permutation, Tensor? factors) -> ()",
+    "silu_and_mul": "(Tensor out, Tensor input) -> ()",
 }
+
+
+def _prepare_moe_input_op(topk_ids, expert_offsets, blockscale_offsets, problem_sizes1, problem_sizes2,
+                          input_permutation, output_permutation, num_experts, n, k):
+    prepare_moe_input(topk_ids, expert_offsets, problem_sizes1, problem_sizes2, input_permutation,
+                      output_permutation, num_experts, n, k, blockscale_offsets)
+
+
+def _silu_and_mul_op(out, input):
+    silu_and_mul(input, out)
+
+
 _IMPLS = {
     "fp8_blockwise_scaled_mm": fp8_blockwise_scaled_mm,
     "sgl_per_token_group_quant_fp8": sgl_per_token_group_quant_fp8,
+    "fp8_blockwise_scaled_grouped_mm": fp8_blockwise_scaled_grouped_mm,
+    "prepare_moe_input": _prepare_moe_input_op,
+    "shuffle_rows": shuffle_rows_into,
+    "apply_shuffle_mul_sum": apply_shuffle_mul_sum,
+    "silu_and_mul": _silu_and_mul_op,
 }
 
 _library = None
@@ -40,4 +69,5 @@ def register_torch_ops() -> None:
 
 register_torch_ops()
 
-__all__ = ["fp8_blockwise_scaled_mm", "sgl_per_token_group_quant_fp8", "register_torch_ops"]
+__all__ = ["fp8_blockwise_scaled_mm", "sgl_per_token_group_quant_fp8", "fp8_blockwise_scaled_grouped_mm",
+           "prepare_moe_input", "shuffle_rows", "apply_shuffle_mul_sum", "silu_and_mul", "register_torch_ops"]

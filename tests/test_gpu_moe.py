@@ -1,0 +1,148 @@
+"""GPU parity: MoE glue kernels and the grouped block-FP8 GEMM against the CPU oracle.
+
+Shapes follow sgl-kernel/tests/test_fp8_blockwise_moe.py (random m_g = 16*U{1..64}, n,k multiples
+of 128), python/sglang/test/test_block_fp8.py:452-525 and the DeepSeek-V3 MoE configuration at
+reduced token count."""
+import pytest
+import torch
+
+from oracle import block_fp8_oracle as O
+from helpers import as_bf16, as_fp8, load_golden, same_bits, t
+
+pytestmark = pytest.mark.gpu
+FP8 = torch.float8_e4m3fn
+
+
+def _status_ok():
+    import ctypes
+    from sglang_b200 import _lib
+    st = ctypes.c_int(0)
+    _lib.check("status", _lib.lib().b200_gemm_device_status(ctypes.byref(st)))
+    assert st.value == 0, f"device status word = {st.value}"
+
+
+@pytest.mark.parametrize("m,topk,E", [(1, 1, 4), (37, 2, 8), (4096, 8, 256), (3000, 6, 64)])
+def test_prepare_moe_input_exact(m, topk, E):
+    from sglang_b200.sgl_kernel import prepare_moe_input
+    g = torch.Generator().manual_seed(m + E)
+    ids = torch.stack([torch.randperm(E, generator=g)[:topk] for _ in range(m)]).to(torch.int32)
+    if m > 30:
+        ids[5, 0] = -1                                   # a masked (non-local) expert id
+    n, k = 2048, 7168
+    offs_r, ps1_r, ps2_r, a_map_r, c_map_r = O.prepare_moe_input(ids, E, n, k)
+    d = dict(dtype=torch.int32, device="cuda")
+    offs, ps1, ps2 = torch.empty(E + 1, **d), torch.empty(E, 3, **d), torch.empty(E, 3, **d)
+    a_map, c_map = torch.full((m * topk,), -7, **d), torch.full((m * topk,), -7, **d)
+    prepare_moe_input(ids.cuda(), offs, ps1, ps2, a_map, c_map, E, n, k)
+    total = int(offs_r[-1])
+    assert torch.equal(offs.cpu(), offs_r) and torch.equal(ps1.cpu(), ps1_r) and torch.equal(ps2.cpu(), ps2_r)
+    assert torch.equal(a_map.cpu()[:total], a_map_r[:total])     # same deterministic order as the oracle
+    assert torch.equal(c_map.cpu(), c_map_r)
+    # twice -> identical (no atomics in the slot assignment)
+    a2, c2 = torch.empty_like(a_map), torch.empty_like(c_map)
+    prepare_moe_input(ids.cuda(), offs, ps1, ps2, a2, c2, E, n, k)
+    assert torch.equal(a2[:total], a_map[:total]) and torch.equal(c2, c_map)
+
+
+@pytest.mark.parametrize("dtype", [torch.float8_e4m3fn, torch.float32, torch.bfloat16])
+def test_shuffle_rows(dtype):
+    from sglang_b200.sgl_kernel import shuffle_rows
+    g = torch.Generator().manual_seed(1)
+    src = torch.randn(50, 256, generator=g).to(dtype)
+    idx = torch.randint(0, 50, (333,), generator=g, dtype=torch.int32)
+    out = shuffle_rows(src.cuda(), idx.cuda(), (333, 256))
+    assert same_bits(out.cpu(), O.shuffle_rows(src, idx))
+    assert shuffle_rows(src.cuda(), idx[:0].cuda(), (0, 256)).shape == (0, 256)
+
+
+def test_silu_and_mul_and_weighted_sum():
+    from sglang_b200.sgl_kernel import apply_shuffle_mul_sum, silu_and_mul
+    g = torch.Generator().manual_seed(2)
+    x = (torch.randn(77, 512, generator=g) * 3).to(torch.bfloat16)
+    out = silu_and_mul(x.cuda()).cpu()
+    ref = O.silu_and_mul(x)
+    assert O.rel_l2(out.float(), ref.float()) < 2e-3      # __expf vs exact exp, then one bf16 rounding
+    m, topk, k = 19, 4, 256
+    c2 = torch.randn(m * topk, k, generator=g).to(torch.bfloat16)
+    perm = torch.randperm(m * topk, generator=g).to(torch.int32)
+    w = torch.rand(m, topk, generator=g).to(torch.bfloat16)
+    res = torch.empty(m, k, dtype=torch.bfloat16, device="cuda")
+    apply_shuffle_mul_sum(c2.cuda(), res, perm.cuda(), w.cuda())
+    ref = O.apply_shuffle_mul_sum(c2, perm, w, m)
+    assert O.rel_l2(res.cpu().float(), ref.float()) < 2e-3
+    res1 = torch.empty(m, k, dtype=torch.bfloat16, device="cuda")
+    apply_shuffle_mul_sum(c2.cuda(), res1, perm.cuda(), None)
+    assert O.rel_l2(res1.cpu().float(), O.apply_shuffle_mul_sum(c2, perm, None, m).float()) < 2e-3
+
+
+def _grouped_problem(E, N, K, counts, seed):
+    g = torch.Generator().manual_seed(seed)
+    rows = int(sum(counts))
+    x = torch.randn(rows, K, generator=g).to(torch.bfloat16)
+    a, sa = O.quant_group_fp8_cuda_semantics(x, 128)
+    wq, ws = [], []
+    for e in range(E):
+        q_, s_ = O.per_block_cast_to_fp8(torch.randn(N, K, generator=g) * 0.02)
+        wq.append(q_); ws.append(s_)
+    offs = torch.zeros(E + 1, dtype=torch.int32)
+    offs[1:] = torch.tensor(counts).cumsum(0)
+    ps = torch.tensor([[c, N, K] for c in counts], dtype=torch.int32)
+    return a, sa, torch.stack(wq), torch.stack(ws), offs, ps
+
+
+@pytest.mark.parametrize("E,N,K,seed", [(4, 256, 512, 0), (8, 384, 256, 1), (16, 512, 1024, 2), (8, 4096, 7168, 3)])
+def test_grouped_gemm(E, N, K, seed):
+    from sglang_b200.sgl_kernel import fp8_blockwise_scaled_grouped_mm
+    g = torch.Generator().manual_seed(100 + seed)
+    counts = [int(c) for c in torch.randint(0, 5, (E,), generator=g) * 50 + torch.randint(0, 30, (E,), generator=g)]
+    counts[0] = 0 if E > 4 else counts[0]                        # an expert without tokens
+    counts[-1] = 130                                             # one m-tile boundary case
+    a, sa, wq, ws, offs, ps = _grouped_problem(E, N, K, counts, seed)
+    rows = a.shape[0]
+    out = torch.full((rows + 3, N), -7.0, dtype=torch.bfloat16, device="cuda")
+    fp8_blockwise_scaled_grouped_mm(out[:rows], None, None, None, None, None, a.cuda(), wq.cuda().transpose(1, 2),
+                                    sa.cuda(), ws.cuda(), None, None, None, None, None, ps.cuda(), offs[:-1].cuda(),
+                                    None)
+    torch.cuda.synchronize()
+    _status_ok()
+    assert torch.all(out[rows:] == -7.0)
+    for e in range(E):
+        lo, hi = int(offs[e]), int(offs[e + 1])
+        if hi > lo:
+            ref = O.block_fp8_matmul_fp32(a[lo:hi], wq[e], sa[lo:hi], ws[e]).to(torch.bfloat16)
+            assert O.rel_l2(out[lo:hi].float().cpu(), ref.float()) <= 1e-3, e
+
+
+def test_fused_moe_small_vs_oracle_and_golden():
+    from sglang_b200.layers.moe.cutlass_moe import fused_experts_block_fp8
+    g = load_golden("moe_native.npz")
+    a = as_bf16(g["a"])
+    w1q, w2q, w1s, w2s = as_fp8(g["w1q"]), as_fp8(g["w2q"]), t(g["w1s"]), t(g["w2s"])
+    score, topk = t(g["score"]), int(g["topk"])
+    w, ids = O.fused_topk_native(score, topk)
+    out = fused_experts_block_fp8(a.cuda(), w1q.cuda(), w2q.cuda(), w1s.cuda(), w2s.cuda(), w.cuda(), ids.cuda()).cpu()
+    ref_seq = O.cutlass_fused_experts_fp8(a, w1q, w2q, w1s, w2s, w, ids)
+    assert O.rel_l2(out.float(), ref_seq.float()) <= 5e-3        # same op order; silu uses __expf
+    # the reference's own torch MoE (different bf16 rounding points): its tolerance is 2e-2 mean-rel-err
+    assert O.mean_rel_err(out, as_bf16(g["out"])) < 2e-2
+    _status_ok()
+
+
+def test_fused_moe_deepseek_shapes_reduced_tokens():
+    """E=32 local experts of the DeepSeek-V3 MoE (hidden 7168, intermediate 2048), 96 tokens, top-8."""
+    from sglang_b200.layers.moe.cutlass_moe import fused_experts_block_fp8
+    E, H, I, m, topk = 32, 7168, 2048, 96, 8
+    g = torch.Generator().manual_seed(4)
+    a = torch.randn(m, H, generator=g).to(torch.bfloat16)
+    w13q, w13s, w2q, w2s = [], [], [], []
+    for e in range(E):
+        q_, s_ = O.per_block_cast_to_fp8(torch.randn(2 * I, H, generator=g) * 0.02); w13q.append(q_); w13s.append(s_)
+        q_, s_ = O.per_block_cast_to_fp8(torch.randn(H, I, generator=g) * 0.02); w2q.append(q_); w2s.append(s_)
+    w13q, w13s, w2q, w2s = torch.stack(w13q), torch.stack(w13s), torch.stack(w2q), torch.stack(w2s)
+    w, ids = O.fused_topk_native(torch.randn(m, E, generator=g), topk)
+    out = fused_experts_block_fp8(a.cuda(), w13q.cuda(), w2q.cuda(), w13s.cuda(), w2s.cuda(), w.cuda(), ids.cuda())
+    out2 = fused_experts_block_fp8(a.cuda(), w13q.cuda(), w2q.cuda(), w13s.cuda(), w2s.cuda(), w.cuda(), ids.cuda())
+    assert same_bits(out, out2)
+    ref = O.cutlass_fused_experts_fp8(a, w13q, w2q, w13s, w2s, w, ids)
+    assert O.rel_l2(out.float().cpu(), ref.float()) <= 5e-3
+    _status_ok()
