@@ -103,3 +103,31 @@ def fused_experts_block_fp8(a, w13, w2, w13_scale, w2_scale, topk_weights, topk_
     (python/sglang/srt/layers/quantization/fp8.py:1030-1065 passes the transposed views)."""
     return cutlass_fused_experts_fp8(a, w13.transpose(1, 2), w2.transpose(1, 2), w13_scale.transpose(1, 2),
                                      w2_scale.transpose(1, 2), topk_weights, topk_ids)
+
+
+def grouped_experts_prequantized(a_q, a_scale, expert_ids, w13, w2, w13_scale, w2_scale, out_dtype=torch.bfloat16):
+    """Expert MLPs over rows that are ALREADY quantised (what an expert-parallel rank receives):
+    a_q [R, k] e4m3, a_scale [R, k/128] fp32, expert_ids [R] int32 (local ids; < 0 = skip).
+    Returns [R, k] in out_dtype, rows in input order, no routing weights applied."""
+    R, k = a_q.shape
+    E, n = w13.shape[0], w2.shape[2]
+    device = a_q.device
+    i32 = dict(dtype=torch.int32, device=device)
+    ids = expert_ids.to(torch.int32).reshape(R, 1).contiguous()
+    expert_offsets = torch.empty(E + 1, **i32)
+    ps1, ps2 = torch.empty((E, 3), **i32), torch.empty((E, 3), **i32)
+    a_map, c_map = torch.zeros(R, **i32), torch.empty(R, **i32)
+    prepare_moe_input(ids, expert_offsets, ps1, ps2, a_map, c_map, E, n, k)
+    rep_q = shuffle_rows(a_q, a_map, (R, k))
+    rep_s = shuffle_rows(a_scale.contiguous(), a_map, (R, k // 128))
+    c1 = torch.empty((R, 2 * n), device=device, dtype=out_dtype)
+    fp8_blockwise_scaled_grouped_mm(c1, None, None, None, None, None, rep_q, w13.transpose(1, 2), rep_s,
+                                    w13_scale, None, None, None, None, None, ps1, expert_offsets[:-1], None)
+    inter = silu_and_mul(c1)
+    inter_q, inter_s = sglang_per_token_group_quant_fp8(inter, 128)
+    c2 = torch.empty((R, k), device=device, dtype=out_dtype)
+    fp8_blockwise_scaled_grouped_mm(c2, None, None, None, None, None, inter_q, w2.transpose(1, 2), inter_s,
+                                    w2_scale, None, None, None, None, None, ps2, expert_offsets[:-1], None)
+    out = torch.empty((R, k), device=device, dtype=out_dtype)
+    apply_shuffle_mul_sum(c2, out, c_map, None)     # topk = 1: pure un-permute back to input order
+    return out

@@ -146,3 +146,24 @@ def test_fused_moe_deepseek_shapes_reduced_tokens():
     ref = O.cutlass_fused_experts_fp8(a, w13q, w2q, w13s, w2s, w, ids)
     assert O.rel_l2(out.float().cpu(), ref.float()) <= 5e-3
     _status_ok()
+
+
+def test_ep_module_single_rank_equals_fused_path():
+    """world size 1: dispatch -> local grouped experts -> combine must give the fused path's bits."""
+    from sglang_b200.distributed import ExpertParallelBlockFp8MoE
+    from sglang_b200.layers.moe.cutlass_moe import fused_experts_block_fp8
+    E, H, I, m, topk = 8, 512, 256, 70, 2
+    g = torch.Generator().manual_seed(6)
+    a = torch.randn(m, H, generator=g).to(torch.bfloat16).cuda()
+    w13q, w13s, w2q, w2s = [], [], [], []
+    for e in range(E):
+        q_, s_ = O.per_block_cast_to_fp8(torch.randn(2 * I, H, generator=g) * 0.05); w13q.append(q_); w13s.append(s_)
+        q_, s_ = O.per_block_cast_to_fp8(torch.randn(H, I, generator=g) * 0.05); w2q.append(q_); w2s.append(s_)
+    w13q, w13s, w2q, w2s = [torch.stack(v).cuda() for v in (w13q, w13s, w2q, w2s)]
+    w, ids = O.fused_topk_native(torch.randn(m, E, generator=g), topk)
+    w, ids = w.cuda(), ids.cuda()
+    ref = fused_experts_block_fp8(a, w13q, w2q, w13s, w2s, w, ids)
+    moe = ExpertParallelBlockFp8MoE(w13q, w2q, w13s, w2s)
+    out = moe(a, w, ids)
+    assert same_bits(out, ref)
+    _status_ok()
