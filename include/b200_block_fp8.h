@@ -131,6 +131,26 @@ int b200_moe_prepare(const int32_t* topk_ids, int64_t num_tokens, int topk, int 
                      int32_t* problem_sizes2, int32_t* input_permutation, int32_t* output_permutation,
                      void* scratch, size_t scratch_bytes, void* stream);
 
+/*
+ * b200_moe_prepare without scratch from the caller and without any allocation.  No counterpart in the
+ * reference (its prepare_moe_input allocates a buffer on every call).
+ * For callers that cannot obtain device memory where the routing tables are built -- a server whose
+ * memory pool already owns the whole GPU, or a latency-critical section in which allocator calls
+ * (which may synchronise the device) are not permitted.  The chunk-count table lives in a 256 KiB array inside the library (held on
+ * every GPU that loads it until the process exits).
+ * Limit: ceil(num_tokens*topk / 2048) * num_experts <= 65536, else B200_ERR_TOO_LARGE and nothing runs.
+ * The first call on a device looks up the array's device address (one runtime query, no launch);
+ * make that first call before any stream capture begins.
+ * All calls on a device share the one array: the result does not depend on what an earlier call left
+ * in it, but two calls whose kernels can overlap on the GPU (different streams, no ordering between
+ * them) race on it -- order them, or use b200_moe_prepare with separate scratch.
+ * Same outputs as b200_moe_prepare.
+ */
+int b200_moe_prepare_noalloc(const int32_t* topk_ids, int64_t num_tokens, int topk, int num_experts, int n, int k,
+                             int32_t* expert_offsets, int32_t* blockscale_offsets, int32_t* problem_sizes1,
+                             int32_t* problem_sizes2, int32_t* input_permutation, int32_t* output_permutation,
+                             void* stream);
+
 /* output[d, :] = input[dst2src_map[d], :] for rows of row_bytes bytes (128-bit copies when rows and
  * bases are 16-byte aligned, narrower ones otherwise).
  * Replaces: shuffle_rows (sgl-kernel/csrc/moe/prepare_moe_input.cu:169-256, schema :204-205). */

@@ -266,6 +266,61 @@ extern "C" int b200_moe_prepare(const int32_t* topk_ids, int64_t num_tokens, int
                             static_cast<int32_t*>(scratch), static_cast<cudaStream_t>(stream));
 }
 
+// ---- routing tables without any allocation by anyone
+//
+// Some callers may not allocate device memory at the point where they build the routing tables: a
+// serving process that has handed every free byte of the GPU to its KV-cache pool has nothing left
+// for cudaMalloc to give, and a latency-critical section may forbid allocator calls (they can
+// synchronise the device) altogether.  For them the chunk-count table lives in a fixed array inside this library
+// instead of in caller-provided scratch.  The array costs kStaticScratchInts * 4 bytes on every GPU
+// that loads the library, for the life of the process.
+constexpr int kStaticScratchInts = 65536;   // 256 KiB: chunks * experts, e.g. 131072 ids x 1024 experts
+static __device__ __align__(256) int32_t g_prepare_scratch[kStaticScratchInts];
+
+namespace b200 {
+namespace {
+// Device address of g_prepare_scratch on the current device.  In host code the array's name is only
+// a handle for the runtime, never an address a kernel could use, so the address is asked for once
+// per device (with that device current) and cached.
+int static_scratch_ptr(int32_t** out) {
+  static int32_t* ptrs[64] = {nullptr};
+  int dev = 0;
+  B200_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return B200_ERR_UNSUPPORTED;
+  if (!ptrs[dev]) {
+    int32_t* ptr = nullptr;
+    B200_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_prepare_scratch));
+    ptrs[dev] = ptr;
+  }
+  *out = ptrs[dev];
+  return B200_OK;
+}
+}  // namespace
+}  // namespace b200
+
+extern "C" int b200_moe_prepare_noalloc(const int32_t* topk_ids, int64_t num_tokens, int topk, int num_experts,
+                                        int n, int k, int32_t* expert_offsets, int32_t* blockscale_offsets,
+                                        int32_t* problem_sizes1, int32_t* problem_sizes2,
+                                        int32_t* input_permutation, int32_t* output_permutation, void* stream) {
+  using namespace b200;
+  if (num_tokens < 0 || topk <= 0 || num_experts <= 0 || n < 0 || k < 0) return B200_ERR_BAD_SHAPE;
+  if (num_experts > 8192) return B200_ERR_TOO_LARGE;
+  if (!expert_offsets || !problem_sizes1 || !problem_sizes2) return B200_ERR_NULL_PTR;
+  const int64_t n_ids = num_tokens * topk;
+  if (n_ids > 0x7fffffffLL) return B200_ERR_TOO_LARGE;
+  if (n_ids > 0 && (!topk_ids || !input_permutation || !output_permutation)) return B200_ERR_NULL_PTR;
+  // the table needs one int per (chunk of 2048 ids, expert); beyond the built-in array: refuse
+  if (moe_prepare_scratch_bytes(n_ids, num_experts) > sizeof(int32_t) * kStaticScratchInts) return B200_ERR_TOO_LARGE;
+  int32_t* scratch = nullptr;
+  const int rc = static_scratch_ptr(&scratch);
+  if (rc != B200_OK) return rc;
+  // Nothing in the table has to start at zero: the counting launch overwrites every entry that the
+  // later launches read, so whatever an earlier call left behind is harmless.
+  return moe_prepare_launch(topk_ids, n_ids, topk, num_experts, n, k, expert_offsets, blockscale_offsets,
+                            problem_sizes1, problem_sizes2, input_permutation, output_permutation, scratch,
+                            static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int b200_shuffle_rows(const void* input, const int32_t* dst2src_map, void* output, int64_t num_dst_rows,
                                  int64_t row_bytes, void* stream) {
   using namespace b200;
