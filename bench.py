@@ -370,7 +370,31 @@ def run_kernel_case(args):
     ms_list = [int(v) for v in str(args.m).split(",")]
     for m in ms_list:
         g = torch.Generator(device=dev).manual_seed(m)
-        if args.kernel == "quant":
+        if args.kernel == "moe":
+            # DeepSeek-V3 MoE layer on one GPU: 256 experts, top-8, hidden 7168, intermediate 2048.
+            # Codes and scales are drawn directly (11.3 GB of weights); parity is covered by the tests.
+            from sglang_b200.layers.moe.cutlass_moe import fused_experts_block_fp8
+            E, H, I, topk = 256, 7168, 2048, 8
+            def codes(*shape):
+                c = torch.randint(0, 0x78, shape, generator=g, device=dev, dtype=torch.uint8)
+                sign = torch.randint(0, 2, shape, generator=g, device=dev, dtype=torch.uint8) << 7
+                return (c | sign).view(torch.float8_e4m3fn)
+            w13 = torch.empty((E, 2 * I, H), dtype=torch.float8_e4m3fn, device=dev)
+            w2 = torch.empty((E, H, I), dtype=torch.float8_e4m3fn, device=dev)
+            for e in range(E):
+                w13[e] = codes(2 * I, H)
+                w2[e] = codes(H, I)
+            w13s = torch.rand((E, 2 * I // 128, H // 128), generator=g, device=dev) * 2e-4 + 1e-5
+            w2s = torch.rand((E, H // 128, I // 128), generator=g, device=dev) * 2e-4 + 1e-5
+            x = torch.randn((m, H), generator=g, device=dev).to(torch.bfloat16)
+            logits = torch.randn((m, E), generator=g, device=dev)
+            tw, ti = torch.topk(torch.softmax(logits.float(), dim=-1), topk, dim=-1)
+            ti = ti.to(torch.int32)
+
+            def fn():
+                return fused_experts_block_fp8(x, w13, w2, w13s, w2s, tw, ti)
+            work, unit, peak = 2.0 * m * topk * (2 * I * H + H * I) / 1e12, "TFLOP/s", 2.0 * pk["bf16_sustained"]
+        elif args.kernel == "quant":
             nbuf = max(2, min(8, int(300e6 // (m * HIDDEN * 2)) + 1))   # rotate buffers: > L2 in total
             xs = []
             for _ in range(nbuf):
@@ -404,13 +428,16 @@ def run_kernel_case(args):
         b.record()
         torch.cuda.synchronize()
         sec = a.elapsed_time(b) / args.steps * 1e-3
-        print(json.dumps({"kernel": args.kernel, "M": m, "us": sec * 1e6, "achieved": work / sec, "unit": unit,
-                          "frac_of_measured_peak": work / sec / peak}))
+        rec = {"kernel": args.kernel, "M": m, "us": sec * 1e6, "achieved": work / sec, "unit": unit,
+               "frac_of_measured_peak": work / sec / peak}
+        if args.kernel == "moe":
+            rec["weight_GBps_if_all_experts_read"] = 256 * (2 * 2048 * 7168 + 7168 * 2048) / sec / 1e9
+        print(json.dumps(rec))
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", default=None, choices=["gemm_gate_up", "gemm_down", "quant"],
+    ap.add_argument("--kernel", default=None, choices=["gemm_gate_up", "gemm_down", "quant", "moe"],
                     help="time one kernel alone instead of the whole step")
     ap.add_argument("--m", default="4096", help="token count(s) for --kernel, comma separated")
     ap.add_argument("--gpus", type=int, default=1)

@@ -18,8 +18,10 @@
 // Division: x/scale is needed correctly rounded.  The default form computes the correctly
 // rounded reciprocal r once per group and then, per element, q0 = x*r, rem = fma(-q0, scale, x),
 // q = fma(rem, r, q0) -- correctly rounded for every scale whose significand is not all ones
-// (Markstein); groups with such a scale, or a non-finite scale, take the plain IEEE division.
-// The *_ieee_div entry point always uses the IEEE division and exists for cross-checking.
+// (Markstein), with no clamp (the saturating conversion does it).  Threads whose group has such a
+// scale or a non-finite one, whose 16 elements contain a NaN, or that were given a non-e4m3 range
+// evaluate the reference's expression literally (IEEE division, fmaxf, fminf).
+// The *_ieee_div entry point always takes the literal form and exists for cross-checking.
 #include "common.cuh"
 
 namespace b200 {
@@ -84,7 +86,7 @@ __device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float 
 }
 
 template <typename T, int GROUP, int PASSES, bool IEEE_DIV>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, (PASSES >= 8 || sizeof(T) == 4) ? 2 : 4)   // 4 blocks/SM: <= 64 registers
 quant_group_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ s, int64_t M, int64_t K,
                    int64_t s_stride_row, int64_t s_stride_grp, float eps, float fp8_min, float fp8_max,
                    int tiles_k) {
@@ -127,44 +129,53 @@ quant_group_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* __re
     for (int off = TPG / 2; off >= 1; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
 
     const float scale = __fdiv_rn(amax, fp8_max);
-    float y[kVec];
-    bool fast = !IEEE_DIV;
-    if (!IEEE_DIV) {
+    const bool std_range = (fp8_max == 448.0f) && (fp8_min == -448.0f);
+    bool fast = !IEEE_DIV && std_range;
+    if (fast) {
       const uint32_t bits = __float_as_uint(scale);
       // all-ones significand or Inf/NaN scale: leave the fast form
       fast = ((bits & 0x007fffffu) != 0x007fffffu) && ((bits & 0x7f800000u) != 0x7f800000u);
     }
+    uint4 out;
+    bool need_slow = !fast;
     if (fast) {
+      // Correctly rounded x/scale from the correctly rounded reciprocal (Markstein): q0 = x*r,
+      // t = fma(q0, scale, -x) = -(x - q0*scale) exactly, q = fma(-t, r, q0).  Written with t = -rem so
+      // that a zero x keeps its sign through both fmas (-0 stays -0, +0 stays +0), as x/scale does.
+      // |q| <= 448*(1 + 2^-23): the saturating conversion clamps that, so no explicit clamp is needed;
+      // only a NaN input must become fp8_min (fmaxf(NaN, lo) = lo in the reference): NaN survives the
+      // arithmetic and converts to code 0x7f / 0xff, which is detected on the packed codes below.
       const float r = __frcp_rn(scale);
+      float y[kVec];
 #pragma unroll
       for (int i = 0; i < kVec; ++i) {
         const float v = data[p].get(i);
         const float q0 = __fmul_rn(v, r);
-        const float rem = __fmaf_rn(-q0, scale, v);
-        // the quotient carries the sign of v (scale > 0); this also restores -0 when q0 is -0
-        y[i] = copysignf(__fmaf_rn(rem, r, q0), v);
+        const float t = __fmaf_rn(q0, scale, -v);
+        y[i] = __fmaf_rn(-t, r, q0);
       }
-    } else {
-#pragma unroll
-      for (int i = 0; i < kVec; ++i) y[i] = __fdiv_rn(data[p].get(i), scale);
-    }
-    // fmaxf maps NaN to fp8_min as the reference's fmaxf/fminf pair does.  The upper clamp is
-    // what the saturating conversion does anyway when fp8_max is the e4m3 maximum.
-#pragma unroll
-    for (int i = 0; i < kVec; ++i) y[i] = fmaxf(y[i], fp8_min);
-    if (fp8_max != 448.0f) {
-#pragma unroll
-      for (int i = 0; i < kVec; ++i) y[i] = fminf(y[i], fp8_max);
-    }
-
-    if (col_ok && row < M) {
-      uint4 out;
       out.x = pack4_e4m3(y[0], y[1], y[2], y[3]);
       out.y = pack4_e4m3(y[4], y[5], y[6], y[7]);
       out.z = pack4_e4m3(y[8], y[9], y[10], y[11]);
       out.w = pack4_e4m3(y[12], y[13], y[14], y[15]);
-      *reinterpret_cast<uint4*>(q + row * K + col) = out;
+      // a byte with all seven low bits set is a NaN code: (b & 0x7f) + 1 carries into bit 7
+      const uint32_t m7 = 0x7f7f7f7fu, one = 0x01010101u;
+      const uint32_t nan_bits = (((out.x & m7) + one) | ((out.y & m7) + one) | ((out.z & m7) + one) |
+                                 ((out.w & m7) + one)) & 0x80808080u;
+      need_slow = nan_bits != 0;
     }
+    if (need_slow) {
+      // the reference's expression, literally
+      float y[kVec];
+#pragma unroll
+      for (int i = 0; i < kVec; ++i)
+        y[i] = fminf(fmaxf(__fdiv_rn(data[p].get(i), scale), fp8_min), fp8_max);
+      out.x = pack4_e4m3(y[0], y[1], y[2], y[3]);
+      out.y = pack4_e4m3(y[4], y[5], y[6], y[7]);
+      out.z = pack4_e4m3(y[8], y[9], y[10], y[11]);
+      out.w = pack4_e4m3(y[12], y[13], y[14], y[15]);
+    }
+    if (col_ok && row < M) *reinterpret_cast<uint4*>(q + row * K + col) = out;
     if ((slot % TPG) == 0) s_tile[(p * ROWS_PER_PASS + row_in_pass) * GPT + slot / TPG] = scale;
   }
   __syncthreads();
