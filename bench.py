@@ -337,7 +337,7 @@ def run_gpu_arm(args):
                     "note": "activations from pinned host memory, bf16 results back to pinned host memory; "
                             "weights stay resident (they are layer parameters)"},
             "gpu_launches": args.steps * 4,
-            "roofline": {"bound": "tensor", "kernel": "gemm_block_fp8_kernel<BLOCK_N=256, 16 epilogue warps, bf16> (gate_up)",
+            "roofline": {"bound": "tensor", "kernel": "gemm_block_fp8_kernel<BLOCK_N=256, 16 epilogue warps, 32-column chunks, bf16> (gate_up)",
                          "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                          "peak_source": f"2 x bf16_tflops_sustained of {pk['src']} (the fp8 pipe does twice the "
                                         "bf16 MACs per clock; the file holds no fp8 entry)",

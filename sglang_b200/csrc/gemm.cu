@@ -5,14 +5,14 @@
 // _w8a8_block_fp8_matmul (python/sglang/srt/layers/quantization/fp8_kernel.py:493-575).
 //
 // One persistent CTA per SM, warp-specialised:
-//   warp 0      TMA producer: per 128-wide k-block one A box (128 rows x 128 B) and one B box
+//   TMA warp    producer: per 128-wide k-block one A box (128 rows x 128 B) and one B box
 //               (BLOCK_N rows x 128 B) into a ring of shared-memory stages (128-byte swizzle).
-//   warp 1      MMA issuer: 4 x tcgen05.mma kind::f8f6f4 (M128 x N BLOCK_N x K32) per k-block into
+//   MMA warp    issuer: 4 x tcgen05.mma kind::f8f6f4 (M128 x N BLOCK_N x K32) per k-block into
 //               a tensor-memory accumulator that is started fresh for every k-block (the fp32
 //               scales differ per k-block, so partial sums cannot be chained inside the tensor
 //               core); accumulators rotate through 512/BLOCK_N tensor-memory buffers.  One
 //               tcgen05.commit per k-block signals both "stage reusable" and "partial sums ready".
-//   warps 2..   promotion + epilogue: each warp owns 32 rows (its tensor-memory lane quadrant)
+//   warps 0..E-1 promotion + epilogue: each warp owns 32 rows (its tensor-memory lane quadrant)
 //               x CPW columns; per k-block it reads the partial sums with tcgen05.ld in chunks,
 //               releases the buffer after the last chunk has landed, and does
 //               acc += partial * (sa[m,kb] * sb[nb,kb]) with packed fp32 FMAs; after the last
@@ -41,9 +41,23 @@ struct Cfg {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kNumAcc = kTmemCols / BLOCK_N;
   static constexpr int kColsPerWarp = BLOCK_N / (EPI_WARPS / 4);
-  static constexpr int kStagerWarp = 2 + EPI_WARPS;             // stages the scale products in shared memory
-  static constexpr int kMmaWarpB = 3 + EPI_WARPS;               // second MMA-issuing warp when ISSUERS == 2
-  static constexpr int kThreads = 32 * (2 + ISSUERS + EPI_WARPS);
+  // Warp roles: epilogue warps first (whole warpgroups, so their register budget can be raised with
+  // setmaxnreg), then one warpgroup of helpers.
+  static constexpr int kTmaWarp = EPI_WARPS;
+  static constexpr int kMmaWarp = EPI_WARPS + 1;
+  static constexpr int kStagerWarp = EPI_WARPS + 2;             // stages the scale products in shared memory
+  static constexpr int kMmaWarpB = EPI_WARPS + 3;               // second MMA-issuing warp when ISSUERS == 2 (else idle)
+  static constexpr int kThreads = 32 * (4 + EPI_WARPS);
+  // With 16 epilogue warps the launch gives every thread 96 registers (20 warps); the helper
+  // warpgroup hands 32 per thread back and the epilogue warps take 8 more each, enough to hold 64
+  // accumulators plus a 32-column chunk.  setmaxnreg.inc WAITS until the CTA's pool holds the
+  // registers it asks for, so the request must never exceed what the helpers release.
+  static constexpr bool kRebalanceRegs = EPI_WARPS == 16;
+  static constexpr int kLaunchRegs = 96;
+  static constexpr int kEpiRegs = 104;
+  static constexpr int kHelperRegs = 64;
+  static_assert(EPI_WARPS * (kEpiRegs - kLaunchRegs) <= 4 * (kLaunchRegs - kHelperRegs),
+                "epilogue warps would wait forever for registers nobody releases");
   static constexpr int kHalves = BLOCK_N / 128;                 // weight-scale blocks per tile row
   static constexpr int kSlotFloats = kScaleGroup * kHalves * BLOCK_M;
   static constexpr int kScaleBytes = kScaleSlots * kSlotFloats * 4;
@@ -157,11 +171,11 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     fence_mbar_init();
     fence_proxy_async_smem();
   }
-  if (warp == 0 && lane == 0) {
+  if (warp == C::kTmaWarp && lane == 0) {
     tma_prefetch_desc(&map_a);
     tma_prefetch_desc(&map_b);
   }
-  if (warp == 1) {
+  if (warp == C::kMmaWarp) {
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
   }
@@ -171,7 +185,10 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
   const int num_tiles = GROUPED ? tile_m_start[p.num_experts] * n_blocks : m_blocks * n_blocks;
 
-  if (warp == 0) {
+  if (warp >= EPI_WARPS) {
+  // ====================================================================== helper warpgroup
+  if constexpr (C::kRebalanceRegs) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(C::kHelperRegs));
+  if (warp == C::kTmaWarp) {
     // ------------------------------------------------------------------ TMA producer
     int stage = 0;
     uint32_t phase = 0;
@@ -191,7 +208,7 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       }
     }
     __syncwarp();
-  } else if (warp == 1 || (ISSUERS == 2 && warp == C::kMmaWarpB)) {
+  } else if (warp == C::kMmaWarp || (ISSUERS == 2 && warp == C::kMmaWarpB)) {
     // ------------------------------------------------------------------ MMA issuer(s)
     // With ISSUERS == 2 (experimental), warp 1 takes the even k-blocks of this CTA's k-block
     // sequence and the second warp the odd ones; k-blocks are independent (own stage, own
@@ -199,7 +216,7 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     constexpr uint32_t idesc = umma_idesc_e4m3(BLOCK_M, BLOCK_N);
     const uint64_t a_desc0 = umma_desc_k128(smem_u32(smem_a));
     const uint64_t b_desc0 = umma_desc_k128(smem_u32(smem_b));
-    const int first = (warp == 1) ? 0 : 1;
+    const int first = (warp == C::kMmaWarp) ? 0 : 1;
     const int my_tiles = (num_tiles > static_cast<int>(blockIdx.x))
                              ? (num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
                                    static_cast<int>(gridDim.x)
@@ -284,13 +301,15 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       }
     }
     __syncwarp();
+  }
   } else {
-    // ------------------------------------------------------------------ promotion + epilogue
+    // ====================================================================== promotion + epilogue warps
+    if constexpr (C::kRebalanceRegs) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(C::kEpiRegs));
     constexpr int CPW = C::kColsPerWarp;
     static_assert(CPW % CHUNK == 0 && (CHUNK == 16 || CHUNK == 32 || CHUNK == 64), "chunking");
     static_assert(CPW <= 128, "a warp's columns lie in one weight-scale block");
     const int quad = warp & 3;         // tensor-memory lane quadrant this warp may read
-    const int part = (warp - 2) >> 2;  // which CPW-wide column slice
+    const int part = warp >> 2;        // which CPW-wide column slice
     const int half = (part * CPW) / 128;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     OutT* out = static_cast<OutT*>(p.out);
@@ -369,7 +388,7 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     // a wait gave up: let copies that may still be in flight land before shared memory is released
     for (int i = 0; i < 200; ++i) __nanosleep(1000);
   }
-  if (warp == 1) {
+  if (warp == C::kMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
@@ -487,7 +506,7 @@ extern "C" int b200_fp8_blockwise_scaled_mm(const void* a, int64_t lda, const vo
   rc = make_map_u8_2d(&mb, b, N, K, ldb, block_n);
   if (rc != B200_OK) return rc;
   if (g_force_block_n >= 1000) return launch_variant(g_force_block_n, ma, mb, p, st);
-  return block_n == 256 ? launch_dtype<256, 16, 16>(ma, mb, p, st) : launch_dtype<128, 8, 64>(ma, mb, p, st);
+  return block_n == 256 ? launch_dtype<256, 16, 32>(ma, mb, p, st) : launch_dtype<128, 8, 64>(ma, mb, p, st);
 }
 
 extern "C" int b200_fp8_blockwise_scaled_grouped_mm(const void* a, int64_t lda, const void* b, int64_t ldb,
@@ -532,7 +551,7 @@ extern "C" int b200_fp8_blockwise_scaled_grouped_mm(const void* a, int64_t lda, 
   rc = make_map_u8_2d(&mb, b, N * num_experts, K, ldb, block_n);
   if (rc != B200_OK) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  return block_n == 256 ? launch_dtype<256, 16, 16, 1, true>(ma, mb, p, st)
+  return block_n == 256 ? launch_dtype<256, 16, 32, 1, true>(ma, mb, p, st)
                         : launch_dtype<128, 8, 64, 1, true>(ma, mb, p, st);
 }
 
