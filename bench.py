@@ -40,8 +40,9 @@ INTER = 18432
 WORKLOAD = "deepseek_v3_dense_mlp_block_fp8_M4096(gate_up K7168 N36864 + down K18432 N7168)"
 FLOPS_PER_STEP = 2.0 * M_TOKENS * (INTER2 * HIDDEN + HIDDEN * INTER)
 NOMINAL_FP8_TFLOPS = 4500.0
-# dram bytes per launch of the gate_up GEMM from the committed ncu capture (profiles/), or None
-GEMM_TRAFFIC_BYTES = None
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the gate_up GEMM at M=4096, from the ncu
+# capture summarised in profiles/gemm_block_fp8_gate_up_M4096_dram.md (algorithmic bytes: 596.9e6)
+GEMM_TRAFFIC_BYTES = 586.4e6
 
 
 def _peaks():

@@ -29,7 +29,8 @@ namespace {
 constexpr int BLOCK_M = 128;
 constexpr int BLOCK_K = 128;
 constexpr int kTmemCols = 512;
-constexpr int kGroupM = 16;     // m-blocks per rasterisation group (keeps A and B tiles of a wave in L2)
+constexpr int kGroupM = 32;     // m-blocks per rasterisation group: the group's A rows (<= 4096 x K bytes) stay in L2
+                                // while every weight slice is streamed once per group
 constexpr int kScaleGroup = 4;   // k-blocks per scale-ring slot
 constexpr int kScaleSlots = 4;   // slots in the ring (the stager runs up to 16 k-blocks ahead)
 
