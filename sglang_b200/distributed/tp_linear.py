@@ -38,9 +38,9 @@ def shard_block_fp8_weight(weight: torch.Tensor, weight_scale: torch.Tensor, dim
     return w, s
 
 
-def _default_linear(x, w, ws, bias):
+def _default_linear(x, w, ws, bias, out=None):
     from ..layers.quantization.fp8_utils import w8a8_block_fp8_linear
-    return w8a8_block_fp8_linear(x, w, [BLOCK, BLOCK], ws, bias=bias)
+    return w8a8_block_fp8_linear(x, w, [BLOCK, BLOCK], ws, bias=bias, out=out)
 
 
 class ColumnParallelBlockFp8Linear:
@@ -64,8 +64,13 @@ class ColumnParallelBlockFp8Linear:
 
 
 class RowParallelBlockFp8Linear:
+    """overlap_chunks > 1: the rows are processed in that many chunks and the all-reduce of chunk i
+    runs on a side stream while chunk i+1 is quantised and multiplied (CUDA only).  The sum per
+    element is the same collective on the same values, so results equal the unchunked form."""
+
     def __init__(self, weight, weight_scale, bias: Optional[torch.Tensor] = None, group=None,
-                 linear_fn: Callable = _default_linear, reduce_results: bool = True, already_sharded: bool = False):
+                 linear_fn: Callable = _default_linear, reduce_results: bool = True, already_sharded: bool = False,
+                 overlap_chunks: int = 1):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -76,12 +81,33 @@ class RowParallelBlockFp8Linear:
         self.bias = bias
         self.reduce_results = reduce_results
         self._linear = linear_fn
+        self.overlap_chunks = max(1, int(overlap_chunks))
+        self._comm_stream = None
 
     def forward(self, x_shard: torch.Tensor) -> torch.Tensor:
         bias = self.bias if self.rank == 0 else None   # added once, before the sum
-        out = self._linear(x_shard, self.weight, self.weight_scale, bias)
-        if self.reduce_results and self.world > 1:
-            dist.all_reduce(out, op=dist.ReduceOp.SUM, group=self.group)
+        reduce = self.reduce_results and self.world > 1
+        M = x_shard.shape[0] if x_shard.dim() == 2 else 0
+        if not (reduce and self.overlap_chunks > 1 and x_shard.is_cuda and M >= 256 * self.overlap_chunks):
+            out = self._linear(x_shard, self.weight, self.weight_scale, bias)
+            if reduce:
+                dist.all_reduce(out, op=dist.ReduceOp.SUM, group=self.group)
+            return out
+        if self._comm_stream is None:
+            self._comm_stream = torch.cuda.Stream(device=x_shard.device)
+        main = torch.cuda.current_stream(x_shard.device)
+        out = torch.empty((M, self.weight.shape[0]), dtype=x_shard.dtype, device=x_shard.device)
+        rows = (M + self.overlap_chunks - 1) // self.overlap_chunks
+        rows = (rows + 127) // 128 * 128
+        for lo in range(0, M, rows):
+            hi = min(M, lo + rows)
+            self._linear(x_shard[lo:hi], self.weight, self.weight_scale, bias, out=out[lo:hi])
+            ready = torch.cuda.Event()
+            ready.record(main)
+            with torch.cuda.stream(self._comm_stream):
+                self._comm_stream.wait_event(ready)
+                dist.all_reduce(out[lo:hi], op=dist.ReduceOp.SUM, group=self.group)
+        main.wait_stream(self._comm_stream)
         return out
 
     __call__ = forward

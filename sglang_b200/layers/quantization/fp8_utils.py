@@ -16,14 +16,15 @@ from .fp8_kernel import sglang_per_token_group_quant_fp8
 
 def w8a8_block_fp8_linear(input: torch.Tensor, weight: torch.Tensor, block_size: List[int],
                           weight_scale: torch.Tensor, input_scale: Optional[torch.Tensor] = None,
-                          bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+                          bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """`out` (extension): a row-major [tokens, N] tensor of the input dtype to write into."""
     assert input_scale is None
     assert list(block_size) == [128, 128]
     input_2d = input.view(-1, input.shape[-1])
     output_shape = [*input.shape[:-1], weight.shape[0]]
     q_input, x_scale = sglang_per_token_group_quant_fp8(
         input_2d, block_size[1], column_major_scales=True)
-    output = fp8_blockwise_scaled_mm(q_input, weight.T, x_scale, weight_scale.T, out_dtype=input_2d.dtype)
+    output = fp8_blockwise_scaled_mm(q_input, weight.T, x_scale, weight_scale.T, out_dtype=input_2d.dtype, out=out)
     if bias is not None:
         output += bias
     return output.to(dtype=input_2d.dtype).view(*output_shape)

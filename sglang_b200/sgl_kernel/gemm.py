@@ -80,9 +80,12 @@ def fp8_blockwise_scaled_mm(
     scales_a: torch.Tensor,
     scales_b: torch.Tensor,
     out_dtype: torch.dtype,
+    out: torch.Tensor = None,
 ) -> torch.Tensor:
     """mat_a [M,K] e4m3 row-major; mat_b [K,N] e4m3 column-major (= weight[N,K].T);
-    scales_a [M,K/128] fp32 M-major; scales_b [K/128,N/128] fp32 K-major; returns [M,N]."""
+    scales_a [M,K/128] fp32 M-major; scales_b [K/128,N/128] fp32 K-major; returns [M,N].
+    `out` (not in the reference signature): write into this [M,N] tensor (rows may be a slice of a
+    larger buffer) instead of allocating."""
     _check(mat_a.is_cuda, "mat_a must be a CUDA tensor")
     _check(mat_b.is_cuda, "mat_b must be a CUDA tensor")
     _check(mat_a.dim() == 2, "mat_a must be a 2D tensor")
@@ -106,7 +109,11 @@ def fp8_blockwise_scaled_mm(
     _check(scales_b.stride(0) == 1 or _is_contiguous_vector(scales_b), "scales_b must be K major")
     _check(scales_a.dtype == torch.float32, "scales_a must be Float32")
     _check(scales_b.dtype == torch.float32, "scales_b must be Float32")
-    out = torch.empty((M, N), dtype=out_dtype, device=mat_a.device)
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=mat_a.device)
+    else:
+        _check(out.shape == (M, N) and out.dtype == out_dtype and out.stride(1) == 1 and out.is_cuda,
+               "out must be a row-major [M,N] CUDA tensor of out_dtype")
     _check((N * out.element_size()) % 16 == 0, "out must be multiple of 16 bytes for memory alignment")
     _check(K % 128 == 0 and N % 128 == 0, "K and N must be multiples of 128 (block scale granularity)")
     if M == 0:

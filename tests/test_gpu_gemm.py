@@ -206,3 +206,11 @@ def test_argument_errors_raise_before_launch():
     with pytest.raises(RuntimeError, match="scales_b"):
         fp8_blockwise_scaled_mm(a, b.t(), sa, torch.ones(3, 1, device="cuda"), torch.bfloat16)
     assert fp8_blockwise_scaled_mm(a[:0], b.t(), sa[:0], sb, torch.bfloat16).shape == (0, 128)
+
+
+@pytest.mark.parametrize("N,K", [(1280, 8192), (7168, 8192), (8192, 1024), (8192, 3584), (10240, 8192)])
+def test_llama70b_tp_shard_shapes(N, K):
+    """Per-rank shapes of the Llama-3-70B layers at tp=8 (and qkv at tp=1): column-parallel shards
+    split N, row-parallel shards split K; M = 128."""
+    a, b, sa, sb = _rand_problem(128, N, K, seed=N + K)
+    _assert_parity(a, b, sa, sb)
