@@ -72,6 +72,19 @@ int b200_per_token_group_quant_fp8_ieee_div(const void* x, int x_dtype, void* q,
                                             float eps, float fp8_min, float fp8_max, void* stream);
 
 /*
+ * SiLU(gate) * up followed by per-token-group (128) FP8 quantisation in one pass: x [M, 2K] holds
+ * gate | up per row (bf16 / fp16); writes codes q [M, K] and scales as above.  The product is formed
+ * in fp32 and rounded to x's type before quantisation, so the result is bit-identical to
+ * b200_silu_and_mul followed by b200_per_token_group_quant_fp8 while skipping the [M, K] round trip.
+ * Replaces the pair silu_and_mul + sglang_per_token_group_quant_fp8 at
+ * python/sglang/srt/layers/moe/cutlass_moe.py:191-194 (the reference fuses the same pair only in its
+ * Triton EP path, python/sglang/srt/layers/moe/ep_moe/kernels.py:317-460).
+ */
+int b200_silu_mul_per_token_group_quant_fp8(const void* x, int x_dtype, void* q, float* s, int64_t M, int64_t K,
+                                            int64_t s_stride_row, int64_t s_stride_grp, float eps, float fp8_min,
+                                            float fp8_max, void* stream);
+
+/*
  * Dense block-scaled FP8 GEMM:  out[m,n] = cast( sum_kb ( sum_{k in kb} a[m,k]*b[n,k] )
  *                                               * sa[m,kb] * sb[n/128,kb] ),  fp32 accumulation.
  * Replaces: fp8_blockwise_scaled_mm

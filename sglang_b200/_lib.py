@@ -33,6 +33,8 @@ _SIGNATURES = {
     "b200_per_token_group_quant_fp8_ieee_div": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64,
                                                         c_int64, c_int64, c_int64, c_float, c_float, c_float,
                                                         c_void_p]),
+    "b200_silu_mul_per_token_group_quant_fp8": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                                                        c_int64, c_float, c_float, c_float, c_void_p]),
     "b200_fp8_blockwise_scaled_mm": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64,
                                              c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int, c_int64, c_int64,
                                              c_int64, c_void_p]),

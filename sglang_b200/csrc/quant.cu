@@ -48,6 +48,11 @@ struct Vec16<__nv_bfloat16> {
     const uint32_t word = w[i >> 1];
     return __uint_as_float((i & 1) ? (word & 0xffff0000u) : (word << 16));
   }
+  __device__ __forceinline__ void from_floats(const float (&f)[16]) {   // round to nearest even, as a bf16 store would
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  }
 };
 template <>
 struct Vec16<__half> {
@@ -63,6 +68,11 @@ struct Vec16<__half> {
     const float2 f = __half22float2(h[i >> 1]);
     return (i & 1) ? f.y : f.x;
   }
+  __device__ __forceinline__ void from_floats(const float (&f)[16]) {
+    __half2* h = reinterpret_cast<__half2*>(v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+  }
 };
 template <>
 struct Vec16<float> {
@@ -77,6 +87,10 @@ struct Vec16<float> {
     for (int i = 0; i < 4; ++i) v[i] = make_uint4(0, 0, 0, 0);
   }
   __device__ __forceinline__ float get(int i) const { return reinterpret_cast<const float*>(v)[i]; }
+  __device__ __forceinline__ void from_floats(const float (&f)[16]) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) reinterpret_cast<float*>(v)[i] = f[i];
+  }
 };
 
 __device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float d) {
@@ -85,7 +99,10 @@ __device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float 
   return lo | (hi << 16);
 }
 
-template <typename T, int GROUP, int PASSES, bool IEEE_DIV>
+// FUSE_SILU: x is [M, 2K] (gate | up); the row to quantise is silu(gate) * up, computed in fp32 and
+// rounded to T exactly as the separate silu_and_mul kernel stores it, so codes and scales equal the
+// two-kernel sequence bit for bit while the [M, K] intermediate never touches HBM.
+template <typename T, int GROUP, int PASSES, bool IEEE_DIV, bool FUSE_SILU = false>
 __global__ void __launch_bounds__(kThreads, (PASSES >= 8 || sizeof(T) == 4) ? 2 : 4)   // 4 blocks/SM: <= 64 registers
 quant_group_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ s, int64_t M, int64_t K,
                    int64_t s_stride_row, int64_t s_stride_grp, float eps, float fp8_min, float fp8_max,
@@ -113,7 +130,20 @@ quant_group_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* __re
   for (int p = 0; p < PASSES; ++p) {
     const int64_t row = row0 + p * ROWS_PER_PASS;
     if (col_ok && row < M) {
-      data[p].load(x + row * K + col);
+      if constexpr (FUSE_SILU) {
+        Vec16<T> gate, up;
+        gate.load(x + row * 2 * K + col);
+        up.load(x + row * 2 * K + K + col);
+        float f[kVec];
+#pragma unroll
+        for (int i = 0; i < kVec; ++i) {
+          const float gv = gate.get(i);
+          f[i] = (gv / (1.0f + __expf(-gv))) * up.get(i);
+        }
+        data[p].from_floats(f);
+      } else {
+        data[p].load(x + row * K + col);
+      }
     } else {
       data[p].zero();
     }
@@ -198,7 +228,7 @@ quant_group_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* __re
   }
 }
 
-template <typename T, int GROUP, bool IEEE_DIV>
+template <typename T, int GROUP, bool IEEE_DIV, bool FUSE_SILU = false>
 int launch_group(const void* x, void* q, float* s, int64_t M, int64_t K, int64_t ssr, int64_t ssg, float eps,
                  float fmin_, float fmax_, cudaStream_t stream) {
   const int tiles_k = static_cast<int>((K + kTileW - 1) / kTileW);
@@ -217,7 +247,7 @@ int launch_group(const void* x, void* q, float* s, int64_t M, int64_t K, int64_t
   const T* xp = static_cast<const T*>(x);
   uint8_t* qp = static_cast<uint8_t*>(q);
 #define B200_LAUNCH_Q(P)                                                                                       \
-  quant_group_kernel<T, GROUP, P, IEEE_DIV><<<grid, kThreads, 0, stream>>>(xp, qp, s, M, K, ssr, ssg, eps, fmin_, \
+  quant_group_kernel<T, GROUP, P, IEEE_DIV, FUSE_SILU><<<grid, kThreads, 0, stream>>>(xp, qp, s, M, K, ssr, ssg, eps, fmin_, \
                                                                            fmax_, tiles_k)
   switch (passes) {
     case 8:
@@ -287,4 +317,28 @@ extern "C" int b200_per_token_group_quant_fp8_ieee_div(const void* x, int x_dtyp
 extern "C" int b200_debug_force_quant_passes(int passes) {
   b200::g_force_quant_passes = passes;
   return B200_OK;
+}
+
+extern "C" int b200_silu_mul_per_token_group_quant_fp8(const void* x, int x_dtype, void* q, float* s, int64_t M,
+                                                       int64_t K, int64_t s_stride_row, int64_t s_stride_grp,
+                                                       float eps, float fp8_min, float fp8_max, void* stream) {
+  using namespace b200;
+  if (M < 0 || K < 0) return B200_ERR_BAD_SHAPE;
+  if (K % 128 != 0) return B200_ERR_BAD_SHAPE;
+  if (M == 0 || K == 0) return B200_OK;
+  if (!x || !q || !s) return B200_ERR_NULL_PTR;
+  if (!aligned16(x) || !aligned16(q)) return B200_ERR_MISALIGNED;
+  if (s_stride_row < 0 || s_stride_grp < 0 || (s_stride_row == 0 && M > 1) || (s_stride_grp == 0 && K / 128 > 1))
+    return B200_ERR_BAD_STRIDE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (x_dtype) {
+    case B200_DT_BF16:
+      return launch_group<__nv_bfloat16, 128, false, true>(x, q, s, M, K, s_stride_row, s_stride_grp, eps, fp8_min,
+                                                           fp8_max, st);
+    case B200_DT_F16:
+      return launch_group<__half, 128, false, true>(x, q, s, M, K, s_stride_row, s_stride_grp, eps, fp8_min, fp8_max,
+                                                    st);
+    default:
+      return B200_ERR_BAD_DTYPE;
+  }
 }

@@ -13,7 +13,7 @@ import torch
 
 from ...sgl_kernel import (apply_shuffle_mul_sum, fp8_blockwise_scaled_grouped_mm, prepare_moe_input, shuffle_rows,
                            silu_and_mul)
-from ..quantization.fp8_kernel import sglang_per_token_group_quant_fp8
+from ..quantization.fp8_kernel import sglang_per_token_group_quant_fp8, silu_and_mul_per_token_group_quant_fp8
 
 
 def cutlass_fused_experts_fp8(
@@ -85,9 +85,9 @@ def cutlass_fused_experts_fp8(
                                     rep_a1_scales, w1_scale, a1_strides, a1_strides, c1_strides, None, None,
                                     problem_sizes1, expert_offsets[:-1], workspace)
 
-    intermediate = torch.empty((m * topk, n), device=device, dtype=out_dtype)
-    silu_and_mul(c1, intermediate)
-    intermediate_q, a2_scale = sglang_per_token_group_quant_fp8(intermediate, 128)
+    # SiLU*mul and the second group quantisation in one pass (bit-identical to the two-kernel sequence
+    # silu_and_mul -> sglang_per_token_group_quant_fp8 of the reference, cutlass_moe.py:191-194)
+    intermediate_q, a2_scale = silu_and_mul_per_token_group_quant_fp8(c1, 128)
     fp8_blockwise_scaled_grouped_mm(c2, a_ptrs, b_ptrs, out_ptrs, a_scales_ptrs, b_scales_ptrs, intermediate_q, w2_q,
                                     a2_scale, w2_scale, a2_strides, a2_strides, c2_strides, None, None,
                                     problem_sizes2, expert_offsets[:-1], workspace)
@@ -123,8 +123,7 @@ def grouped_experts_prequantized(a_q, a_scale, expert_ids, w13, w2, w13_scale, w
     c1 = torch.empty((R, 2 * n), device=device, dtype=out_dtype)
     fp8_blockwise_scaled_grouped_mm(c1, None, None, None, None, None, rep_q, w13.transpose(1, 2), rep_s,
                                     w13_scale, None, None, None, None, None, ps1, expert_offsets[:-1], None)
-    inter = silu_and_mul(c1)
-    inter_q, inter_s = sglang_per_token_group_quant_fp8(inter, 128)
+    inter_q, inter_s = silu_and_mul_per_token_group_quant_fp8(c1, 128)
     c2 = torch.empty((R, k), device=device, dtype=out_dtype)
     fp8_blockwise_scaled_grouped_mm(c2, None, None, None, None, None, inter_q, w2.transpose(1, 2), inter_s,
                                     w2_scale, None, None, None, None, None, ps2, expert_offsets[:-1], None)

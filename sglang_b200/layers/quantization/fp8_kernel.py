@@ -48,6 +48,32 @@ def sglang_per_token_group_quant_fp8(x: torch.Tensor, group_size: int, eps: floa
     return x_q, x_s
 
 
+def silu_and_mul_per_token_group_quant_fp8(x: torch.Tensor, group_size: int = 128, eps: float = 1e-10,
+                                           column_major_scales: bool = False, scale_tma_aligned: bool = False):
+    """x [..., 2K] (gate | up) -> codes [..., K], scales as in sglang_per_token_group_quant_fp8.
+    Bit-identical to silu_and_mul followed by sglang_per_token_group_quant_fp8; one kernel, and the
+    [..., K] intermediate is never written.  (The reference has this fusion only as a Triton kernel
+    in its EP path: python/sglang/srt/layers/moe/ep_moe/kernels.py:317-460.)"""
+    assert group_size == 128, "the fused form is built for 128-wide groups"
+    assert x.is_contiguous() and x.shape[-1] % 256 == 0
+    assert x.dtype in (torch.bfloat16, torch.float16)
+    K = x.shape[-1] // 2
+    out_shape = x.shape[:-1] + (K,)
+    x_q = torch.empty(out_shape, device=x.device, dtype=fp8_dtype)
+    x_s = create_per_token_group_quant_fp8_output_scale(out_shape, x.device, group_size, column_major_scales,
+                                                        scale_tma_aligned, False)
+    M = x.numel() // (2 * K)
+    if M > 0:
+        s2 = x_s.reshape(M, K // 128) if x_s.dim() != 2 else x_s
+        dt = {torch.float16: _lib.DT_F16, torch.bfloat16: _lib.DT_BF16}[x.dtype]
+        with torch.cuda.device(x.device):
+            rc = _lib.lib().b200_silu_mul_per_token_group_quant_fp8(
+                x.data_ptr(), dt, x_q.data_ptr(), s2.data_ptr(), M, K, s2.stride(0), s2.stride(1), eps, fp8_min,
+                fp8_max, torch.cuda.current_stream(x.device).cuda_stream)
+        _lib.check("silu_and_mul_per_token_group_quant_fp8", rc)
+    return x_q, x_s
+
+
 def per_token_group_quant_fp8(x: torch.Tensor, group_size: int, eps: float = 1e-10,
                               column_major_scales: bool = False, scale_tma_aligned: bool = False,
                               scale_ue8m0: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:

@@ -167,3 +167,18 @@ def test_ep_module_single_rank_equals_fused_path():
     out = moe(a, w, ids)
     assert same_bits(out, ref)
     _status_ok()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,K", [(1, 128), (77, 2048), (300, 512)])
+def test_fused_silu_mul_quant_equals_two_kernels(M, K, dtype):
+    from sglang_b200.layers.quantization.fp8_kernel import (sglang_per_token_group_quant_fp8,
+                                                            silu_and_mul_per_token_group_quant_fp8)
+    from sglang_b200.sgl_kernel import silu_and_mul
+    g = torch.Generator().manual_seed(M + K)
+    x = (torch.randn(M, 2 * K, generator=g) * 2).to(dtype).cuda()
+    q_ref, s_ref = sglang_per_token_group_quant_fp8(silu_and_mul(x), 128)
+    q, s = silu_and_mul_per_token_group_quant_fp8(x, 128)
+    assert same_bits(q, q_ref) and same_bits(s, s_ref)
+    q2, s2 = silu_and_mul_per_token_group_quant_fp8(x, 128, column_major_scales=True, scale_tma_aligned=True)
+    assert same_bits(q2, q_ref) and same_bits(s2.contiguous(), s_ref)
