@@ -185,6 +185,22 @@ int b200_apply_shuffle_mul_sum(const void* input, void* output, const int32_t* p
  * wait gave up, value encodes which).  Synchronises the device.  No reference counterpart. */
 int b200_gemm_device_status(int* status_out);
 
+/*
+ * Diagnostics for tests and experiments (process-wide switches; none has a reference counterpart).
+ *   force_block_n:  0 automatic; 128 / 256 single-CTA kernel with that tile width; 2 CTA-pair kernel;
+ *                   1001.. experimental variants of the single-CTA kernel.
+ *   force_quant_passes: rows-of-4 per quantisation tile (1, 2, 4, 8); 0 automatic.
+ *   gemm_mode / wait_hint_ns / set_timing_buffer: timing experiments on the CTA-pair kernel (results
+ *                   are wrong while gemm_mode is non-zero).
+ *   pair_kernel_max_clusters: what the cluster occupancy query returned for the CTA-pair kernel.
+ */
+int b200_debug_force_block_n(int block_n);
+int b200_debug_force_quant_passes(int passes);
+int b200_debug_gemm_mode(int mode);
+int b200_debug_wait_hint_ns(int ns);
+int b200_debug_set_timing_buffer(void* device_buf_5x64_i64);
+int b200_debug_pair_kernel_max_clusters(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -440,7 +440,7 @@ int launch_variant(int id, const CUtensorMap& ma, const CUtensorMap& mb, const G
     case 1007: return launch_dtype<128, 8, 64, 2>(ma, mb, p, st);
     case 1010: return launch_dtype<128, 8, 32, 2>(ma, mb, p, st);
     case 1008: return launch_dtype<128, 16, 32, 2>(ma, mb, p, st);
-    case 1009: return launch_dtype<256, 16, 16, 2>(ma, mb, p, st);
+    case 1009: return launch_dtype<256, 16, 32, 2>(ma, mb, p, st);
     default: return B200_ERR_UNSUPPORTED;
   }
 }

@@ -1,0 +1,83 @@
+"""CPU: the C-ABI library loads, exports every symbol the header declares, and rejects bad
+arguments with the documented codes before touching a device (no compute calls here)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "b200_block_fp8.h")
+
+
+def _declared():
+    src = open(HEADER).read()
+    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    return sorted(set(re.findall(r"\b(b200_[a-z0-9_]+)\s*\(", src)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from sglang_b200 import _lib
+    if not os.path.isfile(_lib.LIB_PATH):
+        from sglang_b200 import build
+        build.build()
+    return _lib.lib()
+
+
+def test_every_declared_symbol_is_exported(lib):
+    names = _declared()
+    assert len(names) >= 14, names
+    missing = [n for n in names if not hasattr(lib, n)]
+    assert not missing, missing
+
+
+def test_python_binding_lists_the_header(lib):
+    from sglang_b200 import _lib
+    bound = set(_lib.exported_symbols())
+    assert set(_declared()) <= bound, sorted(set(_declared()) - bound)
+
+
+def test_error_strings(lib):
+    assert lib.b200_strerror(0) == b"ok"
+    for code in range(-10, 0):
+        assert lib.b200_strerror(code) not in (b"", b"unknown error code")
+    assert lib.b200_strerror(-99) == b"unknown error code"
+    assert lib.b200_abi_version() >= 1
+
+
+def test_argument_checks_return_before_any_device_work(lib):
+    P = ctypes.c_void_p
+    one = P(16)     # an aligned, never dereferenced pointer value
+    # quant: K not a multiple of the group, unsupported group, bad dtype, null pointers, misaligned
+    q = lib.b200_per_token_group_quant_fp8
+    assert q(one, 2, one, one, 4, 100, 128, 1, 1, 1e-10, -448.0, 448.0, None) == -3
+    assert q(one, 2, one, one, 4, 192, 96, 2, 1, 1e-10, -448.0, 448.0, None) == -6
+    assert q(one, 7, one, one, 4, 256, 128, 2, 1, 1e-10, -448.0, 448.0, None) == -2
+    assert q(None, 2, one, one, 4, 256, 128, 2, 1, 1e-10, -448.0, 448.0, None) == -1
+    assert q(P(8), 2, one, one, 4, 256, 128, 2, 1, 1e-10, -448.0, 448.0, None) == -5
+    assert q(one, 2, one, one, 0, 256, 128, 2, 1, 1e-10, -448.0, 448.0, None) == 0       # M == 0: no-op
+    # GEMM: shapes, strides, alignment, dtype
+    mm = lib.b200_fp8_blockwise_scaled_mm
+    assert mm(one, 256, one, 256, one, 1, 4, one, 2, 1, one, 128, 2, -1, 128, 256, None) == -3
+    assert mm(one, 256, one, 256, one, 1, 4, one, 2, 1, one, 128, 2, 0, 128, 256, None) == 0        # M == 0
+    assert mm(None, 256, one, 256, one, 1, 4, one, 2, 1, one, 128, 2, 4, 128, 256, None) == -1
+    assert mm(one, 256, one, 256, one, 1, 4, one, 2, 1, one, 128, 9, 4, 128, 256, None) == -2
+    assert mm(one, 200, one, 256, one, 1, 4, one, 2, 1, one, 128, 2, 4, 128, 256, None) == -4      # lda < K
+    assert mm(one, 264, one, 256, one, 1, 4, one, 2, 1, one, 128, 2, 4, 128, 256, None) == -5      # lda % 16
+    # MoE glue
+    assert lib.b200_shuffle_rows(None, one, one, 4, 64, None) == -1
+    assert lib.b200_shuffle_rows(one, one, one, 0, 64, None) == 0
+    assert lib.b200_silu_and_mul(one, one, 4, 12, 2, None) == -5                                   # d % 8
+    assert lib.b200_apply_shuffle_mul_sum(one, one, one, None, 4, 0, 64, 2, None) == -3            # topk <= 0
+    assert lib.b200_moe_prepare(one, 4, 2, 0, 8, 8, one, None, one, one, one, one, one, 64, None) == -3
+    assert lib.b200_moe_prepare_scratch_bytes(32768, 256) == 16 * 256 * 4
+    assert lib.b200_moe_prepare_noalloc(one, 2048 * 2048, 1, 64, 8, 8, one, None, one, one, one, one, None) == -9
+
+
+def test_missing_library_fails_loudly(monkeypatch):
+    from sglang_b200 import _lib
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", "/nonexistent/libb200_block_fp8.so")
+    with pytest.raises(ImportError, match="no fallback"):
+        _lib.lib()

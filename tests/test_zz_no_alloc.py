@@ -56,6 +56,6 @@ def test_noalloc_rejects_sizes_beyond_its_table():
     from sglang_b200 import _lib
     L = _lib.lib()
     # 2048 chunks x 64 experts = 131072 table entries > 65536: refused on the host, nothing is launched
-    rc = L.b200_moe_prepare_noalloc(1, 2048 * 2048, 1, 64, 8, 8, 1, None, 1, 1, 1, 1, None)
+    rc = L.b200_moe_prepare_noalloc(16, 2048 * 2048, 1, 64, 8, 8, 16, None, 16, 16, 16, 16, None)
     assert rc == -9
     assert b"exceeds" in L.b200_strerror(rc)
