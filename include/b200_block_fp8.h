@@ -106,6 +106,31 @@ int b200_fp8_blockwise_scaled_mm(const void* a, int64_t lda, const void* b, int6
                                  int64_t M, int64_t N, int64_t K, void* stream);
 
 /*
+ * The same product for small M (M <= 128), with the k-blocks of each output tile divided among
+ * `split_k` CTAs so that the weight matrix streams through every SM even when the output has only a
+ * few tiles (decode-size batches of the DeepSeek-V3 down projection: 28 tiles on 148 SMs).  Each CTA
+ * writes fp32 partial sums to workspace[split][M][N]; a second kernel adds them in split order and
+ * converts, so results are deterministic.  The fp32 sum over k-blocks is grouped differently from the
+ * unsplit kernel, so the two agree to rounding (same parity tolerance), not bit for bit.
+ *   split_k  0 = chosen by the library (falls back to 1 when the workspace is missing or too small);
+ *            1 = identical to b200_fp8_blockwise_scaled_mm; 2..64 = forced (needs N % 4 == 0,
+ *            split_k <= ceil(K/128))
+ *   workspace  device memory, 16-byte aligned, at least split_k * M * N * 4 bytes; never allocated here
+ * b200_fp8_blockwise_scaled_mm_splitk_plan reports the split the library would choose for a shape on
+ * a GPU with `sm_count` SMs (<= 0: 148) and the workspace that needs; it touches no device.
+ * No counterpart in the reference (its CUTLASS kernel has no split-K form; the Triton kernel at
+ * python/sglang/srt/layers/quantization/fp8_kernel.py:849-966 covers small M with smaller tiles).
+ */
+int b200_fp8_blockwise_scaled_mm_splitk(const void* a, int64_t lda, const void* b, int64_t ldb,
+                                        const float* sa, int64_t sa_stride_m, int64_t sa_stride_g,
+                                        const float* sb, int64_t sb_stride_n, int64_t sb_stride_g,
+                                        void* out, int64_t ldo, int out_dtype,
+                                        int64_t M, int64_t N, int64_t K,
+                                        int split_k, void* workspace, size_t workspace_bytes, void* stream);
+int b200_fp8_blockwise_scaled_mm_splitk_plan(int64_t M, int64_t N, int64_t K, int sm_count,
+                                             int* split_k, size_t* workspace_bytes);
+
+/*
  * Grouped (per-expert) block-scaled FP8 GEMM: for every expert e,
  *   out[off_e : off_e + m_e, :] = blockscaled( a[off_e : off_e + m_e, :], b[e] )   (same math as above)
  * with off_e = expert_offsets[e], m_e = problem_sizes[3*e] read ON THE DEVICE (no host sync).

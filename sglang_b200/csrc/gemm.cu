@@ -34,7 +34,7 @@ constexpr int kGroupM = 32;     // m-blocks per rasterisation group: the group's
 constexpr int kScaleGroup = 4;   // k-blocks per scale-ring slot
 constexpr int kScaleSlots = 4;   // slots in the ring (the stager runs up to 16 k-blocks ahead)
 
-template <int BLOCK_N, int EPI_WARPS, int ISSUERS = 1>
+template <int BLOCK_N, int EPI_WARPS>
 struct Cfg {
   static constexpr int kStages = BLOCK_N == 256 ? 4 : 6;
   static constexpr int kABytes = BLOCK_M * BLOCK_K;
@@ -47,7 +47,6 @@ struct Cfg {
   static constexpr int kTmaWarp = EPI_WARPS;
   static constexpr int kMmaWarp = EPI_WARPS + 1;
   static constexpr int kStagerWarp = EPI_WARPS + 2;             // stages the scale products in shared memory
-  static constexpr int kMmaWarpB = EPI_WARPS + 3;               // second MMA-issuing warp when ISSUERS == 2 (else idle)
   static constexpr int kThreads = 32 * (4 + EPI_WARPS);
   // With 16 epilogue warps the launch gives every thread 96 registers (20 warps); the helper
   // warpgroup hands 32 per thread back and the epilogue warps take 8 more each, enough to hold 64
@@ -118,11 +117,11 @@ __device__ __forceinline__ TileInfo get_tile(int tile, const GemmParams& p, int 
   return t;
 }
 
-template <int BLOCK_N, int EPI_WARPS, int CHUNK, int ISSUERS, bool GROUPED, typename OutT>
-__global__ void __launch_bounds__(Cfg<BLOCK_N, EPI_WARPS, ISSUERS>::kThreads, 1)
+template <int BLOCK_N, int EPI_WARPS, int CHUNK, bool GROUPED, typename OutT>
+__global__ void __launch_bounds__(Cfg<BLOCK_N, EPI_WARPS>::kThreads, 1)
 gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                       const GemmParams p) {
-  using C = Cfg<BLOCK_N, EPI_WARPS, ISSUERS>;
+  using C = Cfg<BLOCK_N, EPI_WARPS>;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: the 128-byte swizzle pattern is a function of address bits [4,10).
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -185,6 +184,10 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
   const int num_tiles = GROUPED ? tile_m_start[p.num_experts] * n_blocks : m_blocks * n_blocks;
+  // split-K: each tile becomes split_k virtual tiles (split fastest), each covering kbps k-blocks
+  const int split_k = GROUPED ? 1 : p.split_k;
+  const int kbps = GROUPED ? nkb : p.kb_per_split;
+  const int num_vtiles = num_tiles * split_k;
 
   if (warp >= EPI_WARPS) {
   // ====================================================================== helper warpgroup
@@ -194,9 +197,11 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-      const TileInfo t = get_tile<GROUPED, BLOCK_N>(tile, p, m_blocks, n_blocks, tile_m_start);
-      for (int kb = 0; kb < nkb; ++kb) {
+    for (int vt = blockIdx.x; ok && vt < num_vtiles; vt += gridDim.x) {
+      const TileInfo t = get_tile<GROUPED, BLOCK_N>(vt / split_k, p, m_blocks, n_blocks, tile_m_start);
+      const int split = vt % split_k;
+      const int kb_begin = split * kbps, kb_end = min(nkb, kb_begin + kbps);
+      for (int kb = kb_begin; kb < kb_end; ++kb) {
         ok = mbar_wait_warp(&done_bar[stage], phase ^ 1u, p.status, 1);
         if (!ok) break;
         if (elect_one()) {
@@ -209,46 +214,41 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       }
     }
     __syncwarp();
-  } else if (warp == C::kMmaWarp || (ISSUERS == 2 && warp == C::kMmaWarpB)) {
-    // ------------------------------------------------------------------ MMA issuer(s)
-    // With ISSUERS == 2 (experimental), warp 1 takes the even k-blocks of this CTA's k-block
-    // sequence and the second warp the odd ones; k-blocks are independent (own stage, own
-    // accumulator buffer), so the two issue streams may interleave freely.
+  } else if (warp == C::kMmaWarp) {
+    // ------------------------------------------------------------------ MMA issuer
+    // The whole warp walks the loop so that addresses and descriptors stay warp-uniform; one
+    // elected lane issues.  Issuing one k-block (4 MMAs + commit) occupies the thread ~320 cycles.
     constexpr uint32_t idesc = umma_idesc_e4m3(BLOCK_M, BLOCK_N);
     const uint64_t a_desc0 = umma_desc_k128(smem_u32(smem_a));
     const uint64_t b_desc0 = umma_desc_k128(smem_u32(smem_b));
-    const int first = (warp == C::kMmaWarp) ? 0 : 1;
-    const int my_tiles = (num_tiles > static_cast<int>(blockIdx.x))
-                             ? (num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
-                                   static_cast<int>(gridDim.x)
-                             : 0;
-    const long long total_kb = static_cast<long long>(my_tiles) * nkb;
-    int stage = first % C::kStages, acc = first % C::kNumAcc;
+    int stage = 0, acc = 0;
     uint32_t phase = 0, acc_phase = 0;
     bool ok = true;
-    for (long long g = first; ok && g < total_kb; g += ISSUERS) {
-      ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1u, p.status, 2);
-      if (ok) ok = mbar_wait(&full_bar[stage], phase, p.status, 3);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-      const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(stage * (C::kABytes >> 4));
-      const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(stage * (C::kBBytes >> 4));
-      const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BLOCK_N);
-      if (elect_one()) {
+    for (int vt = blockIdx.x; ok && vt < num_vtiles; vt += gridDim.x) {
+      const int split = vt % split_k;
+      const int kb_begin = split * kbps, kb_end = min(nkb, kb_begin + kbps);
+      for (int kb = kb_begin; kb < kb_end; ++kb) {
+        ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1u, p.status, 2);
+        if (ok) ok = mbar_wait(&full_bar[stage], phase, p.status, 3);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(stage * (C::kABytes >> 4));
+        const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(stage * (C::kBBytes >> 4));
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BLOCK_N);
+        if (elect_one()) {
 #pragma unroll
-        for (int k = 0; k < BLOCK_K / 32; ++k) {
-          // advance 32 bytes along K inside the 128-byte swizzle row: +2 in the (addr >> 4) field
-          umma_f8(d_tmem, a_desc + static_cast<uint64_t>(2 * k), b_desc + static_cast<uint64_t>(2 * k), idesc,
-                  k > 0 ? 1u : 0u);
+          for (int k = 0; k < BLOCK_K / 32; ++k) {
+            // advance 32 bytes along K inside the 128-byte swizzle row: +2 in the (addr >> 4) field
+            umma_f8(d_tmem, a_desc + static_cast<uint64_t>(2 * k), b_desc + static_cast<uint64_t>(2 * k), idesc,
+                    k > 0 ? 1u : 0u);
+          }
+          umma_commit(&done_bar[stage]);  // stage reusable and partial sums readable once these MMAs finish
         }
-        umma_commit(&done_bar[stage]);  // stage reusable and partial sums readable once these MMAs finish
+        __syncwarp();
+        if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+        if (++acc == C::kNumAcc) { acc = 0; acc_phase ^= 1u; }
       }
-      __syncwarp();
-      stage += ISSUERS;
-      if (stage >= C::kStages) { stage -= C::kStages; phase ^= 1u; }
-      acc += ISSUERS;
-      if (acc >= C::kNumAcc) { acc -= C::kNumAcc; acc_phase ^= 1u; }
     }
     __syncwarp();
   } else if (warp == C::kStagerWarp) {
@@ -260,10 +260,12 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     int slot = 0;
     uint32_t sphase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-      const TileInfo t = get_tile<GROUPED, BLOCK_N>(tile, p, m_blocks, n_blocks, tile_m_start);
+    for (int vt = blockIdx.x; ok && vt < num_vtiles; vt += gridDim.x) {
+      const TileInfo t = get_tile<GROUPED, BLOCK_N>(vt / split_k, p, m_blocks, n_blocks, tile_m_start);
       const float* sb_base = p.sb + static_cast<int64_t>(t.expert) * p.sb_stride_e;
-      for (int kb0 = 0; kb0 < nkb; kb0 += kScaleGroup) {
+      const int split = vt % split_k;
+      const int kb_begin = split * kbps, kb_end = min(nkb, kb_begin + kbps);
+      for (int kb0 = kb_begin; kb0 < kb_end; kb0 += kScaleGroup) {
         ok = mbar_wait_warp(&scale_empty[slot], sphase ^ 1u, p.status, 5);
         if (!ok) break;
         float* dst = smem_scale + slot * C::kSlotFloats;
@@ -272,7 +274,7 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 #pragma unroll
         for (int j = 0; j < kScaleGroup; ++j) {
           const int kb = kb0 + j;
-          const bool kin = kb < nkb;
+          const bool kin = kb < kb_end;
 #pragma unroll
           for (int r = 0; r < 4; ++r) {
             const int rr = r * 32 + lane;
@@ -318,15 +320,17 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     int acc_i = 0, stage = 0, slot = 0;
     uint32_t phase = 0, sphase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-      const TileInfo t = get_tile<GROUPED, BLOCK_N>(tile, p, m_blocks, n_blocks, tile_m_start);
+    for (int vt = blockIdx.x; ok && vt < num_vtiles; vt += gridDim.x) {
+      const TileInfo t = get_tile<GROUPED, BLOCK_N>(vt / split_k, p, m_blocks, n_blocks, tile_m_start);
+      const int split = vt % split_k;
+      const int kb_begin = split * kbps, kb_end = min(nkb, kb_begin + kbps);
       const int row_in_tile = quad * 32 + lane;
       const int m = t.row0 + row_in_tile;
       const int n0 = t.n_blk * BLOCK_N + part * CPW;
       float acc[CPW];
 #pragma unroll
       for (int c = 0; c < CPW; ++c) acc[c] = 0.f;
-      for (int kb0 = 0; ok && kb0 < nkb; kb0 += kScaleGroup) {
+      for (int kb0 = kb_begin; ok && kb0 < kb_end; kb0 += kScaleGroup) {
         // the four scale products of this group, then the slot goes straight back to the stager
         ok = mbar_wait(&scale_full[slot], sphase, p.status, 6);
         if (!ok) break;
@@ -340,7 +344,7 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 #pragma unroll
         for (int j = 0; j < kScaleGroup; ++j) {
           const int kb = kb0 + j;
-          if (kb < nkb) {
+          if (kb < kb_end) {
             ok = mbar_wait(&done_bar[stage], phase, p.status, 4);
             if (!ok) break;
             tc_fence_after();
@@ -377,7 +381,12 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         }
       }
       if (ok && row_in_tile < t.valid_rows && n0 < p.N) {
-        store_row<CPW>(out + static_cast<int64_t>(m) * p.ldo + n0, acc, p.N - n0, vec_ok);
+        if (split_k > 1) {
+          float* dst = p.partial + (static_cast<int64_t>(split) * p.M + m) * p.N + n0;
+          store_row<CPW>(dst, acc, p.N - n0, (p.N % 4) == 0);
+        } else {
+          store_row<CPW>(out + static_cast<int64_t>(m) * p.ldo + n0, acc, p.N - n0, vec_ok);
+        }
       }
     }
   }
@@ -395,11 +404,44 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   }
 }
 
+// Sum of the split-K partial results, added in split order (so the result does not depend on which
+// CTA finished first), converted to the output type.  One thread per four consecutive columns.
+template <typename OutT>
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial, OutT* __restrict__ out,
+                                                            int M, int N, int64_t ldo, int split_k) {
+  const int n4 = N >> 2;
+  const int64_t total = static_cast<int64_t>(M) * n4;
+  const int64_t plane = static_cast<int64_t>(M) * N;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int m = static_cast<int>(i / n4), c = static_cast<int>(i % n4) * 4;
+    const float* src = partial + static_cast<int64_t>(m) * N + c;
+    float4 acc = __ldcs(reinterpret_cast<const float4*>(src));
+    for (int s = 1; s < split_k; ++s) {
+      const float4 v = __ldcs(reinterpret_cast<const float4*>(src + s * plane));
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    OutT* dst = out + static_cast<int64_t>(m) * ldo + c;
+    dst[0] = cvt1(dst, acc.x); dst[1] = cvt1(dst, acc.y); dst[2] = cvt1(dst, acc.z); dst[3] = cvt1(dst, acc.w);
+  }
+}
+
+template <typename OutT>
+int launch_reduce(const GemmParams& p, cudaStream_t stream) {
+  const int64_t total = static_cast<int64_t>(p.M) * (p.N >> 2);
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > 4 * sm_count()) blocks = 4 * sm_count();
+  splitk_reduce_kernel<OutT><<<static_cast<int>(blocks), 256, 0, stream>>>(p.partial, static_cast<OutT*>(p.out), p.M, p.N,
+                                                                         p.ldo, p.split_k);
+  B200_CUDA_TRY(cudaGetLastError());
+  return B200_OK;
+}
+
 // ------------------------------------------------------------------------------------ host
-template <int BLOCK_N, int EPI_WARPS, int CHUNK, int ISSUERS, bool GROUPED, typename OutT>
+template <int BLOCK_N, int EPI_WARPS, int CHUNK, bool GROUPED, typename OutT>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t stream) {
-  using C = Cfg<BLOCK_N, EPI_WARPS, ISSUERS>;
-  auto kern = gemm_block_fp8_kernel<BLOCK_N, EPI_WARPS, CHUNK, ISSUERS, GROUPED, OutT>;
+  using C = Cfg<BLOCK_N, EPI_WARPS>;
+  auto kern = gemm_block_fp8_kernel<BLOCK_N, EPI_WARPS, CHUNK, GROUPED, OutT>;
   static bool attr_set[64] = {false};
   int dev = 0;
   B200_CUDA_TRY(cudaGetDevice(&dev));
@@ -411,19 +453,19 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cu
   const int n_blocks = (p.N + BLOCK_N - 1) / BLOCK_N;
   // grouped: the tile count lives on the device; m-tiles <= ceil(rows/128) + experts bounds the grid
   const long long tiles = GROUPED ? static_cast<long long>(m_blocks + p.num_experts) * n_blocks
-                                  : static_cast<long long>(m_blocks) * n_blocks;
+                                  : static_cast<long long>(m_blocks) * n_blocks * p.split_k;
   const int grid = tiles < sm_count() ? static_cast<int>(tiles) : sm_count();
   kern<<<grid, C::kThreads, C::kSmemBytes, stream>>>(ma, mb, p);
   B200_CUDA_TRY(cudaGetLastError());
   return B200_OK;
 }
 
-template <int BLOCK_N, int EPI_WARPS, int CHUNK, int ISSUERS = 1, bool GROUPED = false>
+template <int BLOCK_N, int EPI_WARPS, int CHUNK, bool GROUPED = false>
 int launch_dtype(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t stream) {
   switch (p.out_dtype) {
-    case B200_DT_BF16: return launch<BLOCK_N, EPI_WARPS, CHUNK, ISSUERS, GROUPED, __nv_bfloat16>(ma, mb, p, stream);
-    case B200_DT_F16: return launch<BLOCK_N, EPI_WARPS, CHUNK, ISSUERS, GROUPED, __half>(ma, mb, p, stream);
-    case B200_DT_F32: return launch<BLOCK_N, EPI_WARPS, CHUNK, ISSUERS, GROUPED, float>(ma, mb, p, stream);
+    case B200_DT_BF16: return launch<BLOCK_N, EPI_WARPS, CHUNK, GROUPED, __nv_bfloat16>(ma, mb, p, stream);
+    case B200_DT_F16: return launch<BLOCK_N, EPI_WARPS, CHUNK, GROUPED, __half>(ma, mb, p, stream);
+    case B200_DT_F32: return launch<BLOCK_N, EPI_WARPS, CHUNK, GROUPED, float>(ma, mb, p, stream);
     default: return B200_ERR_BAD_DTYPE;
   }
 }
@@ -437,10 +479,6 @@ int launch_variant(int id, const CUtensorMap& ma, const CUtensorMap& mb, const G
     case 1004: return launch_dtype<256, 16, 32>(ma, mb, p, st);
     case 1005: return launch_dtype<256, 16, 16>(ma, mb, p, st);
     case 1006: return launch_dtype<256, 8, 32>(ma, mb, p, st);
-    case 1007: return launch_dtype<128, 8, 64, 2>(ma, mb, p, st);
-    case 1010: return launch_dtype<128, 8, 32, 2>(ma, mb, p, st);
-    case 1008: return launch_dtype<128, 16, 32, 2>(ma, mb, p, st);
-    case 1009: return launch_dtype<256, 16, 32, 2>(ma, mb, p, st);
     default: return B200_ERR_UNSUPPORTED;
   }
 }
@@ -460,11 +498,28 @@ int launch_gemm_pair(const void* a, int64_t lda, const void* b, int64_t ldb, con
 
 }  // namespace b200
 
-extern "C" int b200_fp8_blockwise_scaled_mm(const void* a, int64_t lda, const void* b, int64_t ldb, const float* sa,
-                                            int64_t sa_stride_m, int64_t sa_stride_g, const float* sb,
-                                            int64_t sb_stride_n, int64_t sb_stride_g, void* out, int64_t ldo,
-                                            int out_dtype, int64_t M, int64_t N, int64_t K, void* stream) {
-  using namespace b200;
+namespace b200 {
+namespace {
+
+// Split count for small M: when the output has fewer 128x256 tiles than half the SMs, the k-blocks
+// of each tile are spread over several CTAs so that the weights stream through all SMs at once.
+int plan_split_k(int64_t M, int64_t N, int64_t K, int sms) {
+  if (M > BLOCK_M || (N % 4) != 0) return 1;
+  const int64_t tiles = (N + 255) / 256;
+  const int64_t nkb = (K + BLOCK_K - 1) / BLOCK_K;
+  // measured on DeepSeek-V3 shapes: below 32 k-blocks the launch and pipeline ramp dominate and the
+  // extra reduce kernel costs more than the idle SMs
+  if (tiles * 2 > sms || nkb < 32) return 1;
+  int64_t s = sms / tiles;
+  if (s > nkb / 8) s = nkb / 8;  // at least eight k-blocks per CTA
+  if (s > 16) s = 16;
+  return s < 2 ? 1 : static_cast<int>(s);
+}
+
+int dense_mm(const void* a, int64_t lda, const void* b, int64_t ldb, const float* sa, int64_t sa_stride_m,
+             int64_t sa_stride_g, const float* sb, int64_t sb_stride_n, int64_t sb_stride_g, void* out, int64_t ldo,
+             int out_dtype, int64_t M, int64_t N, int64_t K, int split_k, void* workspace, size_t workspace_bytes,
+             void* stream) {
   if (M < 0 || N < 0 || K <= 0) return B200_ERR_BAD_SHAPE;
   if (M == 0 || N == 0) return B200_OK;
   if (M > 0x7fffff00LL || N > 0x7fffff00LL || K > 0x7fffff00LL) return B200_ERR_TOO_LARGE;
@@ -473,8 +528,23 @@ extern "C" int b200_fp8_blockwise_scaled_mm(const void* a, int64_t lda, const vo
   if (lda < K || ldb < K || ldo < N) return B200_ERR_BAD_STRIDE;
   if ((lda % 16) != 0 || (ldb % 16) != 0 || !aligned16(a) || !aligned16(b)) return B200_ERR_MISALIGNED;
   if (sa_stride_m < 0 || sa_stride_g < 0 || sb_stride_n < 0 || sb_stride_g < 0) return B200_ERR_BAD_STRIDE;
+  const int nkb = static_cast<int>((K + BLOCK_K - 1) / BLOCK_K);
+  if (split_k < 0 || split_k > 64) return B200_ERR_BAD_SHAPE;
+  if (split_k > 1) {
+    if ((N % 4) != 0 || split_k > nkb) return B200_ERR_BAD_SHAPE;
+    if (!workspace) return B200_ERR_NULL_PTR;
+    if (!aligned16(workspace)) return B200_ERR_MISALIGNED;
+    if (workspace_bytes < static_cast<size_t>(split_k) * M * N * sizeof(float)) return B200_ERR_TOO_LARGE;
+  }
   int rc = require_sm100();
   if (rc != B200_OK) return rc;
+  if (split_k == 0) {
+    // automatic: split only when the caller gave room for it
+    split_k = plan_split_k(M, N, K, sm_count());
+    if (split_k > 1 && (!workspace || !aligned16(workspace) ||
+                        workspace_bytes < static_cast<size_t>(split_k) * M * N * sizeof(float)))
+      split_k = 1;
+  }
 
   GemmParams p;
   p.sa = sa; p.sb = sb; p.out = out;
@@ -485,29 +555,71 @@ extern "C" int b200_fp8_blockwise_scaled_mm(const void* a, int64_t lda, const vo
   p.out_dtype = out_dtype;
   p.status = gemm_status_ptr();
   p.expert_offsets = nullptr; p.problem_sizes = nullptr; p.sb_stride_e = 0; p.num_experts = 0;
+  p.split_k = split_k < 1 ? 1 : split_k;
+  p.kb_per_split = (nkb + p.split_k - 1) / p.split_k;
+  // every split must own at least one k-block (an empty one would store zeros, which is still right,
+  // but the count is trimmed so that no CTA is launched for nothing)
+  p.split_k = (nkb + p.kb_per_split - 1) / p.kb_per_split;
+  p.partial = static_cast<float*>(workspace);
   p.debug_mode = g_gemm_debug_mode;
   p.debug_buf = g_gemm_debug_buf;
   p.wait_hint_ns = static_cast<uint32_t>(g_gemm_wait_hint_ns);
   if (!p.status) return B200_ERR_CUDA;
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // One CTA per tile: 128 x 256 when that still gives every SM a tile, else 128 x 128.  (The CTA-pair
+  // One CTA per tile: 128 x 256 when that fills at least three quarters of the SMs in one wave (two
+  // waves of half-size tiles take as long), else 128 x 128.  (The CTA-pair
   // kernel in gemm_2cta.cu is correct but measured slower; it runs only when forced.)
-  if (g_force_block_n == 2) return launch_gemm_pair(a, lda, b, ldb, p, st);
+  if (g_force_block_n == 2 && p.split_k == 1) return launch_gemm_pair(a, lda, b, ldb, p, st);
   const int64_t m_blocks = (M + BLOCK_M - 1) / BLOCK_M;
   int block_n = 256;
-  if (m_blocks * ((N + 255) / 256) < sm_count()) block_n = 128;
+  if (p.split_k == 1 && 4 * m_blocks * ((N + 255) / 256) < 3 * sm_count()) block_n = 128;
   if (g_force_block_n == 128 || g_force_block_n == 256) block_n = g_force_block_n;
-  if (g_force_block_n >= 1000)
-    block_n = (g_force_block_n <= 1003 || g_force_block_n == 1007 || g_force_block_n == 1008 || g_force_block_n == 1010) ? 128 : 256;
+  if (g_force_block_n >= 1000) block_n = g_force_block_n <= 1003 ? 128 : 256;
 
   CUtensorMap ma, mb;
   rc = make_map_u8_2d(&ma, a, M, K, lda, BLOCK_M);
   if (rc != B200_OK) return rc;
   rc = make_map_u8_2d(&mb, b, N, K, ldb, block_n);
   if (rc != B200_OK) return rc;
-  if (g_force_block_n >= 1000) return launch_variant(g_force_block_n, ma, mb, p, st);
-  return block_n == 256 ? launch_dtype<256, 16, 32>(ma, mb, p, st) : launch_dtype<128, 8, 64>(ma, mb, p, st);
+  if (g_force_block_n >= 1000) rc = launch_variant(g_force_block_n, ma, mb, p, st);
+  else rc = block_n == 256 ? launch_dtype<256, 16, 32>(ma, mb, p, st) : launch_dtype<128, 8, 64>(ma, mb, p, st);
+  if (rc != B200_OK || p.split_k == 1) return rc;
+  switch (out_dtype) {
+    case B200_DT_BF16: return launch_reduce<__nv_bfloat16>(p, st);
+    case B200_DT_F16: return launch_reduce<__half>(p, st);
+    default: return launch_reduce<float>(p, st);
+  }
+}
+
+}  // namespace
+}  // namespace b200
+
+extern "C" int b200_fp8_blockwise_scaled_mm(const void* a, int64_t lda, const void* b, int64_t ldb, const float* sa,
+                                            int64_t sa_stride_m, int64_t sa_stride_g, const float* sb,
+                                            int64_t sb_stride_n, int64_t sb_stride_g, void* out, int64_t ldo,
+                                            int out_dtype, int64_t M, int64_t N, int64_t K, void* stream) {
+  return b200::dense_mm(a, lda, b, ldb, sa, sa_stride_m, sa_stride_g, sb, sb_stride_n, sb_stride_g, out, ldo, out_dtype,
+                        M, N, K, 1, nullptr, 0, stream);
+}
+
+extern "C" int b200_fp8_blockwise_scaled_mm_splitk(const void* a, int64_t lda, const void* b, int64_t ldb,
+                                                   const float* sa, int64_t sa_stride_m, int64_t sa_stride_g,
+                                                   const float* sb, int64_t sb_stride_n, int64_t sb_stride_g, void* out,
+                                                   int64_t ldo, int out_dtype, int64_t M, int64_t N, int64_t K,
+                                                   int split_k, void* workspace, size_t workspace_bytes, void* stream) {
+  return b200::dense_mm(a, lda, b, ldb, sa, sa_stride_m, sa_stride_g, sb, sb_stride_n, sb_stride_g, out, ldo, out_dtype,
+                        M, N, K, split_k, workspace, workspace_bytes, stream);
+}
+
+extern "C" int b200_fp8_blockwise_scaled_mm_splitk_plan(int64_t M, int64_t N, int64_t K, int sm_count, int* split_k,
+                                                        size_t* workspace_bytes) {
+  if (M < 0 || N < 0 || K <= 0) return B200_ERR_BAD_SHAPE;
+  if (!split_k || !workspace_bytes) return B200_ERR_NULL_PTR;
+  const int s = (M == 0 || N == 0) ? 1 : b200::plan_split_k(M, N, K, sm_count > 0 ? sm_count : 148);
+  *split_k = s;
+  *workspace_bytes = s > 1 ? static_cast<size_t>(s) * M * N * sizeof(float) : 0;
+  return B200_OK;
 }
 
 extern "C" int b200_fp8_blockwise_scaled_grouped_mm(const void* a, int64_t lda, const void* b, int64_t ldb,
@@ -520,7 +632,7 @@ extern "C" int b200_fp8_blockwise_scaled_grouped_mm(const void* a, int64_t lda, 
   using namespace b200;
   if (total_rows < 0 || N < 0 || K <= 0 || num_experts <= 0) return B200_ERR_BAD_SHAPE;
   if (total_rows == 0 || N == 0) return B200_OK;
-  if (num_experts > Cfg<256, 16, 1>::kMaxExperts) return B200_ERR_TOO_LARGE;
+  if (num_experts > Cfg<256, 16>::kMaxExperts) return B200_ERR_TOO_LARGE;
   if (total_rows > 0x7fffff00LL || K > 0x7fffff00LL || N * num_experts > 0x7fffff00LL) return B200_ERR_TOO_LARGE;
   if (!a || !b || !sa || !sb || !out || !expert_offsets || !problem_sizes) return B200_ERR_NULL_PTR;
   if (out_dtype != B200_DT_BF16 && out_dtype != B200_DT_F16 && out_dtype != B200_DT_F32) return B200_ERR_BAD_DTYPE;
@@ -540,6 +652,7 @@ extern "C" int b200_fp8_blockwise_scaled_grouped_mm(const void* a, int64_t lda, 
   p.out_dtype = out_dtype;
   p.status = gemm_status_ptr();
   p.expert_offsets = expert_offsets; p.problem_sizes = problem_sizes; p.num_experts = num_experts;
+  p.split_k = 1; p.kb_per_split = 0; p.partial = nullptr;
   p.debug_mode = 0; p.debug_buf = nullptr; p.wait_hint_ns = 0;
   if (!p.status) return B200_ERR_CUDA;
 
@@ -552,8 +665,8 @@ extern "C" int b200_fp8_blockwise_scaled_grouped_mm(const void* a, int64_t lda, 
   rc = make_map_u8_2d(&mb, b, N * num_experts, K, ldb, block_n);
   if (rc != B200_OK) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  return block_n == 256 ? launch_dtype<256, 16, 32, 1, true>(ma, mb, p, st)
-                        : launch_dtype<128, 8, 64, 1, true>(ma, mb, p, st);
+  return block_n == 256 ? launch_dtype<256, 16, 32, true>(ma, mb, p, st)
+                        : launch_dtype<128, 8, 64, true>(ma, mb, p, st);
 }
 
 extern "C" int b200_debug_set_timing_buffer(void* device_buf_5x64_i64) {

@@ -19,6 +19,11 @@ struct GemmParams {
   const int32_t* problem_sizes;
   int64_t sb_stride_e;
   int num_experts;
+  // split-K form (dense, small M): the k-blocks of a tile are divided among split_k CTAs, each writing
+  // fp32 partial sums to partial[split][M][N]; a second kernel adds them in split order
+  int split_k;
+  int kb_per_split;
+  float* partial;
   uint32_t wait_hint_ns;  // suspend-time hint for mbarrier waits (0 = none)
   long long* debug_buf;  // timing experiments: clock64 samples [5][64] of pair 0's leader CTA, or null
   int debug_mode;  // timing experiments only (results are wrong when non-zero); 0 in normal use
@@ -45,6 +50,7 @@ __device__ __forceinline__ uint32_t pack2(__half*, float a, float b) {
 }
 __device__ __forceinline__ __nv_bfloat16 cvt1(__nv_bfloat16*, float a) { return __float2bfloat16_rn(a); }
 __device__ __forceinline__ __half cvt1(__half*, float a) { return __float2half_rn(a); }
+__device__ __forceinline__ float cvt1(float*, float a) { return a; }
 
 // Store NCOLS consecutive outputs of one row; `valid` = columns left before N.
 template <int NCOLS, typename OutT>

@@ -33,6 +33,37 @@ def _is_contiguous_vector(t: torch.Tensor) -> bool:
     return t.is_contiguous() and (t.dim() == 1 or (t.dim() == 2 and min(t.shape) == 1))
 
 
+_SM_COUNT: dict = {}
+_WORKSPACE: dict = {}
+# Split-K for decode-size batches: "auto" lets the library choose, "off" always runs the unsplit kernel.
+SPLIT_K_MODE = "auto"
+
+
+def _splitk_plan(M: int, N: int, K: int, device: torch.device):
+    """Split count and workspace bytes the library chooses for this shape (1, 0 = no split)."""
+    if M > 128 or SPLIT_K_MODE != "auto":
+        return 1, 0
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    sms = _SM_COUNT.get(idx)
+    if sms is None:
+        sms = _SM_COUNT[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    import ctypes
+    s, b = ctypes.c_int(1), ctypes.c_size_t(0)
+    _lib.check("fp8_blockwise_scaled_mm_splitk_plan",
+               _lib.lib().b200_fp8_blockwise_scaled_mm_splitk_plan(M, N, K, sms, ctypes.byref(s), ctypes.byref(b)))
+    return s.value, b.value
+
+
+def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Per-(device, stream) split-K workspace, grown on demand and reused: kernels on one stream run in
+    order, so consecutive calls may share it; a different stream gets its own."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    ws = _WORKSPACE.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = _WORKSPACE[key] = torch.empty(max(nbytes, 1 << 22), dtype=torch.uint8, device=device)
+    return ws
+
+
 def sgl_per_token_group_quant_fp8(
     input: torch.Tensor,
     output_q: torch.Tensor,
@@ -118,11 +149,18 @@ def fp8_blockwise_scaled_mm(
     _check(K % 128 == 0 and N % 128 == 0, "K and N must be multiples of 128 (block scale granularity)")
     if M == 0:
         return out
-    with torch.cuda.device(mat_a.device):
-        rc = _lib.lib().b200_fp8_blockwise_scaled_mm(
-            mat_a.data_ptr(), mat_a.stride(0), mat_b.data_ptr(), mat_b.stride(1),
+    args = (mat_a.data_ptr(), mat_a.stride(0), mat_b.data_ptr(), mat_b.stride(1),
             scales_a.data_ptr(), scales_a.stride(0), scales_a.stride(1),
             scales_b.data_ptr(), scales_b.stride(1), scales_b.stride(0),
-            out.data_ptr(), out.stride(0), _DT[out_dtype], M, N, K, _stream_ptr(mat_a.device))
+            out.data_ptr(), out.stride(0), _DT[out_dtype], M, N, K)
+    with torch.cuda.device(mat_a.device):
+        split_k, ws_bytes = _splitk_plan(M, N, K, mat_a.device)
+        if split_k > 1:
+            # decode-size batch on a narrow output: spread each tile's k-blocks over the idle SMs
+            ws = _workspace(mat_a.device, ws_bytes)
+            rc = _lib.lib().b200_fp8_blockwise_scaled_mm_splitk(*args, split_k, ws.data_ptr(), ws.numel(),
+                                                                _stream_ptr(mat_a.device))
+        else:
+            rc = _lib.lib().b200_fp8_blockwise_scaled_mm(*args, _stream_ptr(mat_a.device))
     _lib.check("fp8_blockwise_scaled_mm", rc)
     return out

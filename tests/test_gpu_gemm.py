@@ -68,13 +68,102 @@ def _assert_parity(a, b, sa, sb, force_block_n=0):
     return c32, cbf
 
 
+@pytest.fixture
+def no_split_k():
+    """Runs the unsplit kernel even for decode-size batches."""
+    from sglang_b200.sgl_kernel import gemm
+    gemm.SPLIT_K_MODE = "off"
+    yield
+    gemm.SPLIT_K_MODE = "auto"
+
+
 @pytest.mark.parametrize("block_n", [128, 256, 2])   # 2 = CTA-pair kernel
 @pytest.mark.parametrize("K", [128, 256, 512, 1024])
 @pytest.mark.parametrize("N", [128, 256, 512, 1152])
 @pytest.mark.parametrize("M", [1, 3, 5, 127, 128, 129, 512])
-def test_small_grid(M, N, K, block_n):
+def test_small_grid(M, N, K, block_n, no_split_k):
     a, b, sa, sb = _rand_problem(M, N, K, seed=M * 7 + N * 3 + K, scale_kind="uniform")
     _assert_parity(a, b, sa, sb, block_n)
+
+
+# ---------------------------------------------------------------------------- split-K (small M)
+def _run_splitk(a, b, sa, sb, out_dtype, split_k, ws_floats=None):
+    """Straight through the C ABI with a forced split count."""
+    from sglang_b200 import _lib
+    from sglang_b200.sgl_kernel.gemm import _DT
+    M, K = a.shape
+    N = b.shape[0]
+    ad, bd = a.cuda(), b.cuda()
+    sad, sbd = sa.cuda().contiguous(), sb.cuda().contiguous()
+    out = torch.full((M, N), float("nan"), dtype=out_dtype, device="cuda")
+    n_ws = split_k * M * N if ws_floats is None else ws_floats
+    ws = torch.full((max(n_ws, 4),), float("nan"), dtype=torch.float32, device="cuda")
+    rc = _lib.lib().b200_fp8_blockwise_scaled_mm_splitk(
+        ad.data_ptr(), K, bd.data_ptr(), K, sad.data_ptr(), sad.stride(0), sad.stride(1),
+        sbd.data_ptr(), sbd.stride(0), sbd.stride(1), out.data_ptr(), N, _DT[out_dtype], M, N, K,
+        split_k, ws.data_ptr(), n_ws * 4, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    return rc, out
+
+
+@pytest.mark.parametrize("block_n", [0, 128])
+@pytest.mark.parametrize("split_k", [2, 3, 5, 8])
+@pytest.mark.parametrize("M,N,K", [(1, 512, 1024), (16, 384, 1152), (128, 1152, 2048), (77, 256, 4096),
+                                   (5, 128, 1024)])
+def test_split_k_forced(M, N, K, split_k, block_n):
+    from sglang_b200 import _lib
+    a, b, sa, sb = _rand_problem(M, N, K, seed=M + N + K + split_k, scale_kind="uniform")
+    ref32 = O.block_fp8_matmul_fp32(a, b, sa, sb)
+    _lib.lib().b200_debug_force_block_n(block_n)
+    try:
+        rc32, c32 = _run_splitk(a, b, sa, sb, torch.float32, split_k)
+        rcbf, cbf = _run_splitk(a, b, sa, sb, torch.bfloat16, split_k)
+    finally:
+        _lib.lib().b200_debug_force_block_n(0)
+    assert rc32 == 0 and rcbf == 0
+    _status_ok()
+    assert O.rel_l2(c32.cpu(), ref32) <= TOL
+    assert O.rel_l2(cbf.cpu().float(), ref32.to(torch.bfloat16).float()) <= TOL
+
+
+def test_split_k_is_deterministic_and_matches_unsplit_to_rounding():
+    a, b, sa, sb = _rand_problem(32, 1024, 4096, seed=5)
+    _, c1 = _run_splitk(a, b, sa, sb, torch.float32, 1)
+    _, c4a = _run_splitk(a, b, sa, sb, torch.float32, 4)
+    _, c4b = _run_splitk(a, b, sa, sb, torch.float32, 4)
+    assert same_bits(c4a, c4b)
+    assert O.rel_l2(c4a.cpu(), c1.cpu()) <= 1e-6
+
+
+@pytest.mark.parametrize("M", [1, 16, 64, 128])
+@pytest.mark.parametrize("N,K", [(7168, 18432), (36864, 7168), (1536, 7168)])
+def test_split_k_auto_decode_shapes(M, N, K):
+    """DeepSeek-V3 down / gate_up / q_a projections at decode-size batches through the
+    reference-facing wrapper (which picks the split), against the oracle."""
+    import ctypes
+    from sglang_b200 import _lib
+    a, b, sa, sb = _rand_problem(M, N, K, seed=M + N)
+    ref32 = O.block_fp8_matmul_fp32(a, b, sa, sb)
+    cbf = _run_sgl(a, b, sa, sb).cpu()
+    _status_ok()
+    assert O.rel_l2(cbf.float(), ref32.to(torch.bfloat16).float()) <= TOL
+    s, nb = ctypes.c_int(0), ctypes.c_size_t(0)
+    assert _lib.lib().b200_fp8_blockwise_scaled_mm_splitk_plan(M, N, K, 148, ctypes.byref(s), ctypes.byref(nb)) == 0
+    assert (s.value > 1) == (N <= 148 * 128) and nb.value == (s.value * M * N * 4 if s.value > 1 else 0)
+
+
+def test_split_k_argument_errors():
+    from sglang_b200 import _lib
+    a, b, sa, sb = _rand_problem(8, 256, 1024, seed=1)
+    rc, _ = _run_splitk(a, b, sa, sb, torch.bfloat16, 4, ws_floats=4 * 8 * 256 - 1)   # workspace one float short
+    assert rc < 0
+    rc, _ = _run_splitk(a, b, sa, sb, torch.bfloat16, 9)                               # more splits than k-blocks
+    assert rc < 0
+    rc, _ = _run_splitk(a, b, sa, sb, torch.bfloat16, 65)
+    assert rc < 0
+    # automatic split with no room falls back to the unsplit kernel
+    rc, out = _run_splitk(a, b, sa, sb, torch.bfloat16, 0, ws_floats=0)
+    assert rc == 0 and bool(torch.isfinite(out.float()).all())
 
 
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float16])
