@@ -50,6 +50,21 @@ _IMPLS = {
     "silu_and_mul": _silu_and_mul_op,
 }
 
+
+
+def _mm_meta(mat_a, mat_b, scales_a, scales_b, out_dtype):
+    return mat_a.new_empty((mat_a.shape[0], mat_b.shape[1]), dtype=out_dtype)
+
+
+def _nothing_meta(*args):
+    return None
+
+
+# Shape functions for tracing (meta tensors / fake tensors): only the dense GEMM returns a tensor; the
+# other operators write into tensors the caller allocated.
+_META = {name: _nothing_meta for name in _SCHEMAS}
+_META["fp8_blockwise_scaled_mm"] = _mm_meta
+
 _library = None
 
 
@@ -65,6 +80,7 @@ def register_torch_ops() -> None:
         except RuntimeError:
             continue  # already defined elsewhere: leave that definition alone
         _library.impl(name, _IMPLS[name], "CUDA")
+        _library.impl(name, _META[name], "Meta")
 
 
 register_torch_ops()

@@ -100,3 +100,26 @@ def test_missing_library_fails_loudly(monkeypatch):
     monkeypatch.setattr(_lib, "LIB_PATH", "/nonexistent/libb200_block_fp8.so")
     with pytest.raises(ImportError, match="no fallback"):
         _lib.lib()
+
+
+def test_operator_schemas_and_shape_functions():
+    """torch.ops.sgl_kernel.* carry the reference's schemas (sgl-kernel/csrc/common_extension.cc:111-119,
+    192-207) and trace on meta tensors without a device."""
+    import torch
+    import sglang_b200.sgl_kernel  # noqa: F401  (registers the operators)
+    ops = torch.ops.sgl_kernel
+    schema = str(ops.fp8_blockwise_scaled_mm.default._schema)
+    assert "Tensor mat_a, Tensor mat_b, Tensor scales_a, Tensor scales_b, ScalarType out_dtype" in schema
+    assert "bool scale_ue8m0" in str(ops.sgl_per_token_group_quant_fp8.default._schema)
+    assert "Tensor? blockscale_offsets" in str(ops.prepare_moe_input.default._schema)
+    fp8 = torch.float8_e4m3fn
+    a = torch.empty(64, 7168, dtype=fp8, device="meta")
+    b = torch.empty(4096, 7168, dtype=fp8, device="meta").t()
+    sa = torch.empty(56, 64, device="meta").t()
+    sb = torch.empty(32, 56, device="meta").t()
+    out = ops.fp8_blockwise_scaled_mm(a, b, sa, sb, torch.bfloat16)
+    assert out.device.type == "meta" and out.shape == (64, 4096) and out.dtype == torch.bfloat16
+    x = torch.empty(64, 7168, dtype=torch.bfloat16, device="meta")
+    q = torch.empty(64, 7168, dtype=fp8, device="meta")
+    s = torch.empty(64, 56, device="meta")
+    assert ops.sgl_per_token_group_quant_fp8(x, q, s, 128, 1e-10, -448.0, 448.0, False) is None

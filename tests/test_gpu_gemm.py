@@ -303,3 +303,23 @@ def test_llama70b_tp_shard_shapes(N, K):
     split N, row-parallel shards split K; M = 128."""
     a, b, sa, sb = _rand_problem(128, N, K, seed=N + K)
     _assert_parity(a, b, sa, sb)
+
+
+def test_fp8_linear_method_apply():
+    """Fp8LinearMethod owning a merged column-parallel shard: create -> load -> apply vs the oracle linear."""
+    from sglang_b200.layers.quantization.fp8 import Fp8Config, Fp8LinearMethod
+    cfg = Fp8Config.from_config({"quant_method": "fp8", "activation_scheme": "dynamic", "weight_block_size": [128, 128]})
+    method = Fp8LinearMethod(cfg)
+    layer = torch.nn.Module()
+    method.create_weights(layer, 1024, [256, 256], 1024, 4096, torch.bfloat16, tp_size=8, device="cuda")
+    wq, ws = O.gen_weight(512, 1024, seed=3)
+    layer.weight.data.copy_(wq.cuda())
+    layer.weight_scale_inv.data.copy_(ws.cuda())
+    method.process_weights_after_loading(layer)
+    x = O.gen_activation(48, 1024, seed=4)
+    bias = torch.randn(512).to(torch.bfloat16)
+    out = method.apply(layer, x.cuda().view(3, 16, 1024), bias.cuda()).cpu()
+    ref = O.block_fp8_linear(x, wq, ws, bias=bias)
+    assert out.shape == (3, 16, 512) and out.dtype == torch.bfloat16
+    assert O.rel_l2(out.view(48, 512).float(), ref.float()) <= TOL
+    _status_ok()

@@ -182,3 +182,33 @@ def test_fused_silu_mul_quant_equals_two_kernels(M, K, dtype):
     assert same_bits(q, q_ref) and same_bits(s, s_ref)
     q2, s2 = silu_and_mul_per_token_group_quant_fp8(x, 128, column_major_scales=True, scale_tma_aligned=True)
     assert same_bits(q2, q_ref) and same_bits(s2.contiguous(), s_ref)
+
+
+def test_fp8_moe_method_apply():
+    """Fp8MoEMethod owning the expert weights ([E, 2I, H] / [E, H, I]): create -> load -> apply, equal to the
+    fused path called directly and within tolerance of the oracle; routed_scaling_factor is applied last."""
+    from sglang_b200.layers.moe.cutlass_moe import fused_experts_block_fp8
+    from sglang_b200.layers.quantization.fp8 import Fp8Config, Fp8MoEMethod
+    E, H, I, m, topk = 8, 512, 256, 64, 2
+    g = torch.Generator().manual_seed(9)
+    method = Fp8MoEMethod(Fp8Config.from_config(
+        {"quant_method": "fp8", "activation_scheme": "dynamic", "weight_block_size": [128, 128]}))
+    layer = torch.nn.Module()
+    method.create_weights(layer, E, H, I, torch.bfloat16, device="cuda")
+    w13q, w13s, w2q, w2s = [], [], [], []
+    for e in range(E):
+        q_, s_ = O.per_block_cast_to_fp8(torch.randn(2 * I, H, generator=g) * 0.05); w13q.append(q_); w13s.append(s_)
+        q_, s_ = O.per_block_cast_to_fp8(torch.randn(H, I, generator=g) * 0.05); w2q.append(q_); w2s.append(s_)
+    w13q, w13s, w2q, w2s = torch.stack(w13q), torch.stack(w13s), torch.stack(w2q), torch.stack(w2s)
+    layer.w13_weight.data.copy_(w13q.cuda()); layer.w2_weight.data.copy_(w2q.cuda())
+    layer.w13_weight_scale_inv.data.copy_(w13s.cuda()); layer.w2_weight_scale_inv.data.copy_(w2s.cuda())
+    a = torch.randn(m, H, generator=g).to(torch.bfloat16)
+    w, ids = O.fused_topk_native(torch.randn(m, E, generator=g), topk)
+    out = method.apply(layer, a.cuda(), (w.cuda(), ids.cuda(), None))
+    direct = fused_experts_block_fp8(a.cuda(), w13q.cuda(), w2q.cuda(), w13s.cuda(), w2s.cuda(), w.cuda(), ids.cuda())
+    assert same_bits(out, direct)
+    ref = O.cutlass_fused_experts_fp8(a, w13q, w2q, w13s, w2s, w, ids)
+    assert O.rel_l2(out.float().cpu(), ref.float()) <= 5e-3
+    scaled = method.apply(layer, a.cuda(), (w.cuda(), ids.cuda(), None), routed_scaling_factor=2.5)
+    assert same_bits(scaled, direct * 2.5)
+    _status_ok()
