@@ -396,7 +396,7 @@ def run_kernel_case(args):
             # DeepSeek-V3 MoE layer on one GPU: 256 experts, top-8, hidden 7168, intermediate 2048.
             # Codes and scales are drawn directly (11.3 GB of weights); parity is covered by the tests.
             from sglang_b200.layers.moe.cutlass_moe import fused_experts_block_fp8
-            E, H, I, topk = 256, 7168, 2048, 8
+            E, H, I, topk = args.experts, 7168, 2048, 8
             def codes(*shape):
                 c = torch.randint(0, 0x78, shape, generator=g, device=dev, dtype=torch.uint8)
                 sign = torch.randint(0, 2, shape, generator=g, device=dev, dtype=torch.uint8) << 7
@@ -453,7 +453,8 @@ def run_kernel_case(args):
         rec = {"kernel": args.kernel, "M": m, "us": sec * 1e6, "achieved": work / sec, "unit": unit,
                "frac_of_measured_peak": work / sec / peak}
         if args.kernel == "moe":
-            rec["weight_GBps_if_all_experts_read"] = 256 * (2 * 2048 * 7168 + 7168 * 2048) / sec / 1e9
+            rec["experts"] = args.experts
+            rec["weight_GBps_if_all_experts_read"] = args.experts * (2 * 2048 * 7168 + 7168 * 2048) / sec / 1e9
         print(json.dumps(rec))
 
 
@@ -462,6 +463,8 @@ def main():
     ap.add_argument("--kernel", default=None, choices=["gemm_gate_up", "gemm_down", "quant", "moe"],
                     help="time one kernel alone instead of the whole step")
     ap.add_argument("--m", default="4096", help="token count(s) for --kernel, comma separated")
+    ap.add_argument("--experts", type=int, default=256,
+                    help="--kernel moe: experts held on this GPU (256 = whole layer, 32 = one rank of 8)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)

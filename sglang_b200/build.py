@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import argparse
 import os
+import re
 import subprocess
 import sys
 from concurrent.futures import ThreadPoolExecutor
@@ -37,6 +38,31 @@ def _deps_mtime() -> float:
     return max(os.path.getmtime(h) for h in hdrs)
 
 
+# Kernels that move registers between warpgroups with setmaxnreg: the arithmetic in their Cfg structs
+# assumes the launch allocates exactly this many registers per thread.  If ptxas ever allocates fewer,
+# setmaxnreg.inc would wait for registers nobody releases, so the build refuses the object instead.
+_FIXED_REGS = [
+    (re.compile(r"gemm_block_fp8_kernelILi(128|256)ELi16E"), 96),
+    (re.compile(r"gemm_block_fp8_swapab_kernelILi128E"), 168),
+]
+
+
+def check_register_counts(ptxas_log: str) -> None:
+    name = None
+    for line in ptxas_log.splitlines():
+        m = re.search(r"Compiling entry function '([^']+)'", line)
+        if m:
+            name = m.group(1)
+            continue
+        m = re.search(r"Used (\d+) registers", line)
+        if m and name:
+            for pat, want in _FIXED_REGS:
+                if pat.search(name) and int(m.group(1)) != want:
+                    raise RuntimeError(f"{name}: ptxas allocated {m.group(1)} registers, the kernel's register "
+                                       f"rebalancing needs {want}")
+            name = None
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(OBJ, exist_ok=True)
     dep_t = _deps_mtime()
@@ -54,6 +80,11 @@ def build(force: bool = False, verbose: bool = False) -> str:
             f.write(r.stderr)
         if r.returncode != 0:
             raise RuntimeError(f"nvcc failed for {src}:\n{r.stderr}")
+        try:
+            check_register_counts(r.stderr)
+        except RuntimeError:
+            os.remove(obj)
+            raise
         if verbose:
             print(r.stderr)
         return obj

@@ -113,12 +113,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
   return true;
 }
 
-// The same wait for a whole converged warp; the outcome is made warp-uniform so that all lanes
-// leave their loop together when a wait gives up.
+// The same wait for a whole converged warp: lane 0 polls and the outcome is broadcast, so that all
+// lanes leave their loop together when a wait gives up.  (32 lanes polling one mbarrier are 32
+// operations on one shared-memory word; with several warps spinning, that traffic alone cost hundreds
+// of cycles per wait.)  The shuffle orders the other lanes' later accesses after lane 0's acquire.
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, int* status, int code,
                                                uint32_t hint_ns = 0) {
-  const bool ok = mbar_wait(bar, parity, status, code, hint_ns);
-  return __all_sync(0xffffffffu, ok);
+  bool ok = true;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, status, code, hint_ns);
+  return __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
 }
 
 // ---- TMA (tiled bulk tensor copy global -> shared, completion on an mbarrier; no multicast)
@@ -195,6 +198,36 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
         "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
+}
+// 16 lanes x (8 * X) consecutive fp32 columns in the accumulator-fragment layout: for column group g
+// (8 columns) thread t gets v[4g + 0..1] = lane (base_lane + t/4), columns 8g + 2(t%4) + 0..1 and
+// v[4g + 2..3] = lane (base_lane + 8 + t/4), same columns.  base_lane is a multiple of 16 inside the
+// warp's own lane quadrant.
+template <int X>
+__device__ __forceinline__ void tmem_ld_16x256b(uint32_t taddr, float* v);
+template <>
+__device__ __forceinline__ void tmem_ld_16x256b<2>(uint32_t taddr, float* v) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile("tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
+}
+template <>
+__device__ __forceinline__ void tmem_ld_16x256b<4>(uint32_t taddr, float* v) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile("tcgen05.ld.sync.aligned.16x256b.x4.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+               : "r"(taddr)
+               : "memory");
+}
+template <>
+__device__ __forceinline__ void tmem_ld_16x256b<8>(uint32_t taddr, float* v) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile("tcgen05.ld.sync.aligned.16x256b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+               : "r"(taddr)
+               : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 

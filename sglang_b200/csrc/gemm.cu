@@ -495,6 +495,14 @@ int g_gemm_wait_hint_ns = 0;
 long long* g_gemm_debug_buf = nullptr;
 
 int launch_gemm_pair(const void* a, int64_t lda, const void* b, int64_t ldb, const GemmParams& p, cudaStream_t stream);
+int launch_gemm_swapab(const void* a, int64_t lda, int64_t a_rows, const void* b, int64_t ldb, int64_t w_rows,
+                       const GemmParams& p, bool grouped, int token_tile, cudaStream_t stream);
+
+// g_force_block_n values that select the weight-streaming (swapped-operand) kernel: 3 = token tile
+// chosen from the shape, 3032 / 3064 / 3128 = that token tile; 4 = never use it.
+inline int forced_token_tile() {
+  return g_force_block_n == 3032 ? 32 : g_force_block_n == 3064 ? 64 : g_force_block_n == 3128 ? 128 : 0;
+}
 
 }  // namespace b200
 
@@ -571,6 +579,17 @@ int dense_mm(const void* a, int64_t lda, const void* b, int64_t ldb, const float
   // waves of half-size tiles take as long), else 128 x 128.  (The CTA-pair
   // kernel in gemm_2cta.cu is correct but measured slower; it runs only when forced.)
   if (g_force_block_n == 2 && p.split_k == 1) return launch_gemm_pair(a, lda, b, ldb, p, st);
+  if (g_force_block_n == 3 || forced_token_tile() != 0) {
+    int tt = forced_token_tile();
+    if (tt == 0) tt = M <= 32 ? 32 : (M <= 64 ? 64 : 128);
+    rc = launch_gemm_swapab(a, lda, M, b, ldb, N, p, false, tt, st);
+    if (rc != B200_OK || p.split_k == 1) return rc;
+    switch (out_dtype) {
+      case B200_DT_BF16: return launch_reduce<__nv_bfloat16>(p, st);
+      case B200_DT_F16: return launch_reduce<__half>(p, st);
+      default: return launch_reduce<float>(p, st);
+    }
+  }
   const int64_t m_blocks = (M + BLOCK_M - 1) / BLOCK_M;
   int block_n = 256;
   if (p.split_k == 1 && 4 * m_blocks * ((N + 255) / 256) < 3 * sm_count()) block_n = 128;
@@ -653,18 +672,25 @@ extern "C" int b200_fp8_blockwise_scaled_grouped_mm(const void* a, int64_t lda, 
   p.status = gemm_status_ptr();
   p.expert_offsets = expert_offsets; p.problem_sizes = problem_sizes; p.num_experts = num_experts;
   p.split_k = 1; p.kb_per_split = 0; p.partial = nullptr;
-  p.debug_mode = 0; p.debug_buf = nullptr; p.wait_hint_ns = 0;
+  p.debug_mode = g_gemm_debug_mode; p.debug_buf = g_gemm_debug_buf;
+  p.wait_hint_ns = static_cast<uint32_t>(g_gemm_wait_hint_ns);
   if (!p.status) return B200_ERR_CUDA;
 
   // An expert's weights are rows [e*N, (e+1)*N) of one [E*N, K] matrix; a 128 x 256 tile must not
   // straddle two experts' rows, so the wide tile needs N % 256 == 0.
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if ((g_force_block_n == 3 || forced_token_tile() != 0) && N % 128 == 0) {
+    int tt = forced_token_tile();
+    const int64_t avg = total_rows / num_experts;
+    if (tt == 0) tt = avg <= 24 ? 32 : (avg <= 48 ? 64 : 128);
+    return launch_gemm_swapab(a, lda, total_rows, b, ldb, N * num_experts, p, true, tt, st);
+  }
   const int block_n = (N % 256 == 0 && g_force_block_n != 128) ? 256 : 128;
   CUtensorMap ma, mb;
   rc = make_map_u8_2d(&ma, a, total_rows, K, lda, BLOCK_M);
   if (rc != B200_OK) return rc;
   rc = make_map_u8_2d(&mb, b, N * num_experts, K, ldb, block_n);
   if (rc != B200_OK) return rc;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
   return block_n == 256 ? launch_dtype<256, 16, 32, true>(ma, mb, p, st)
                         : launch_dtype<128, 8, 64, true>(ma, mb, p, st);
 }

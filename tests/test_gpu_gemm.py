@@ -77,7 +77,7 @@ def no_split_k():
     gemm.SPLIT_K_MODE = "auto"
 
 
-@pytest.mark.parametrize("block_n", [128, 256, 2])   # 2 = CTA-pair kernel
+@pytest.mark.parametrize("block_n", [128, 256, 2, 3, 3032])   # 2 = CTA-pair kernel, 3xxx = weight-streaming kernel
 @pytest.mark.parametrize("K", [128, 256, 512, 1024])
 @pytest.mark.parametrize("N", [128, 256, 512, 1152])
 @pytest.mark.parametrize("M", [1, 3, 5, 127, 128, 129, 512])
@@ -106,7 +106,7 @@ def _run_splitk(a, b, sa, sb, out_dtype, split_k, ws_floats=None):
     return rc, out
 
 
-@pytest.mark.parametrize("block_n", [0, 128])
+@pytest.mark.parametrize("block_n", [0, 128, 3, 3064])
 @pytest.mark.parametrize("split_k", [2, 3, 5, 8])
 @pytest.mark.parametrize("M,N,K", [(1, 512, 1024), (16, 384, 1152), (128, 1152, 2048), (77, 256, 4096),
                                    (5, 128, 1024)])

@@ -90,8 +90,10 @@ def _grouped_problem(E, N, K, counts, seed):
     return a, sa, torch.stack(wq), torch.stack(ws), offs, ps
 
 
+@pytest.mark.parametrize("kernel", [0, 3, 3032, 3064, 3128])   # 0 = automatic; 3xxx = weight-streaming kernel
 @pytest.mark.parametrize("E,N,K,seed", [(4, 256, 512, 0), (8, 384, 256, 1), (16, 512, 1024, 2), (8, 4096, 7168, 3)])
-def test_grouped_gemm(E, N, K, seed):
+def test_grouped_gemm(E, N, K, seed, kernel):
+    from sglang_b200 import _lib
     from sglang_b200.sgl_kernel import fp8_blockwise_scaled_grouped_mm
     g = torch.Generator().manual_seed(100 + seed)
     counts = [int(c) for c in torch.randint(0, 5, (E,), generator=g) * 50 + torch.randint(0, 30, (E,), generator=g)]
@@ -100,10 +102,14 @@ def test_grouped_gemm(E, N, K, seed):
     a, sa, wq, ws, offs, ps = _grouped_problem(E, N, K, counts, seed)
     rows = a.shape[0]
     out = torch.full((rows + 3, N), -7.0, dtype=torch.bfloat16, device="cuda")
-    fp8_blockwise_scaled_grouped_mm(out[:rows], None, None, None, None, None, a.cuda(), wq.cuda().transpose(1, 2),
-                                    sa.cuda(), ws.cuda(), None, None, None, None, None, ps.cuda(), offs[:-1].cuda(),
-                                    None)
-    torch.cuda.synchronize()
+    _lib.lib().b200_debug_force_block_n(kernel)
+    try:
+        fp8_blockwise_scaled_grouped_mm(out[:rows], None, None, None, None, None, a.cuda(), wq.cuda().transpose(1, 2),
+                                        sa.cuda(), ws.cuda(), None, None, None, None, None, ps.cuda(),
+                                        offs[:-1].cuda(), None)
+        torch.cuda.synchronize()
+    finally:
+        _lib.lib().b200_debug_force_block_n(0)
     _status_ok()
     assert torch.all(out[rows:] == -7.0)
     for e in range(E):
