@@ -72,7 +72,16 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // suspended in hardware for up to that long; hint 0 uses the plain form.
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity, uint32_t hint_ns = 0) {
   uint32_t ok;
-  if (hint_ns != 0) {
+  if (hint_ns == 1) {
+    // non-blocking form: returns at once whether or not the phase has completed
+    asm volatile(
+        "{\n\t.reg .pred P;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, P;\n\t}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+  } else if (hint_ns != 0) {
     asm volatile(
         "{\n\t.reg .pred P;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
