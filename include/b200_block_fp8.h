@@ -72,6 +72,20 @@ int b200_per_token_group_quant_fp8_ieee_div(const void* x, int x_dtype, void* q,
                                             float eps, float fp8_min, float fp8_max, void* stream);
 
 /*
+ * Per-token-group (128) quantisation with power-of-two scales packed as biased-exponent bytes
+ * (UE8M0), the scale_ue8m0 = true form of sgl_per_token_group_quant_fp8
+ * (sgl-kernel/csrc/gemm/per_token_group_quant_8bit.cu:54-61,86-97):
+ *   s = exp2f(ceilf(log2f(max(amax / fp8_max, 1e-10f)))),  q = e4m3(clamp(x / s)),
+ *   byte = (uint8)((int)log2f(s) + 127)
+ * s_packed: int32 words holding four consecutive k-groups of one row (little-endian byte order), element
+ * (row r, word w) at s_packed[w * s_stride_pack + r]  (s_stride_pack >= M; the reference passes
+ * align4(M)).  Whole words are written: groups past K/128 inside the last word are zero bytes.
+ */
+int b200_per_token_group_quant_fp8_ue8m0(const void* x, int x_dtype, void* q, uint32_t* s_packed,
+                                         int64_t M, int64_t K, int64_t s_stride_pack,
+                                         float eps, float fp8_min, float fp8_max, void* stream);
+
+/*
  * SiLU(gate) * up followed by per-token-group (128) FP8 quantisation in one pass: x [M, 2K] holds
  * gate | up per row (bf16 / fp16); writes codes q [M, K] and scales as above.  The product is formed
  * in fp32 and rounded to x's type before quantisation, so the result is bit-identical to

@@ -88,6 +88,55 @@ def native_per_token_group_quant_fp8(x, group_size, eps=1e-10, dtype=FP8):
     return x_q.reshape(x.shape), x_s.reshape(x.shape[:-1] + (x.shape[-1] // group_size,))
 
 
+def ceil_to_ue8m0(x: torch.Tensor) -> torch.Tensor:
+    """2 ** ceil(log2(|x|)) in fp32 (python/sglang/test/test_block_fp8_deep_gemm_blackwell.py:48-50;
+    the CUDA kernel's exp2f(ceilf(log2f(.))), per_token_group_quant_8bit.cu:87-89)."""
+    return torch.pow(2.0, torch.ceil(torch.log2(x.abs())))
+
+
+def quant_group_fp8_ue8m0_cuda_semantics(x: torch.Tensor, group_size: int = 128, eps: float = 1e-10):
+    """The scale_ue8m0 = true arithmetic of per_token_group_quant_8bit.cu:45,86-97,110-111:
+    amax = max(eps, max|x|); s = 2 ** ceil(log2(max(amax / 448, 1e-10))); q = e4m3(clamp(x / s));
+    byte = int(log2(s)) + 127.  Returns (codes [M, K], scales fp32 [M, G], packed int32 [M, ceil(G/4)]
+    with group g of a row in byte g % 4 of word g // 4, missing groups zero)."""
+    M, K = x.shape
+    G = K // group_size
+    xf = x.to(torch.float32).reshape(M, G, group_size)
+    amax = xf.abs().amax(dim=-1).clamp_min(eps)
+    s = ceil_to_ue8m0((amax / 448.0).clamp_min(1e-10))
+    q = (xf / s.unsqueeze(-1)).clamp(-448.0, 448.0).to(FP8).reshape(M, K)
+    expo = torch.log2(s).to(torch.int32) + 127
+    words = (G + 3) // 4
+    padded = torch.zeros(M, words * 4, dtype=torch.int32)
+    padded[:, :G] = expo & 0xFF
+    p4 = padded.reshape(M, words, 4)
+    packed = p4[..., 0] | (p4[..., 1] << 8) | (p4[..., 2] << 16) | (p4[..., 3] << 24)
+    return q, s, packed.to(torch.int32)
+
+
+def per_token_group_quant_mxfp8(x: torch.Tensor):
+    """The reference test's power-of-two token quantiser (test_block_fp8_deep_gemm_blackwell.py:53-59):
+    amax clamped at 1e-4, multiplication by the (exact) reciprocal of the power-of-two scale."""
+    m, n = x.shape
+    xv = x.view(m, -1, 128)
+    amax = xv.abs().float().amax(dim=2).view(m, -1).clamp(1e-4)
+    sf = ceil_to_ue8m0(amax / 448.0)
+    return (xv * (1.0 / sf.unsqueeze(2))).to(FP8).view(m, n), sf
+
+
+def per_block_quant_mxfp8(x: torch.Tensor):
+    """128 x 128 weight blocks with power-of-two scales (test_block_fp8_deep_gemm_blackwell.py:62-76)."""
+    m, n = x.shape
+    pm, pn = (m + 127) // 128 * 128, (n + 127) // 128 * 128
+    xp = torch.zeros((pm, pn), dtype=x.dtype)
+    xp[:m, :n] = x
+    xv = xp.view(-1, 128, pn // 128, 128)
+    amax = xv.abs().float().amax(dim=(1, 3), keepdim=True).clamp(1e-4)
+    sf = ceil_to_ue8m0(amax / 448.0)
+    xs = (xv * (1.0 / sf)).to(FP8)
+    return xs.view_as(xp)[:m, :n].contiguous(), sf.view(xv.size(0), xv.size(2))
+
+
 def scale_layout(s_row_major: torch.Tensor, layout: str) -> torch.Tensor:
     """Re-lay a row-major [M,G] scale matrix into one of the reference's layouts
     (python/sglang/srt/layers/quantization/fp8_kernel.py:300-341).

@@ -35,6 +35,8 @@ _SIGNATURES = {
                                                         c_void_p]),
     "b200_silu_mul_per_token_group_quant_fp8": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                                         c_int64, c_float, c_float, c_float, c_void_p]),
+    "b200_per_token_group_quant_fp8_ue8m0": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                                                     c_float, c_float, c_float, c_void_p]),
     "b200_fp8_blockwise_scaled_mm": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64,
                                              c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int, c_int64, c_int64,
                                              c_int64, c_void_p]),

@@ -102,7 +102,12 @@ __device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float 
 // FUSE_SILU: x is [M, 2K] (gate | up); the row to quantise is silu(gate) * up, computed in fp32 and
 // rounded to T exactly as the separate silu_and_mul kernel stores it, so codes and scales equal the
 // two-kernel sequence bit for bit while the [M, K] intermediate never touches HBM.
-template <typename T, int GROUP, int PASSES, bool IEEE_DIV, bool FUSE_SILU = false>
+// UE8M0: the scale is rounded up to a power of two, exp2f(ceilf(log2f(max(amax/448, 1e-10)))), and
+// stored as its biased exponent byte, four k-groups per int32, column-major: the byte of (row r,
+// group g) lives at byte ((g/4) * s_stride_grp + r) * 4 + g%4 of s
+// (sgl-kernel/csrc/gemm/per_token_group_quant_8bit.cu:54-61,86-97).  s_stride_row is unused (rows are
+// contiguous).  The tile writes whole words; groups past K/GROUP inside the last word are zero bytes.
+template <typename T, int GROUP, int PASSES, bool IEEE_DIV, bool FUSE_SILU = false, bool UE8M0 = false>
 __global__ void __launch_bounds__(kThreads, (PASSES >= 8 || sizeof(T) == 4) ? 2 : 4)   // 4 blocks/SM: <= 64 registers
 quant_group_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ s, int64_t M, int64_t K,
                    int64_t s_stride_row, int64_t s_stride_grp, float eps, float fp8_min, float fp8_max,
@@ -158,7 +163,8 @@ quant_group_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* __re
 #pragma unroll
     for (int off = TPG / 2; off >= 1; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
 
-    const float scale = __fdiv_rn(amax, fp8_max);
+    float scale = __fdiv_rn(amax, fp8_max);
+    if constexpr (UE8M0) scale = exp2f(ceilf(log2f(fmaxf(scale, 1e-10f))));
     const bool std_range = (fp8_max == 448.0f) && (fp8_min == -448.0f);
     bool fast = !IEEE_DIV && std_range;
     if (fast) {
@@ -214,6 +220,25 @@ quant_group_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* __re
   const int64_t g0 = static_cast<int64_t>(tile_k) * GPT;
   const int64_t G = K / GROUP;
   const int64_t r0 = tile_m * ROWS;
+  if constexpr (UE8M0) {
+    static_assert(GPT % 4 == 0, "a tile row must hold whole packed words");
+    uint32_t* sp = reinterpret_cast<uint32_t*>(s);
+    for (int idx = tid; idx < ROWS * (GPT / 4); idx += kThreads) {
+      const int w = idx / ROWS, r = idx % ROWS;   // rows are the contiguous dimension
+      if (r0 + r < M && g0 + 4 * w < G) {
+        uint32_t word = 0;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          if (g0 + 4 * w + b < G) {
+            const uint32_t byte = static_cast<uint8_t>(static_cast<int>(log2f(s_tile[r * GPT + 4 * w + b])) + 127);
+            word |= byte << (8 * b);
+          }
+        }
+        sp[(g0 / 4 + w) * s_stride_grp + (r0 + r)] = word;
+      }
+    }
+    return;
+  }
   const bool rows_contig = s_stride_row <= s_stride_grp;
   for (int idx = tid; idx < ROWS * GPT; idx += kThreads) {
     int r, g;
@@ -228,7 +253,7 @@ quant_group_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* __re
   }
 }
 
-template <typename T, int GROUP, bool IEEE_DIV, bool FUSE_SILU = false>
+template <typename T, int GROUP, bool IEEE_DIV, bool FUSE_SILU = false, bool UE8M0 = false>
 int launch_group(const void* x, void* q, float* s, int64_t M, int64_t K, int64_t ssr, int64_t ssg, float eps,
                  float fmin_, float fmax_, cudaStream_t stream) {
   const int tiles_k = static_cast<int>((K + kTileW - 1) / kTileW);
@@ -247,7 +272,7 @@ int launch_group(const void* x, void* q, float* s, int64_t M, int64_t K, int64_t
   const T* xp = static_cast<const T*>(x);
   uint8_t* qp = static_cast<uint8_t*>(q);
 #define B200_LAUNCH_Q(P)                                                                                       \
-  quant_group_kernel<T, GROUP, P, IEEE_DIV, FUSE_SILU><<<grid, kThreads, 0, stream>>>(xp, qp, s, M, K, ssr, ssg, eps, fmin_, \
+  quant_group_kernel<T, GROUP, P, IEEE_DIV, FUSE_SILU, UE8M0><<<grid, kThreads, 0, stream>>>(xp, qp, s, M, K, ssr, ssg, eps, fmin_, \
                                                                            fmax_, tiles_k)
   switch (passes) {
     case 8:
@@ -338,6 +363,30 @@ extern "C" int b200_silu_mul_per_token_group_quant_fp8(const void* x, int x_dtyp
     case B200_DT_F16:
       return launch_group<__half, 128, false, true>(x, q, s, M, K, s_stride_row, s_stride_grp, eps, fp8_min, fp8_max,
                                                     st);
+    default:
+      return B200_ERR_BAD_DTYPE;
+  }
+}
+
+extern "C" int b200_per_token_group_quant_fp8_ue8m0(const void* x, int x_dtype, void* q, uint32_t* s_packed, int64_t M,
+                                                    int64_t K, int64_t s_stride_pack, float eps, float fp8_min,
+                                                    float fp8_max, void* stream) {
+  using namespace b200;
+  if (M < 0 || K < 0) return B200_ERR_BAD_SHAPE;
+  if (K % 128 != 0) return B200_ERR_BAD_SHAPE;
+  if (M == 0 || K == 0) return B200_OK;
+  if (!x || !q || !s_packed) return B200_ERR_NULL_PTR;
+  if (!aligned16(x) || !aligned16(q)) return B200_ERR_MISALIGNED;
+  if (s_stride_pack < M) return B200_ERR_BAD_STRIDE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  float* s = reinterpret_cast<float*>(s_packed);
+  switch (x_dtype) {
+    case B200_DT_BF16:
+      return launch_group<__nv_bfloat16, 128, false, false, true>(x, q, s, M, K, 1, s_stride_pack, eps, fp8_min, fp8_max, st);
+    case B200_DT_F16:
+      return launch_group<__half, 128, false, false, true>(x, q, s, M, K, 1, s_stride_pack, eps, fp8_min, fp8_max, st);
+    case B200_DT_F32:
+      return launch_group<float, 128, false, false, true>(x, q, s, M, K, 1, s_stride_pack, eps, fp8_min, fp8_max, st);
     default:
       return B200_ERR_BAD_DTYPE;
   }

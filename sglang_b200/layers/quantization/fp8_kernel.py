@@ -23,7 +23,14 @@ fp8_min = -fp8_max
 def create_per_token_group_quant_fp8_output_scale(x_shape, device, group_size, column_major_scales: bool,
                                                   scale_tma_aligned: bool, scale_ue8m0: bool):
     if scale_ue8m0:
-        raise NotImplementedError("UE8M0-packed scales are not built; use fp32 scales")
+        # biased-exponent bytes, four k-groups per int32, column-major and padded to 4 rows / 4 groups
+        # (python/sglang/srt/layers/quantization/fp8_kernel.py:308-319); zero-filled like the reference
+        assert column_major_scales and scale_tma_aligned
+        assert group_size == 128 and len(x_shape) == 2
+        x_q_mn, x_q_k = x_shape
+        aligned_mn = (x_q_mn + 3) // 4 * 4
+        aligned_k = (x_q_k // 128 + 3) // 4 * 4
+        return torch.zeros((aligned_k // 4, aligned_mn), device=device, dtype=torch.int).transpose(0, 1)[:x_q_mn, :]
     if column_major_scales:
         if scale_tma_aligned:
             aligned_size = (x_shape[-2] + 3) // 4 * 4

@@ -88,12 +88,27 @@ def sgl_per_token_group_quant_fp8(
     _check(input.dtype in _DT, "input must be float32, float16 or bfloat16")
     if output_q.dtype != FP8:
         raise NotImplementedError("only float8_e4m3fn codes are built (the int8 variant belongs to the INT8 path)")
-    if scale_ue8m0:
-        raise NotImplementedError("UE8M0-packed scales are not built; use fp32 scales")
-    _check(output_s.dtype == torch.float32, "output_s must be float32")
     K = input.shape[-1]
     _check(K % group_size == 0, "the last dimension of input must be divisible by group_size")
     M = input.numel() // K
+    if scale_ue8m0:
+        # packed power-of-two scales: int32 [M, ceil(G/4)] view with rows contiguous
+        # (per_token_group_quant_8bit.cu:54-61,153-156: column-major is required for this form)
+        _check(output_s.dtype == torch.int32, "output_s must be int32 for UE8M0 scales")
+        _check(group_size == 128, "UE8M0 scales are built for 128-wide groups")
+        _check(output_s.stride(0) < output_s.stride(1) or output_s.shape[1] == 1,
+               "UE8M0 scales must be column-major")
+        _check(output_s.shape[0] == M and output_s.shape[1] == (K // 128 + 3) // 4 and output_s.stride(0) == 1,
+               "output_s shape mismatch")
+        if M == 0:
+            return
+        with torch.cuda.device(input.device):
+            rc = _lib.lib().b200_per_token_group_quant_fp8_ue8m0(
+                input.data_ptr(), _DT[input.dtype], output_q.data_ptr(), output_s.data_ptr(), M, K,
+                output_s.stride(1), float(eps), float(fp8_min), float(fp8_max), _stream_ptr(input.device))
+        _lib.check("sgl_per_token_group_quant_fp8", rc)
+        return
+    _check(output_s.dtype == torch.float32, "output_s must be float32")
     if M == 0:
         return
     _check(output_s.shape[0] == M and output_s.shape[1] == K // group_size, "output_s shape mismatch")

@@ -16,8 +16,10 @@ Sources executed (paths inside the reference checkout):
   sgl-kernel/tests/test_fp8_blockwise_moe.py    calc_diff, per_token_cast_to_fp8,
                                                 per_block_cast_to_fp8
   test/srt/quant/test_fp8_kernel.py         TestFP8Base._make_A / _make_B (known-answer generators)
+  python/sglang/test/test_block_fp8_deep_gemm_blackwell.py   ceil_to_ue8m0, per_token_group_quant_mxfp8,
+                                            per_block_quant_mxfp8 (power-of-two scales)
 
-Usage:  python tests/golden/make_golden.py [--reference /root/reference]
+Usage:  python tests/golden/make_golden.py [--reference /root/reference] [--only ue8m0]
 """
 from __future__ import annotations
 
@@ -66,7 +68,28 @@ class _SiluAndMul:
         return F.silu(x[..., :d]) * x[..., d:]
 
 
-def main(reference: str):
+def make_ue8m0(reference: str):
+    """Power-of-two (UE8M0) scales: the reference's torch functions on seeded inputs."""
+    ns = {"torch": torch, "Tuple": Tuple}
+    _extract(os.path.join(reference, "python/sglang/test/test_block_fp8_deep_gemm_blackwell.py"),
+             ["ceil_div", "align", "ceil_to_ue8m0", "per_token_group_quant_mxfp8", "per_block_quant_mxfp8"], ns)
+    torch.manual_seed(7)
+    x = (torch.randn(37, 1024) * torch.where(torch.rand(37, 1024) < 1e-2, 100.0, 1.0)).to(torch.bfloat16)
+    xq, xs = ns["per_token_group_quant_mxfp8"](x)
+    x32 = torch.randn(9, 384) * 3.0
+    x32q, x32s = ns["per_token_group_quant_mxfp8"](x32)
+    w = torch.randn(200, 384) * 0.02
+    wq, ws = ns["per_block_quant_mxfp8"](w)
+    np.savez_compressed(os.path.join(HERE, "quant_ue8m0.npz"), x=_np(x), xq=_np(xq), xs=_np(xs),
+                        x32=_np(x32), x32q=_np(x32q), x32s=_np(x32s), w=_np(w), wq=_np(wq), ws=_np(ws))
+
+
+def main(reference: str, only: str = ""):
+    if only in ("", "ue8m0"):
+        make_ue8m0(reference)
+        if only:
+            print("golden vectors written to", HERE)
+            return
     ns = {"torch": torch, "Optional": Optional, "Tuple": Tuple, "Type": Type, "SiluAndMul": _SiluAndMul}
     _extract(os.path.join(reference, "python/sglang/test/test_block_fp8.py"),
              ["native_per_token_group_quant_fp8", "native_w8a8_block_fp8_matmul", "torch_w8a8_block_fp8_moe"], ns)
@@ -147,4 +170,6 @@ def main(reference: str):
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
-    main(ap.parse_args().reference)
+    ap.add_argument("--only", default="", choices=["", "ue8m0"], help="write just this group of vectors")
+    a = ap.parse_args()
+    main(a.reference, a.only)

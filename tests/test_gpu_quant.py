@@ -141,3 +141,50 @@ def test_full_size_checksum_property():
     deq = q.float().view(M, K // 128, 128) * s.unsqueeze(-1)
     err = (deq - x.float().view(M, K // 128, 128)).abs().amax(-1)
     assert bool(torch.all(err <= s * 16.001 + 1e-30))   # 16 = half the e4m3 step at the top binade
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("M,K", [(1, 128), (5, 512), (37, 1024), (130, 7168), (2048, 7168), (6, 640)])
+def test_ue8m0_packed_scales_bit_exact(M, K, dtype):
+    """scale_ue8m0=True: power-of-two scales as packed exponent bytes (int32, column-major, padded to 4 rows and
+    4 groups), codes and words bit-exact against the oracle; padding rows / words stay zero."""
+    x = O.gen_activation(M, K, seed=M + K, dtype=dtype, outlier_frac=1e-3)
+    q, s = _quant(x, 128, column_major_scales=True, scale_tma_aligned=True, scale_ue8m0=True)
+    q_ref, s_ref, packed_ref = O.quant_group_fp8_ue8m0_cuda_semantics(x, 128)
+    words = (K // 128 + 3) // 4
+    assert s.dtype == torch.int32 and tuple(s.shape) == (M, words) and s.stride(0) == 1
+    assert s.stride(1) == (M + 3) // 4 * 4
+    assert count_diff_bits(q.cpu(), q_ref) == 0
+    assert torch.equal(s.cpu(), packed_ref)
+    storage = torch.as_strided(s, (words, s.stride(1)), (s.stride(1), 1)).cpu()
+    assert bool((storage[:, M:] == 0).all())
+
+
+def test_ue8m0_golden_and_edge_cases():
+    g = load_golden("quant_ue8m0.npz")
+    x = as_bf16(g["x"])
+    q, s = _quant(x, 128, column_major_scales=True, scale_tma_aligned=True, scale_ue8m0=True)
+    assert same_bits(q.cpu(), as_fp8(g["xq"]))
+    sf = t(g["xs"])
+    by = torch.stack([(s.cpu() >> (8 * b)) & 0xFF for b in range(4)], dim=-1).reshape(x.shape[0], -1)
+    assert torch.equal(torch.pow(2.0, (by[:, :sf.shape[1]] - 127).float()), sf)
+    # an all-zero group: amax = eps -> scale 2**ceil(log2(1e-10)) = 2**-33 (byte 94), codes zero;
+    # exact powers of two times 448 keep their exponent (ceil of an integer)
+    z = torch.zeros(2, 256, dtype=torch.bfloat16)
+    z[1, :128] = 448.0 * 2.0 ** -3
+    z[1, 128:] = 448.0 * 2.0 ** 5
+    qz, sz = _quant(z, 128, column_major_scales=True, scale_tma_aligned=True, scale_ue8m0=True)
+    qr, sr, pr = O.quant_group_fp8_ue8m0_cuda_semantics(z, 128)
+    assert torch.equal(sz.cpu(), pr) and count_diff_bits(qz.cpu(), qr) == 0
+    assert int(sz[0, 0]) & 0xFF == 94 and int(sz[1, 0]) & 0xFF == 124 and (int(sz[1, 0]) >> 8) & 0xFF == 132
+
+
+def test_ue8m0_argument_errors():
+    from sglang_b200.sgl_kernel import sgl_per_token_group_quant_fp8
+    x = torch.randn(8, 256, device="cuda").to(torch.bfloat16)
+    q = torch.empty(8, 256, device="cuda", dtype=torch.float8_e4m3fn)
+    with pytest.raises(RuntimeError):      # fp32 scale tensor with scale_ue8m0
+        sgl_per_token_group_quant_fp8(x, q, torch.empty(8, 2, device="cuda"), 128, 1e-10, -448.0, 448.0, True)
+    with pytest.raises(RuntimeError):      # row-major int32
+        sgl_per_token_group_quant_fp8(x, q, torch.zeros(8, 2, device="cuda", dtype=torch.int32)[:, :1], 128, 1e-10,
+                                      -448.0, 448.0, True)

@@ -22,6 +22,25 @@ def test_quant_matches_reference_torch_twin():
         assert same_bits(s, t(g["randn_bf16_s"]))
 
 
+def test_quant_ue8m0_matches_reference_functions():
+    """Power-of-two scales: the reference's torch functions (make_golden.py --only ue8m0) vs the oracle's
+    restatements, and the CUDA-semantics form (eps 1e-10, division) on the same non-degenerate inputs."""
+    g = load_golden("quant_ue8m0.npz")
+    for xk, qk, sk, conv in (("x", "xq", "xs", as_bf16), ("x32", "x32q", "x32s", t)):
+        x = conv(g[xk])
+        q, s = O.per_token_group_quant_mxfp8(x)
+        assert same_bits(q, as_fp8(g[qk])) and same_bits(s, t(g[sk]))
+        q2, s2, packed = O.quant_group_fp8_ue8m0_cuda_semantics(x, 128)
+        assert same_bits(q2, as_fp8(g[qk])) and same_bits(s2, t(g[sk]))
+        # the packed bytes decode to the same powers of two
+        G = s2.shape[1]
+        by = torch.stack([(packed >> (8 * b)) & 0xFF for b in range(4)], dim=-1).reshape(s2.shape[0], -1)
+        assert torch.equal(torch.pow(2.0, (by[:, :G] - 127).float()), s2)
+        assert bool((by[:, G:] == 0).all())
+    wq, ws = O.per_block_quant_mxfp8(t(g["w"]))
+    assert same_bits(wq, as_fp8(g["wq"])) and same_bits(ws, t(g["ws"]))
+
+
 def test_quant_known_answer():
     """test/srt/quant/test_fp8_kernel.py:90-100: scales equal, <1e-4 of codes differ."""
     g = load_golden("known_answer.npz")
