@@ -432,26 +432,50 @@ def run_kernel_case(args):
             work, unit, peak = 3.03125 * m * HIDDEN / 1e9, "GB/s", pk["hbm_gbs"]
         else:
             n, k = (INTER2, HIDDEN) if args.kernel == "gemm_gate_up" else (HIDDEN, INTER)
-            wq, ws = gen_weight_device(n, k, 1, dev)
+            # small batches are weight-streaming: rotate through enough weight copies (> 2x L2) that no
+            # call finds its weights in L2
+            ncopy = 1 if m > 512 else max(2, int(300e6 // (n * k)) + 1)
+            copies = [gen_weight_device(n, k, 1 + c, dev) for c in range(ncopy)]
             x = torch.randn((m, k), generator=g, device=dev).to(torch.bfloat16)
             xq, xs_ = sglang_per_token_group_quant_fp8(x, 128, column_major_scales=True)
-            w_t, ws_t = wq.T, ws.T
+            views = [(wq.T, ws.T) for wq, ws in copies]
+            it = [0]
 
             def fn():
+                it[0] += 1
+                w_t, ws_t = views[it[0] % ncopy]
                 return fp8_blockwise_scaled_mm(xq, w_t, xs_, ws_t, torch.bfloat16)
             work, unit, peak = 2.0 * m * n * k / 1e12, "TFLOP/s", 2.0 * pk["bf16_sustained"]
         for _ in range(max(3, args.warmup)):
             fn()
         torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(args.steps):
-            fn()
-        b.record()
+        if args.graph:
+            # the launches of all timed steps captured once and replayed: device time without the
+            # Python call overhead (a decode loop runs this way)
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                fn()                                   # per-stream workspace allocated before capture
+            torch.cuda.current_stream().wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(args.steps):
+                    fn()
+            graph.replay()
+            torch.cuda.synchronize()
+            a.record()
+            graph.replay()
+            b.record()
+        else:
+            a.record()
+            for _ in range(args.steps):
+                fn()
+            b.record()
         torch.cuda.synchronize()
         sec = a.elapsed_time(b) / args.steps * 1e-3
         rec = {"kernel": args.kernel, "M": m, "us": sec * 1e6, "achieved": work / sec, "unit": unit,
-               "frac_of_measured_peak": work / sec / peak}
+               "frac_of_measured_peak": work / sec / peak, "graph": bool(args.graph)}
         if args.kernel == "moe":
             rec["experts"] = args.experts
             rec["weight_GBps_if_all_experts_read"] = args.experts * (2 * 2048 * 7168 + 7168 * 2048) / sec / 1e9
@@ -465,6 +489,8 @@ def main():
     ap.add_argument("--m", default="4096", help="token count(s) for --kernel, comma separated")
     ap.add_argument("--experts", type=int, default=256,
                     help="--kernel moe: experts held on this GPU (256 = whole layer, 32 = one rank of 8)")
+    ap.add_argument("--graph", action="store_true",
+                    help="--kernel: replay the timed steps from a CUDA graph (excludes Python call overhead)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)

@@ -509,11 +509,16 @@ inline int forced_token_tile() {
 namespace b200 {
 namespace {
 
-// Split count for small M: when the output has fewer 128x256 tiles than half the SMs, the k-blocks
-// of each tile are spread over several CTAs so that the weights stream through all SMs at once.
+// Which kernel a dense problem gets: up to 64 tokens the weight-streaming kernel (gemm_swapab.cu,
+// 128 weight rows x tokens per tile) measured 10-30 % faster on every DeepSeek-V3 projection; above
+// that the 128-token x 128/256-column tiles of this file.
+inline bool dense_uses_swapab(int64_t M) { return M <= 64; }
+
+// Split count for small M: when the output has too few tiles for the SMs, the k-blocks of each tile
+// are spread over several CTAs so that the weights stream through all SMs at once.
 int plan_split_k(int64_t M, int64_t N, int64_t K, int sms) {
   if (M > BLOCK_M || (N % 4) != 0) return 1;
-  const int64_t tiles = (N + 255) / 256;
+  const int64_t tiles = dense_uses_swapab(M) ? (N + 127) / 128 : (N + 255) / 256;
   const int64_t nkb = (K + BLOCK_K - 1) / BLOCK_K;
   // measured on DeepSeek-V3 shapes: below 32 k-blocks the launch and pipeline ramp dominate and the
   // extra reduce kernel costs more than the idle SMs
@@ -579,7 +584,7 @@ int dense_mm(const void* a, int64_t lda, const void* b, int64_t ldb, const float
   // waves of half-size tiles take as long), else 128 x 128.  (The CTA-pair
   // kernel in gemm_2cta.cu is correct but measured slower; it runs only when forced.)
   if (g_force_block_n == 2 && p.split_k == 1) return launch_gemm_pair(a, lda, b, ldb, p, st);
-  if (g_force_block_n == 3 || forced_token_tile() != 0) {
+  if (g_force_block_n == 3 || forced_token_tile() != 0 || (g_force_block_n == 0 && dense_uses_swapab(M))) {
     int tt = forced_token_tile();
     if (tt == 0) tt = M <= 32 ? 32 : (M <= 64 ? 64 : 128);
     rc = launch_gemm_swapab(a, lda, M, b, ldb, N, p, false, tt, st);
@@ -679,10 +684,14 @@ extern "C" int b200_fp8_blockwise_scaled_grouped_mm(const void* a, int64_t lda, 
   // An expert's weights are rows [e*N, (e+1)*N) of one [E*N, K] matrix; a 128 x 256 tile must not
   // straddle two experts' rows, so the wide tile needs N % 256 == 0.
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if ((g_force_block_n == 3 || forced_token_tile() != 0) && N % 128 == 0) {
+  // Up to ~144 rows per expert on average the weight-streaming kernel is used (measured on the
+  // DeepSeek-V3 expert shapes: 1.25x at 16 rows per expert, 1.06x at 64, level at 128); beyond that the
+  // 128-row token tiles of this file are fuller and their wider MMAs win.
+  const int64_t avg_rows = total_rows / num_experts;
+  const bool auto_swap = g_force_block_n == 0 && avg_rows <= 144;
+  if ((g_force_block_n == 3 || forced_token_tile() != 0 || auto_swap) && N % 128 == 0) {
     int tt = forced_token_tile();
-    const int64_t avg = total_rows / num_experts;
-    if (tt == 0) tt = avg <= 24 ? 32 : (avg <= 48 ? 64 : 128);
+    if (tt == 0) tt = avg_rows <= 20 ? 32 : 64;
     return launch_gemm_swapab(a, lda, total_rows, b, ldb, N * num_experts, p, true, tt, st);
   }
   const int block_n = (N % 256 == 0 && g_force_block_n != 128) ? 256 : 128;

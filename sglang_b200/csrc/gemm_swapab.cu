@@ -11,11 +11,12 @@
 //   * a tile is 128 weight rows x up to TN tokens, so the tensor-core and read-out work follows the
 //     number of tokens (rounded up to 16) instead of whole 128-row token tiles, and an expert's
 //     weights are streamed once however its rows fall on 128-row boundaries;
-//   * a pipeline stage holds 16 KB of weights and only TN x 128 B of activations, so 6 to 10 stages
-//     fit and enough weight bytes are in flight per SM to cover the loaded DRAM latency;
-//   * the accumulator of one k-block is TN tensor-memory columns, so 4 to 8 of them rotate and the
-//     hand-off between the MMA warp and the read-out warps is off the critical path.
-// Roles, barriers, bounded waits and the common exit are those of gemm.cu.
+//   * a pipeline stage holds 2 x 16 KB of weights and only 2 x TN x 128 B of activations, so 3 to 5
+//     two-k-block stages fit and enough weight bytes are in flight per SM to cover the DRAM latency;
+//   * the accumulator of one k-block is TN tensor-memory columns, so 4 to 8 of them rotate.
+// Every hand-off (operands landed, MMAs complete, accumulators read) covers TWO k-blocks: the cost of
+// a barrier round trip and of the loop around it was the bound with one k-block per hand-off.
+// Roles, bounded waits and the common exit are those of gemm.cu.
 #include "gemm_common.cuh"
 
 namespace b200 {
@@ -24,26 +25,28 @@ namespace {
 constexpr int BLOCK_W = 128;     // weight rows per tile = rows of the MMA = tensor-memory lanes
 constexpr int BLOCK_K = 128;
 constexpr int kTmemCols = 512;
+constexpr int kPair = 2;         // k-blocks per pipeline stage and per hand-off
 constexpr int kScaleGroup = 8;   // k-blocks per scale-ring slot (8 fp32 scales of a token = one 32-byte sector)
+constexpr int kScaleSlots = 4;
 constexpr int kEpiWarps = 8;     // 4 lane quadrants x 2 column halves
 constexpr int kMaxExperts = 1024;
 
 template <int TN>
 struct SwapCfg {
   static_assert(TN == 32 || TN == 64 || TN == 128, "token tile");
-  static constexpr int kWBytes = BLOCK_W * BLOCK_K;
-  static constexpr int kXBytes = TN * BLOCK_K;
-  static constexpr int kStageBytes = kWBytes + kXBytes;
-  static constexpr int kStages = TN == 128 ? 6 : (TN == 64 ? 8 : 10);
-  static constexpr int kAccStride = TN;   // tensor-memory columns between accumulators
-  static constexpr int kNumAcc = (kTmemCols / kAccStride) < 8 ? (kTmemCols / kAccStride) : 8;
-  static_assert(kNumAcc <= kStages, "the MMA warp must not lap a stage's completion barrier");
+  static constexpr int kWBytes = BLOCK_W * BLOCK_K;    // one k-block of weights
+  static constexpr int kXBytes = TN * BLOCK_K;         // one k-block of activations
+  static constexpr int kStageBytes = kPair * (kWBytes + kXBytes);
+  static constexpr int kStages = TN == 128 ? 3 : (TN == 64 ? 4 : 5);
+  static constexpr int kAccPairs = (kTmemCols / (kPair * TN)) < 4 ? (kTmemCols / (kPair * TN)) : 4;
+  static_assert(kAccPairs <= kStages, "the MMA warp must not lap a stage's completion barrier");
   static constexpr int kColsPerWarp = TN / 2;
   static constexpr int kTmaWarp = kEpiWarps;
   static constexpr int kMmaWarp = kEpiWarps + 1;
   static constexpr int kStagerWarp = kEpiWarps + 2;
+  static constexpr int kStagers = 2;   // both stage scale products, taking alternate slot fills
   static constexpr int kThreads = 32 * (kEpiWarps + 4);
-  // Register rebalancing for the widest tile (64 accumulators + a 32-column chunk + 16 scale
+  // Register rebalancing for the widest tile (64 accumulators + two 32-register fragments + 32 scale
   // products per read-out thread): the launch gives each of the 384 threads 168 registers; the helper
   // warpgroup hands 88 per thread back and the two read-out warpgroups take 40 more each.
   // setmaxnreg.inc WAITS until the CTA's pool holds what it asks for, so the request must never
@@ -55,10 +58,8 @@ struct SwapCfg {
   static constexpr int kEpiRegs = 208;
   static_assert(kEpiWarps * (kEpiRegs - kLaunchRegs) <= 4 * (kLaunchRegs - kHelperRegs),
                 "read-out warps would wait forever for registers nobody releases");
-  static constexpr int kScaleSlots = 4;
   static constexpr int kSlotFloats = kScaleGroup * TN;
   static constexpr int kScaleBytes = kScaleSlots * kSlotFloats * 4;
-  static constexpr int kStagers = 2;   // both stage scale products, taking alternate slot fills
   static constexpr int kSmemBytes = kStages * kStageBytes + kScaleBytes + 1024 /*alignment slack*/ + 512 /*barriers*/ +
                                     (kMaxExperts + 1) * 4;
 };
@@ -105,13 +106,20 @@ __device__ __forceinline__ SwapTile get_swap_tile(int tile, const GemmParams& p,
   return t;
 }
 
-// Timing experiments: CTA 0 records clock64 samples of k-blocks [start, start + 64) of its own sequence
-// into debug_buf[row][64] (start = 8 * (debug_mode >> 8)).  No effect when debug_buf is null.
-__device__ __forceinline__ void stamp(const GemmParams& p, int row, int i) {
-  if (p.debug_buf != nullptr && blockIdx.x == 0) {
-    const int k = i - 8 * (p.debug_mode >> 8);
-    if (k >= 0 && k < 64) p.debug_buf[row * 64 + k] = clock64();
-  }
+// acc[i] += v[i] * s[col(i)] for one 16-lane fragment: v[4g + 2rp + e] belongs to token column 8g + 2q + e,
+// whose scale product is sv[2g + e].
+template <int NG>
+__device__ __forceinline__ void promote(float* acc, const float* v, const float* sv) {
+#pragma unroll
+  for (int g = 0; g < NG; ++g)
+#pragma unroll
+    for (int rp = 0; rp < 2; ++rp) {
+      const int i = 4 * g + 2 * rp;
+      const float2 r = __ffma2_rn(make_float2(v[i], v[i + 1]), make_float2(sv[2 * g], sv[2 * g + 1]),
+                                  make_float2(acc[i], acc[i + 1]));
+      acc[i] = r.x;
+      acc[i + 1] = r.y;
+    }
 }
 
 template <int TN, bool GROUPED, typename OutT>
@@ -121,16 +129,16 @@ gemm_block_fp8_swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __
   using C = SwapCfg<TN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* smem_w = smem;
-  uint8_t* smem_x = smem + C::kStages * C::kWBytes;
+  uint8_t* smem_w = smem;                                        // [stage][kPair][128 x 128 B]
+  uint8_t* smem_x = smem + C::kStages * kPair * C::kWBytes;      // [stage][kPair][TN x 128 B]
   float* smem_scale = reinterpret_cast<float*>(smem + C::kStages * C::kStageBytes);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes + C::kScaleBytes);
-  uint64_t* full_bar = bars;                     // operands of the stage have landed
-  uint64_t* done_bar = bars + C::kStages;        // the k-block's MMAs completed
-  uint64_t* acc_empty = bars + 2 * C::kStages;   // accumulator buffer has been read out
-  uint64_t* scale_full = acc_empty + C::kNumAcc;
-  uint64_t* scale_empty = scale_full + C::kScaleSlots;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(scale_empty + C::kScaleSlots);
+  uint64_t* full_bar = bars;                     // operands of the stage (two k-blocks) have landed
+  uint64_t* done_bar = bars + C::kStages;        // the stage's MMAs completed
+  uint64_t* acc_empty = bars + 2 * C::kStages;   // accumulator pair has been read out
+  uint64_t* scale_full = acc_empty + C::kAccPairs;
+  uint64_t* scale_empty = scale_full + kScaleSlots;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(scale_empty + kScaleSlots);
   int* tile_start = reinterpret_cast<int*>(tmem_slot + 2);   // [num_experts + 1], grouped form only
 
   const int warp = threadIdx.x >> 5;
@@ -157,8 +165,8 @@ gemm_block_fp8_swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __
       mbar_init(&full_bar[i], 1);
       mbar_init(&done_bar[i], 1);
     }
-    for (int i = 0; i < C::kNumAcc; ++i) mbar_init(&acc_empty[i], kEpiWarps);
-    for (int i = 0; i < C::kScaleSlots; ++i) {
+    for (int i = 0; i < C::kAccPairs; ++i) mbar_init(&acc_empty[i], kEpiWarps);
+    for (int i = 0; i < kScaleSlots; ++i) {
       mbar_init(&scale_full[i], 1);
       mbar_init(&scale_empty[i], kEpiWarps);
     }
@@ -187,23 +195,29 @@ gemm_block_fp8_swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __
   if constexpr (C::kRebalanceRegs) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(C::kHelperRegs));
   if (warp == C::kTmaWarp) {
     // ------------------------------------------------------------------ TMA producer
-    int stage = 0, seq = 0;
+    int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
     for (int vt = blockIdx.x; ok && vt < num_vtiles; vt += gridDim.x) {
       const SwapTile t = get_swap_tile<GROUPED, TN>(vt / split_k, p, m_tiles, n_tiles, tile_start);
       const int split = vt % split_k;
       const int kb_begin = split * kbps, kb_end = min(nkb, kb_begin + kbps);
-      for (int kb = kb_begin; kb < kb_end; ++kb, ++seq) {
-        ok = mbar_wait_warp(&done_bar[stage], phase ^ 1u, p.status, 1, p.wait_hint_ns);
+      for (int kb = kb_begin; kb < kb_end; kb += kPair) {
+        ok = mbar_wait_warp(&done_bar[stage], phase ^ 1u, p.status, 1);
         if (!ok) break;
-        if (lane == 0) stamp(p, 0, seq);
         if (elect_one()) {
           // timing experiments (results are wrong): bit 2 = no activation loads, bit 8 = no weight loads
           const bool load_x = !(p.debug_mode & 2), load_w = !(p.debug_mode & 8);
-          mbar_expect_tx(&full_bar[stage], (load_w ? C::kWBytes : 0) + (load_x ? C::kXBytes : 0));
-          if (load_w) tma_load_2d(smem_w + stage * C::kWBytes, &map_w, &full_bar[stage], kb * BLOCK_K, t.w_row0);
-          if (load_x) tma_load_2d(smem_x + stage * C::kXBytes, &map_x, &full_bar[stage], kb * BLOCK_K, t.row0);
+          const int n = min(kPair, kb_end - kb);
+          mbar_expect_tx(&full_bar[stage], n * ((load_w ? C::kWBytes : 0) + (load_x ? C::kXBytes : 0)));
+          for (int j = 0; j < n; ++j) {
+            if (load_w)
+              tma_load_2d(smem_w + (stage * kPair + j) * C::kWBytes, &map_w, &full_bar[stage], (kb + j) * BLOCK_K,
+                          t.w_row0);
+            if (load_x)
+              tma_load_2d(smem_x + (stage * kPair + j) * C::kXBytes, &map_x, &full_bar[stage], (kb + j) * BLOCK_K,
+                          t.row0);
+          }
         }
         __syncwarp();
         if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
@@ -213,11 +227,12 @@ gemm_block_fp8_swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __
   } else if (warp == C::kMmaWarp) {
     // ------------------------------------------------------------------ MMA issuer
     // D[weight row, token] = W_tile (128 x 128 B, the instruction's M side) x X_tile^T (tn tokens, its
-    // N side); tn = tokens of the tile rounded up to 16, encoded in the instruction descriptor.
+    // N side); tn = tokens of the tile rounded up to 16, encoded in the instruction descriptor.  The two
+    // k-blocks of a stage go to the two accumulators of a pair; one commit covers both.
     const uint64_t w_desc0 = umma_desc_k128(smem_u32(smem_w));
     const uint64_t x_desc0 = umma_desc_k128(smem_u32(smem_x));
-    int stage = 0, acc = 0, seq = 0;
-    uint32_t phase = 0, acc_phase = 0;
+    int stage = 0, ap = 0;
+    uint32_t phase = 0, ap_phase = 0;
     bool ok = true;
     for (int vt = blockIdx.x; ok && vt < num_vtiles; vt += gridDim.x) {
       const SwapTile t = get_swap_tile<GROUPED, TN>(vt / split_k, p, m_tiles, n_tiles, tile_start);
@@ -225,30 +240,33 @@ gemm_block_fp8_swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __
       const uint32_t idesc = umma_idesc_e4m3(BLOCK_W, tn);
       const int split = vt % split_k;
       const int kb_begin = split * kbps, kb_end = min(nkb, kb_begin + kbps);
-      for (int kb = kb_begin; kb < kb_end; ++kb, ++seq) {
-        ok = mbar_wait_warp(&acc_empty[acc], acc_phase ^ 1u, p.status, 2, p.wait_hint_ns);
-        if (ok) ok = mbar_wait_warp(&full_bar[stage], phase, p.status, 3, p.wait_hint_ns);
+      for (int kb = kb_begin; kb < kb_end; kb += kPair) {
+        ok = mbar_wait(&acc_empty[ap], ap_phase ^ 1u, p.status, 2);
+        if (ok) ok = mbar_wait(&full_bar[stage], phase, p.status, 3);
+        ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        if (lane == 0) stamp(p, 1, seq);
         tc_fence_after();
-        const uint64_t w_desc = w_desc0 + static_cast<uint64_t>(stage * (C::kWBytes >> 4));
-        const uint64_t x_desc = x_desc0 + static_cast<uint64_t>(stage * (C::kXBytes >> 4));
-        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * C::kAccStride);
+        const int n = min(kPair, kb_end - kb);
         if (elect_one()) {
           if (p.debug_mode & 16) {   // timing experiment: no tensor-core work at all, only the barrier
             mbar_arrive(&done_bar[stage]);
           } else {
+            for (int j = 0; j < n; ++j) {
+              const uint64_t w_desc = w_desc0 + static_cast<uint64_t>((stage * kPair + j) * (C::kWBytes >> 4));
+              const uint64_t x_desc = x_desc0 + static_cast<uint64_t>((stage * kPair + j) * (C::kXBytes >> 4));
+              const uint32_t d_tmem = tmem_base + static_cast<uint32_t>((ap * kPair + j) * TN);
 #pragma unroll
-            for (int k = 0; k < BLOCK_K / 32; ++k) {
-              umma_f8(d_tmem, w_desc + static_cast<uint64_t>(2 * k), x_desc + static_cast<uint64_t>(2 * k), idesc,
-                      k > 0 ? 1u : 0u);
+              for (int k = 0; k < BLOCK_K / 32; ++k) {
+                umma_f8(d_tmem, w_desc + static_cast<uint64_t>(2 * k), x_desc + static_cast<uint64_t>(2 * k), idesc,
+                        k > 0 ? 1u : 0u);
+              }
             }
             umma_commit(&done_bar[stage]);
           }
         }
         __syncwarp();
         if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
-        if (++acc == C::kNumAcc) { acc = 0; acc_phase ^= 1u; }
+        if (++ap == C::kAccPairs) { ap = 0; ap_phase ^= 1u; }
       }
     }
     __syncwarp();
@@ -275,8 +293,8 @@ gemm_block_fp8_swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __
       const bool vec = row_major_vec && (kb_begin & 3) == 0;
       for (int kb0 = kb_begin; kb0 < kb_end; kb0 += kScaleGroup, ++fill) {
         if ((fill & 1) != which) continue;
-        const int slot = fill % C::kScaleSlots;
-        const uint32_t sphase = static_cast<uint32_t>(fill / C::kScaleSlots) & 1u;
+        const int slot = fill % kScaleSlots;
+        const uint32_t sphase = static_cast<uint32_t>(fill / kScaleSlots) & 1u;
         float a[TN / 32][kScaleGroup];
         float bsc[kScaleGroup];
 #pragma unroll
@@ -300,7 +318,7 @@ gemm_block_fp8_swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __
 #pragma unroll
         for (int j = 0; j < kScaleGroup; ++j)
           bsc[j] = kb0 + j < kb_end ? __ldg(sb_row + static_cast<int64_t>(kb0 + j) * p.sb_stride_g) : 0.f;
-        ok = mbar_wait_warp(&scale_empty[slot], sphase ^ 1u, p.status, 5, p.wait_hint_ns);
+        ok = mbar_wait_warp(&scale_empty[slot], sphase ^ 1u, p.status, 5);
         if (!ok) break;
         float* dst = smem_scale + slot * C::kSlotFloats;
 #pragma unroll
@@ -325,18 +343,19 @@ gemm_block_fp8_swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __
     // The accumulator is read in the 16-lane fragment layout (tcgen05.ld 16x256b): a thread then holds
     // 4 weight rows x CPW/4 tokens instead of 1 row x CPW tokens, so it needs only CPW/4 scale products
     // per k-block.  (With one row per thread every thread reads every token's product, and the
-    // shared-memory-to-register path, 128 B/clk per SM, was the bottleneck of the whole kernel.)
-    // Register v[32h + 4g + 2rp + e] <-> weight row 32*quad + 16h + 8rp + lane/4,
-    //                                     token col0 + 8g + 2(lane%4) + e.
+    // shared-memory-to-register path, 128 B/clk per SM, was the bottleneck.)
+    // Fragment h (lanes 16h..16h+15 of the quadrant): register 4g + 2rp + e <-> weight row
+    // 32*quad + 16h + 8rp + lane/4, token col0 + 8g + 2(lane%4) + e.
     constexpr int CPW = C::kColsPerWarp;
     constexpr int NG = CPW / 8;          // 8-column groups per warp
     constexpr int SPT = CPW / 4;         // scale products per thread per k-block
+    constexpr int FR = 4 * NG;           // registers per fragment
     const int quad = warp & 3;
     const int part = warp >> 2;
     const int q = lane & 3;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     OutT* out = static_cast<OutT*>(p.out);
-    int acc_i = 0, stage = 0, slot = 0, seq = 0;
+    int stage = 0, ap = 0, slot = 0;
     uint32_t phase = 0, sphase = 0;
     bool ok = true;
     for (int vt = blockIdx.x; ok && vt < num_vtiles; vt += gridDim.x) {
@@ -346,62 +365,67 @@ gemm_block_fp8_swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __
       const int col0 = part * CPW;                    // first token column of this warp
       const int my_cols = min(CPW, t.valid - col0);   // <= 0: nothing to read for this warp
       const bool live = my_cols > 0 && !(p.debug_mode & 1);
-      float acc[2 * 4 * NG];
+      float acc0[FR], acc1[FR];                       // fragment 0 / fragment 1
 #pragma unroll
-      for (int c = 0; c < 2 * 4 * NG; ++c) acc[c] = 0.f;
+      for (int c = 0; c < FR; ++c) acc0[c] = acc1[c] = 0.f;
       for (int kb0 = kb_begin; ok && kb0 < kb_end; kb0 += kScaleGroup) {
-        ok = mbar_wait_warp(&scale_full[slot], sphase, p.status, 6, p.wait_hint_ns);
+        ok = mbar_wait(&scale_full[slot], sphase, p.status, 6);
         if (!ok) break;
         // this thread's SPT products of k-block j: slot[j][part][q][2g + e]  (see the stagers)
         const float* sc = smem_scale + slot * C::kSlotFloats + col0 + q * SPT;
 #pragma unroll 1
-        for (int j = 0; j < kScaleGroup; ++j) {
-          const int kb = kb0 + j;
+        for (int jj = 0; jj < kScaleGroup; jj += kPair) {
+          const int kb = kb0 + jj;
           if (kb < kb_end) {
-            if (warp == 0 && lane == 0) stamp(p, 4, seq);
-            ok = mbar_wait_warp(&done_bar[stage], phase, p.status, 4, p.wait_hint_ns);
+            const bool two = kb + 1 < kb_end;
+            ok = mbar_wait(&done_bar[stage], phase, p.status, 4);
             if (!ok) break;
-            if (warp == 0 && lane == 0) stamp(p, 2, seq);
             tc_fence_after();
-            const uint32_t taddr = tmem_base + lane_addr + static_cast<uint32_t>(acc_i * C::kAccStride + col0);
-            float v[2 * 4 * NG];
-            float sv[SPT];
             if (live) {   // warp-uniform: columns past the tile's tokens hold nothing
-              tmem_ld_16x256b<NG>(taddr, v);
-              tmem_ld_16x256b<NG>(taddr + (16u << 16), v + 4 * NG);
+              const uint32_t t0 = tmem_base + lane_addr + static_cast<uint32_t>((ap * kPair) * TN + col0);
+              const uint32_t t1 = t0 + TN;
+              float v0[FR], v1[FR], sv0[SPT], sv1[SPT];
+              tmem_ld_16x256b<NG>(t0, v0);
+              tmem_ld_16x256b<NG>(t0 + (16u << 16), v1);
+              // the scale products are fetched while the tensor-memory reads are in flight
+#pragma unroll
+              for (int i = 0; i < SPT; i += 4) {
+                *reinterpret_cast<float4*>(sv0 + i) = *reinterpret_cast<const float4*>(sc + jj * TN + i);
+                *reinterpret_cast<float4*>(sv1 + i) = *reinterpret_cast<const float4*>(sc + (jj + 1) * TN + i);
+              }
+              tmem_ld_wait();
+              if (two) {
+                promote<NG>(acc0, v0, sv0);
+                tmem_ld_16x256b<NG>(t1, v0);                 // second k-block, fragment 0, while ...
+                promote<NG>(acc1, v1, sv0);                  // ... fragment 1 of the first is promoted
+                tmem_ld_wait();
+                tmem_ld_16x256b<NG>(t1 + (16u << 16), v1);
+                promote<NG>(acc0, v0, sv1);
+                tmem_ld_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[ap]);
+                promote<NG>(acc1, v1, sv1);
+              } else {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[ap]);
+                promote<NG>(acc0, v0, sv0);
+                promote<NG>(acc1, v1, sv0);
+              }
+            } else {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&acc_empty[ap]);
             }
-            // the scale products are fetched while the tensor-memory reads are in flight
-#pragma unroll
-            for (int i = 0; i < SPT; i += 4)
-              *reinterpret_cast<float4*>(sv + i) = *reinterpret_cast<const float4*>(sc + j * TN + i);
-            if (live) tmem_ld_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[acc_i]);
-            if (live) {
-#pragma unroll
-              for (int h = 0; h < 2; ++h)
-#pragma unroll
-                for (int g = 0; g < NG; ++g)
-#pragma unroll
-                  for (int rp = 0; rp < 2; ++rp) {
-                    const int i = 4 * NG * h + 4 * g + 2 * rp;
-                    const float2 r = __ffma2_rn(make_float2(v[i], v[i + 1]), make_float2(sv[2 * g], sv[2 * g + 1]),
-                                                make_float2(acc[i], acc[i + 1]));
-                    acc[i] = r.x;
-                    acc[i + 1] = r.y;
-                  }
-            }
-            if (warp == 0 && lane == 0) stamp(p, 3, seq);
-            ++seq;
-            if (++acc_i == C::kNumAcc) acc_i = 0;
+            if (++ap == C::kAccPairs) ap = 0;
             if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
           }
         }
         // the slot's products have been consumed by this warp
         __syncwarp();
         if (lane == 0) mbar_arrive(&scale_empty[slot]);
-        if (++slot == C::kScaleSlots) { slot = 0; sphase ^= 1u; }
+        if (++slot == kScaleSlots) { slot = 0; sphase ^= 1u; }
       }
       // out[token, n]: one store instruction covers 4 tokens x 8 consecutive output columns
       if (ok && my_cols > 0) {
@@ -416,7 +440,7 @@ gemm_block_fp8_swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                   const int c = 8 * g + 2 * q + e;
-                  const float val = acc[4 * NG * h + 4 * g + 2 * rp + e];
+                  const float val = h == 0 ? acc0[4 * g + 2 * rp + e] : acc1[4 * g + 2 * rp + e];
                   if (c < my_cols) {
                     const int64_t tok = t.row0 + col0 + c;
                     if (split_k > 1) {

@@ -39,11 +39,19 @@ _WORKSPACE: dict = {}
 SPLIT_K_MODE = "auto"
 
 
+_PLAN: dict = {}
+
+
 def _splitk_plan(M: int, N: int, K: int, device: torch.device):
-    """Split count and workspace bytes the library chooses for this shape (1, 0 = no split)."""
+    """Split count and workspace bytes the library chooses for this shape (1, 0 = no split); cached per
+    shape and device (a decode loop asks for the same few shapes every step)."""
     if M > 128 or SPLIT_K_MODE != "auto":
         return 1, 0
     idx = device.index if device.index is not None else torch.cuda.current_device()
+    key = (M, N, K, idx)
+    hit = _PLAN.get(key)
+    if hit is not None:
+        return hit
     sms = _SM_COUNT.get(idx)
     if sms is None:
         sms = _SM_COUNT[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
@@ -51,7 +59,8 @@ def _splitk_plan(M: int, N: int, K: int, device: torch.device):
     s, b = ctypes.c_int(1), ctypes.c_size_t(0)
     _lib.check("fp8_blockwise_scaled_mm_splitk_plan",
                _lib.lib().b200_fp8_blockwise_scaled_mm_splitk_plan(M, N, K, sms, ctypes.byref(s), ctypes.byref(b)))
-    return s.value, b.value
+    _PLAN[key] = (s.value, b.value)
+    return _PLAN[key]
 
 
 def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:

@@ -82,13 +82,14 @@ def test_split_k_plan_needs_no_device(lib):
         assert lib.b200_fp8_blockwise_scaled_mm_splitk_plan(M, N, K, sms, ctypes.byref(s), ctypes.byref(b)) == 0
         assert b.value == (s.value * M * N * 4 if s.value > 1 else 0)
         return s.value
-    assert plan(16, 7168, 18432) == 5          # 28 tiles of 128 x 256 on 148 SMs
+    assert plan(16, 7168, 18432) == 2          # <= 64 tokens: 56 tiles of 128 weight rows on 148 SMs
+    assert plan(128, 7168, 18432) == 5         # 65..128 tokens: 28 tiles of 128 x 256
     assert plan(1, 1536, 7168) == 7            # capped at eight k-blocks per CTA
-    assert plan(16, 36864, 7168) == 1          # already one tile per SM
+    assert plan(16, 36864, 7168) == 1          # already more tiles than SMs
     assert plan(16, 7168, 2048) == 1           # too few k-blocks to pay for the reduce kernel
     assert plan(129, 7168, 18432) == 1
     assert plan(0, 7168, 18432) == 1
-    assert plan(16, 7168, 18432, sms=0) == 5   # <= 0 means a 148-SM part
+    assert plan(16, 7168, 18432, sms=0) == 2   # <= 0 means a 148-SM part
     s, b = ctypes.c_int(0), ctypes.c_size_t(0)
     assert lib.b200_fp8_blockwise_scaled_mm_splitk_plan(-1, 128, 128, 148, ctypes.byref(s), ctypes.byref(b)) < 0
     assert lib.b200_fp8_blockwise_scaled_mm_splitk_plan(1, 128, 128, 148, None, None) < 0
