@@ -276,6 +276,39 @@ def run_gpu_arm(args):
     for _ in range(max(3, args.warmup)):
         step()
     barrier()
+    # Tensor-parallel ranks replay the step from a CUDA graph (kernels, the side-stream fork/join and the
+    # NCCL all-reduces captured once): a rank's share of the step is a few hundred microseconds of device
+    # work, less than the Python calls that enqueue it.
+    graph = None
+    if world > 1 and not args.eager:
+        cap = torch.cuda.Stream(device=dev)
+        cap.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(cap):
+            step()
+        torch.cuda.current_stream().wait_stream(cap)
+        barrier()
+        # thread-local capture mode: the process group's watchdog thread polls events while this thread
+        # captures.  Nothing executes during capture, so a rank whose capture fails can still agree with
+        # the others (one small all-reduce afterwards) to run eagerly.
+        captured = 1
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=cap, capture_error_mode="thread_local"):
+                step()
+        except Exception as e:  # noqa: BLE001
+            captured = 0
+            graph = None
+            print(f"[bench rank {rank}] graph capture failed, running eagerly: {e}", file=sys.stderr, flush=True)
+        torch.cuda.synchronize()
+        flag = torch.tensor([captured], device=dev, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            graph = None
+        if graph is not None:
+            for _ in range(3):
+                graph.replay()
+                torch.cuda.synchronize()
+        barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -284,10 +317,17 @@ def run_gpu_arm(args):
     barrier()
     t0.record()
     for _ in range(args.steps):
-        step(record=True)
+        if graph is not None:
+            graph.replay()
+        else:
+            step(record=True)
     t1.record()
     barrier()
     ms = t0.elapsed_time(t1) / args.steps
+    if graph is not None:
+        for _ in range(5):          # per-kernel times from a few eager steps (events cannot be timed inside a graph)
+            step(record=True)
+        barrier()
     per_kernel = {}
     for name, a, b in kernel_events:
         per_kernel.setdefault(name, []).append(a.elapsed_time(b))
@@ -351,7 +391,8 @@ def run_gpu_arm(args):
             "data": "synthetic",
             "config": {"workload": WORKLOAD,
                        "parallelism": (f"tp{world}: gate_up column-parallel, down row-parallel in {TP_CHUNKS} row chunks "
-                                       "with the bf16 NCCL all-reduce of each chunk overlapped") if world > 1 else "single",
+                                       "with the bf16 NCCL all-reduce of each chunk overlapped"
+                                       + ("; step replayed from a CUDA graph" if graph is not None else "")) if world > 1 else "single",
                        "l2": "inputs larger than L2 (weights 396 MB e4m3 + activations 210 MB bf16 per step)",
                        "kernels_ms": per_kernel},
             "e2e": {"value": FLOPS_PER_STEP / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
@@ -374,8 +415,20 @@ def run_gpu_arm(args):
             _, _, info = cpu_reference_run(steps=5, warmup=1, sample_rows=M_TOKENS)
             line["cpu_baseline"] = info
         print(json.dumps(line))
+        sys.stdout.flush()
     if world > 1:
+        # release the captured graph before the communicator it references, and never let a slow
+        # communicator teardown keep a finished benchmark alive
+        if graph is not None:
+            graph.reset()
+            graph = None
+        torch.cuda.synchronize()
+        dist.barrier()
+        guard = threading.Timer(20.0, lambda: os._exit(0))
+        guard.daemon = True
+        guard.start()
         dist.destroy_process_group()
+        guard.cancel()
 
 
 def run_kernel_case(args):
@@ -489,6 +542,7 @@ def main():
     ap.add_argument("--m", default="4096", help="token count(s) for --kernel, comma separated")
     ap.add_argument("--experts", type=int, default=256,
                     help="--kernel moe: experts held on this GPU (256 = whole layer, 32 = one rank of 8)")
+    ap.add_argument("--eager", action="store_true", help="N > 1: enqueue every step from Python instead of graph replay")
     ap.add_argument("--graph", action="store_true",
                     help="--kernel: replay the timed steps from a CUDA graph (excludes Python call overhead)")
     ap.add_argument("--gpus", type=int, default=1)
