@@ -233,7 +233,7 @@ def run_gpu_arm(args):
 
     ev = lambda: torch.cuda.Event(enable_timing=True)
     kernel_events = []   # (name, start, stop) inside the timed region
-    TP_CHUNKS = 4
+    TP_CHUNKS = args.tp_chunks
     y2_buf = torch.empty((M_TOKENS, HIDDEN), dtype=torch.bfloat16, device=dev)
     comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
 
@@ -542,6 +542,8 @@ def main():
     ap.add_argument("--m", default="4096", help="token count(s) for --kernel, comma separated")
     ap.add_argument("--experts", type=int, default=256,
                     help="--kernel moe: experts held on this GPU (256 = whole layer, 32 = one rank of 8)")
+    ap.add_argument("--tp-chunks", type=int, default=4, choices=[1, 2, 4, 8],
+                    help="N > 1: row chunks of the row-parallel projection whose all-reduces overlap the next chunk")
     ap.add_argument("--eager", action="store_true", help="N > 1: enqueue every step from Python instead of graph replay")
     ap.add_argument("--graph", action="store_true",
                     help="--kernel: replay the timed steps from a CUDA graph (excludes Python call overhead)")
