@@ -145,6 +145,22 @@ int b200_fp8_blockwise_scaled_mm_splitk_plan(int64_t M, int64_t N, int64_t K, in
                                              int* split_k, size_t* workspace_bytes);
 
 /*
+ * The same product with the ACTIVATION scales given as packed UE8M0 exponent bytes, i.e. what
+ * b200_per_token_group_quant_fp8_ue8m0 writes: element (m, kb) is byte kb % 4 of the 32-bit word at
+ * sa_packed[(kb / 4) * sa_stride_pack + m * sa_stride_m], worth 2^(byte - 127).  Weight scales stay fp32
+ * (power-of-two values after the reference's requantisation, but any fp32 value is accepted).
+ * Stands in for w8a8_block_fp8_matmul_deepgemm on the activations side
+ * (python/sglang/srt/layers/quantization/fp8_kernel.py:849-867, called from
+ * deepgemm_w8a8_block_fp8_linear_with_fallback, fp8_utils.py:215-258).  The scales are decoded and
+ * applied in fp32 exactly like the fp32-scale kernel; no hardware block scaling is used.
+ */
+int b200_fp8_blockwise_scaled_mm_ue8m0(const void* a, int64_t lda, const void* b, int64_t ldb,
+                                       const uint32_t* sa_packed, int64_t sa_stride_m, int64_t sa_stride_pack,
+                                       const float* sb, int64_t sb_stride_n, int64_t sb_stride_g,
+                                       void* out, int64_t ldo, int out_dtype,
+                                       int64_t M, int64_t N, int64_t K, void* stream);
+
+/*
  * Grouped (per-expert) block-scaled FP8 GEMM: for every expert e,
  *   out[off_e : off_e + m_e, :] = blockscaled( a[off_e : off_e + m_e, :], b[e] )   (same math as above)
  * with off_e = expert_offsets[e], m_e = problem_sizes[3*e] read ON THE DEVICE (no host sync).

@@ -45,6 +45,9 @@ _SIGNATURES = {
                                                     c_int64, c_int64, c_int, c_void_p, ctypes.c_size_t, c_void_p]),
     "b200_fp8_blockwise_scaled_mm_splitk_plan": (c_int, [c_int64, c_int64, c_int64, c_int, ctypes.POINTER(c_int),
                                                          ctypes.POINTER(ctypes.c_size_t)]),
+    "b200_fp8_blockwise_scaled_mm_ue8m0": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64,
+                                                   c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int, c_int64,
+                                                   c_int64, c_int64, c_void_p]),
     "b200_gemm_device_status": (c_int, [ctypes.POINTER(c_int)]),
     "b200_fp8_blockwise_scaled_grouped_mm": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64,
                                                      c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int,

@@ -278,10 +278,7 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 #pragma unroll
           for (int r = 0; r < 4; ++r) {
             const int rr = r * 32 + lane;
-            a[j][r] = (kin && rr < t.valid_rows)
-                          ? __ldg(p.sa + static_cast<int64_t>(t.row0 + rr) * p.sa_stride_m +
-                                  static_cast<int64_t>(kb) * p.sa_stride_g)
-                          : 0.f;
+            a[j][r] = (kin && rr < t.valid_rows) ? load_sa(p, t.row0 + rr, kb) : 0.f;
           }
 #pragma unroll
           for (int h = 0; h < C::kHalves; ++h) {
@@ -529,10 +526,17 @@ int plan_split_k(int64_t M, int64_t N, int64_t K, int sms) {
   return s < 2 ? 1 : static_cast<int>(s);
 }
 
+// Split-K workspace: split_k fp32 planes of [M, N].  (Folding the sum into the GEMM kernel -- the CTA that
+// completes a tile's last split adds the planes -- was measured slower than the second kernel at every M:
+// the device-wide fences and the CTA-wide meeting it needs cost more than a launch.)
+inline size_t splitk_workspace_bytes(int split_k, int64_t M, int64_t N) {
+  return static_cast<size_t>(split_k) * M * N * sizeof(float);
+}
+
 int dense_mm(const void* a, int64_t lda, const void* b, int64_t ldb, const float* sa, int64_t sa_stride_m,
              int64_t sa_stride_g, const float* sb, int64_t sb_stride_n, int64_t sb_stride_g, void* out, int64_t ldo,
              int out_dtype, int64_t M, int64_t N, int64_t K, int split_k, void* workspace, size_t workspace_bytes,
-             void* stream) {
+             void* stream, int sa_ue8m0 = 0) {
   if (M < 0 || N < 0 || K <= 0) return B200_ERR_BAD_SHAPE;
   if (M == 0 || N == 0) return B200_OK;
   if (M > 0x7fffff00LL || N > 0x7fffff00LL || K > 0x7fffff00LL) return B200_ERR_TOO_LARGE;
@@ -547,15 +551,14 @@ int dense_mm(const void* a, int64_t lda, const void* b, int64_t ldb, const float
     if ((N % 4) != 0 || split_k > nkb) return B200_ERR_BAD_SHAPE;
     if (!workspace) return B200_ERR_NULL_PTR;
     if (!aligned16(workspace)) return B200_ERR_MISALIGNED;
-    if (workspace_bytes < static_cast<size_t>(split_k) * M * N * sizeof(float)) return B200_ERR_TOO_LARGE;
+    if (workspace_bytes < splitk_workspace_bytes(split_k, M, N)) return B200_ERR_TOO_LARGE;
   }
   int rc = require_sm100();
   if (rc != B200_OK) return rc;
   if (split_k == 0) {
     // automatic: split only when the caller gave room for it
     split_k = plan_split_k(M, N, K, sm_count());
-    if (split_k > 1 && (!workspace || !aligned16(workspace) ||
-                        workspace_bytes < static_cast<size_t>(split_k) * M * N * sizeof(float)))
+    if (split_k > 1 && (!workspace || !aligned16(workspace) || workspace_bytes < splitk_workspace_bytes(split_k, M, N)))
       split_k = 1;
   }
 
@@ -574,6 +577,7 @@ int dense_mm(const void* a, int64_t lda, const void* b, int64_t ldb, const float
   // but the count is trimmed so that no CTA is launched for nothing)
   p.split_k = (nkb + p.kb_per_split - 1) / p.kb_per_split;
   p.partial = static_cast<float*>(workspace);
+  p.sa_ue8m0 = sa_ue8m0;
   p.debug_mode = g_gemm_debug_mode;
   p.debug_buf = g_gemm_debug_buf;
   p.wait_hint_ns = static_cast<uint32_t>(g_gemm_wait_hint_ns);
@@ -583,7 +587,7 @@ int dense_mm(const void* a, int64_t lda, const void* b, int64_t ldb, const float
   // One CTA per tile: 128 x 256 when that fills at least three quarters of the SMs in one wave (two
   // waves of half-size tiles take as long), else 128 x 128.  (The CTA-pair
   // kernel in gemm_2cta.cu is correct but measured slower; it runs only when forced.)
-  if (g_force_block_n == 2 && p.split_k == 1) return launch_gemm_pair(a, lda, b, ldb, p, st);
+  if (g_force_block_n == 2 && p.split_k == 1 && !sa_ue8m0) return launch_gemm_pair(a, lda, b, ldb, p, st);
   if (g_force_block_n == 3 || forced_token_tile() != 0 || (g_force_block_n == 0 && dense_uses_swapab(M))) {
     int tt = forced_token_tile();
     if (tt == 0) tt = M <= 32 ? 32 : (M <= 64 ? 64 : 128);
@@ -636,13 +640,22 @@ extern "C" int b200_fp8_blockwise_scaled_mm_splitk(const void* a, int64_t lda, c
                         M, N, K, split_k, workspace, workspace_bytes, stream);
 }
 
+extern "C" int b200_fp8_blockwise_scaled_mm_ue8m0(const void* a, int64_t lda, const void* b, int64_t ldb,
+                                                  const uint32_t* sa_packed, int64_t sa_stride_m, int64_t sa_stride_pack,
+                                                  const float* sb, int64_t sb_stride_n, int64_t sb_stride_g, void* out,
+                                                  int64_t ldo, int out_dtype, int64_t M, int64_t N, int64_t K,
+                                                  void* stream) {
+  return b200::dense_mm(a, lda, b, ldb, reinterpret_cast<const float*>(sa_packed), sa_stride_m, sa_stride_pack, sb,
+                        sb_stride_n, sb_stride_g, out, ldo, out_dtype, M, N, K, 1, nullptr, 0, stream, 1);
+}
+
 extern "C" int b200_fp8_blockwise_scaled_mm_splitk_plan(int64_t M, int64_t N, int64_t K, int sm_count, int* split_k,
                                                         size_t* workspace_bytes) {
   if (M < 0 || N < 0 || K <= 0) return B200_ERR_BAD_SHAPE;
   if (!split_k || !workspace_bytes) return B200_ERR_NULL_PTR;
   const int s = (M == 0 || N == 0) ? 1 : b200::plan_split_k(M, N, K, sm_count > 0 ? sm_count : 148);
   *split_k = s;
-  *workspace_bytes = s > 1 ? static_cast<size_t>(s) * M * N * sizeof(float) : 0;
+  *workspace_bytes = s > 1 ? b200::splitk_workspace_bytes(s, M, N) : 0;
   return B200_OK;
 }
 
@@ -676,7 +689,7 @@ extern "C" int b200_fp8_blockwise_scaled_grouped_mm(const void* a, int64_t lda, 
   p.out_dtype = out_dtype;
   p.status = gemm_status_ptr();
   p.expert_offsets = expert_offsets; p.problem_sizes = problem_sizes; p.num_experts = num_experts;
-  p.split_k = 1; p.kb_per_split = 0; p.partial = nullptr;
+  p.split_k = 1; p.kb_per_split = 0; p.partial = nullptr; p.sa_ue8m0 = 0;
   p.debug_mode = g_gemm_debug_mode; p.debug_buf = g_gemm_debug_buf;
   p.wait_hint_ns = static_cast<uint32_t>(g_gemm_wait_hint_ns);
   if (!p.status) return B200_ERR_CUDA;

@@ -24,6 +24,9 @@ struct GemmParams {
   int split_k;
   int kb_per_split;
   float* partial;
+  // activation scales given as packed UE8M0 exponent bytes (four k-blocks per 32-bit word) instead of fp32:
+  // element (m, kb) is byte kb % 4 of the word at sa[(kb / 4) * sa_stride_g + m * sa_stride_m]
+  int sa_ue8m0;
   uint32_t wait_hint_ns;  // suspend-time hint for mbarrier waits (0 = none)
   long long* debug_buf;  // timing experiments: clock64 samples [5][64] of pair 0's leader CTA, or null
   int debug_mode;  // timing experiments only (results are wrong when non-zero); 0 in normal use
@@ -40,6 +43,16 @@ int* gemm_status_ptr();
 int make_map_u8_2d(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows);
 
 #if defined(__CUDACC__)
+// Activation scale of (row, k-block) in either representation.
+__device__ __forceinline__ float load_sa(const GemmParams& p, int64_t row, int kb) {
+  if (p.sa_ue8m0) {
+    const uint32_t* w = reinterpret_cast<const uint32_t*>(p.sa);
+    const uint32_t word = __ldg(w + static_cast<int64_t>(kb >> 2) * p.sa_stride_g + row * p.sa_stride_m);
+    return __uint_as_float(((word >> (8 * (kb & 3))) & 0xffu) << 23);   // 2 ** (byte - 127); byte 0 -> 0
+  }
+  return __ldg(p.sa + row * p.sa_stride_m + static_cast<int64_t>(kb) * p.sa_stride_g);
+}
+
 __device__ __forceinline__ uint32_t pack2(__nv_bfloat16*, float a, float b) {
   __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&t);

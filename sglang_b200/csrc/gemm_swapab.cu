@@ -280,7 +280,7 @@ gemm_block_fp8_swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __
     // sector of a token, fetched as two 16-byte loads), the loads are issued before the wait for the
     // slot, and two warps take alternate fills.
     const int which = warp - C::kStagerWarp;
-    const bool row_major_vec = p.sa_stride_g == 1 && (p.sa_stride_m & 3) == 0 &&
+    const bool row_major_vec = !p.sa_ue8m0 && p.sa_stride_g == 1 && (p.sa_stride_m & 3) == 0 &&
                                (reinterpret_cast<uintptr_t>(p.sa) & 15u) == 0;
     int fill = 0;   // running count of slot fills of this CTA; fill % slots is the slot, its quotient the phase
     bool ok = true;
@@ -311,8 +311,7 @@ gemm_block_fp8_swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __
           } else {
 #pragma unroll
             for (int j = 0; j < kScaleGroup; ++j)
-              a[r][j] = (c < t.valid && kb0 + j < kb_end)
-                            ? __ldg(src + static_cast<int64_t>(kb0 + j) * p.sa_stride_g) : 0.f;
+              a[r][j] = (c < t.valid && kb0 + j < kb_end) ? load_sa(p, t.row0 + c, kb0 + j) : 0.f;
           }
         }
 #pragma unroll
@@ -428,31 +427,35 @@ gemm_block_fp8_swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __
         if (++slot == kScaleSlots) { slot = 0; sphase ^= 1u; }
       }
       // out[token, n]: one store instruction covers 4 tokens x 8 consecutive output columns
-      if (ok && my_cols > 0) {
+      auto for_each_owned = [&](auto&& fn) {   // fn(value, token row, output column) for this thread's elements
+        if (my_cols > 0) {
 #pragma unroll
-        for (int h = 0; h < 2; ++h)
+          for (int h = 0; h < 2; ++h)
 #pragma unroll
-          for (int rp = 0; rp < 2; ++rp) {
-            const int n = t.n0 + quad * 32 + 16 * h + 8 * rp + (lane >> 2);
-            if (n < p.N) {
+            for (int rp = 0; rp < 2; ++rp) {
+              const int n = t.n0 + quad * 32 + 16 * h + 8 * rp + (lane >> 2);
+              if (n < p.N) {
 #pragma unroll
-              for (int g = 0; g < NG; ++g)
+                for (int g = 0; g < NG; ++g)
 #pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                  const int c = 8 * g + 2 * q + e;
-                  const float val = h == 0 ? acc0[4 * g + 2 * rp + e] : acc1[4 * g + 2 * rp + e];
-                  if (c < my_cols) {
-                    const int64_t tok = t.row0 + col0 + c;
-                    if (split_k > 1) {
-                      p.partial[(static_cast<int64_t>(split) * p.M + tok) * p.N + n] = val;
-                    } else {
-                      OutT* dst = out + tok * p.ldo + n;
-                      *dst = cvt1(dst, val);
-                    }
+                  for (int e = 0; e < 2; ++e) {
+                    const int c = 8 * g + 2 * q + e;
+                    const float val = h == 0 ? acc0[4 * g + 2 * rp + e] : acc1[4 * g + 2 * rp + e];
+                    if (c < my_cols) fn(val, static_cast<int64_t>(t.row0 + col0 + c), n);
                   }
-                }
+              }
             }
-          }
+        }
+      };
+      if (ok && split_k == 1) {
+        for_each_owned([&](float val, int64_t tok, int n) {
+          OutT* dst = out + tok * p.ldo + n;
+          *dst = cvt1(dst, val);
+        });
+      } else if (ok) {
+        for_each_owned([&](float val, int64_t tok, int n) {
+          p.partial[(static_cast<int64_t>(split) * p.M + tok) * p.N + n] = val;
+        });
       }
     }
   }

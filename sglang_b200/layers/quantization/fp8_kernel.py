@@ -118,3 +118,32 @@ def w8a8_block_fp8_matmul(A: torch.Tensor, B: torch.Tensor, As: torch.Tensor, Bs
             C.data_ptr(), N, dt, M, N, K, torch.cuda.current_stream(A.device).cuda_stream)
     _lib.check("w8a8_block_fp8_matmul", rc)
     return C
+
+
+def w8a8_block_fp8_matmul_deepgemm(A: torch.Tensor, B: torch.Tensor, As: torch.Tensor, Bs: torch.Tensor,
+                                   block_size: List[int], output_dtype: torch.dtype) -> torch.Tensor:
+    """C = A @ B.T with block scales where `As` may be the packed UE8M0 tensor that
+    sglang_per_token_group_quant_fp8(..., scale_ue8m0=True) returns (int32 [M, ceil(K/512)], rows contiguous)
+    or fp32 scales [M, K/128]; `Bs` fp32 [N/128, K/128].  Mirrors the call surface of the reference's
+    w8a8_block_fp8_matmul_deepgemm (python/sglang/srt/layers/quantization/fp8_kernel.py:849-867); bf16 only,
+    like DeepGEMM."""
+    assert list(block_size) == [128, 128] and output_dtype == torch.bfloat16
+    if As.dtype != torch.int32:
+        return w8a8_block_fp8_matmul(A, B, As, Bs, block_size, output_dtype)
+    assert A.dim() == 2 and A.is_contiguous() and B.dim() == 2 and B.is_contiguous()
+    M, K = A.shape
+    N = B.shape[0]
+    assert B.shape[1] == K and K % 128 == 0 and N % 128 == 0
+    assert A.dtype == fp8_dtype and B.dtype == fp8_dtype and Bs.dtype == torch.float32
+    assert As.shape == (M, (K // 128 + 3) // 4) and (As.stride(0) == 1 or M == 1), "packed scales must be column-major"
+    assert Bs.shape == (N // 128, K // 128)
+    C = torch.empty((M, N), dtype=output_dtype, device=A.device)
+    if M == 0:
+        return C
+    with torch.cuda.device(A.device):
+        rc = _lib.lib().b200_fp8_blockwise_scaled_mm_ue8m0(
+            A.data_ptr(), K, B.data_ptr(), K, As.data_ptr(), As.stride(0), As.stride(1),
+            Bs.data_ptr(), Bs.stride(0), Bs.stride(1), C.data_ptr(), N, _lib.DT_BF16, M, N, K,
+            torch.cuda.current_stream(A.device).cuda_stream)
+    _lib.check("w8a8_block_fp8_matmul_deepgemm", rc)
+    return C

@@ -11,7 +11,7 @@ from typing import Callable, List, Optional
 import torch
 
 from ...sgl_kernel import fp8_blockwise_scaled_mm
-from .fp8_kernel import sglang_per_token_group_quant_fp8
+from .fp8_kernel import sglang_per_token_group_quant_fp8, w8a8_block_fp8_matmul_deepgemm
 
 
 def w8a8_block_fp8_linear(input: torch.Tensor, weight: torch.Tensor, block_size: List[int],
@@ -31,6 +31,31 @@ def w8a8_block_fp8_linear(input: torch.Tensor, weight: torch.Tensor, block_size:
 
 
 cutlass_w8a8_block_fp8_linear_with_fallback = w8a8_block_fp8_linear
+
+
+def deepgemm_w8a8_block_fp8_linear_with_fallback(input: torch.Tensor, weight: torch.Tensor, block_size: List[int],
+                                                 weight_scale: torch.Tensor,
+                                                 input_scale: Optional[torch.Tensor] = None,
+                                                 bias: Optional[torch.Tensor] = None,
+                                                 scale_ue8m0: bool = True) -> torch.Tensor:
+    """The reference's DeepGEMM linear (python/sglang/srt/layers/quantization/fp8_utils.py:215-258):
+    activations quantised with column-major, 4-row-aligned scales -- power-of-two, packed UE8M0 when
+    `scale_ue8m0` (the reference reads that switch from DEEPGEMM_SCALE_UE8M0, on for Blackwell) -- then the
+    block-scaled product, bias, view back.  Shapes or dtypes the DeepGEMM path does not take fall back to
+    the fp32-scale linear, as the reference falls back to its Triton kernel."""
+    assert input_scale is None
+    if not (input.dtype == torch.bfloat16 and weight.shape[0] % 64 == 0 and weight.shape[1] % 128 == 0
+            and weight.shape[0] % 128 == 0):
+        return w8a8_block_fp8_linear(input, weight, block_size, weight_scale, input_scale, bias)
+    input_2d = input.view(-1, input.shape[-1])
+    output_shape = [*input.shape[:-1], weight.shape[0]]
+    q_input, x_scale = sglang_per_token_group_quant_fp8(input_2d, block_size[1], column_major_scales=True,
+                                                        scale_tma_aligned=True, scale_ue8m0=scale_ue8m0)
+    output = w8a8_block_fp8_matmul_deepgemm(q_input, weight, x_scale, weight_scale, block_size,
+                                            output_dtype=input.dtype)
+    if bias is not None:
+        output += bias
+    return output.to(dtype=input.dtype).view(*output_shape)
 
 
 def dispatch_w8a8_block_fp8_linear() -> Callable:

@@ -323,3 +323,46 @@ def test_fp8_linear_method_apply():
     assert out.shape == (3, 16, 512) and out.dtype == torch.bfloat16
     assert O.rel_l2(out.view(48, 512).float(), ref.float()) <= TOL
     _status_ok()
+
+
+# ---------------------------------------------------------------------------- packed UE8M0 activation scales
+@pytest.mark.parametrize("M,N,K", [(1, 256, 512), (16, 512, 1024), (64, 1152, 640), (130, 256, 7168), (512, 384, 1024)])
+def test_ue8m0_scaled_matmul(M, N, K):
+    """Activation scales as packed exponent bytes (what the quant op writes with scale_ue8m0=True), weights
+    with power-of-two block scales: equal to the fp32-scale kernel given the decoded scales (bit for bit),
+    and within tolerance of the oracle."""
+    from sglang_b200.layers.quantization.fp8_kernel import (sglang_per_token_group_quant_fp8,
+                                                            w8a8_block_fp8_matmul_deepgemm)
+    x = O.gen_activation(M, K, seed=M + K, outlier_frac=1e-3)
+    w = torch.randn(N, K, generator=torch.Generator().manual_seed(N)) * 0.02
+    wq, ws = O.per_block_quant_mxfp8(w)
+    q_ref, s_ref, packed_ref = O.quant_group_fp8_ue8m0_cuda_semantics(x, 128)
+    q, s_packed = sglang_per_token_group_quant_fp8(x.cuda(), 128, column_major_scales=True, scale_tma_aligned=True,
+                                                   scale_ue8m0=True)
+    assert torch.equal(s_packed.cpu(), packed_ref)
+    out = w8a8_block_fp8_matmul_deepgemm(q, wq.cuda(), s_packed, ws.cuda(), [128, 128], torch.bfloat16).cpu()
+    _status_ok()
+    ref32 = O.block_fp8_matmul_fp32(q_ref, wq, s_ref, ws)
+    assert O.rel_l2(out.float(), ref32.to(torch.bfloat16).float()) <= TOL
+    same = _run_w8a8(q_ref, wq, s_ref, ws, torch.bfloat16).cpu()
+    assert same_bits(out, same)
+
+
+def test_deepgemm_shaped_linear():
+    """deepgemm_w8a8_block_fp8_linear_with_fallback: quantise with packed power-of-two scales, multiply, add
+    bias, view back; the fp32-scale fallback for shapes the DeepGEMM path does not take."""
+    from sglang_b200.layers.quantization.fp8_utils import deepgemm_w8a8_block_fp8_linear_with_fallback as lin
+    x = O.gen_activation(48, 1024, seed=11)
+    w = torch.randn(512, 1024, generator=torch.Generator().manual_seed(12)) * 0.02
+    wq, ws = O.per_block_quant_mxfp8(w)
+    bias = torch.randn(512).to(torch.bfloat16)
+    out = lin(x.cuda().view(3, 16, 1024), wq.cuda(), [128, 128], ws.cuda(), bias=bias.cuda()).cpu()
+    q_ref, s_ref, _ = O.quant_group_fp8_ue8m0_cuda_semantics(x, 128)
+    ref = O.block_fp8_matmul_fp32(q_ref, wq, s_ref, ws).to(torch.bfloat16) + bias
+    assert out.shape == (3, 16, 512)
+    assert O.rel_l2(out.view(48, 512).float(), ref.float()) <= TOL
+    # fp16 activations are not a DeepGEMM case: falls back to the fp32-scale linear
+    out16 = lin(x.to(torch.float16).cuda(), wq.cuda(), [128, 128], ws.cuda()).cpu()
+    ref16 = O.block_fp8_linear(x.to(torch.float16), wq, ws, out_dtype=torch.float16)
+    assert out16.dtype == torch.float16 and O.rel_l2(out16.float(), ref16.float()) <= TOL
+    _status_ok()
