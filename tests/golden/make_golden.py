@@ -19,7 +19,7 @@ Sources executed (paths inside the reference checkout):
   python/sglang/test/test_block_fp8_deep_gemm_blackwell.py   ceil_to_ue8m0, per_token_group_quant_mxfp8,
                                             per_block_quant_mxfp8 (power-of-two scales)
 
-Usage:  python tests/golden/make_golden.py [--reference /root/reference] [--only ue8m0]
+Usage:  python tests/golden/make_golden.py [--reference <reference checkout>] [--only ue8m0]
 """
 from __future__ import annotations
 
