@@ -522,7 +522,11 @@ def run_kernel_case(args):
                                                         scale_tma_aligned=True)
             work, unit, peak = 3.03125 * m * HIDDEN / 1e9, "GB/s", pk["hbm_gbs"]
         else:
-            n, k = (INTER2, HIDDEN) if args.kernel == "gemm_gate_up" else (HIDDEN, INTER)
+            if args.kernel == "gemm":   # e.g. the Llama-3-70B tensor-parallel shard shapes (N/p or K/p)
+                assert args.n > 0 and args.k > 0 and args.n % 128 == 0 and args.k % 128 == 0, "--n/--k: multiples of 128"
+                n, k = args.n, args.k
+            else:
+                n, k = (INTER2, HIDDEN) if args.kernel == "gemm_gate_up" else (HIDDEN, INTER)
             # small batches are weight-streaming: rotate through enough weight copies (> 2x L2) that no
             # call finds its weights in L2
             ncopy = 1 if m > 512 else max(2, int(300e6 // (n * k)) + 1)
@@ -565,7 +569,8 @@ def run_kernel_case(args):
             b.record()
         torch.cuda.synchronize()
         sec = a.elapsed_time(b) / args.steps * 1e-3
-        rec = {"kernel": args.kernel, "M": m, "us": sec * 1e6, "achieved": work / sec, "unit": unit,
+        rec = {"kernel": args.kernel if args.kernel != "gemm" else f"gemm N={args.n} K={args.k}", "M": m,
+               "us": sec * 1e6, "achieved": work / sec, "unit": unit,
                "frac_of_measured_peak": work / sec / peak, "graph": bool(args.graph)}
         if args.kernel == "moe":
             rec["experts"] = args.experts
@@ -575,8 +580,10 @@ def run_kernel_case(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", default=None, choices=["gemm_gate_up", "gemm_down", "quant", "moe"],
-                    help="time one kernel alone instead of the whole step")
+    ap.add_argument("--kernel", default=None, choices=["gemm_gate_up", "gemm_down", "gemm", "quant", "moe"],
+                    help="time one kernel alone instead of the whole step (gemm: any shape, see --n / --k)")
+    ap.add_argument("--n", type=int, default=0, help="--kernel gemm: output features (multiple of 128)")
+    ap.add_argument("--k", type=int, default=0, help="--kernel gemm: input features (multiple of 128)")
     ap.add_argument("--m", default="4096", help="token count(s) for --kernel, comma separated")
     ap.add_argument("--experts", type=int, default=256,
                     help="--kernel moe: experts held on this GPU (256 = whole layer, 32 = one rank of 8)")
