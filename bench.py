@@ -418,7 +418,14 @@ def run_gpu_arm(args):
         peak = 2.0 * pk["bf16_sustained"]
         quant_bytes = 3.03125 * M_TOKENS * HIDDEN
         quant_gbs = quant_bytes / (per_kernel["quant_x"] * 1e-3) / 1e9
-        launches_per_step = 4 if world == 1 else 2 + 2 * TP_CHUNKS
+        # our kernels per step: two quant launches (one per row chunk when tensor-parallel), the GEMMs, and one
+        # small reduce launch after every GEMM whose last wave of tiles the library splits
+        from sglang_b200.sgl_kernel.gemm import _splitk_plan
+        split1 = _splitk_plan(M_TOKENS, n1, HIDDEN, dev)[0] > 1
+        rows2 = M_TOKENS if world == 1 else M_TOKENS // TP_CHUNKS
+        split2 = _splitk_plan(rows2, HIDDEN, k2, dev)[0] > 1
+        chunks2 = 1 if world == 1 else TP_CHUNKS
+        launches_per_step = (1 + 1 + int(split1)) + chunks2 * (1 + 1 + int(split2))
         h2d = x.numel() * 2 + h.numel() * 2
         d2h = y1_host[0].numel() * 2 + y2_host[0].numel() * 2
         line = {

@@ -130,6 +130,11 @@ int b200_fp8_blockwise_scaled_mm(const void* a, int64_t lda, const void* b, int6
  *            1 = identical to b200_fp8_blockwise_scaled_mm; 2..64 = forced (needs N % 4 == 0,
  *            split_k <= ceil(K/128))
  *   workspace  device memory, 16-byte aligned, at least split_k * M * N * 4 bytes; never allocated here
+ * With split_k = 0 and M > 128 the library may instead split only the LAST WAVE of output tiles: when
+ * tiles mod SMs is at most half of the SMs (896 tiles on 148 SMs leave a seventh wave of 8 tiles),
+ * those tiles' k-blocks are divided among the SMs, their fp32 partial tiles go to the workspace (compact:
+ * tail tiles x splits x 128 x tile width x 4 bytes) and a small second kernel adds them in split order.
+ * Same rounding remark as above; the other tiles are bit-identical to the unsplit kernel.
  * b200_fp8_blockwise_scaled_mm_splitk_plan reports the split the library would choose for a shape on
  * a GPU with `sm_count` SMs (<= 0: 148) and the workspace that needs; it touches no device.
  * No counterpart in the reference (its CUTLASS kernel has no split-K form; the Triton kernel at

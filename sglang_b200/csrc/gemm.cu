@@ -117,6 +117,20 @@ __device__ __forceinline__ TileInfo get_tile(int tile, const GemmParams& p, int 
   return t;
 }
 
+// One unit of a CTA's work list: a whole tile, or one split of a tile's k-blocks.
+struct Work {
+  int tile, split, kb_begin, kb_end;
+  bool partial;   // the result is a partial sum for the workspace, not an output tile
+};
+__device__ __forceinline__ Work decode_work(int vt, const GemmParams& p, int nkb, bool grouped) {
+  if (grouped || p.split_k == 1) return Work{vt, 0, 0, nkb, false};
+  if (vt < p.tail_first) return Work{vt, 0, 0, nkb, false};
+  const int r = vt - p.tail_first;
+  const int tile = p.tail_first + r / p.split_k, split = r % p.split_k;
+  const int kb0 = split * p.kb_per_split;
+  return Work{tile, split, kb0, min(nkb, kb0 + p.kb_per_split), true};
+}
+
 template <int BLOCK_N, int EPI_WARPS, int CHUNK, bool GROUPED, typename OutT>
 __global__ void __launch_bounds__(Cfg<BLOCK_N, EPI_WARPS>::kThreads, 1)
 gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -184,10 +198,11 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
   const int num_tiles = GROUPED ? tile_m_start[p.num_experts] * n_blocks : m_blocks * n_blocks;
-  // split-K: each tile becomes split_k virtual tiles (split fastest), each covering kbps k-blocks
+  // split-K: every tile from tail_first on becomes split_k work units (split fastest), each covering
+  // kb_per_split k-blocks; tail_first = 0 splits all tiles (decode-size M), otherwise only the last wave
   const int split_k = GROUPED ? 1 : p.split_k;
-  const int kbps = GROUPED ? nkb : p.kb_per_split;
-  const int num_vtiles = num_tiles * split_k;
+  const int tail_first = (GROUPED || split_k == 1) ? num_tiles : p.tail_first;
+  const int num_vtiles = tail_first + (num_tiles - tail_first) * split_k;
 
   if (warp >= EPI_WARPS) {
   // ====================================================================== helper warpgroup
@@ -198,9 +213,9 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     uint32_t phase = 0;
     bool ok = true;
     for (int vt = blockIdx.x; ok && vt < num_vtiles; vt += gridDim.x) {
-      const TileInfo t = get_tile<GROUPED, BLOCK_N>(vt / split_k, p, m_blocks, n_blocks, tile_m_start);
-      const int split = vt % split_k;
-      const int kb_begin = split * kbps, kb_end = min(nkb, kb_begin + kbps);
+      const Work w = decode_work(vt, p, nkb, GROUPED);
+      const TileInfo t = get_tile<GROUPED, BLOCK_N>(w.tile, p, m_blocks, n_blocks, tile_m_start);
+      const int kb_begin = w.kb_begin, kb_end = w.kb_end;
       for (int kb = kb_begin; kb < kb_end; ++kb) {
         ok = mbar_wait_warp(&done_bar[stage], phase ^ 1u, p.status, 1);
         if (!ok) break;
@@ -225,8 +240,8 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     uint32_t phase = 0, acc_phase = 0;
     bool ok = true;
     for (int vt = blockIdx.x; ok && vt < num_vtiles; vt += gridDim.x) {
-      const int split = vt % split_k;
-      const int kb_begin = split * kbps, kb_end = min(nkb, kb_begin + kbps);
+      const Work w = decode_work(vt, p, nkb, GROUPED);
+      const int kb_begin = w.kb_begin, kb_end = w.kb_end;
       for (int kb = kb_begin; kb < kb_end; ++kb) {
         ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1u, p.status, 2);
         if (ok) ok = mbar_wait(&full_bar[stage], phase, p.status, 3);
@@ -261,10 +276,10 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     uint32_t sphase = 0;
     bool ok = true;
     for (int vt = blockIdx.x; ok && vt < num_vtiles; vt += gridDim.x) {
-      const TileInfo t = get_tile<GROUPED, BLOCK_N>(vt / split_k, p, m_blocks, n_blocks, tile_m_start);
+      const Work w = decode_work(vt, p, nkb, GROUPED);
+      const TileInfo t = get_tile<GROUPED, BLOCK_N>(w.tile, p, m_blocks, n_blocks, tile_m_start);
       const float* sb_base = p.sb + static_cast<int64_t>(t.expert) * p.sb_stride_e;
-      const int split = vt % split_k;
-      const int kb_begin = split * kbps, kb_end = min(nkb, kb_begin + kbps);
+      const int kb_begin = w.kb_begin, kb_end = w.kb_end;
       for (int kb0 = kb_begin; kb0 < kb_end; kb0 += kScaleGroup) {
         ok = mbar_wait_warp(&scale_empty[slot], sphase ^ 1u, p.status, 5);
         if (!ok) break;
@@ -275,10 +290,18 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         for (int j = 0; j < kScaleGroup; ++j) {
           const int kb = kb0 + j;
           const bool kin = kb < kb_end;
+          if (p.sa_ue8m0) {   // warp-uniform; each branch is a batch of independent loads
 #pragma unroll
-          for (int r = 0; r < 4; ++r) {
-            const int rr = r * 32 + lane;
-            a[j][r] = (kin && rr < t.valid_rows) ? load_sa(p, t.row0 + rr, kb) : 0.f;
+            for (int r = 0; r < 4; ++r) {
+              const int rr = r * 32 + lane;
+              a[j][r] = (kin && rr < t.valid_rows) ? load_sa<true>(p, t.row0 + rr, kb) : 0.f;
+            }
+          } else {
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+              const int rr = r * 32 + lane;
+              a[j][r] = (kin && rr < t.valid_rows) ? load_sa<false>(p, t.row0 + rr, kb) : 0.f;
+            }
           }
 #pragma unroll
           for (int h = 0; h < C::kHalves; ++h) {
@@ -318,9 +341,9 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     uint32_t phase = 0, sphase = 0;
     bool ok = true;
     for (int vt = blockIdx.x; ok && vt < num_vtiles; vt += gridDim.x) {
-      const TileInfo t = get_tile<GROUPED, BLOCK_N>(vt / split_k, p, m_blocks, n_blocks, tile_m_start);
-      const int split = vt % split_k;
-      const int kb_begin = split * kbps, kb_end = min(nkb, kb_begin + kbps);
+      const Work w = decode_work(vt, p, nkb, GROUPED);
+      const TileInfo t = get_tile<GROUPED, BLOCK_N>(w.tile, p, m_blocks, n_blocks, tile_m_start);
+      const int kb_begin = w.kb_begin, kb_end = w.kb_end;
       const int row_in_tile = quad * 32 + lane;
       const int m = t.row0 + row_in_tile;
       const int n0 = t.n_blk * BLOCK_N + part * CPW;
@@ -378,8 +401,14 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         }
       }
       if (ok && row_in_tile < t.valid_rows && n0 < p.N) {
-        if (split_k > 1) {
-          float* dst = p.partial + (static_cast<int64_t>(split) * p.M + m) * p.N + n0;
+        if (w.partial && p.tail_first > 0) {
+          // tail split: compact planes of whole tiles, [(tile - tail_first) * split_k + split][128][BLOCK_N]
+          float* dst = p.partial +
+                       (static_cast<int64_t>(w.tile - p.tail_first) * split_k + w.split) * (BLOCK_M * BLOCK_N) +
+                       row_in_tile * BLOCK_N + part * CPW;
+          store_row<CPW>(dst, acc, CPW, true);
+        } else if (w.partial) {
+          float* dst = p.partial + (static_cast<int64_t>(w.split) * p.M + m) * p.N + n0;
           store_row<CPW>(dst, acc, p.N - n0, (p.N % 4) == 0);
         } else {
           store_row<CPW>(out + static_cast<int64_t>(m) * p.ldo + n0, acc, p.N - n0, vec_ok);
@@ -434,6 +463,50 @@ int launch_reduce(const GemmParams& p, cudaStream_t stream) {
   return B200_OK;
 }
 
+// Sum of the tail tiles' partial planes (tail split), added in split order, converted and written into the
+// output tile with its row / column bounds.  grid = (tail tiles, 16 slices of 8 rows): a tile's planes are
+// megabytes, so one block per tile would make this kernel longer than the wave it saves.
+constexpr int kTailSlices = 16;
+template <typename OutT, int BLOCK_N>
+__global__ void __launch_bounds__(256) tail_reduce_kernel(const float* __restrict__ partial, OutT* __restrict__ out,
+                                                          int M, int N, int64_t ldo, int split_k, int tail_first,
+                                                          int m_blocks, int n_blocks) {
+  int m_blk, n_blk;
+  tile_coords(tail_first + blockIdx.x, m_blocks, n_blocks, m_blk, n_blk);
+  const float* base = partial + static_cast<int64_t>(blockIdx.x) * split_k * (BLOCK_M * BLOCK_N);
+  constexpr int kRows = BLOCK_M / kTailSlices;
+  for (int i = threadIdx.x; i < kRows * BLOCK_N / 4; i += blockDim.x) {
+    const int r = blockIdx.y * kRows + i / (BLOCK_N / 4), c = (i % (BLOCK_N / 4)) * 4;
+    const int m = m_blk * BLOCK_M + r, n = n_blk * BLOCK_N + c;
+    if (m >= M || n >= N) continue;
+    float4 acc = __ldcs(reinterpret_cast<const float4*>(base + r * BLOCK_N + c));
+    for (int s = 1; s < split_k; ++s) {
+      const float4 v = __ldcs(reinterpret_cast<const float4*>(base + s * (BLOCK_M * BLOCK_N) + r * BLOCK_N + c));
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    OutT* dst = out + static_cast<int64_t>(m) * ldo + n;
+    const float vals[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (n + j < N) dst[j] = cvt1(dst, vals[j]);
+  }
+}
+
+template <typename OutT>
+int launch_tail_reduce(const GemmParams& p, int block_n, cudaStream_t stream) {
+  const int m_blocks = (p.M + BLOCK_M - 1) / BLOCK_M;
+  const int n_blocks = (p.N + block_n - 1) / block_n;
+  const dim3 grid(m_blocks * n_blocks - p.tail_first, kTailSlices);
+  if (block_n == 256)
+    tail_reduce_kernel<OutT, 256><<<grid, 256, 0, stream>>>(p.partial, static_cast<OutT*>(p.out), p.M, p.N, p.ldo,
+                                                            p.split_k, p.tail_first, m_blocks, n_blocks);
+  else
+    tail_reduce_kernel<OutT, 128><<<grid, 256, 0, stream>>>(p.partial, static_cast<OutT*>(p.out), p.M, p.N, p.ldo,
+                                                            p.split_k, p.tail_first, m_blocks, n_blocks);
+  B200_CUDA_TRY(cudaGetLastError());
+  return B200_OK;
+}
+
 // ------------------------------------------------------------------------------------ host
 template <int BLOCK_N, int EPI_WARPS, int CHUNK, bool GROUPED, typename OutT>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t stream) {
@@ -449,8 +522,10 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cu
   const int m_blocks = (p.M + BLOCK_M - 1) / BLOCK_M;
   const int n_blocks = (p.N + BLOCK_N - 1) / BLOCK_N;
   // grouped: the tile count lives on the device; m-tiles <= ceil(rows/128) + experts bounds the grid
+  const long long dense_tiles = static_cast<long long>(m_blocks) * n_blocks;
+  const long long split_from = p.split_k == 1 ? dense_tiles : p.tail_first;
   const long long tiles = GROUPED ? static_cast<long long>(m_blocks + p.num_experts) * n_blocks
-                                  : static_cast<long long>(m_blocks) * n_blocks * p.split_k;
+                                  : split_from + (dense_tiles - split_from) * p.split_k;
   const int grid = tiles < sm_count() ? static_cast<int>(tiles) : sm_count();
   kern<<<grid, C::kThreads, C::kSmemBytes, stream>>>(ma, mb, p);
   B200_CUDA_TRY(cudaGetLastError());
@@ -533,6 +608,38 @@ inline size_t splitk_workspace_bytes(int split_k, int64_t M, int64_t N) {
   return static_cast<size_t>(split_k) * M * N * sizeof(float);
 }
 
+// Tile width of the 128-token-tile kernel for a dense problem: 128 x 256 when that fills at least three
+// quarters of the SMs in one wave (two waves of half-size tiles take as long), else 128 x 128.
+inline int dense_block_n(int64_t M, int64_t N, int sms) {
+  const int64_t m_blocks = (M + BLOCK_M - 1) / BLOCK_M;
+  return 4 * m_blocks * ((N + 255) / 256) < 3 * sms ? 128 : 256;
+}
+
+// Tail split for large M: when the last wave of tiles would occupy at most half of the SMs, those
+// tiles' k-blocks are divided among the SMs instead (e.g. 896 tiles on 148 SMs: six full waves, then
+// 8 tiles x 18 splits instead of a seventh wave that is 5 % full).
+struct TailPlan {
+  int tail_first = 0, split_k = 1, kb_per_split = 0;
+  size_t bytes = 0;
+};
+TailPlan plan_tail(int64_t M, int64_t N, int64_t K, int block_n, int sms) {
+  TailPlan t;
+  const int64_t tiles = ((M + BLOCK_M - 1) / BLOCK_M) * ((N + block_n - 1) / block_n);
+  const int64_t nkb = (K + BLOCK_K - 1) / BLOCK_K;
+  if (M <= BLOCK_M || tiles <= sms || tiles > 0x3fffffff || nkb < 16) return t;
+  const int64_t tail = tiles % sms;
+  if (tail == 0 || tail * 2 > sms) return t;   // at least two splits per tail tile
+  int64_t s = sms / tail;
+  if (s > nkb / 4) s = nkb / 4;   // at least four k-blocks per work unit
+  if (s > 32) s = 32;
+  if (s < 2) return t;
+  t.kb_per_split = static_cast<int>((nkb + s - 1) / s);
+  t.split_k = static_cast<int>((nkb + t.kb_per_split - 1) / t.kb_per_split);
+  t.tail_first = static_cast<int>(tiles - tail);
+  t.bytes = static_cast<size_t>(tail) * t.split_k * BLOCK_M * block_n * sizeof(float);
+  return t;
+}
+
 int dense_mm(const void* a, int64_t lda, const void* b, int64_t ldb, const float* sa, int64_t sa_stride_m,
              int64_t sa_stride_g, const float* sb, int64_t sb_stride_n, int64_t sb_stride_g, void* out, int64_t ldo,
              int out_dtype, int64_t M, int64_t N, int64_t K, int split_k, void* workspace, size_t workspace_bytes,
@@ -555,11 +662,16 @@ int dense_mm(const void* a, int64_t lda, const void* b, int64_t ldb, const float
   }
   int rc = require_sm100();
   if (rc != B200_OK) return rc;
+  TailPlan tail;
   if (split_k == 0) {
     // automatic: split only when the caller gave room for it
     split_k = plan_split_k(M, N, K, sm_count());
     if (split_k > 1 && (!workspace || !aligned16(workspace) || workspace_bytes < splitk_workspace_bytes(split_k, M, N)))
       split_k = 1;
+    if (split_k == 1 && M > BLOCK_M && g_force_block_n == 0 && workspace && aligned16(workspace)) {
+      tail = plan_tail(M, N, K, dense_block_n(M, N, sm_count()), sm_count());
+      if (tail.split_k > 1 && workspace_bytes < tail.bytes) tail = TailPlan();
+    }
   }
 
   GemmParams p;
@@ -576,6 +688,12 @@ int dense_mm(const void* a, int64_t lda, const void* b, int64_t ldb, const float
   // every split must own at least one k-block (an empty one would store zeros, which is still right,
   // but the count is trimmed so that no CTA is launched for nothing)
   p.split_k = (nkb + p.kb_per_split - 1) / p.kb_per_split;
+  p.tail_first = 0;
+  if (tail.split_k > 1) {
+    p.split_k = tail.split_k;
+    p.kb_per_split = tail.kb_per_split;
+    p.tail_first = tail.tail_first;
+  }
   p.partial = static_cast<float*>(workspace);
   p.sa_ue8m0 = sa_ue8m0;
   p.debug_mode = g_gemm_debug_mode;
@@ -601,7 +719,7 @@ int dense_mm(const void* a, int64_t lda, const void* b, int64_t ldb, const float
   }
   const int64_t m_blocks = (M + BLOCK_M - 1) / BLOCK_M;
   int block_n = 256;
-  if (p.split_k == 1 && 4 * m_blocks * ((N + 255) / 256) < 3 * sm_count()) block_n = 128;
+  if (p.split_k == 1 || p.tail_first > 0) block_n = dense_block_n(M, N, sm_count());
   if (g_force_block_n == 128 || g_force_block_n == 256) block_n = g_force_block_n;
   if (g_force_block_n >= 1000) block_n = g_force_block_n <= 1003 ? 128 : 256;
 
@@ -613,6 +731,13 @@ int dense_mm(const void* a, int64_t lda, const void* b, int64_t ldb, const float
   if (g_force_block_n >= 1000) rc = launch_variant(g_force_block_n, ma, mb, p, st);
   else rc = block_n == 256 ? launch_dtype<256, 16, 32>(ma, mb, p, st) : launch_dtype<128, 8, 64>(ma, mb, p, st);
   if (rc != B200_OK || p.split_k == 1) return rc;
+  if (p.tail_first > 0) {
+    switch (out_dtype) {
+      case B200_DT_BF16: return launch_tail_reduce<__nv_bfloat16>(p, block_n, st);
+      case B200_DT_F16: return launch_tail_reduce<__half>(p, block_n, st);
+      default: return launch_tail_reduce<float>(p, block_n, st);
+    }
+  }
   switch (out_dtype) {
     case B200_DT_BF16: return launch_reduce<__nv_bfloat16>(p, st);
     case B200_DT_F16: return launch_reduce<__half>(p, st);
@@ -653,9 +778,17 @@ extern "C" int b200_fp8_blockwise_scaled_mm_splitk_plan(int64_t M, int64_t N, in
                                                         size_t* workspace_bytes) {
   if (M < 0 || N < 0 || K <= 0) return B200_ERR_BAD_SHAPE;
   if (!split_k || !workspace_bytes) return B200_ERR_NULL_PTR;
-  const int s = (M == 0 || N == 0) ? 1 : b200::plan_split_k(M, N, K, sm_count > 0 ? sm_count : 148);
+  const int sms = sm_count > 0 ? sm_count : 148;
+  const int s = (M == 0 || N == 0) ? 1 : b200::plan_split_k(M, N, K, sms);
   *split_k = s;
   *workspace_bytes = s > 1 ? b200::splitk_workspace_bytes(s, M, N) : 0;
+  if (s == 1 && M > 128 && N > 0) {   // large M: split of the last, mostly empty wave of tiles
+    const b200::TailPlan t = b200::plan_tail(M, N, K, b200::dense_block_n(M, N, sms), sms);
+    if (t.split_k > 1) {
+      *split_k = t.split_k;
+      *workspace_bytes = t.bytes;
+    }
+  }
   return B200_OK;
 }
 
@@ -689,7 +822,7 @@ extern "C" int b200_fp8_blockwise_scaled_grouped_mm(const void* a, int64_t lda, 
   p.out_dtype = out_dtype;
   p.status = gemm_status_ptr();
   p.expert_offsets = expert_offsets; p.problem_sizes = problem_sizes; p.num_experts = num_experts;
-  p.split_k = 1; p.kb_per_split = 0; p.partial = nullptr; p.sa_ue8m0 = 0;
+  p.split_k = 1; p.kb_per_split = 0; p.partial = nullptr; p.tail_first = 0; p.sa_ue8m0 = 0;
   p.debug_mode = g_gemm_debug_mode; p.debug_buf = g_gemm_debug_buf;
   p.wait_hint_ns = static_cast<uint32_t>(g_gemm_wait_hint_ns);
   if (!p.status) return B200_ERR_CUDA;

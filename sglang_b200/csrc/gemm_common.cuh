@@ -24,6 +24,10 @@ struct GemmParams {
   int split_k;
   int kb_per_split;
   float* partial;
+  // tail split (dense, large M): tiles [0, tail_first) are whole; each tile from tail_first on -- the ones
+  // that would form a mostly empty last wave -- is divided among split_k CTAs, partial sums stored compactly
+  // as partial[(tile - tail_first) * split_k + split][128][block_n].  0 = the uniform split above.
+  int tail_first;
   // activation scales given as packed UE8M0 exponent bytes (four k-blocks per 32-bit word) instead of fp32:
   // element (m, kb) is byte kb % 4 of the word at sa[(kb / 4) * sa_stride_g + m * sa_stride_m]
   int sa_ue8m0;
@@ -43,14 +47,18 @@ int* gemm_status_ptr();
 int make_map_u8_2d(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows);
 
 #if defined(__CUDACC__)
-// Activation scale of (row, k-block) in either representation.
+// Activation scale of (row, k-block), fp32 or packed UE8M0.  The representation is a template argument so
+// that a stager's batch of loads stays a straight line of independent loads: with a run-time test inside
+// every load the compiler serialised them and the stager fell behind the tensor pipe.
+template <bool UE8M0>
 __device__ __forceinline__ float load_sa(const GemmParams& p, int64_t row, int kb) {
-  if (p.sa_ue8m0) {
+  if constexpr (UE8M0) {
     const uint32_t* w = reinterpret_cast<const uint32_t*>(p.sa);
     const uint32_t word = __ldg(w + static_cast<int64_t>(kb >> 2) * p.sa_stride_g + row * p.sa_stride_m);
     return __uint_as_float(((word >> (8 * (kb & 3))) & 0xffu) << 23);   // 2 ** (byte - 127); byte 0 -> 0
+  } else {
+    return __ldg(p.sa + row * p.sa_stride_m + static_cast<int64_t>(kb) * p.sa_stride_g);
   }
-  return __ldg(p.sa + row * p.sa_stride_m + static_cast<int64_t>(kb) * p.sa_stride_g);
 }
 
 __device__ __forceinline__ uint32_t pack2(__nv_bfloat16*, float a, float b) {

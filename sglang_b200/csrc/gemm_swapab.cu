@@ -308,10 +308,14 @@ gemm_block_fp8_swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __
               if (c < t.valid && kb0 + 4 * h < kb_end) v = __ldg(reinterpret_cast<const float4*>(src + kb0 + 4 * h));
               a[r][4 * h] = v.x; a[r][4 * h + 1] = v.y; a[r][4 * h + 2] = v.z; a[r][4 * h + 3] = v.w;
             }
+          } else if (p.sa_ue8m0) {
+#pragma unroll
+            for (int j = 0; j < kScaleGroup; ++j)
+              a[r][j] = (c < t.valid && kb0 + j < kb_end) ? load_sa<true>(p, t.row0 + c, kb0 + j) : 0.f;
           } else {
 #pragma unroll
             for (int j = 0; j < kScaleGroup; ++j)
-              a[r][j] = (c < t.valid && kb0 + j < kb_end) ? load_sa(p, t.row0 + c, kb0 + j) : 0.f;
+              a[r][j] = (c < t.valid && kb0 + j < kb_end) ? load_sa<false>(p, t.row0 + c, kb0 + j) : 0.f;
           }
         }
 #pragma unroll

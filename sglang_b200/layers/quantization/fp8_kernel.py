@@ -13,6 +13,7 @@ from typing import List, Tuple
 import torch
 
 from ...sgl_kernel import fp8_blockwise_scaled_mm, sgl_per_token_group_quant_fp8
+from ...sgl_kernel.gemm import launch_dense_mm
 from ... import _lib
 
 fp8_dtype = torch.float8_e4m3fn
@@ -110,12 +111,8 @@ def w8a8_block_fp8_matmul(A: torch.Tensor, B: torch.Tensor, As: torch.Tensor, Bs
         return C
     As2 = As.reshape(M, As.shape[-1]) if As.dim() != 2 else As
     dt = {torch.float32: _lib.DT_F32, torch.float16: _lib.DT_F16, torch.bfloat16: _lib.DT_BF16}[output_dtype]
-    with torch.cuda.device(A.device):
-        rc = _lib.lib().b200_fp8_blockwise_scaled_mm(
-            A.data_ptr(), K, B.data_ptr(), K,
-            As2.data_ptr(), As2.stride(0), As2.stride(1),
-            Bs.data_ptr(), Bs.stride(0), Bs.stride(1),
-            C.data_ptr(), N, dt, M, N, K, torch.cuda.current_stream(A.device).cuda_stream)
+    rc = launch_dense_mm((A.data_ptr(), K, B.data_ptr(), K, As2.data_ptr(), As2.stride(0), As2.stride(1),
+                          Bs.data_ptr(), Bs.stride(0), Bs.stride(1), C.data_ptr(), N, dt, M, N, K), M, N, K, A.device)
     _lib.check("w8a8_block_fp8_matmul", rc)
     return C
 

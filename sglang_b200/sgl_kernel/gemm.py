@@ -43,9 +43,10 @@ _PLAN: dict = {}
 
 
 def _splitk_plan(M: int, N: int, K: int, device: torch.device):
-    """Split count and workspace bytes the library chooses for this shape (1, 0 = no split); cached per
-    shape and device (a decode loop asks for the same few shapes every step)."""
-    if M > 128 or SPLIT_K_MODE != "auto":
+    """Split count and workspace bytes the library chooses for this shape (1, 0 = no split): all tiles
+    for decode-size M on narrow deep projections, only the last wave of tiles for large M when that wave
+    would be mostly empty.  Cached per shape and device."""
+    if SPLIT_K_MODE != "auto":
         return 1, 0
     idx = device.index if device.index is not None else torch.cuda.current_device()
     key = (M, N, K, idx)
@@ -71,6 +72,19 @@ def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
     if ws is None or ws.numel() < nbytes:
         ws = _WORKSPACE[key] = torch.empty(max(nbytes, 1 << 22), dtype=torch.uint8, device=device)
     return ws
+
+
+def launch_dense_mm(args: tuple, M: int, N: int, K: int, device: torch.device) -> int:
+    """Enqueue the dense block-scaled GEMM on the current stream of `device`; `args` are the C-ABI arguments up to
+    and including K.  Asks the split plan (cached) and passes a per-stream workspace when the library wants one:
+    k-blocks of tiles that would leave most SMs idle are spread over those SMs.  Returns the C-ABI status."""
+    with torch.cuda.device(device):
+        split_k, ws_bytes = _splitk_plan(M, N, K, device)
+        if split_k > 1:
+            ws = _workspace(device, ws_bytes)
+            return _lib.lib().b200_fp8_blockwise_scaled_mm_splitk(*args, 0, ws.data_ptr(), ws.numel(),
+                                                                  _stream_ptr(device))
+        return _lib.lib().b200_fp8_blockwise_scaled_mm(*args, _stream_ptr(device))
 
 
 def sgl_per_token_group_quant_fp8(
@@ -177,14 +191,6 @@ def fp8_blockwise_scaled_mm(
             scales_a.data_ptr(), scales_a.stride(0), scales_a.stride(1),
             scales_b.data_ptr(), scales_b.stride(1), scales_b.stride(0),
             out.data_ptr(), out.stride(0), _DT[out_dtype], M, N, K)
-    with torch.cuda.device(mat_a.device):
-        split_k, ws_bytes = _splitk_plan(M, N, K, mat_a.device)
-        if split_k > 1:
-            # decode-size batch on a narrow output: spread each tile's k-blocks over the idle SMs
-            ws = _workspace(mat_a.device, ws_bytes)
-            rc = _lib.lib().b200_fp8_blockwise_scaled_mm_splitk(*args, split_k, ws.data_ptr(), ws.numel(),
-                                                                _stream_ptr(mat_a.device))
-        else:
-            rc = _lib.lib().b200_fp8_blockwise_scaled_mm(*args, _stream_ptr(mat_a.device))
+    rc = launch_dense_mm(args, M, N, K, mat_a.device)
     _lib.check("fp8_blockwise_scaled_mm", rc)
     return out

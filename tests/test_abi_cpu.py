@@ -80,16 +80,27 @@ def test_split_k_plan_needs_no_device(lib):
     def plan(M, N, K, sms=148):
         s, b = ctypes.c_int(-1), ctypes.c_size_t(1)
         assert lib.b200_fp8_blockwise_scaled_mm_splitk_plan(M, N, K, sms, ctypes.byref(s), ctypes.byref(b)) == 0
-        assert b.value == (s.value * M * N * 4 if s.value > 1 else 0)
+        if M <= 128:
+            assert b.value == (s.value * M * N * 4 if s.value > 1 else 0)
         return s.value
     assert plan(16, 7168, 18432) == 2          # <= 64 tokens: 56 tiles of 128 weight rows on 148 SMs
     assert plan(128, 7168, 18432) == 5         # 65..128 tokens: 28 tiles of 128 x 256
     assert plan(1, 1536, 7168) == 7            # capped at eight k-blocks per CTA
     assert plan(16, 36864, 7168) == 1          # already more tiles than SMs
     assert plan(16, 7168, 2048) == 1           # too few k-blocks to pay for the reduce kernel
-    assert plan(129, 7168, 18432) == 1
+    assert plan(129, 7168, 18432) == 1         # 56 tiles: fewer than the SMs, nothing to balance
     assert plan(0, 7168, 18432) == 1
     assert plan(16, 7168, 18432, sms=0) == 2   # <= 0 means a 148-SM part
+    # large M: only the last, mostly empty wave of tiles is split
+    assert plan(4096, 7168, 18432) == 18       # 896 tiles of 128 x 256: six waves + 8 tiles -> 8 x 18 work units
+    s, b = ctypes.c_int(0), ctypes.c_size_t(0)
+    assert lib.b200_fp8_blockwise_scaled_mm_splitk_plan(4096, 7168, 18432, 148, ctypes.byref(s), ctypes.byref(b)) == 0
+    assert b.value == 8 * 18 * 128 * 256 * 4
+    assert plan(4096, 36864, 7168) == 7        # 4608 tiles: 31 waves + 20 tiles
+    assert plan(16384, 36864, 7168) == 1       # 18432 tiles: the last wave is 80 tiles, more than half of the SMs
+    assert plan(8192, 2560, 8192) == 3         # 640 tiles: four waves + 48 tiles -> 48 x 3 work units
+    assert plan(8192, 1280, 8192) == 6         # 320 tiles: two waves + 24 tiles
+    assert plan(4096, 7168, 1024) == 1         # too few k-blocks to divide
     s, b = ctypes.c_int(0), ctypes.c_size_t(0)
     assert lib.b200_fp8_blockwise_scaled_mm_splitk_plan(-1, 128, 128, 148, ctypes.byref(s), ctypes.byref(b)) < 0
     assert lib.b200_fp8_blockwise_scaled_mm_splitk_plan(1, 128, 128, 148, None, None) < 0

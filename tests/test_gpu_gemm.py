@@ -366,3 +366,40 @@ def test_deepgemm_shaped_linear():
     ref16 = O.block_fp8_linear(x.to(torch.float16), wq, ws, out_dtype=torch.float16)
     assert out16.dtype == torch.float16 and O.rel_l2(out16.float(), ref16.float()) <= TOL
     _status_ok()
+
+
+# ---------------------------------------------------------------------------- tail split (large M)
+@pytest.mark.parametrize("M,N,K", [(4096, 7168, 2048), (4100, 7168, 2048), (8192, 1280, 4096), (4096, 7040, 2176)])
+def test_tail_split_large_m(M, N, K):
+    """Shapes whose last wave of tiles is mostly empty: the wrapper asks the plan, the library splits only
+    those tiles' k-blocks.  Equal to the unsplit kernel to fp32 rounding (bit-identical outside the tail
+    tiles), deterministic, within tolerance of the fp32 reference; M and N need not be tile multiples."""
+    import ctypes
+    from sglang_b200 import _lib
+    from sglang_b200.sgl_kernel import gemm as G
+    from sglang_b200.layers.quantization.fp8_kernel import sglang_per_token_group_quant_fp8, w8a8_block_fp8_matmul
+    s, nb = ctypes.c_int(0), ctypes.c_size_t(0)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    assert _lib.lib().b200_fp8_blockwise_scaled_mm_splitk_plan(M, N, K, sms, ctypes.byref(s), ctypes.byref(nb)) == 0
+    if sms == 148:
+        assert s.value > 1 and nb.value > 0, "the case is meant to have a mostly empty last wave"
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+    a, sa = sglang_per_token_group_quant_fp8(x, 128)
+    wq, ws = O.gen_weight((N + 127) // 128 * 128, K, seed=5)
+    b, sb = wq[:N].contiguous().cuda(), ws.cuda()
+    out = w8a8_block_fp8_matmul(a, b, sa, sb, [128, 128], torch.bfloat16)
+    out2 = w8a8_block_fp8_matmul(a, b, sa, sb, [128, 128], torch.bfloat16)
+    assert same_bits(out, out2), "not deterministic"
+    G.SPLIT_K_MODE = "off"
+    try:
+        plain = w8a8_block_fp8_matmul(a, b, sa, sb, [128, 128], torch.bfloat16)
+    finally:
+        G.SPLIT_K_MODE = "auto"
+    _status_ok()
+    ref = _gpu_ref_fp32(a, b, sa, sb)
+    assert O.rel_l2(out.float().cpu(), ref.to(torch.bfloat16).float().cpu()) <= TOL
+    assert O.rel_l2(out.float().cpu(), plain.float().cpu()) <= 2e-4      # a bf16 ulp here and there in the tail tiles
+    if s.value > 1:
+        differing_rows = int((out != plain).any(dim=1).sum())
+        assert differing_rows <= 128 * 74, differing_rows   # only tail tiles (at most half a wave) may differ at all
