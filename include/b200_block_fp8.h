@@ -120,7 +120,7 @@ int b200_fp8_blockwise_scaled_mm(const void* a, int64_t lda, const void* b, int6
                                  int64_t M, int64_t N, int64_t K, void* stream);
 
 /*
- * The same product for small M (M <= 128), with the k-blocks of each output tile divided among
+ * The same product for small M (M <= 512), with the k-blocks of each output tile divided among
  * `split_k` CTAs so that the weight matrix streams through every SM even when the output has only a
  * few tiles (decode-size batches of the DeepSeek-V3 down projection: 28 tiles on 148 SMs).  Each CTA
  * writes fp32 partial sums to workspace[split][M][N]; a second kernel adds them in split order and

@@ -586,11 +586,12 @@ namespace {
 // that the 128-token x 128/256-column tiles of this file.
 inline bool dense_uses_swapab(int64_t M) { return M <= 64; }
 
-// Split count for small M: when the output has too few tiles for the SMs, the k-blocks of each tile
-// are spread over several CTAs so that the weights stream through all SMs at once.
+// Split count for small M (up to 512 rows): when the output has too few tiles for the SMs, the k-blocks of
+// each tile are spread over several CTAs so that the weights stream through all SMs at once.
 int plan_split_k(int64_t M, int64_t N, int64_t K, int sms) {
-  if (M > BLOCK_M || (N % 4) != 0) return 1;
-  const int64_t tiles = dense_uses_swapab(M) ? (N + 127) / 128 : (N + 255) / 256;
+  if (M > 4 * BLOCK_M || (N % 4) != 0) return 1;   // beyond 512 rows the tile count is never that small
+  const int64_t m_blocks = (M + BLOCK_M - 1) / BLOCK_M;
+  const int64_t tiles = dense_uses_swapab(M) ? (N + 127) / 128 : m_blocks * ((N + 255) / 256);
   const int64_t nkb = (K + BLOCK_K - 1) / BLOCK_K;
   // measured on DeepSeek-V3 shapes: below 32 k-blocks the launch and pipeline ramp dominate and the
   // extra reduce kernel costs more than the idle SMs

@@ -80,7 +80,7 @@ def test_split_k_plan_needs_no_device(lib):
     def plan(M, N, K, sms=148):
         s, b = ctypes.c_int(-1), ctypes.c_size_t(1)
         assert lib.b200_fp8_blockwise_scaled_mm_splitk_plan(M, N, K, sms, ctypes.byref(s), ctypes.byref(b)) == 0
-        if M <= 128:
+        if M <= 512:
             assert b.value == (s.value * M * N * 4 if s.value > 1 else 0)
         return s.value
     assert plan(16, 7168, 18432) == 2          # <= 64 tokens: 56 tiles of 128 weight rows on 148 SMs
@@ -88,7 +88,8 @@ def test_split_k_plan_needs_no_device(lib):
     assert plan(1, 1536, 7168) == 7            # capped at eight k-blocks per CTA
     assert plan(16, 36864, 7168) == 1          # already more tiles than SMs
     assert plan(16, 7168, 2048) == 1           # too few k-blocks to pay for the reduce kernel
-    assert plan(129, 7168, 18432) == 1         # 56 tiles: fewer than the SMs, nothing to balance
+    assert plan(129, 7168, 18432) == 2         # two row blocks x 28: 56 tiles of 128 x 256
+    assert plan(512, 7168, 18432) == 1         # 112 tiles: most SMs busy already
     assert plan(0, 7168, 18432) == 1
     assert plan(16, 7168, 18432, sms=0) == 2   # <= 0 means a 148-SM part
     # large M: only the last, mostly empty wave of tiles is split

@@ -135,7 +135,7 @@ def test_split_k_is_deterministic_and_matches_unsplit_to_rounding():
     assert O.rel_l2(c4a.cpu(), c1.cpu()) <= 1e-6
 
 
-@pytest.mark.parametrize("M", [1, 16, 64, 128])
+@pytest.mark.parametrize("M", [1, 16, 64, 128, 256])
 @pytest.mark.parametrize("N,K", [(7168, 18432), (36864, 7168), (1536, 7168)])
 def test_split_k_auto_decode_shapes(M, N, K):
     """DeepSeek-V3 down / gate_up / q_a projections at decode-size batches through the
