@@ -241,6 +241,18 @@ int b200_silu_and_mul(const void* x, void* out, int64_t rows, int64_t d, int dty
 int b200_apply_shuffle_mul_sum(const void* input, void* output, const int32_t* permutation, const void* factors,
                                int64_t m, int64_t topk, int64_t row_len, int dtype, void* stream);
 
+/*
+ * Router: weights = softmax(gating_output.float(), dim=-1), then the topk largest per token and their expert
+ * ids (ties to the lower id); with renormalize != 0 the k weights are divided by their sum.
+ * Replaces: topk_softmax (sgl-kernel/csrc/moe/moe_topk_softmax_kernels.cu:502-570, schema
+ * common_extension.cc:172) -- the kernel behind fused_topk (python/sglang/srt/layers/moe/topk.py:337-363).
+ * gating_output [num_tokens, num_experts] fp32 / fp16 / bf16, rows row_stride elements apart;
+ * topk_weights [num_tokens, topk] fp32, topk_ids [num_tokens, topk] int32.  num_experts <= 1024, topk <= 32.
+ */
+int b200_topk_softmax(const void* gating_output, int dtype, int64_t row_stride, float* topk_weights,
+                      int32_t* topk_ids, int64_t num_tokens, int num_experts, int topk, int renormalize,
+                      void* stream);
+
 /* Reads and clears this device's GEMM status word (0 = ok; non-zero = a bounded device-side
  * wait gave up, value encodes which).  Synchronises the device.  No reference counterpart. */
 int b200_gemm_device_status(int* status_out);

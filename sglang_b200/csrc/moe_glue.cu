@@ -407,3 +407,120 @@ extern "C" int b200_apply_shuffle_mul_sum(const void* input, void* output, const
   B200_CUDA_TRY(cudaGetLastError());
   return B200_OK;
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// Router: softmax over the experts, then the top-k probabilities and their expert ids
+// (sgl-kernel/csrc/moe/moe_topk_softmax_kernels.cu:502-570; torch form: softmax(logits.float()) -> topk,
+// python/sglang/srt/layers/moe/topk.py:284-302).  One warp per token, up to 32 experts per lane in registers;
+// ties go to the lower expert id.  With `renormalize` the k weights are divided by their sum.
+namespace b200 {
+namespace {
+
+constexpr int kRouterMaxPerLane = 32;   // experts <= 1024
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T, int PER_LANE>
+__global__ void __launch_bounds__(128) topk_softmax_kernel(const T* __restrict__ logits, float* __restrict__ weights,
+                                                           int32_t* __restrict__ ids, int64_t num_tokens,
+                                                           int num_experts, int topk, int64_t logits_stride,
+                                                           int renormalize) {
+  const int lane = threadIdx.x & 31;
+  const int64_t token = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (token >= num_tokens) return;
+  const T* row = logits + token * logits_stride;
+  float v[PER_LANE];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < PER_LANE; ++i) {
+    const int e = i * 32 + lane;
+    v[i] = e < num_experts ? to_f32<T>(row[e]) : -INFINITY;
+    mx = fmaxf(mx, v[i]);
+  }
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < PER_LANE; ++i) {
+    const bool real = (i * 32 + lane) < num_experts;
+    v[i] = real ? expf(v[i] - mx) : -1.f;   // padding can never be picked
+    sum += real ? v[i] : 0.f;
+  }
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+  const float inv = 1.0f / sum;
+  float picked_sum = 0.f;
+  float my_w = 0.f;      // lane j keeps the j-th pick (topk <= 32)
+  int my_id = 0;
+  for (int j = 0; j < topk; ++j) {
+    // lane-local best (value descending, expert id ascending), then the warp's best
+    float best = -1.f;
+    int best_e = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i) {
+      const int e = i * 32 + lane;
+      if (v[i] > best) { best = v[i]; best_e = e; }   // equal values keep the earlier (lower) id
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, off);
+      if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+    }
+    if ((best_e & 31) == lane) {
+#pragma unroll
+      for (int i = 0; i < PER_LANE; ++i)
+        if (i == (best_e >> 5)) v[i] = -1.f;   // taken
+    }
+    const float w = best * inv;
+    picked_sum += w;
+    if (lane == j) { my_w = w; my_id = best_e; }
+  }
+  if (lane < topk) {
+    weights[token * topk + lane] = renormalize ? my_w / picked_sum : my_w;
+    ids[token * topk + lane] = my_id;
+  }
+}
+
+template <typename T>
+int launch_router(const void* logits, float* weights, int32_t* ids, int64_t num_tokens, int num_experts, int topk,
+                  int64_t stride, int renormalize, cudaStream_t st) {
+  const unsigned blocks = static_cast<unsigned>((num_tokens + 3) / 4);
+  const T* lp = static_cast<const T*>(logits);
+  const int per_lane = (num_experts + 31) / 32;
+  if (per_lane <= 2) topk_softmax_kernel<T, 2><<<blocks, 128, 0, st>>>(lp, weights, ids, num_tokens, num_experts, topk, stride, renormalize);
+  else if (per_lane <= 8) topk_softmax_kernel<T, 8><<<blocks, 128, 0, st>>>(lp, weights, ids, num_tokens, num_experts, topk, stride, renormalize);
+  else topk_softmax_kernel<T, kRouterMaxPerLane><<<blocks, 128, 0, st>>>(lp, weights, ids, num_tokens, num_experts, topk, stride, renormalize);
+  B200_CUDA_TRY(cudaGetLastError());
+  return B200_OK;
+}
+
+}  // namespace
+}  // namespace b200
+
+extern "C" int b200_topk_softmax(const void* gating_output, int dtype, int64_t row_stride, float* topk_weights,
+                                 int32_t* topk_ids, int64_t num_tokens, int num_experts, int topk, int renormalize,
+                                 void* stream) {
+  using namespace b200;
+  if (num_tokens < 0 || num_experts <= 0 || topk <= 0) return B200_ERR_BAD_SHAPE;
+  if (topk > num_experts || topk > 32) return B200_ERR_BAD_SHAPE;
+  if (num_experts > 32 * kRouterMaxPerLane) return B200_ERR_TOO_LARGE;
+  if (num_tokens == 0) return B200_OK;
+  if (!gating_output || !topk_weights || !topk_ids) return B200_ERR_NULL_PTR;
+  if (row_stride < num_experts) return B200_ERR_BAD_STRIDE;
+  if (num_tokens > 0x7fffffffLL) return B200_ERR_TOO_LARGE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case B200_DT_F32: return launch_router<float>(gating_output, topk_weights, topk_ids, num_tokens, num_experts, topk, row_stride, renormalize, st);
+    case B200_DT_F16: return launch_router<__half>(gating_output, topk_weights, topk_ids, num_tokens, num_experts, topk, row_stride, renormalize, st);
+    case B200_DT_BF16: return launch_router<__nv_bfloat16>(gating_output, topk_weights, topk_ids, num_tokens, num_experts, topk, row_stride, renormalize, st);
+    default: return B200_ERR_BAD_DTYPE;
+  }
+}

@@ -9,7 +9,7 @@ import torch
 
 from .gemm import fp8_blockwise_scaled_mm, sgl_per_token_group_quant_fp8
 from .moe import (apply_shuffle_mul_sum, fp8_blockwise_scaled_grouped_mm, prepare_moe_input, shuffle_rows,
-                  shuffle_rows_into, silu_and_mul)
+                  shuffle_rows_into, silu_and_mul, topk_softmax)
 
 _SCHEMAS = {
     "fp8_blockwise_scaled_mm":
@@ -27,6 +27,7 @@ _SCHEMAS = {
     "shuffle_rows": "(Tensor input, Tensor dst2src_map, Tensor output) -> ()",
     "apply_shuffle_mul_sum": "(Tensor input, Tensor output, Tensor permutation, Tensor? factors) -> ()",
     "silu_and_mul": "(Tensor out, Tensor input) -> ()",
+    "topk_softmax": "(Tensor! topk_weights, Tensor! topk_indices, Tensor gating_output, bool renormalize) -> ()",
 }
 
 
@@ -48,6 +49,7 @@ _IMPLS = {
     "shuffle_rows": shuffle_rows_into,
     "apply_shuffle_mul_sum": apply_shuffle_mul_sum,
     "silu_and_mul": _silu_and_mul_op,
+    "topk_softmax": topk_softmax,
 }
 
 
@@ -86,4 +88,5 @@ def register_torch_ops() -> None:
 register_torch_ops()
 
 __all__ = ["fp8_blockwise_scaled_mm", "sgl_per_token_group_quant_fp8", "fp8_blockwise_scaled_grouped_mm",
-           "prepare_moe_input", "shuffle_rows", "apply_shuffle_mul_sum", "silu_and_mul", "register_torch_ops"]
+           "prepare_moe_input", "shuffle_rows", "apply_shuffle_mul_sum", "silu_and_mul", "topk_softmax",
+           "register_torch_ops"]

@@ -18,6 +18,34 @@ from .. import _lib
 from .gemm import _DT, FP8, _check, _stream_ptr
 
 
+def topk_softmax(topk_weights: torch.Tensor, topk_ids: torch.Tensor, gating_output: torch.Tensor,
+                 renormalize: bool = False) -> None:
+    """In place: topk_weights [m, k] fp32 <- the k largest softmax probabilities of each row of
+    gating_output [m, E] (fp32 / fp16 / bf16), topk_ids [m, k] int32 <- their expert ids.
+    Mirrors sgl_kernel.topk_softmax (sgl-kernel/python/sgl_kernel/moe.py:28-36) and the checks of its C++ entry
+    (sgl-kernel/csrc/moe/moe_topk_softmax_kernels.cu:508-529)."""
+    _check(gating_output.dtype in _DT, "gating_output must be float32, float16, or bfloat16")
+    _check(gating_output.dim() == 2, "gating_output must be 2D tensor [num_tokens, num_experts]")
+    _check(topk_weights.dim() == 2, "topk_weights must be 2D tensor [num_tokens, topk]")
+    _check(topk_ids.dim() == 2, "topk_indices must be 2D tensor [num_tokens, topk]")
+    _check(gating_output.size(0) == topk_weights.size(0),
+           "First dimension of topk_weights must match num_tokens in gating_output")
+    _check(gating_output.size(0) == topk_ids.size(0),
+           "First dimension of topk_indices must match num_tokens in gating_output")
+    _check(topk_weights.size(-1) == topk_ids.size(-1), "Second dimension of topk_indices must match topk in topk_weights")
+    _check(topk_weights.size(-1) <= gating_output.size(-1), "topk must be less than or equal to num_experts")
+    _check(gating_output.is_cuda and topk_weights.is_cuda and topk_ids.is_cuda, "tensors must be CUDA tensors")
+    _check(topk_weights.dtype == torch.float32 and topk_weights.is_contiguous(), "topk_weights must be contiguous float32")
+    _check(topk_ids.dtype == torch.int32 and topk_ids.is_contiguous(), "topk_indices must be contiguous int32")
+    _check(gating_output.stride(1) == 1, "gating_output rows must be contiguous")
+    m, E = gating_output.shape
+    with torch.cuda.device(gating_output.device):
+        rc = _lib.lib().b200_topk_softmax(gating_output.data_ptr(), _DT[gating_output.dtype], gating_output.stride(0),
+                                          topk_weights.data_ptr(), topk_ids.data_ptr(), m, E, topk_weights.size(1),
+                                          int(bool(renormalize)), _stream_ptr(gating_output.device))
+    _lib.check("topk_softmax", rc)
+
+
 def prepare_moe_input(topk_ids, expert_offsets, problem_sizes1, problem_sizes2, input_permutation,
                       output_permutation, num_experts, n, k, blockscale_offsets: Optional[torch.Tensor] = None):
     """In place.  topk_ids [m, topk] int32; expert_offsets [E+1]; problem_sizes* [E,3];

@@ -125,6 +125,7 @@ def test_operator_schemas_and_shape_functions():
     assert "Tensor mat_a, Tensor mat_b, Tensor scales_a, Tensor scales_b, ScalarType out_dtype" in schema
     assert "bool scale_ue8m0" in str(ops.sgl_per_token_group_quant_fp8.default._schema)
     assert "Tensor? blockscale_offsets" in str(ops.prepare_moe_input.default._schema)
+    assert "Tensor gating_output, bool renormalize" in str(ops.topk_softmax.default._schema)
     fp8 = torch.float8_e4m3fn
     a = torch.empty(64, 7168, dtype=fp8, device="meta")
     b = torch.empty(4096, 7168, dtype=fp8, device="meta").t()

@@ -218,3 +218,57 @@ def test_fp8_moe_method_apply():
     scaled = method.apply(layer, a.cuda(), (w.cuda(), ids.cuda(), None), routed_scaling_factor=2.5)
     assert same_bits(scaled, direct * 2.5)
     _status_ok()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("m,E,topk", [(1, 8, 2), (37, 64, 6), (513, 256, 8), (100, 160, 6), (9, 1024, 32), (33, 4, 4)])
+@pytest.mark.parametrize("renorm", [False, True])
+def test_topk_softmax_router(m, E, topk, dtype, renorm):
+    """softmax(logits.float()) -> top-k against the torch form (python/sglang/srt/layers/moe/topk.py:284-302):
+    weights to 1e-6 relative, ids exact wherever the k-th and (k+1)-th probabilities are not within rounding."""
+    from sglang_b200.layers.moe.topk import fused_topk
+    g = torch.Generator().manual_seed(m * 7 + E + topk)
+    logits = (torch.randn(m, E, generator=g) * 3).to(dtype)
+    w, ids = fused_topk(torch.empty(m, 1, device="cuda"), logits.cuda(), topk, renorm)
+    assert w.dtype == torch.float32 and ids.dtype == torch.int32 and w.shape == (m, topk)
+    probs = torch.softmax(logits.float(), dim=-1)
+    w_ref, ids_ref = torch.topk(probs, topk, dim=-1)
+    if renorm:
+        w_ref = w_ref / w_ref.sum(dim=-1, keepdim=True)
+    torch.testing.assert_close(w.cpu(), w_ref, rtol=2e-6, atol=1e-9)
+    # the picked experts carry the picked probabilities; exact id equality except at rounding-level ties
+    picked = probs.gather(1, ids.cpu().long())
+    if renorm:
+        picked = picked / picked.sum(dim=-1, keepdim=True)
+    torch.testing.assert_close(picked, w_ref, rtol=2e-6, atol=1e-9)
+    srt = torch.sort(probs, dim=-1, descending=True).values
+    clear = (srt[:, :-1] - srt[:, 1:]).abs().min(dim=-1).values > 1e-7 if E > 1 else torch.ones(m, dtype=torch.bool)
+    assert torch.equal(ids.cpu()[clear], ids_ref.to(torch.int32)[clear])
+    assert bool((ids.cpu().sort(dim=-1).values.diff(dim=-1) != 0).all()) if topk > 1 else True
+
+
+def test_topk_softmax_ties_and_moe_pipeline():
+    """Equal logits: the lower expert ids win, in order.  Then router -> fused experts on the device, equal to the
+    same call fed with the oracle's routing."""
+    from sglang_b200.layers.moe.topk import fused_topk
+    from sglang_b200.layers.moe.cutlass_moe import fused_experts_block_fp8
+    flat = torch.zeros(3, 16, device="cuda")
+    w, ids = fused_topk(flat, flat, 4, False)
+    assert torch.equal(ids.cpu(), torch.arange(4, dtype=torch.int32).repeat(3, 1))
+    torch.testing.assert_close(w.cpu(), torch.full((3, 4), 1 / 16))
+    g = torch.Generator().manual_seed(3)
+    E, H, I, m, topk = 8, 256, 128, 40, 2
+    w13q, w13s, w2q, w2s = [], [], [], []
+    for _ in range(E):
+        q_, s_ = O.per_block_cast_to_fp8(torch.randn(2 * I, H, generator=g) * 0.05); w13q.append(q_); w13s.append(s_)
+        q_, s_ = O.per_block_cast_to_fp8(torch.randn(H, I, generator=g) * 0.05); w2q.append(q_); w2s.append(s_)
+    w13q, w13s, w2q, w2s = (torch.stack(v).cuda() for v in (w13q, w13s, w2q, w2s))
+    a = torch.randn(m, H, generator=g).to(torch.bfloat16).cuda()
+    score = torch.randn(m, E, generator=g)
+    tw, ti = fused_topk(a, score.cuda(), topk, False)
+    tw_ref, ti_ref = O.fused_topk_native(score, topk)
+    assert torch.equal(ti.cpu(), ti_ref)
+    out = fused_experts_block_fp8(a, w13q, w2q, w13s, w2s, tw, ti)
+    out_ref = fused_experts_block_fp8(a, w13q, w2q, w13s, w2s, tw_ref.cuda(), ti_ref.cuda())
+    assert O.rel_l2(out.float().cpu(), out_ref.float().cpu()) <= 1e-3
+    _status_ok()
