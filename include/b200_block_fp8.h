@@ -242,6 +242,19 @@ int b200_apply_shuffle_mul_sum(const void* input, void* output, const int32_t* p
                                int64_t m, int64_t topk, int64_t row_len, int dtype, void* stream);
 
 /*
+ * DeepSeek-V3 gate: s = sigmoid(gating_output); choice = s + bias; a group's score is the sum of its two
+ * largest choice values; the topk_group best groups stay; the topk largest choice values among their experts
+ * are picked (ties to the lower index); topk_weights = s[picked] / sum(s[picked]).
+ * Replaces: moe_fused_gate (sgl-kernel/csrc/moe/moe_fused_gate.cu:56-260, schema common_extension.cc:176-179)
+ * = biased_grouped_topk_impl with renormalize (python/sglang/srt/layers/moe/topk.py:462-530), without fused
+ * shared experts.  gating_output [num_tokens, num_experts] fp32, bias [num_experts] fp32;
+ * num_expert_group <= 32 divides num_experts (<= 1024), at least two experts per group, topk <= 32.
+ */
+int b200_moe_fused_gate(const float* gating_output, int64_t row_stride, const float* bias, float* topk_weights,
+                        int32_t* topk_ids, int64_t num_tokens, int num_experts, int num_expert_group,
+                        int topk_group, int topk, void* stream);
+
+/*
  * Router: weights = softmax(gating_output.float(), dim=-1), then the topk largest per token and their expert
  * ids (ties to the lower id); with renormalize != 0 the k weights are divided by their sum.
  * Replaces: topk_softmax (sgl-kernel/csrc/moe/moe_topk_softmax_kernels.cu:502-570, schema

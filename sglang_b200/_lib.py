@@ -58,6 +58,8 @@ _SIGNATURES = {
     "b200_moe_prepare_noalloc": (c_int, [c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                          c_void_p, c_void_p, c_void_p, c_void_p]),
     "b200_topk_softmax": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
+    "b200_moe_fused_gate": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int,
+                                    c_void_p]),
     "b200_shuffle_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "b200_silu_and_mul": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
     "b200_apply_shuffle_mul_sum": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,

@@ -524,3 +524,130 @@ extern "C" int b200_topk_softmax(const void* gating_output, int dtype, int64_t r
     default: return B200_ERR_BAD_DTYPE;
   }
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// DeepSeek-V3 gate: sigmoid scores, a per-expert bias used for the CHOICE only, group-limited top-k
+// (sgl-kernel/csrc/moe/moe_fused_gate.cu:56-260; torch form biased_grouped_topk_impl,
+// python/sglang/srt/layers/moe/topk.py:462-530):
+//   s = sigmoid(x);  c = s + bias;  group score = sum of the two largest c in the group;
+//   keep the topk_group best groups;  pick the topk largest c among their experts;
+//   weights = s[picked] / sum(s[picked]).
+// One warp per token; lane g scores group g (num_expert_group <= 32); ties go to the lower index.
+namespace b200 {
+namespace {
+
+template <int PER_LANE>
+__global__ void __launch_bounds__(128) fused_gate_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
+                                                         float* __restrict__ weights, int32_t* __restrict__ ids,
+                                                         int64_t num_tokens, int num_experts, int num_groups,
+                                                         int topk_group, int topk, int64_t logits_stride) {
+  extern __shared__ float smem_choice[];   // [warps][num_experts]
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  const int64_t token = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + wib;
+  if (token >= num_tokens) return;
+  float* choice = smem_choice + wib * num_experts;
+  const float* row = logits + token * logits_stride;
+  const int group_size = num_experts / num_groups;
+  float s[PER_LANE], c[PER_LANE];
+#pragma unroll
+  for (int i = 0; i < PER_LANE; ++i) {
+    const int e = i * 32 + lane;
+    if (e < num_experts) {
+      s[i] = 1.0f / (1.0f + expf(-row[e]));
+      c[i] = s[i] + bias[e];
+      choice[e] = c[i];
+    } else {
+      s[i] = 0.f;
+      c[i] = -INFINITY;
+    }
+  }
+  __syncwarp();
+  // lane g: sum of the two largest choice scores of group g
+  float gscore = -INFINITY;
+  if (lane < num_groups) {
+    float m1 = -INFINITY, m2 = -INFINITY;
+    for (int j = 0; j < group_size; ++j) {
+      const float x = choice[lane * group_size + j];
+      if (x > m1) { m2 = m1; m1 = x; } else if (x > m2) { m2 = x; }
+    }
+    gscore = m1 + m2;
+  }
+  // the topk_group best groups -> bit mask
+  uint32_t keep = 0;
+  for (int j = 0; j < topk_group; ++j) {
+    float best = gscore;
+    int best_g = lane < num_groups ? lane : 0x7fffffff;
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+      const int og = __shfl_xor_sync(0xffffffffu, best_g, off);
+      if (ob > best || (ob == best && og < best_g)) { best = ob; best_g = og; }
+    }
+    keep |= 1u << best_g;
+    if (lane == best_g) gscore = -INFINITY;
+  }
+#pragma unroll
+  for (int i = 0; i < PER_LANE; ++i) {
+    const int e = i * 32 + lane;
+    if (e < num_experts && !((keep >> (e / group_size)) & 1u)) c[i] = -INFINITY;
+  }
+  float picked_sum = 0.f, my_w = 0.f;
+  int my_id = 0;
+  for (int j = 0; j < topk; ++j) {
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+    float best_s = 0.f;
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i) {
+      const int e = i * 32 + lane;
+      if (e < num_experts && c[i] > best) { best = c[i]; best_e = e; best_s = s[i]; }   // equal values keep the lower id
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, off);
+      const float os = __shfl_xor_sync(0xffffffffu, best_s, off);
+      if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; best_s = os; }
+    }
+    if ((best_e & 31) == lane) {
+#pragma unroll
+      for (int i = 0; i < PER_LANE; ++i)
+        if (i == (best_e >> 5)) c[i] = -INFINITY;   // taken
+    }
+    picked_sum += best_s;
+    if (lane == j) { my_w = best_s; my_id = best_e; }
+  }
+  if (lane < topk) {
+    weights[token * topk + lane] = my_w / picked_sum;
+    ids[token * topk + lane] = my_id;
+  }
+}
+
+}  // namespace
+}  // namespace b200
+
+extern "C" int b200_moe_fused_gate(const float* gating_output, int64_t row_stride, const float* bias, float* topk_weights,
+                                   int32_t* topk_ids, int64_t num_tokens, int num_experts, int num_expert_group,
+                                   int topk_group, int topk, void* stream) {
+  using namespace b200;
+  if (num_tokens < 0 || num_experts <= 0 || num_expert_group <= 0 || topk_group <= 0 || topk <= 0) return B200_ERR_BAD_SHAPE;
+  if (num_experts % num_expert_group != 0 || num_expert_group > 32 || topk_group > num_expert_group) return B200_ERR_BAD_SHAPE;
+  const int group_size = num_experts / num_expert_group;
+  if (group_size < 2 || topk > 32 || topk > topk_group * group_size) return B200_ERR_BAD_SHAPE;
+  if (num_experts > 1024) return B200_ERR_TOO_LARGE;
+  if (num_tokens == 0) return B200_OK;
+  if (!gating_output || !bias || !topk_weights || !topk_ids) return B200_ERR_NULL_PTR;
+  if (row_stride < num_experts) return B200_ERR_BAD_STRIDE;
+  if (num_tokens > 0x7fffffffLL) return B200_ERR_TOO_LARGE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned blocks = static_cast<unsigned>((num_tokens + 3) / 4);
+  const size_t smem = 4 * static_cast<size_t>(num_experts) * sizeof(float);
+  if (num_experts <= 256)
+    fused_gate_kernel<8><<<blocks, 128, smem, st>>>(gating_output, bias, topk_weights, topk_ids, num_tokens, num_experts,
+                                                   num_expert_group, topk_group, topk, row_stride);
+  else
+    fused_gate_kernel<32><<<blocks, 128, smem, st>>>(gating_output, bias, topk_weights, topk_ids, num_tokens, num_experts,
+                                                    num_expert_group, topk_group, topk, row_stride);
+  B200_CUDA_TRY(cudaGetLastError());
+  return B200_OK;
+}

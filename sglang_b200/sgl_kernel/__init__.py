@@ -9,7 +9,7 @@ import torch
 
 from .gemm import fp8_blockwise_scaled_mm, sgl_per_token_group_quant_fp8
 from .moe import (apply_shuffle_mul_sum, fp8_blockwise_scaled_grouped_mm, prepare_moe_input, shuffle_rows,
-                  shuffle_rows_into, silu_and_mul, topk_softmax)
+                  shuffle_rows_into, silu_and_mul, topk_softmax, moe_fused_gate)
 
 _SCHEMAS = {
     "fp8_blockwise_scaled_mm":
@@ -89,4 +89,4 @@ register_torch_ops()
 
 __all__ = ["fp8_blockwise_scaled_mm", "sgl_per_token_group_quant_fp8", "fp8_blockwise_scaled_grouped_mm",
            "prepare_moe_input", "shuffle_rows", "apply_shuffle_mul_sum", "silu_and_mul", "topk_softmax",
-           "register_torch_ops"]
+           "moe_fused_gate", "register_torch_ops"]

@@ -46,6 +46,33 @@ def topk_softmax(topk_weights: torch.Tensor, topk_ids: torch.Tensor, gating_outp
     _lib.check("topk_softmax", rc)
 
 
+def moe_fused_gate(input_tensor: torch.Tensor, bias: torch.Tensor, num_expert_group: int, topk_group: int, topk: int,
+                   num_fused_shared_experts: int = 0, routed_scaling_factor: float = 0):
+    """DeepSeek-V3 gate (sigmoid scores, choice bias, group-limited top-k, weights renormalised): returns
+    (topk_weights fp32 [m, k], topk_ids int32 [m, k]).  Mirrors sgl_kernel.moe_fused_gate
+    (sgl-kernel/python/sgl_kernel/moe.py:39-66); the fused shared expert of the reference
+    (num_fused_shared_experts > 0, which is where routed_scaling_factor enters) is not built."""
+    if num_fused_shared_experts:
+        raise NotImplementedError("fused shared experts are not built")
+    _check(input_tensor.is_cuda and bias.is_cuda, "tensors must be CUDA tensors")
+    _check(input_tensor.dim() == 2 and bias.dim() == 1 and bias.numel() == input_tensor.size(1), "shape mismatch")
+    _check(input_tensor.dtype == torch.float32 and bias.dtype == torch.float32, "input and bias must be float32")
+    _check(input_tensor.stride(1) == 1 and bias.is_contiguous(), "rows must be contiguous")
+    m, E = input_tensor.shape
+    _check(E % num_expert_group == 0 and num_expert_group <= 32 and E // num_expert_group >= 2 and E <= 1024,
+           "unsupported expert grouping")
+    _check(0 < topk_group <= num_expert_group and 0 < topk <= min(32, topk_group * (E // num_expert_group)),
+           "unsupported topk / topk_group")
+    weights = torch.empty((m, topk), dtype=torch.float32, device=input_tensor.device)
+    ids = torch.empty((m, topk), dtype=torch.int32, device=input_tensor.device)
+    with torch.cuda.device(input_tensor.device):
+        rc = _lib.lib().b200_moe_fused_gate(input_tensor.data_ptr(), input_tensor.stride(0), bias.data_ptr(),
+                                            weights.data_ptr(), ids.data_ptr(), m, E, num_expert_group, topk_group, topk,
+                                            _stream_ptr(input_tensor.device))
+    _lib.check("moe_fused_gate", rc)
+    return weights, ids
+
+
 def prepare_moe_input(topk_ids, expert_offsets, problem_sizes1, problem_sizes2, input_permutation,
                       output_permutation, num_experts, n, k, blockscale_offsets: Optional[torch.Tensor] = None):
     """In place.  topk_ids [m, topk] int32; expert_offsets [E+1]; problem_sizes* [E,3];

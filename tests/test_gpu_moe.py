@@ -272,3 +272,37 @@ def test_topk_softmax_ties_and_moe_pipeline():
     out_ref = fused_experts_block_fp8(a, w13q, w2q, w13s, w2s, tw_ref.cuda(), ti_ref.cuda())
     assert O.rel_l2(out.float().cpu(), out_ref.float().cpu()) <= 1e-3
     _status_ok()
+
+
+def _biased_grouped_topk_ref(logits, bias, G, topk_group, topk):
+    """The torch form of python/sglang/srt/layers/moe/topk.py:477-524 (renormalize=True, no shared experts)."""
+    scores = logits.sigmoid()
+    m, E = scores.shape
+    choice = scores + bias.unsqueeze(0)
+    group_scores = choice.view(m, G, -1).topk(2, dim=-1)[0].sum(dim=-1)
+    group_idx = torch.topk(group_scores, k=topk_group, dim=-1, sorted=False)[1]
+    group_mask = torch.zeros_like(group_scores).scatter_(1, group_idx, 1)
+    score_mask = group_mask.unsqueeze(-1).expand(m, G, E // G).reshape(m, -1)
+    tmp = choice.masked_fill(~score_mask.bool(), float("-inf"))
+    _, ids = torch.topk(tmp, k=topk, dim=-1)
+    w = scores.gather(1, ids)
+    return w / w.sum(dim=-1, keepdim=True), ids
+
+
+@pytest.mark.parametrize("m,E,G,topk_group,topk", [(1, 256, 8, 4, 8), (300, 256, 8, 4, 8), (77, 64, 4, 2, 6),
+                                                   (40, 512, 16, 4, 8), (5, 16, 8, 8, 16), (64, 128, 32, 3, 5)])
+def test_moe_fused_gate(m, E, G, topk_group, topk):
+    from sglang_b200.sgl_kernel import moe_fused_gate
+    g = torch.Generator().manual_seed(m + E + G)
+    logits = torch.randn(m, E, generator=g) * 2
+    bias = torch.randn(E, generator=g) * 0.1
+    w, ids = moe_fused_gate(logits.cuda(), bias.cuda(), G, topk_group, topk)
+    w_ref, ids_ref = _biased_grouped_topk_ref(logits, bias, G, topk_group, topk)
+    # same SET of experts per token (the reference does not order them), same weights per expert
+    got = torch.zeros(m, E).scatter_(1, ids.cpu().long(), w.cpu())
+    want = torch.zeros(m, E).scatter_(1, ids_ref, w_ref)
+    assert torch.equal(got != 0, want != 0)
+    torch.testing.assert_close(got, want, rtol=3e-6, atol=1e-8)
+    torch.testing.assert_close(w.sum(dim=-1).cpu(), torch.ones(m), rtol=1e-5, atol=1e-6)
+    with pytest.raises(NotImplementedError):
+        moe_fused_gate(logits.cuda(), bias.cuda(), G, topk_group, topk, num_fused_shared_experts=1, routed_scaling_factor=2.5)
