@@ -306,3 +306,42 @@ def test_moe_fused_gate(m, E, G, topk_group, topk):
     torch.testing.assert_close(w.sum(dim=-1).cpu(), torch.ones(m), rtol=1e-5, atol=1e-6)
     with pytest.raises(NotImplementedError):
         moe_fused_gate(logits.cuda(), bias.cuda(), G, topk_group, topk, num_fused_shared_experts=1, routed_scaling_factor=2.5)
+
+
+def test_checkpoint_to_moe_layer(tmp_path):
+    """A synthetic safetensors checkpoint (Hugging Face naming) -> Fp8MoEMethod parameters on the device for one
+    expert-parallel rank's experts -> router -> fused experts, against the oracle on the same tensors."""
+    import json
+    from safetensors.torch import save_file
+    from sglang_b200.layers.moe.topk import fused_topk
+    from sglang_b200.layers.quantization.fp8 import Fp8MoEMethod
+    from sglang_b200.model_loader.block_fp8_checkpoint import (SafetensorsIndex, expert_range, load_experts,
+                                                               read_quantization_config)
+    E, H, I, m, topk = 4, 256, 128, 32, 2
+    g = torch.Generator().manual_seed(21)
+    tensors, w13q, w13s, w2q, w2s = {}, [], [], [], []
+    for e in range(E):
+        gq, gs = O.per_block_cast_to_fp8(torch.randn(I, H, generator=g) * 0.05)
+        uq, us = O.per_block_cast_to_fp8(torch.randn(I, H, generator=g) * 0.05)
+        dq, ds = O.per_block_cast_to_fp8(torch.randn(H, I, generator=g) * 0.05)
+        p = f"model.layers.3.mlp.experts.{e}."
+        tensors.update({p + "gate_proj.weight": gq, p + "gate_proj.weight_scale_inv": gs.contiguous(),
+                        p + "up_proj.weight": uq, p + "up_proj.weight_scale_inv": us.contiguous(),
+                        p + "down_proj.weight": dq, p + "down_proj.weight_scale_inv": ds.contiguous()})
+        w13q.append(torch.cat([gq, uq])); w13s.append(torch.cat([gs, us])); w2q.append(dq); w2s.append(ds)
+    save_file(tensors, str(tmp_path / "model.safetensors"))
+    (tmp_path / "config.json").write_text(json.dumps({"quantization_config": {
+        "quant_method": "fp8", "activation_scheme": "dynamic", "weight_block_size": [128, 128]}}))
+    method = Fp8MoEMethod(read_quantization_config(str(tmp_path)))
+    layer = torch.nn.Module()
+    method.create_weights(layer, E, H, I, torch.bfloat16, device="cuda")
+    load_experts(method, layer, SafetensorsIndex(str(tmp_path)), "model.layers.3.mlp.experts", expert_range(E, 0, 1))
+    a = torch.randn(m, H, generator=g).to(torch.bfloat16)
+    score = torch.randn(m, E, generator=g)
+    tw, ti = fused_topk(a.cuda(), score.cuda(), topk, False)
+    out = method.apply(layer, a.cuda(), (tw, ti, None)).cpu()
+    tw_ref, ti_ref = O.fused_topk_native(score, topk)
+    ref = O.cutlass_fused_experts_fp8(a, torch.stack(w13q), torch.stack(w2q), torch.stack(w13s), torch.stack(w2s),
+                                      tw_ref, ti_ref)
+    assert O.rel_l2(out.float(), ref.float()) <= 5e-3
+    _status_ok()
