@@ -281,8 +281,6 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       const float* sb_base = p.sb + static_cast<int64_t>(t.expert) * p.sb_stride_e;
       const int kb_begin = w.kb_begin, kb_end = w.kb_end;
       for (int kb0 = kb_begin; kb0 < kb_end; kb0 += kScaleGroup) {
-        ok = mbar_wait_warp(&scale_empty[slot], sphase ^ 1u, p.status, 5);
-        if (!ok) break;
         float* dst = smem_scale + slot * C::kSlotFloats;
         float a[kScaleGroup][4];
         float bsc[kScaleGroup][C::kHalves];
@@ -311,6 +309,9 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                             : 0.f;
           }
         }
+        // the loads above do not depend on the slot: issued first, they are in flight during this wait
+        ok = mbar_wait_warp(&scale_empty[slot], sphase ^ 1u, p.status, 5);
+        if (!ok) break;
 #pragma unroll
         for (int j = 0; j < kScaleGroup; ++j)
 #pragma unroll

@@ -327,10 +327,10 @@ def test_fp8_linear_method_apply():
 
 # ---------------------------------------------------------------------------- packed UE8M0 activation scales
 @pytest.mark.parametrize("M,N,K", [(1, 256, 512), (16, 512, 1024), (64, 1152, 640), (130, 256, 7168), (512, 384, 1024)])
-def test_ue8m0_scaled_matmul(M, N, K):
+def test_ue8m0_scaled_matmul(M, N, K, no_split_k):
     """Activation scales as packed exponent bytes (what the quant op writes with scale_ue8m0=True), weights
-    with power-of-two block scales: equal to the fp32-scale kernel given the decoded scales (bit for bit),
-    and within tolerance of the oracle."""
+    with power-of-two block scales: equal to the (unsplit) fp32-scale kernel given the decoded scales, bit for
+    bit, and within tolerance of the oracle."""
     from sglang_b200.layers.quantization.fp8_kernel import (sglang_per_token_group_quant_fp8,
                                                             w8a8_block_fp8_matmul_deepgemm)
     x = O.gen_activation(M, K, seed=M + K, outlier_frac=1e-3)
