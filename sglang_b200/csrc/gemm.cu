@@ -284,11 +284,29 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         float* dst = smem_scale + slot * C::kSlotFloats;
         float a[kScaleGroup][4];
         float bsc[kScaleGroup][C::kHalves];
+        // Row-major activation scales (the grouped form): the four k-blocks of a row are 16 contiguous bytes, one
+        // load per row instead of four loads that each touch 32 different sectors.
+        static_assert(kScaleGroup == 4, "one float4 per row and slot");
+        const bool row_vec = !p.sa_ue8m0 && p.sa_stride_g == 1 && (p.sa_stride_m & 3) == 0 && (kb_begin & 3) == 0 &&
+                             (reinterpret_cast<uintptr_t>(p.sa) & 15u) == 0 && kb0 + kScaleGroup <= ((nkb + 3) & ~3) &&
+                             (p.sa_stride_m >= ((nkb + 3) & ~3));
+        if (row_vec) {
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            const int rr = r * 32 + lane;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (rr < t.valid_rows)
+              v = __ldg(reinterpret_cast<const float4*>(p.sa + static_cast<int64_t>(t.row0 + rr) * p.sa_stride_m + kb0));
+            a[0][r] = v.x; a[1][r] = v.y; a[2][r] = v.z; a[3][r] = v.w;
+          }
+        }
 #pragma unroll
         for (int j = 0; j < kScaleGroup; ++j) {
           const int kb = kb0 + j;
           const bool kin = kb < kb_end;
-          if (p.sa_ue8m0) {   // warp-uniform; each branch is a batch of independent loads
+          if (row_vec) {
+            // loaded above
+          } else if (p.sa_ue8m0) {   // warp-uniform; each branch is a batch of independent loads
 #pragma unroll
             for (int r = 0; r < 4; ++r) {
               const int rr = r * 32 + lane;
