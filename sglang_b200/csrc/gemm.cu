@@ -850,11 +850,11 @@ extern "C" int b200_fp8_blockwise_scaled_grouped_mm(const void* a, int64_t lda, 
   // An expert's weights are rows [e*N, (e+1)*N) of one [E*N, K] matrix; a 128 x 256 tile must not
   // straddle two experts' rows, so the wide tile needs N % 256 == 0.
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // Up to ~144 rows per expert on average the weight-streaming kernel is used (measured on the
-  // DeepSeek-V3 expert shapes: 1.25x at 16 rows per expert, 1.06x at 64, level at 128); beyond that the
-  // 128-row token tiles of this file are fuller and their wider MMAs win.
+  // Up to 64 rows per expert on average the weight-streaming kernel is used (measured on the DeepSeek-V3
+  // expert shapes, 256 experts: 1.25x at 16-32 rows per expert, level at 64); beyond that an expert fills most
+  // of a 128-row token tile and the wider MMAs of this file's kernel win (1.15x at 96 rows, level at 128).
   const int64_t avg_rows = total_rows / num_experts;
-  const bool auto_swap = g_force_block_n == 0 && avg_rows <= 144;
+  const bool auto_swap = g_force_block_n == 0 && avg_rows <= 64;
   if ((g_force_block_n == 3 || forced_token_tile() != 0 || auto_swap) && N % 128 == 0) {
     int tt = forced_token_tile();
     if (tt == 0) tt = avg_rows <= 20 ? 32 : 64;
