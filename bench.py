@@ -233,7 +233,7 @@ def run_gpu_arm(args):
 
     ev = lambda: torch.cuda.Event(enable_timing=True)
     kernel_events = []   # (name, start, stop) inside the timed region
-    TP_CHUNKS = args.tp_chunks
+    TP_CHUNKS = args.tp_chunks or 4
     y2_buf = torch.empty((M_TOKENS, HIDDEN), dtype=torch.bfloat16, device=dev)
     comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
 
@@ -280,7 +280,9 @@ def run_gpu_arm(args):
     # NCCL all-reduces captured once): a rank's share of the step is a few hundred microseconds of device
     # work, less than the Python calls that enqueue it.
     graph = None
-    if world > 1 and not args.eager:
+
+    def capture_step():
+        """The step captured into a CUDA graph on every rank, or None on every rank (the ranks agree)."""
         cap = torch.cuda.Stream(device=dev)
         cap.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(cap):
@@ -291,24 +293,66 @@ def run_gpu_arm(args):
         # captures.  Nothing executes during capture, so a rank whose capture fails can still agree with
         # the others (one small all-reduce afterwards) to run eagerly.
         captured = 1
+        g_ = None
         try:
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=cap, capture_error_mode="thread_local"):
+            g_ = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g_, stream=cap, capture_error_mode="thread_local"):
                 step()
         except Exception as e:  # noqa: BLE001
             captured = 0
-            graph = None
+            g_ = None
             print(f"[bench rank {rank}] graph capture failed, running eagerly: {e}", file=sys.stderr, flush=True)
         torch.cuda.synchronize()
         flag = torch.tensor([captured], device=dev, dtype=torch.int32)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         if int(flag.item()) == 0:
-            graph = None
-        if graph is not None:
-            for _ in range(3):
-                graph.replay()
-                torch.cuda.synchronize()
+            if g_ is not None:
+                g_.reset()
+            return None
+        for _ in range(3):
+            g_.replay()
+            torch.cuda.synchronize()
         barrier()
+        return g_
+
+    if world > 1 and not args.eager:
+        # How many row chunks the row-parallel projection is cut into is a trade between overlap (the
+        # all-reduce of one chunk under the GEMM of the next) and the fixed cost of each collective; which
+        # wins depends on the rank count.  With --tp-chunks 0 the warm-up measures the candidates (five
+        # replays each, slowest rank counts) and the timed region runs the fastest.
+        candidates = [args.tp_chunks] if args.tp_chunks else [4, 2, 1]
+        best = None
+        for c in candidates:
+            TP_CHUNKS = c
+            g_ = capture_step()
+            if g_ is None:
+                break
+            if len(candidates) == 1:
+                best = (0.0, c, g_)
+                break
+            a, b = ev(), ev()
+            barrier()
+            a.record()
+            for _ in range(5):
+                g_.replay()
+            b.record()
+            barrier()
+            t = torch.tensor([a.elapsed_time(b)], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            t = float(t.item())
+            if best is None or t < best[0]:
+                if best is not None:
+                    best[2].reset()
+                best = (t, c, g_)
+            else:
+                g_.reset()
+        if best is not None:
+            _, TP_CHUNKS, graph = best
+        else:
+            TP_CHUNKS = args.tp_chunks or 4
+        barrier()
+    elif world > 1:
+        TP_CHUNKS = args.tp_chunks or 4
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -325,7 +369,12 @@ def run_gpu_arm(args):
     barrier()
     ms = t0.elapsed_time(t1) / args.steps
     if graph is not None:
-        for _ in range(5):          # per-kernel times from a few eager steps (events cannot be timed inside a graph)
+        # per-kernel times from a few eager steps (events cannot be timed inside a graph); the capture emptied
+        # the allocator's cache, so two unrecorded steps first take the device allocations out of the figures
+        for _ in range(2):
+            step()
+        barrier()
+        for _ in range(5):
             step(record=True)
         barrier()
     per_kernel = {}
@@ -594,7 +643,7 @@ def main():
     ap.add_argument("--m", default="4096", help="token count(s) for --kernel, comma separated")
     ap.add_argument("--experts", type=int, default=256,
                     help="--kernel moe: experts held on this GPU (256 = whole layer, 32 = one rank of 8)")
-    ap.add_argument("--tp-chunks", type=int, default=4, choices=[1, 2, 4, 8],
+    ap.add_argument("--tp-chunks", type=int, default=0, choices=[0, 1, 2, 4, 8],
                     help="N > 1: row chunks of the row-parallel projection whose all-reduces overlap the next chunk")
     ap.add_argument("--eager", action="store_true", help="N > 1: enqueue every step from Python instead of graph replay")
     ap.add_argument("--graph", action="store_true",

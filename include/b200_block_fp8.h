@@ -205,6 +205,28 @@ int b200_moe_prepare(const int32_t* topk_ids, int64_t num_tokens, int topk, int 
                      void* scratch, size_t scratch_bytes, void* stream);
 
 /*
+ * moe_align_block_size: replaces the op `moe_align_block_size`
+ * (sgl-kernel/csrc/moe/moe_align_kernel.cu:283-366; declared sgl-kernel/include/sgl_kernel_ops.h:226; called from
+ * python/sglang/srt/layers/moe/fused_moe_triton/fused_moe.py:558-628).
+ * topk_ids: `numel` expert ids (int32, or int64 when ids_are_int64), -1 = filtered out.  num_experts counts the
+ * SLOTS as in the reference (real experts + 1; slot = id + 1).  Outputs, all int32:
+ *   sorted_token_ids[sorted_capacity]  flat indices grouped by slot, each slot's run padded to a multiple of
+ *                                      block_size; padding positions are written (`numel`) only when
+ *                                      pad_sorted_token_ids != 0, else the caller pre-filled them
+ *   expert_ids[expert_ids_capacity]    slot - 1 of every block_size run
+ *   num_tokens_post_pad[1]             total padded length
+ *   cumsum_buffer[num_experts + 1]     padded exclusive prefix per slot
+ * Inside a slot the flat indices ascend (the reference's order there is unspecified).  Ids outside
+ * [-1, num_experts - 2] are skipped.  scratch: b200_moe_align_block_size_scratch_bytes(numel, num_experts)
+ * bytes of device memory (0 for numel <= 4096: one launch; else three launches).  num_experts <= 2048.
+ */
+size_t b200_moe_align_block_size_scratch_bytes(int64_t numel, int num_experts);
+int b200_moe_align_block_size(const void* topk_ids, int ids_are_int64, int64_t numel, int num_experts, int block_size,
+                              int32_t* sorted_token_ids, int64_t sorted_capacity, int32_t* expert_ids,
+                              int64_t expert_ids_capacity, int32_t* num_tokens_post_pad, int32_t* cumsum_buffer,
+                              int pad_sorted_token_ids, void* scratch, size_t scratch_bytes, void* stream);
+
+/*
  * b200_moe_prepare without scratch from the caller and without any allocation.  No counterpart in the
  * reference (its prepare_moe_input allocates a buffer on every call).
  * For callers that cannot obtain device memory where the routing tables are built -- a server whose

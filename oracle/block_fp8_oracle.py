@@ -317,6 +317,40 @@ def prepare_moe_input(topk_ids: torch.Tensor, num_experts: int, n: int, k: int):
     return offs.to(i32), ps1.to(i32), ps2.to(i32), a_map.to(i32), c_map.to(i32)
 
 
+def moe_align_block_size(topk_ids: torch.Tensor, num_slots: int, block_size: int, sorted_capacity: Optional[int] = None):
+    """sgl-kernel/csrc/moe/moe_align_kernel.cu:57-216 (one-block count, padded prefix, block -> expert table) and
+    :28-41 (placement), with the caller's sizing of fused_moe_triton/fused_moe.py:598-605.
+
+    `num_slots` is what the op receives as num_experts: real experts + 1, slot = id + 1, so slot 0 collects the
+    id -1 of experts filtered out under expert parallelism.  Returns (sorted_token_ids[capacity],
+    expert_ids[capacity // block_size rounded up], num_tokens_post_pad, cumsum[num_slots + 1]); positions not
+    holding a flat index hold numel.  Inside a slot the flat indices ascend: the reference places them with
+    atomics, so any order inside a slot is a valid output of it, this is the reproducible one.  Pinned by
+    the worked example in the caller's docstring (fused_moe.py:583-596, ids shifted to start at 0).
+    """
+    flat = topk_ids.reshape(-1).to(torch.int64)
+    numel = flat.numel()
+    if sorted_capacity is None:
+        sorted_capacity = numel + num_slots * (block_size - 1)
+    slot = flat + 1
+    valid = (slot >= 0) & (slot < num_slots)
+    counts = torch.zeros(num_slots, dtype=torch.int64)
+    counts.scatter_add_(0, slot[valid], torch.ones_like(slot[valid]))
+    padded = (counts + block_size - 1) // block_size * block_size
+    cumsum = torch.zeros(num_slots + 1, dtype=torch.int64)
+    cumsum[1:] = padded.cumsum(0)
+    total = int(cumsum[-1])
+    sorted_ids = torch.full((sorted_capacity,), numel, dtype=torch.int64)
+    expert_ids = torch.zeros(((sorted_capacity + block_size - 1) // block_size,), dtype=torch.int64)
+    order = torch.argsort(torch.where(valid, slot, torch.full_like(slot, num_slots)), stable=True)[: int(valid.sum())]
+    within = torch.arange(order.numel()) - (counts.cumsum(0) - counts)[slot[order]]
+    sorted_ids[cumsum[slot[order]] + within] = order
+    for e in range(num_slots):
+        expert_ids[int(cumsum[e]) // block_size: int(cumsum[e + 1]) // block_size] = e - 1
+    i32 = torch.int32
+    return sorted_ids.to(i32), expert_ids.to(i32), total, cumsum.to(i32)
+
+
 def shuffle_rows(inp: torch.Tensor, dst2src: torch.Tensor, out_rows: Optional[int] = None):
     """prepare_moe_input.cu:169-197: out[d] = inp[dst2src[d]]."""
     idx = dst2src.to(torch.int64)

@@ -57,6 +57,9 @@ _SIGNATURES = {
                                  c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_void_p]),
     "b200_moe_prepare_noalloc": (c_int, [c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                          c_void_p, c_void_p, c_void_p, c_void_p]),
+    "b200_moe_align_block_size_scratch_bytes": (ctypes.c_size_t, [c_int64, c_int]),
+    "b200_moe_align_block_size": (c_int, [c_void_p, c_int, c_int64, c_int, c_int, c_void_p, c_int64, c_void_p, c_int64,
+                                          c_void_p, c_void_p, c_int, c_void_p, ctypes.c_size_t, c_void_p]),
     "b200_topk_softmax": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
     "b200_moe_fused_gate": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int,
                                     c_void_p]),

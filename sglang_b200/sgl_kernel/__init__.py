@@ -1,7 +1,7 @@
 """Drop-in for the block-FP8 subset of the reference's `sgl_kernel` package.
 
 Importing this module registers the operators under torch.ops.sgl_kernel with the reference's
-schemas verbatim (sgl-kernel/csrc/common_extension.cc:111-119,192-207), implemented for the
+schemas verbatim (sgl-kernel/csrc/common_extension.cc:111-119,165-170,192-207), implemented for the
 CUDA dispatch key by the B200 C-ABI library, and exposes the same-named Python wrappers
 (sgl-kernel/python/sgl_kernel/{gemm,moe}.py).
 """
@@ -9,7 +9,7 @@ import torch
 
 from .gemm import fp8_blockwise_scaled_mm, sgl_per_token_group_quant_fp8
 from .moe import (apply_shuffle_mul_sum, fp8_blockwise_scaled_grouped_mm, prepare_moe_input, shuffle_rows,
-                  shuffle_rows_into, silu_and_mul, topk_softmax, moe_fused_gate)
+                  shuffle_rows_into, silu_and_mul, topk_softmax, moe_fused_gate, moe_align_block_size)
 
 _SCHEMAS = {
     "fp8_blockwise_scaled_mm":
@@ -28,6 +28,9 @@ _SCHEMAS = {
     "apply_shuffle_mul_sum": "(Tensor input, Tensor output, Tensor permutation, Tensor? factors) -> ()",
     "silu_and_mul": "(Tensor out, Tensor input) -> ()",
     "topk_softmax": "(Tensor! topk_weights, Tensor! topk_indices, Tensor gating_output, bool renormalize) -> ()",
+    "moe_align_block_size":
+        "(Tensor topk_ids, int num_experts, int block_size, Tensor! sorted_token_ids, Tensor! experts_ids, "
+        "Tensor! num_tokens_post_pad, Tensor! cumsum_buffer, bool pad_sorted_token_ids) -> ()",
 }
 
 
@@ -50,6 +53,7 @@ _IMPLS = {
     "apply_shuffle_mul_sum": apply_shuffle_mul_sum,
     "silu_and_mul": _silu_and_mul_op,
     "topk_softmax": topk_softmax,
+    "moe_align_block_size": moe_align_block_size,
 }
 
 
@@ -89,4 +93,4 @@ register_torch_ops()
 
 __all__ = ["fp8_blockwise_scaled_mm", "sgl_per_token_group_quant_fp8", "fp8_blockwise_scaled_grouped_mm",
            "prepare_moe_input", "shuffle_rows", "apply_shuffle_mul_sum", "silu_and_mul", "topk_softmax",
-           "moe_fused_gate", "register_torch_ops"]
+           "moe_fused_gate", "moe_align_block_size", "register_torch_ops"]

@@ -46,6 +46,37 @@ def topk_softmax(topk_weights: torch.Tensor, topk_ids: torch.Tensor, gating_outp
     _lib.check("topk_softmax", rc)
 
 
+def moe_align_block_size(topk_ids: torch.Tensor, num_experts: int, block_size: int, sorted_token_ids: torch.Tensor,
+                         experts_ids: torch.Tensor, num_tokens_post_pad: torch.Tensor, cumsum_buffer: torch.Tensor,
+                         pad_sorted_token_ids: bool = False) -> None:
+    """In place: the flat indices of topk_ids grouped by expert into sorted_token_ids, every expert's run padded
+    to a multiple of block_size; experts_ids <- the expert of each block; num_tokens_post_pad <- padded length.
+    `num_experts` counts the slots (experts + 1, slot 0 = id -1) as in the reference.  Mirrors
+    sgl_kernel.moe_align_block_size (sgl-kernel/python/sgl_kernel/moe.py:6-25; kernel
+    sgl-kernel/csrc/moe/moe_align_kernel.cu:283-366).  Inside an expert the indices ascend."""
+    _check(topk_ids.is_cuda and sorted_token_ids.is_cuda and experts_ids.is_cuda and num_tokens_post_pad.is_cuda
+           and cumsum_buffer.is_cuda, "tensors must be CUDA tensors")
+    _check(topk_ids.dtype in (torch.int32, torch.int64) and topk_ids.is_contiguous(),
+           "topk_ids must be contiguous int32 or int64")
+    for name, t in (("sorted_token_ids", sorted_token_ids), ("experts_ids", experts_ids),
+                    ("num_tokens_post_pad", num_tokens_post_pad), ("cumsum_buffer", cumsum_buffer)):
+        _check(t.dtype == torch.int32 and t.is_contiguous(), f"{name} must be contiguous int32")
+    _check(num_tokens_post_pad.numel() >= 1, "num_tokens_post_pad must hold one element")
+    _check(cumsum_buffer.numel() >= num_experts + 1, "cumsum_buffer must hold num_experts + 1 elements")
+    numel = topk_ids.numel()
+    lib = _lib.lib()
+    need = lib.b200_moe_align_block_size_scratch_bytes(numel, num_experts)
+    scratch = torch.empty((max(need, 4) // 4,), dtype=torch.int32, device=topk_ids.device) if need else None
+    with torch.cuda.device(topk_ids.device):
+        rc = lib.b200_moe_align_block_size(topk_ids.data_ptr(), int(topk_ids.dtype == torch.int64), numel, num_experts,
+                                           block_size, sorted_token_ids.data_ptr(), sorted_token_ids.numel(),
+                                           experts_ids.data_ptr(), experts_ids.numel(), num_tokens_post_pad.data_ptr(),
+                                           cumsum_buffer.data_ptr(), int(bool(pad_sorted_token_ids)),
+                                           scratch.data_ptr() if scratch is not None else None, need,
+                                           _stream_ptr(topk_ids.device))
+    _lib.check("moe_align_block_size", rc)
+
+
 def moe_fused_gate(input_tensor: torch.Tensor, bias: torch.Tensor, num_expert_group: int, topk_group: int, topk: int,
                    num_fused_shared_experts: int = 0, routed_scaling_factor: float = 0):
     """DeepSeek-V3 gate (sigmoid scores, choice bias, group-limited top-k, weights renormalised): returns

@@ -345,3 +345,63 @@ def test_checkpoint_to_moe_layer(tmp_path):
                                       tw_ref, ti_ref)
     assert O.rel_l2(out.float(), ref.float()) <= 5e-3
     _status_ok()
+
+
+@pytest.mark.parametrize("pad", [True, False])
+@pytest.mark.parametrize("dtype", [torch.int32, torch.int64])
+@pytest.mark.parametrize("block_size,m,topk,E", [
+    (4, 4, 3, 4), (32, 1, 1, 64), (64, 16, 8, 256), (128, 128, 8, 256), (32, 512, 8, 257), (128, 511, 8, 256),
+    (256, 513, 8, 160), (16, 4096, 8, 256), (128, 4099, 6, 260), (64, 2048, 2, 8), (128, 16384, 8, 256)])
+def test_moe_align_block_size_exact(block_size, m, topk, E, dtype, pad):
+    """Shapes of sgl-kernel/tests/test_moe_align.py:140-151 (block sizes, token counts, expert counts incl. the
+    non-power-of-two ones) through the reference's call convention (num_experts + 1 slots, caller-sized buffers,
+    fused_moe.py:598-627).  Everything the op defines is compared exactly: padded length, the block -> expert
+    table, the prefix, and sorted_token_ids (ascending inside an expert, `numel` in the padding)."""
+    from sglang_b200.sgl_kernel import moe_align_block_size
+    g = torch.Generator().manual_seed(block_size + m + E)
+    ids = torch.argsort(torch.rand(m, E, generator=g), dim=1)[:, :topk].to(dtype)
+    if m >= 16:
+        ids[3, 0] = -1                                   # an expert filtered out by expert parallelism
+        ids[m - 1, topk - 1] = -1
+    numel = ids.numel()
+    cap = numel + (E + 1) * (block_size - 1)
+    sorted_ids = torch.empty(cap, dtype=torch.int32, device="cuda")
+    if not pad:
+        sorted_ids.fill_(numel)
+    nblocks = (cap + block_size - 1) // block_size
+    expert_ids = torch.zeros(nblocks, dtype=torch.int32, device="cuda")
+    post = torch.empty(1, dtype=torch.int32, device="cuda")
+    cumsum = torch.empty(E + 2, dtype=torch.int32, device="cuda")
+    torch.ops.sgl_kernel.moe_align_block_size(ids.cuda(), E + 1, block_size, sorted_ids, expert_ids, post, cumsum, pad)
+    s_ref, e_ref, total, c_ref = O.moe_align_block_size(ids, E + 1, block_size, cap)
+    assert int(post.item()) == total
+    assert torch.equal(cumsum.cpu()[: E + 2], c_ref)
+    assert torch.equal(expert_ids.cpu()[: total // block_size], e_ref[: total // block_size])
+    assert torch.equal(sorted_ids.cpu()[:total], s_ref[:total])
+    if not pad:
+        assert bool((sorted_ids.cpu()[total:] == numel).all())     # nothing written past the padded length
+    # size-independent properties: a permutation of the valid flat indices, each in a block of its own expert
+    got = sorted_ids.cpu()[:total].long()
+    real = got[got < numel]
+    flat = ids.reshape(-1).long()
+    assert torch.equal(real.sort().values, torch.nonzero(flat >= -1).squeeze(1))
+    pos = torch.nonzero(got < numel).squeeze(1)
+    assert torch.equal(expert_ids.cpu().long()[pos // block_size], flat[real])
+
+
+def test_moe_align_block_size_docstring_example_and_errors():
+    """The worked example of fused_moe.py:583-596 (ids shifted to start at 0), and the argument checks."""
+    from sglang_b200.sgl_kernel import moe_align_block_size
+    ids = (torch.tensor([[2, 3, 4], [1, 2, 4], [1, 3, 4], [1, 2, 3]], dtype=torch.int32) - 1).cuda()
+    sorted_ids = torch.empty(12 + 5 * 3, dtype=torch.int32, device="cuda")
+    expert_ids = torch.empty(7, dtype=torch.int32, device="cuda")
+    post = torch.empty(1, dtype=torch.int32, device="cuda")
+    cumsum = torch.empty(6, dtype=torch.int32, device="cuda")
+    moe_align_block_size(ids, 5, 4, sorted_ids, expert_ids, post, cumsum, True)
+    assert int(post.item()) == 16
+    assert sorted_ids.cpu()[:16].tolist() == [3, 6, 9, 12, 0, 4, 10, 12, 1, 7, 11, 12, 2, 5, 8, 12]
+    assert expert_ids.cpu()[:4].tolist() == [0, 1, 2, 3]
+    with pytest.raises(RuntimeError):
+        moe_align_block_size(ids.float(), 5, 4, sorted_ids, expert_ids, post, cumsum, True)
+    with pytest.raises(RuntimeError):
+        moe_align_block_size(ids, 5, 4, sorted_ids, expert_ids, post, cumsum[:3], True)

@@ -124,3 +124,27 @@ def test_zero_group_and_nan_follow_cuda_kernel():
     assert float(s[0, 0]) == np.float32(1e-10) / np.float32(448.0)
     assert float(s[1, 0]) == np.float32(3.0) / np.float32(448.0)
     assert float(q[1, 5].float()) == -448.0 and float(q[1, 7].float()) == 448.0
+
+
+def test_moe_align_block_size_docstring_example():
+    """The oracle's moe_align_block_size against the worked example the reference gives for the op
+    (python/sglang/srt/layers/moe/fused_moe_triton/fused_moe.py:583-596; its 1-based ids shifted to start at 0),
+    plus the invariants of sgl-kernel/tests/test_moe_align.py on a random case with filtered (-1) ids."""
+    ids = torch.tensor([[2, 3, 4], [1, 2, 4], [1, 3, 4], [1, 2, 3]]) - 1
+    s, e, total, c = O.moe_align_block_size(ids, 5, 4)
+    assert total == 16
+    assert s[:16].tolist() == [3, 6, 9, 12, 0, 4, 10, 12, 1, 7, 11, 12, 2, 5, 8, 12]
+    assert e[:4].tolist() == [0, 1, 2, 3] and c.tolist() == [0, 0, 4, 8, 12, 16]
+    g = torch.Generator().manual_seed(5)
+    E, bs = 37, 16
+    ids = torch.argsort(torch.rand(300, E, generator=g), dim=1)[:, :6]
+    ids[7, 2] = -1
+    s, e, total, c = O.moe_align_block_size(ids, E + 1, bs)
+    flat = ids.reshape(-1)
+    assert total % bs == 0 and int(c[-1]) == total and int(c[1]) == bs      # the single -1 pads to one block
+    got = s[:total].long()
+    real = got[got < flat.numel()]
+    assert torch.equal(real.sort().values, torch.arange(flat.numel()))
+    pos = torch.nonzero(got < flat.numel()).squeeze(1)
+    assert torch.equal(e.long()[pos // bs], flat[real])
+    assert bool((s[total:] == flat.numel()).all())
