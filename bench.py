@@ -318,10 +318,11 @@ def run_gpu_arm(args):
     if world > 1 and not args.eager:
         # How many row chunks the row-parallel projection is cut into is a trade between overlap (the
         # all-reduce of one chunk under the GEMM of the next) and the fixed cost of each collective; which
-        # wins depends on the rank count.  With --tp-chunks 0 the warm-up measures the candidates (five
+        # wins depends on the rank count.  With --tp-chunks 0 the warm-up measures the candidates (ten
         # replays each, slowest rank counts) and the timed region runs the fastest.
         candidates = [args.tp_chunks] if args.tp_chunks else [4, 2, 1]
         best = None
+        chunk_ms = {}
         for c in candidates:
             TP_CHUNKS = c
             g_ = capture_step()
@@ -333,13 +334,14 @@ def run_gpu_arm(args):
             a, b = ev(), ev()
             barrier()
             a.record()
-            for _ in range(5):
+            for _ in range(10):
                 g_.replay()
             b.record()
             barrier()
             t = torch.tensor([a.elapsed_time(b)], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            t = float(t.item())
+            t = float(t.item()) / 10
+            chunk_ms[str(c)] = round(t, 4)
             if best is None or t < best[0]:
                 if best is not None:
                     best[2].reset()
@@ -353,6 +355,7 @@ def run_gpu_arm(args):
         barrier()
     elif world > 1:
         TP_CHUNKS = args.tp_chunks or 4
+        chunk_ms = {}
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -487,7 +490,8 @@ def run_gpu_arm(args):
                                        "with the bf16 NCCL all-reduce of each chunk overlapped"
                                        + ("; step replayed from a CUDA graph" if graph is not None else "")) if world > 1 else "single",
                        "l2": "inputs larger than L2 (weights 396 MB e4m3 + activations 210 MB bf16 per step)",
-                       "kernels_ms": per_kernel},
+                       "kernels_ms": per_kernel,
+                       **({"row_chunk_candidates_ms": chunk_ms} if world > 1 and chunk_ms else {})},
             "e2e": {"value": FLOPS_PER_STEP / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
                     "note": "every step copies its activations from pinned host memory and its bf16 results back; the "
