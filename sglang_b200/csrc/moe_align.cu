@@ -62,9 +62,10 @@ __device__ __forceinline__ void write_tables(const int32_t* s_cnt, const int32_t
   if (pad) {
     const int32_t fill = static_cast<int32_t>(numel);
     // padding positions of every slot, then the reference's round-up of the filled range to 4 entries
-    for (int e = 0; e < slots; ++e) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    for (int e = warp; e < slots; e += nwarps) {
       const int lo = s_off[e] + s_cnt[e], hi = s_off[e + 1];
-      for (int i = lo + threadIdx.x; i < hi; i += blockDim.x)
+      for (int i = lo + lane; i < hi; i += 32)
         if (i < sorted_capacity) sorted_token_ids[i] = fill;
     }
     const int64_t end4 = (static_cast<int64_t>(total) + 3) / 4 * 4;
@@ -76,9 +77,9 @@ __device__ __forceinline__ void write_tables(const int32_t* s_cnt, const int32_t
 // Stable placement of `count` ids (held in s_ids) by one warp: 32 ids at a time, equal slots inside the 32
 // ranked with a match mask.  s_next[slot] = next free position of the slot.
 __device__ __forceinline__ void place_warp0(const int32_t* s_ids, int count, int64_t base, int slots, int32_t* s_next,
-                                            int32_t* sorted_token_ids, int64_t sorted_capacity) {
-  const int lane = threadIdx.x;
-  for (int i0 = 0; i0 < count; i0 += 32) {
+                                            int32_t* sorted_token_ids, int64_t sorted_capacity, int first = 0) {
+  const int lane = threadIdx.x & 31;
+  for (int i0 = first; i0 < count; i0 += 32) {
     const int i = i0 + lane;
     const int slot = i < count ? s_ids[i] + 1 : -1;
     const bool valid = slot >= 0 && slot < slots;
@@ -93,9 +94,11 @@ __device__ __forceinline__ void place_warp0(const int32_t* s_ids, int count, int
   }
 }
 
-// ---- one-block form (numel <= kAlignSmall)
+// ---- one-block form (numel <= kAlignSmall).  `walkers` warps each own a contiguous segment of the ids (a
+// multiple of 32 long): per-warp histograms, a scan over the warps per slot, then every warp places its own
+// segment, so the order inside a slot still follows the flat index.
 __global__ void __launch_bounds__(1024)
-align_small_kernel(const void* __restrict__ ids, int is64, int64_t numel, int slots, int block_size,
+align_small_kernel(const void* __restrict__ ids, int is64, int64_t numel, int slots, int block_size, int walkers,
                    int32_t* __restrict__ sorted_token_ids, int64_t sorted_capacity, int32_t* __restrict__ expert_ids,
                    int64_t expert_ids_capacity, int32_t* __restrict__ num_tokens_post_pad, int32_t* __restrict__ cumsum,
                    int pad) {
@@ -103,22 +106,41 @@ align_small_kernel(const void* __restrict__ ids, int is64, int64_t numel, int sl
   int32_t* s_cnt = s_mem;                  // [slots]
   int32_t* s_off = s_cnt + slots;          // [slots + 1]
   int32_t* s_ids = s_off + slots + 1;      // [kAlignSmall]
-  for (int e = threadIdx.x; e < slots; e += blockDim.x) s_cnt[e] = 0;
-  __syncthreads();
+  int32_t* s_w = s_ids + kAlignSmall;      // [walkers][slots]
   const int n = static_cast<int>(numel);
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const int id = load_id(ids, is64, i);
-    s_ids[i] = id;
-    const int slot = id + 1;
-    if (slot >= 0 && slot < slots) atomicAdd(&s_cnt[slot], 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int seg = ((n + walkers - 1) / walkers + 31) / 32 * 32;
+  for (int i = threadIdx.x; i < walkers * slots; i += blockDim.x) s_w[i] = 0;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) s_ids[i] = load_id(ids, is64, i);
+  __syncthreads();
+  const int seg_lo = min(warp * seg, n), seg_hi = min(seg_lo + seg, n);
+  if (warp < walkers) {
+    for (int i = seg_lo + lane; i < seg_hi; i += 32) {
+      const int slot = s_ids[i] + 1;
+      if (slot >= 0 && slot < slots) atomicAdd(&s_w[warp * slots + slot], 1);
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < slots; e += blockDim.x) {
+    int run = 0;
+    for (int w = 0; w < walkers; ++w) {
+      const int v = s_w[w * slots + e];
+      s_w[w * slots + e] = run;
+      run += v;
+    }
+    s_cnt[e] = run;
   }
   __syncthreads();
   if (threadIdx.x < 32) padded_prefix_warp0(s_cnt, s_off, slots, block_size);
   __syncthreads();
+  for (int e = threadIdx.x; e < slots; e += blockDim.x) {
+    const int off = s_off[e];
+    for (int w = 0; w < walkers; ++w) s_w[w * slots + e] += off;
+  }
   write_tables(s_cnt, s_off, slots, block_size, numel, sorted_token_ids, sorted_capacity, expert_ids,
                expert_ids_capacity, num_tokens_post_pad, cumsum, pad);
   __syncthreads();
-  if (threadIdx.x < 32) place_warp0(s_ids, n, 0, slots, s_off, sorted_token_ids, sorted_capacity);
+  if (warp < walkers) place_warp0(s_ids, seg_hi, 0, slots, s_w + warp * slots, sorted_token_ids, sorted_capacity, seg_lo);
 }
 
 // ---- three-launch form.  Phase 1: per-chunk histogram -> scratch[chunk][slots]
@@ -214,8 +236,13 @@ extern "C" int b200_moe_align_block_size(const void* topk_ids, int ids_are_int64
     return B200_ERR_TOO_LARGE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (numel <= kAlignSmall) {
-    const size_t smem = (static_cast<size_t>(2 * num_experts + 1) + kAlignSmall) * sizeof(int32_t);
-    align_small_kernel<<<1, 1024, smem, st>>>(topk_ids, ids_are_int64, numel, num_experts, block_size, sorted_token_ids,
+    // as many walking warps (<= 16) as 48 KB of shared memory holds histograms for
+    const int room = 48 * 1024 / 4 - kAlignSmall - (2 * num_experts + 1);
+    const int walkers = room / num_experts >= 16 ? 16 : (room / num_experts >= 1 ? room / num_experts : 1);
+    const size_t smem = (static_cast<size_t>(2 * num_experts + 1) + kAlignSmall +
+                         static_cast<size_t>(walkers) * num_experts) * sizeof(int32_t);
+    align_small_kernel<<<1, 1024, smem, st>>>(topk_ids, ids_are_int64, numel, num_experts, block_size, walkers,
+                                              sorted_token_ids,
                                               sorted_capacity, expert_ids, expert_ids_capacity, num_tokens_post_pad,
                                               cumsum_buffer, pad_sorted_token_ids);
     B200_CUDA_TRY(cudaGetLastError());
