@@ -288,25 +288,57 @@ int b200_topk_softmax(const void* gating_output, int dtype, int64_t row_stride, 
                       int32_t* topk_ids, int64_t num_tokens, int num_experts, int topk, int renormalize,
                       void* stream);
 
-/* Reads and clears this device's GEMM status word (0 = ok; non-zero = a bounded device-side
- * wait gave up, value encodes which).  Synchronises the device.  No reference counterpart. */
-int b200_gemm_device_status(int* status_out);
+/*
+ * Sum of bf16 / fp16 buffers across 2..8 GPUs of one NVSwitch domain, one process per GPU.
+ * Replaces: the reference's custom all-reduce (sgl-kernel/csrc/allreduce/custom_all_reduce.cuh, one-shot
+ * and two-shot kernels over IPC peer pointers; registered as `all_reduce` in
+ * sgl-kernel/csrc/common_extension.cc) and the NCCL all-reduce that RowParallelLinear.forward calls
+ * (python/sglang/srt/layers/linear.py:1294-1300).
+ *
+ * peer_buffers[r] / peer_signal_pads[r]: rank r's symmetric buffer and signal pad (zero-initialised,
+ * at least 4 * b200_allreduce_flag_words(world_size) bytes) as mapped into THIS process, r < world_size.
+ * multicast_buffer: the multicast address of the buffer (NVLink SHARP: the switch adds), or NULL to use
+ * peer loads and stores.  The range [offset_bytes, offset_bytes + bytes) of the buffer is reduced:
+ *   one_shot = 0: in place on every rank (rank r reduces slice r and writes it to all ranks);
+ *                 bytes % (16 * world_size) == 0.
+ *   one_shot = 1: into `out` (local memory, bytes long); bytes % 16 == 0.  For small buffers.
+ * Every element is the fp32 sum over ranks rounded once: identical bits on all ranks, run to run.
+ * The kernels of the ranks wait for one another at flag barriers (bounded, about a second): every rank
+ * must call with the same arguments, in the same order, and nothing else may use the flag words
+ * [flag_base_words, + b200_allreduce_flag_words(world_size)) of the signal pads meanwhile.  *status
+ * (device memory, zero before the first call) receives a non-zero code if a peer never arrived; the
+ * result is then undefined but the kernel still ends.  num_blocks: 0 = default, at most
+ * b200_allreduce_max_blocks().
+ */
+int b200_allreduce(void* const* peer_buffers, void* const* peer_signal_pads, void* multicast_buffer, void* out,
+                   int* status, int64_t offset_bytes, int64_t bytes, int dtype, int rank, int world_size,
+                   int one_shot, int num_blocks, int64_t flag_base_words, void* stream);
+int b200_allreduce_flag_words(int world_size);
+int b200_allreduce_max_blocks(void);
 
 /*
- * Diagnostics for tests and experiments (process-wide switches; none has a reference counterpart).
- *   force_block_n:  0 automatic; 128 / 256 single-CTA kernel with that tile width; 2 CTA-pair kernel;
- *                   1001.. experimental variants of the single-CTA kernel.
- *   force_quant_passes: rows-of-4 per quantisation tile (1, 2, 4, 8); 0 automatic.
- *   gemm_mode / wait_hint_ns / set_timing_buffer: timing experiments on the CTA-pair kernel (results
- *                   are wrong while gemm_mode is non-zero).
- *   pair_kernel_max_clusters: what the cluster occupancy query returned for the CTA-pair kernel.
+ * Device-side waits in the GEMM kernels are bounded (about a second of SM clocks).  A wait that gives up
+ * makes its kernel drain and exit, and records a code that is STICKY for the device, like a CUDA error:
+ *   - every later GEMM entry point on that device returns B200_ERR_DEVICE_TIMEOUT without launching
+ *     (the code is mirrored into pinned host memory, so this test costs no synchronisation);
+ *   - b200_gemm_poll_status reads that host mirror (no synchronisation; 0 = nothing reported so far);
+ *   - b200_gemm_device_status synchronises the device, returns the code and CLEARS it, after which
+ *     launches are accepted again.
+ * The output of the launch that gave up is undefined.  Launches that were already queued behind it are
+ * not affected by it: each launch watches its own slot of a ring of status words, so a stale code can
+ * never make a healthy kernel abandon its waits.  The first GEMM call on a device allocates the pinned
+ * mirror (4 bytes); make that call before any stream capture.  No reference counterpart.
+ */
+int b200_gemm_device_status(int* status_out);
+int b200_gemm_poll_status(int* status_out);
+
+/*
+ * Test hook (process-wide; no reference counterpart): which GEMM kernel the dispatcher picks, so that the
+ * tests reach every kernel on every shape.  0 automatic; 128 / 256: the 128-token-tile kernel with that
+ * tile width; 3: the weight-streaming kernel with its token tile chosen from the shape, 3032 / 3064 /
+ * 3128: that token tile; 4: never the weight-streaming kernel.
  */
 int b200_debug_force_block_n(int block_n);
-int b200_debug_force_quant_passes(int passes);
-int b200_debug_gemm_mode(int mode);
-int b200_debug_wait_hint_ns(int ns);
-int b200_debug_set_timing_buffer(void* device_buf_5x64_i64);
-int b200_debug_pair_kernel_max_clusters(void);
 
 #ifdef __cplusplus
 }

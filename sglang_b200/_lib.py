@@ -49,6 +49,7 @@ _SIGNATURES = {
                                                    c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int, c_int64,
                                                    c_int64, c_int64, c_void_p]),
     "b200_gemm_device_status": (c_int, [ctypes.POINTER(c_int)]),
+    "b200_gemm_poll_status": (c_int, [ctypes.POINTER(c_int)]),
     "b200_fp8_blockwise_scaled_grouped_mm": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64,
                                                      c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int,
                                                      c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p]),
@@ -67,12 +68,11 @@ _SIGNATURES = {
     "b200_silu_and_mul": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
     "b200_apply_shuffle_mul_sum": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,
                                            c_void_p]),
+    "b200_allreduce": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int,
+                               c_int, c_int, c_int, c_int64, c_void_p]),
+    "b200_allreduce_flag_words": (c_int, [c_int]),
+    "b200_allreduce_max_blocks": (c_int, []),
     "b200_debug_force_block_n": (c_int, [c_int]),
-    "b200_debug_force_quant_passes": (c_int, [c_int]),
-    "b200_debug_pair_kernel_max_clusters": (c_int, []),
-    "b200_debug_gemm_mode": (c_int, [c_int]),
-    "b200_debug_wait_hint_ns": (c_int, [c_int]),
-    "b200_debug_set_timing_buffer": (c_int, [c_void_p]),
 }
 
 

@@ -1,0 +1,248 @@
+// Sum of bf16 / fp16 buffers across the GPUs of one NVSwitch domain, for the row-parallel linear's
+// partial outputs.  Stands in for the reference's custom all-reduce
+// (sgl-kernel/csrc/allreduce/custom_all_reduce.cuh: one-shot and two-shot kernels over IPC peer
+// pointers) and for the NCCL all-reduce behind tensor_model_parallel_all_reduce
+// (python/sglang/srt/distributed/communication_op.py:11-13).
+//
+// Every rank passes the same symmetric buffer (same size, same offset on every rank): its own
+// address, the peers' addresses of it, and -- where the driver could bind the buffers to an NVLink
+// multicast object -- the multicast address.  Two forms:
+//   two-shot, in place   rank r owns the r-th slice.  With a multicast address it pulls the slice's sum
+//                        out of the switch (multimem.ld_reduce: the switch reads the slice from every
+//                        GPU and adds in fp32) and pushes the result to every GPU (multimem.st); without
+//                        one it reads the slice from every peer, adds in fp32 in rank order, and stores
+//                        the result into every peer's buffer.
+//   one-shot, out of place  every rank sums the whole buffer into a local output; one pass and two
+//                        barriers, for buffers of a few hundred kilobytes where latency is everything.
+// Either way every element is the fp32 sum of all ranks' values rounded once -- the same bits on every
+// rank, independent of timing.
+//
+// Ranks meet at flag barriers in the peers' signal pads (one 32-bit flag per block and peer,
+// compare-and-swap 0 -> 1 by the sender, 1 -> 0 by the receiver, so the flags need no epoch).  Every
+// spin is bounded; a rank whose peer never arrives records an error code in `status` (a device word of
+// the caller) and carries on without waiting, so a missing rank costs wrong data, not a hung GPU.
+// These kernels wait for kernels on OTHER GPUs: one process per GPU, never two ranks on one GPU.
+#include "common.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int kMaxRanks = 8;
+constexpr int kArThreads = 512;
+constexpr long long kArWaitCycles = 2000000000LL;   // about a second
+
+struct ArParams {
+  void* local;                   // this rank's buffer
+  void* peers[kMaxRanks];        // every rank's buffer, as mapped into this process (peers[rank] == local)
+  uint32_t* signals[kMaxRanks];  // every rank's signal pad, as mapped into this process
+  void* mc;                      // multicast address of the buffer, or null
+  void* out;                     // one-shot: local output
+  int* status;                   // device word: 0, or the code of the first wait that gave up
+  int64_t offset_bytes;          // of the reduced range inside the buffer (multiple of 16 * world)
+  int64_t bytes;                 // length of the reduced range (multiple of 16 * world for two-shot, 16 for one-shot)
+  int rank, world;
+  uint32_t flag_base;            // first flag word used by this call site inside the signal pads
+};
+
+__device__ __forceinline__ uint32_t cas_release_sys(uint32_t* addr, uint32_t cmp, uint32_t val) {
+  uint32_t old;
+  asm volatile("atom.global.release.sys.cas.b32 %0, [%1], %2, %3;" : "=r"(old) : "l"(addr), "r"(cmp), "r"(val) : "memory");
+  return old;
+}
+__device__ __forceinline__ uint32_t cas_acquire_sys(uint32_t* addr, uint32_t cmp, uint32_t val) {
+  uint32_t old;
+  asm volatile("atom.global.acquire.sys.cas.b32 %0, [%1], %2, %3;" : "=r"(old) : "l"(addr), "r"(cmp), "r"(val) : "memory");
+  return old;
+}
+
+// All ranks' blocks with the same index meet.  Thread t < world of each block signals rank t's pad and
+// waits for rank t's signal in its own pad.  Flags of block b: words [flag_base + b*world, +world).
+__device__ __forceinline__ void rank_barrier(const ArParams& p, int code) {
+  __syncthreads();
+  if (threadIdx.x < p.world) {
+    const int peer = threadIdx.x;
+    uint32_t* theirs = p.signals[peer] + p.flag_base + blockIdx.x * p.world + p.rank;
+    uint32_t* mine = p.signals[p.rank] + p.flag_base + blockIdx.x * p.world + peer;
+    const long long t0 = clock64();
+    bool ok = true;
+    while (cas_release_sys(theirs, 0u, 1u) != 0u) {
+      if (clock64() - t0 > kArWaitCycles) { ok = false; break; }
+    }
+    if (ok) {
+      while (cas_acquire_sys(mine, 1u, 0u) != 1u) {
+        if (clock64() - t0 > kArWaitCycles) { ok = false; break; }
+      }
+    }
+    if (!ok) atomicCAS(p.status, 0, code);
+  }
+  __syncthreads();
+}
+
+struct alignas(16) Vec16 { uint32_t w[4]; };
+
+template <typename T> struct Pair2;
+template <> struct Pair2<__nv_bfloat16> {
+  __device__ static float2 unpack(uint32_t w) { return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&w)); }
+  __device__ static uint32_t pack(float2 f) { __nv_bfloat162 t = __float22bfloat162_rn(f); return *reinterpret_cast<uint32_t*>(&t); }
+};
+template <> struct Pair2<__half> {
+  __device__ static float2 unpack(uint32_t w) { return __half22float2(*reinterpret_cast<__half2*>(&w)); }
+  __device__ static uint32_t pack(float2 f) { __half2 t = __float22half2_rn(f); return *reinterpret_cast<uint32_t*>(&t); }
+};
+
+template <typename T>
+__device__ __forceinline__ Vec16 multimem_ld_reduce(const void* mc_addr);
+template <>
+__device__ __forceinline__ Vec16 multimem_ld_reduce<__nv_bfloat16>(const void* mc_addr) {
+  Vec16 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3]) : "l"(mc_addr) : "memory");
+  return v;
+}
+template <>
+__device__ __forceinline__ Vec16 multimem_ld_reduce<__half>(const void* mc_addr) {
+  Vec16 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3]) : "l"(mc_addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st(void* mc_addr, const Vec16& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+               ::"l"(mc_addr), "r"(v.w[0]), "r"(v.w[1]), "r"(v.w[2]), "r"(v.w[3]) : "memory");
+}
+
+// Sum over ranks of one 16-byte vector read from every rank's buffer, fp32, rank order.
+template <typename T>
+__device__ __forceinline__ Vec16 peer_sum(const ArParams& p, int64_t byte_off) {
+  float2 acc[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
+  Vec16 v[kMaxRanks];
+#pragma unroll
+  for (int r = 0; r < kMaxRanks; ++r)
+    if (r < p.world) v[r] = *reinterpret_cast<const Vec16*>(static_cast<const char*>(p.peers[r]) + byte_off);
+#pragma unroll
+  for (int r = 0; r < kMaxRanks; ++r)
+    if (r < p.world) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = Pair2<T>::unpack(v[r].w[j]);
+        acc[j].x += f.x;
+        acc[j].y += f.y;
+      }
+    }
+  Vec16 o;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) o.w[j] = Pair2<T>::pack(acc[j]);
+  return o;
+}
+
+template <typename T, bool MULTIMEM>
+__global__ void __launch_bounds__(kArThreads) allreduce_twoshot_kernel(const ArParams p) {
+  rank_barrier(p, 21);   // every rank's partial values are in its buffer
+  const int64_t slice = p.bytes / p.world;
+  const int64_t base = p.offset_bytes + slice * p.rank;
+  const int64_t nvec = slice / 16;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  constexpr int U = 4;
+  for (int64_t i0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < nvec; i0 += stride * U) {
+    Vec16 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t i = i0 + u * stride;
+      if (i < nvec) {
+        if constexpr (MULTIMEM) v[u] = multimem_ld_reduce<T>(static_cast<const char*>(p.mc) + base + i * 16);
+        else v[u] = peer_sum<T>(p, base + i * 16);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t i = i0 + u * stride;
+      if (i < nvec) {
+        if constexpr (MULTIMEM) {
+          multimem_st(static_cast<char*>(p.mc) + base + i * 16, v[u]);
+        } else {
+#pragma unroll
+          for (int r = 0; r < kMaxRanks; ++r)
+            if (r < p.world) *reinterpret_cast<Vec16*>(static_cast<char*>(p.peers[r]) + base + i * 16) = v[u];
+        }
+      }
+    }
+  }
+  __threadfence_system();
+  rank_barrier(p, 22);   // every slice has reached every rank
+}
+
+template <typename T, bool MULTIMEM>
+__global__ void __launch_bounds__(kArThreads) allreduce_oneshot_kernel(const ArParams p) {
+  rank_barrier(p, 23);
+  const int64_t nvec = p.bytes / 16;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    Vec16 v;
+    if constexpr (MULTIMEM) v = multimem_ld_reduce<T>(static_cast<const char*>(p.mc) + p.offset_bytes + i * 16);
+    else v = peer_sum<T>(p, p.offset_bytes + i * 16);
+    *reinterpret_cast<Vec16*>(static_cast<char*>(p.out) + i * 16) = v;
+  }
+  rank_barrier(p, 24);   // nobody overwrites its buffer while a peer still reads it
+}
+
+}  // namespace
+}  // namespace b200
+
+extern "C" int b200_allreduce_max_blocks(void) { return 64; }
+
+extern "C" int b200_allreduce_flag_words(int world_size) { return 64 * world_size; }
+
+extern "C" int b200_allreduce(void* const* peer_buffers, void* const* peer_signal_pads, void* multicast_buffer,
+                              void* out, int* status, int64_t offset_bytes, int64_t bytes, int dtype, int rank,
+                              int world_size, int one_shot, int num_blocks, int64_t flag_base_words, void* stream) {
+  using namespace b200;
+  if (!peer_buffers || !peer_signal_pads || !status) return B200_ERR_NULL_PTR;
+  if (world_size < 2 || world_size > kMaxRanks || rank < 0 || rank >= world_size) return B200_ERR_BAD_SHAPE;
+  if (dtype != B200_DT_BF16 && dtype != B200_DT_F16) return B200_ERR_BAD_DTYPE;
+  if (bytes < 0 || offset_bytes < 0 || flag_base_words < 0) return B200_ERR_BAD_SHAPE;
+  if (bytes == 0) return B200_OK;
+  if (one_shot ? (bytes % 16 != 0) : (bytes % (16 * world_size) != 0)) return B200_ERR_BAD_SHAPE;
+  if (offset_bytes % 16 != 0) return B200_ERR_MISALIGNED;
+  if (one_shot && !out) return B200_ERR_NULL_PTR;
+  if (num_blocks <= 0) num_blocks = 32;
+  if (num_blocks > b200_allreduce_max_blocks()) num_blocks = b200_allreduce_max_blocks();
+  int rc = require_sm100();
+  if (rc != B200_OK) return rc;
+  ArParams p;
+  for (int r = 0; r < kMaxRanks; ++r) {
+    p.peers[r] = r < world_size ? peer_buffers[r] : nullptr;
+    p.signals[r] = r < world_size ? static_cast<uint32_t*>(peer_signal_pads[r]) : nullptr;
+    if (r < world_size && (!p.peers[r] || !p.signals[r])) return B200_ERR_NULL_PTR;
+    if (r < world_size && !aligned16(p.peers[r])) return B200_ERR_MISALIGNED;
+  }
+  p.local = p.peers[rank];
+  p.mc = multicast_buffer;
+  p.out = out;
+  p.status = status;
+  p.offset_bytes = offset_bytes;
+  p.bytes = bytes;
+  p.rank = rank;
+  p.world = world_size;
+  p.flag_base = static_cast<uint32_t>(flag_base_words);
+  // no more blocks than 16-byte vectors of work per rank
+  const int64_t vecs = (one_shot ? bytes : bytes / world_size) / 16;
+  const int64_t want = (vecs + kArThreads - 1) / kArThreads;
+  if (want < num_blocks) num_blocks = static_cast<int>(want < 1 ? 1 : want);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool mm = multicast_buffer != nullptr;
+#define B200_AR_LAUNCH(KERN, T)                                                       \
+  do {                                                                                \
+    if (mm) KERN<T, true><<<num_blocks, kArThreads, 0, st>>>(p);                      \
+    else KERN<T, false><<<num_blocks, kArThreads, 0, st>>>(p);                        \
+  } while (0)
+  if (one_shot) {
+    if (dtype == B200_DT_BF16) B200_AR_LAUNCH(allreduce_oneshot_kernel, __nv_bfloat16);
+    else B200_AR_LAUNCH(allreduce_oneshot_kernel, __half);
+  } else {
+    if (dtype == B200_DT_BF16) B200_AR_LAUNCH(allreduce_twoshot_kernel, __nv_bfloat16);
+    else B200_AR_LAUNCH(allreduce_twoshot_kernel, __half);
+  }
+#undef B200_AR_LAUNCH
+  B200_CUDA_TRY(cudaGetLastError());
+  return B200_OK;
+}

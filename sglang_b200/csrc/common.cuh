@@ -101,8 +101,30 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity, ui
   return ok != 0;
 }
 
+// Status words of the GEMM kernels: one 4 KB-aligned ring of ints per device.  Word 0 is the device's
+// sticky error code, words 2..3 hold the device address of its mirror in pinned host memory, words
+// kStatusFirstSlot.. are per-launch slots (a launch watches only its own slot, so a code left by an
+// earlier launch cannot make a healthy kernel abandon its waits).
+constexpr int kStatusRingInts = 1024;
+constexpr int kStatusFirstSlot = 8;
+
+// Records that a wait of this launch gave up: the launch's slot (read by the launch's other waiters),
+// the device's sticky word and its host mirror (read by the host without a synchronisation).
+__device__ __forceinline__ void report_wait_failure(int* slot, int code) {
+  atomicCAS(slot, 0, code);
+  int* ring = reinterpret_cast<int*>(reinterpret_cast<uintptr_t>(slot) & ~uintptr_t(kStatusRingInts * 4 - 1));
+  if (atomicCAS(ring, 0, code) == 0) {
+    int* host = *reinterpret_cast<int* volatile*>(ring + 2);
+    if (host != nullptr) {
+      *reinterpret_cast<volatile int*>(host) = code;
+      __threadfence_system();
+    }
+  }
+}
+
 // Bounded wait: gives up after ~kWaitLimitCycles SM clocks (about a second), records `code`
-// in *status (first failure wins) and returns false.  Callers leave their loops on false.
+// (first failure wins) and returns false.  `status` is the launch's slot of the status ring.
+// Callers leave their loops on false.
 constexpr long long kWaitLimitCycles = 2000000000LL;
 
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code,
@@ -112,9 +134,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity, hint_ns)) {
     if ((++spins & 0xffu) == 0) {
-      if (*reinterpret_cast<volatile int*>(status) != 0) return false;  // someone else gave up
+      if (*reinterpret_cast<volatile int*>(status) != 0) return false;  // another wait of this launch gave up
       if (clock64() - t0 > kWaitLimitCycles) {
-        atomicCAS(status, 0, code);
+        report_wait_failure(status, code);
         return false;
       }
     }

@@ -110,8 +110,10 @@ __device__ __forceinline__ TileInfo get_tile(int tile, const GemmParams& p, int 
     t.expert = lo;
     const int m_blk = mt - tile_m_start[lo];
     const int m_e = p.problem_sizes[lo * 3];
-    t.row0 = p.expert_offsets[lo] + m_blk * BLOCK_M;
-    t.valid_rows = min(BLOCK_M, m_e - m_blk * BLOCK_M);
+    // Tables that do not describe the buffers (left over from another batch, never filled) must not send a
+    // store outside `out`: the tile is clamped into [0, total rows).
+    t.row0 = min(max(p.expert_offsets[lo] + m_blk * BLOCK_M, 0), p.M - 1);
+    t.valid_rows = max(0, min(min(BLOCK_M, m_e - m_blk * BLOCK_M), p.M - t.row0));
     t.b_row0 = lo * p.N + t.n_blk * BLOCK_N;
   }
   return t;
@@ -561,31 +563,12 @@ int launch_dtype(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams&
   }
 }
 
-// Experimental variants selectable through b200_debug_force_block_n (values >= 1000).
-int launch_variant(int id, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t st) {
-  switch (id) {
-    case 1001: return launch_dtype<128, 16, 32>(ma, mb, p, st);
-    case 1002: return launch_dtype<128, 8, 64>(ma, mb, p, st);
-    case 1003: return launch_dtype<128, 8, 32>(ma, mb, p, st);
-    case 1004: return launch_dtype<256, 16, 32>(ma, mb, p, st);
-    case 1005: return launch_dtype<256, 16, 16>(ma, mb, p, st);
-    case 1006: return launch_dtype<256, 8, 32>(ma, mb, p, st);
-    default: return B200_ERR_UNSUPPORTED;
-  }
-}
-
 }  // namespace
 
-// Kernel override for experiments and tests: 0 = automatic, 128 / 256 = single-CTA kernel with that
-// BLOCK_N, 2 = CTA-pair kernel, 1001.. = single-CTA variants (see launch_variant).
+// Kernel override for the tests, so that every kernel is reached on every shape: 0 = automatic,
+// 128 / 256 = the 128-token-tile kernel with that BLOCK_N, 3 / 3032 / 3064 / 3128 and 4: see below.
 int g_force_block_n = 0;
-// Pair-kernel timing experiments (bit mask): 1 = epilogue skips tensor-memory reads and FMAs,
-// 2 = no TMA and the MMA does not wait for operands, 16 = epilogue skips only the FMAs.
-int g_gemm_debug_mode = 0;
-int g_gemm_wait_hint_ns = 0;
-long long* g_gemm_debug_buf = nullptr;
 
-int launch_gemm_pair(const void* a, int64_t lda, const void* b, int64_t ldb, const GemmParams& p, cudaStream_t stream);
 int launch_gemm_swapab(const void* a, int64_t lda, int64_t a_rows, const void* b, int64_t ldb, int64_t w_rows,
                        const GemmParams& p, bool grouped, int token_tile, cudaStream_t stream);
 
@@ -682,6 +665,7 @@ int dense_mm(const void* a, int64_t lda, const void* b, int64_t ldb, const float
   }
   int rc = require_sm100();
   if (rc != B200_OK) return rc;
+  if (gemm_sticky_status() != 0) return B200_ERR_DEVICE_TIMEOUT;   // sticky until b200_gemm_device_status clears it
   TailPlan tail;
   if (split_k == 0) {
     // automatic: split only when the caller gave room for it
@@ -716,16 +700,11 @@ int dense_mm(const void* a, int64_t lda, const void* b, int64_t ldb, const float
   }
   p.partial = static_cast<float*>(workspace);
   p.sa_ue8m0 = sa_ue8m0;
-  p.debug_mode = g_gemm_debug_mode;
-  p.debug_buf = g_gemm_debug_buf;
-  p.wait_hint_ns = static_cast<uint32_t>(g_gemm_wait_hint_ns);
   if (!p.status) return B200_ERR_CUDA;
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // One CTA per tile: 128 x 256 when that fills at least three quarters of the SMs in one wave (two
-  // waves of half-size tiles take as long), else 128 x 128.  (The CTA-pair
-  // kernel in gemm_2cta.cu is correct but measured slower; it runs only when forced.)
-  if (g_force_block_n == 2 && p.split_k == 1 && !sa_ue8m0) return launch_gemm_pair(a, lda, b, ldb, p, st);
+  // waves of half-size tiles take as long), else 128 x 128.
   if (g_force_block_n == 3 || forced_token_tile() != 0 || (g_force_block_n == 0 && dense_uses_swapab(M))) {
     int tt = forced_token_tile();
     if (tt == 0) tt = M <= 32 ? 32 : (M <= 64 ? 64 : 128);
@@ -741,15 +720,13 @@ int dense_mm(const void* a, int64_t lda, const void* b, int64_t ldb, const float
   int block_n = 256;
   if (p.split_k == 1 || p.tail_first > 0) block_n = dense_block_n(M, N, sm_count());
   if (g_force_block_n == 128 || g_force_block_n == 256) block_n = g_force_block_n;
-  if (g_force_block_n >= 1000) block_n = g_force_block_n <= 1003 ? 128 : 256;
 
   CUtensorMap ma, mb;
   rc = make_map_u8_2d(&ma, a, M, K, lda, BLOCK_M);
   if (rc != B200_OK) return rc;
   rc = make_map_u8_2d(&mb, b, N, K, ldb, block_n);
   if (rc != B200_OK) return rc;
-  if (g_force_block_n >= 1000) rc = launch_variant(g_force_block_n, ma, mb, p, st);
-  else rc = block_n == 256 ? launch_dtype<256, 16, 32>(ma, mb, p, st) : launch_dtype<128, 8, 64>(ma, mb, p, st);
+  rc = block_n == 256 ? launch_dtype<256, 16, 32>(ma, mb, p, st) : launch_dtype<128, 8, 64>(ma, mb, p, st);
   if (rc != B200_OK || p.split_k == 1) return rc;
   if (p.tail_first > 0) {
     switch (out_dtype) {
@@ -830,8 +807,12 @@ extern "C" int b200_fp8_blockwise_scaled_grouped_mm(const void* a, int64_t lda, 
   if ((lda % 16) != 0 || (ldb % 16) != 0 || !aligned16(a) || !aligned16(b)) return B200_ERR_MISALIGNED;
   if (sa_stride_m < 0 || sa_stride_g < 0 || sb_stride_e < 0 || sb_stride_n < 0 || sb_stride_g < 0)
     return B200_ERR_BAD_STRIDE;
+  // an expert's weights are rows [e*N, (e+1)*N) of one matrix and its scales are indexed by 128-row block:
+  // with N % 128 != 0 both would straddle experts
+  if (N % 128 != 0) return B200_ERR_BAD_SHAPE;
   int rc = require_sm100();
   if (rc != B200_OK) return rc;
+  if (gemm_sticky_status() != 0) return B200_ERR_DEVICE_TIMEOUT;
 
   GemmParams p;
   p.sa = sa; p.sb = sb; p.out = out;
@@ -843,8 +824,6 @@ extern "C" int b200_fp8_blockwise_scaled_grouped_mm(const void* a, int64_t lda, 
   p.status = gemm_status_ptr();
   p.expert_offsets = expert_offsets; p.problem_sizes = problem_sizes; p.num_experts = num_experts;
   p.split_k = 1; p.kb_per_split = 0; p.partial = nullptr; p.tail_first = 0; p.sa_ue8m0 = 0;
-  p.debug_mode = g_gemm_debug_mode; p.debug_buf = g_gemm_debug_buf;
-  p.wait_hint_ns = static_cast<uint32_t>(g_gemm_wait_hint_ns);
   if (!p.status) return B200_ERR_CUDA;
 
   // An expert's weights are rows [e*N, (e+1)*N) of one [E*N, K] matrix; a 128 x 256 tile must not
@@ -868,21 +847,6 @@ extern "C" int b200_fp8_blockwise_scaled_grouped_mm(const void* a, int64_t lda, 
   if (rc != B200_OK) return rc;
   return block_n == 256 ? launch_dtype<256, 16, 32, true>(ma, mb, p, st)
                         : launch_dtype<128, 8, 64, true>(ma, mb, p, st);
-}
-
-extern "C" int b200_debug_set_timing_buffer(void* device_buf_5x64_i64) {
-  b200::g_gemm_debug_buf = static_cast<long long*>(device_buf_5x64_i64);
-  return B200_OK;
-}
-
-extern "C" int b200_debug_wait_hint_ns(int ns) {
-  b200::g_gemm_wait_hint_ns = ns;
-  return B200_OK;
-}
-
-extern "C" int b200_debug_gemm_mode(int mode) {
-  b200::g_gemm_debug_mode = mode;
-  return B200_OK;
 }
 
 extern "C" int b200_debug_force_block_n(int block_n) {

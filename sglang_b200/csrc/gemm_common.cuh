@@ -31,17 +31,13 @@ struct GemmParams {
   // activation scales given as packed UE8M0 exponent bytes (four k-blocks per 32-bit word) instead of fp32:
   // element (m, kb) is byte kb % 4 of the word at sa[(kb / 4) * sa_stride_g + m * sa_stride_m]
   int sa_ue8m0;
-  uint32_t wait_hint_ns;  // suspend-time hint for mbarrier waits (0 = none)
-  long long* debug_buf;  // timing experiments: clock64 samples [5][64] of pair 0's leader CTA, or null
-  int debug_mode;  // timing experiments only (results are wrong when non-zero); 0 in normal use
 };
 
 
-extern int g_gemm_debug_mode;
-extern int g_gemm_wait_hint_ns;
-extern long long* g_gemm_debug_buf;
-// Device status word of the GEMM kernels on the current device (0 = ok), or nullptr on error.
+// A fresh slot of the current device's status ring for one launch, or nullptr on error.
 int* gemm_status_ptr();
+// The device's sticky error code as mirrored in pinned host memory (0 = none); no synchronisation.
+int gemm_sticky_status();
 // 2-D tensor map over a row-major [rows, cols] byte matrix with leading dimension ld, box =
 // box_rows x 128 bytes, 128-byte swizzle, zero fill outside the matrix.
 int make_map_u8_2d(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows);

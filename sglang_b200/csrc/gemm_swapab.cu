@@ -98,8 +98,11 @@ __device__ __forceinline__ SwapTile get_swap_tile(int tile, const GemmParams& p,
     }
     const int sub = mt - tile_start[lo];
     t.expert = lo;
-    t.row0 = p.expert_offsets[lo] + sub * TN;
-    t.valid = min(TN, p.problem_sizes[lo * 3] - sub * TN);
+    // Tables that do not describe the buffers (left over from another batch, never filled) must not send a
+    // store outside `out`: the tile is clamped into [0, total rows); what it then computes is meaningless,
+    // but so were the tables.
+    t.row0 = min(max(p.expert_offsets[lo] + sub * TN, 0), p.M - 1);
+    t.valid = max(1, min(min(TN, p.problem_sizes[lo * 3] - sub * TN), p.M - t.row0));
     t.n0 = nt * BLOCK_W;
     t.w_row0 = lo * p.N + t.n0;
   }
@@ -206,17 +209,13 @@ gemm_block_fp8_swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __
         ok = mbar_wait_warp(&done_bar[stage], phase ^ 1u, p.status, 1);
         if (!ok) break;
         if (elect_one()) {
-          // timing experiments (results are wrong): bit 2 = no activation loads, bit 8 = no weight loads
-          const bool load_x = !(p.debug_mode & 2), load_w = !(p.debug_mode & 8);
           const int n = min(kPair, kb_end - kb);
-          mbar_expect_tx(&full_bar[stage], n * ((load_w ? C::kWBytes : 0) + (load_x ? C::kXBytes : 0)));
+          mbar_expect_tx(&full_bar[stage], n * (C::kWBytes + C::kXBytes));
           for (int j = 0; j < n; ++j) {
-            if (load_w)
-              tma_load_2d(smem_w + (stage * kPair + j) * C::kWBytes, &map_w, &full_bar[stage], (kb + j) * BLOCK_K,
-                          t.w_row0);
-            if (load_x)
-              tma_load_2d(smem_x + (stage * kPair + j) * C::kXBytes, &map_x, &full_bar[stage], (kb + j) * BLOCK_K,
-                          t.row0);
+            tma_load_2d(smem_w + (stage * kPair + j) * C::kWBytes, &map_w, &full_bar[stage], (kb + j) * BLOCK_K,
+                        t.w_row0);
+            tma_load_2d(smem_x + (stage * kPair + j) * C::kXBytes, &map_x, &full_bar[stage], (kb + j) * BLOCK_K,
+                        t.row0);
           }
         }
         __syncwarp();
@@ -236,7 +235,7 @@ gemm_block_fp8_swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __
     bool ok = true;
     for (int vt = blockIdx.x; ok && vt < num_vtiles; vt += gridDim.x) {
       const SwapTile t = get_swap_tile<GROUPED, TN>(vt / split_k, p, m_tiles, n_tiles, tile_start);
-      const int tn = (p.debug_mode & 4) ? 16 : ((t.valid + 15) & ~15);   // bit 4: timing experiment, narrow MMA
+      const int tn = (t.valid + 15) & ~15;
       const uint32_t idesc = umma_idesc_e4m3(BLOCK_W, tn);
       const int split = vt % split_k;
       const int kb_begin = split * kbps, kb_end = min(nkb, kb_begin + kbps);
@@ -248,21 +247,17 @@ gemm_block_fp8_swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __
         tc_fence_after();
         const int n = min(kPair, kb_end - kb);
         if (elect_one()) {
-          if (p.debug_mode & 16) {   // timing experiment: no tensor-core work at all, only the barrier
-            mbar_arrive(&done_bar[stage]);
-          } else {
-            for (int j = 0; j < n; ++j) {
-              const uint64_t w_desc = w_desc0 + static_cast<uint64_t>((stage * kPair + j) * (C::kWBytes >> 4));
-              const uint64_t x_desc = x_desc0 + static_cast<uint64_t>((stage * kPair + j) * (C::kXBytes >> 4));
-              const uint32_t d_tmem = tmem_base + static_cast<uint32_t>((ap * kPair + j) * TN);
+          for (int j = 0; j < n; ++j) {
+            const uint64_t w_desc = w_desc0 + static_cast<uint64_t>((stage * kPair + j) * (C::kWBytes >> 4));
+            const uint64_t x_desc = x_desc0 + static_cast<uint64_t>((stage * kPair + j) * (C::kXBytes >> 4));
+            const uint32_t d_tmem = tmem_base + static_cast<uint32_t>((ap * kPair + j) * TN);
 #pragma unroll
-              for (int k = 0; k < BLOCK_K / 32; ++k) {
-                umma_f8(d_tmem, w_desc + static_cast<uint64_t>(2 * k), x_desc + static_cast<uint64_t>(2 * k), idesc,
-                        k > 0 ? 1u : 0u);
-              }
+            for (int k = 0; k < BLOCK_K / 32; ++k) {
+              umma_f8(d_tmem, w_desc + static_cast<uint64_t>(2 * k), x_desc + static_cast<uint64_t>(2 * k), idesc,
+                      k > 0 ? 1u : 0u);
             }
-            umma_commit(&done_bar[stage]);
           }
+          umma_commit(&done_bar[stage]);
         }
         __syncwarp();
         if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
@@ -367,7 +362,7 @@ gemm_block_fp8_swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __
       const int kb_begin = split * kbps, kb_end = min(nkb, kb_begin + kbps);
       const int col0 = part * CPW;                    // first token column of this warp
       const int my_cols = min(CPW, t.valid - col0);   // <= 0: nothing to read for this warp
-      const bool live = my_cols > 0 && !(p.debug_mode & 1);
+      const bool live = my_cols > 0;
       float acc0[FR], acc1[FR];                       // fragment 0 / fragment 1
 #pragma unroll
       for (int c = 0; c < FR; ++c) acc0[c] = acc1[c] = 0.f;

@@ -25,7 +25,6 @@
 #include "common.cuh"
 
 namespace b200 {
-int g_force_quant_passes = 0;  // experiments: 1, 2, 4 or 8 rows-of-4 per tile; 0 = automatic
 namespace {
 
 constexpr int kThreads = 256;
@@ -265,7 +264,6 @@ int launch_group(const void* x, void* q, float* s, int64_t M, int64_t K, int64_t
   auto tiles_for = [&](int passes) { return ((M + 4 * passes - 1) / (4 * passes)) * tiles_k; };
   int passes = kDefaultPasses;
   while (passes > 1 && tiles_for(passes) < 4LL * sms) passes >>= 1;
-  if (g_force_quant_passes > 0 && g_force_quant_passes <= kMaxPasses) passes = g_force_quant_passes;
   const int64_t tiles = tiles_for(passes);
   if (tiles > 0x7fffffffLL) return B200_ERR_TOO_LARGE;
   const dim3 grid(static_cast<unsigned>(tiles));
@@ -337,11 +335,6 @@ extern "C" int b200_per_token_group_quant_fp8_ieee_div(const void* x, int x_dtyp
                                                        void* stream) {
   return b200::quant_entry<true>(x, x_dtype, q, s, M, K, group_size, s_stride_row, s_stride_grp, eps, fp8_min,
                                  fp8_max, stream);
-}
-
-extern "C" int b200_debug_force_quant_passes(int passes) {
-  b200::g_force_quant_passes = passes;
-  return B200_OK;
 }
 
 extern "C" int b200_silu_mul_per_token_group_quant_fp8(const void* x, int x_dtype, void* q, float* s, int64_t M,

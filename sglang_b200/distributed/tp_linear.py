@@ -64,13 +64,17 @@ class ColumnParallelBlockFp8Linear:
 
 
 class RowParallelBlockFp8Linear:
-    """overlap_chunks > 1: the rows are processed in that many chunks and the all-reduce of chunk i
-    runs on a side stream while chunk i+1 is quantised and multiplied (CUDA only).  The sum per
-    element is the same collective on the same values, so results equal the unchunked form."""
+    """all_reduce: a SymmetricAllReduce (custom_all_reduce.py) to sum the partial outputs with this
+    library's NVLink kernels; the GEMM then writes straight into the symmetric buffer.  None = NCCL
+    (`dist.all_reduce`), as the reference does.
+
+    overlap_chunks > 1: the rows are processed in that many chunks and the all-reduce of chunk i runs on
+    a side stream while chunk i+1 is quantised and multiplied (CUDA only).  The sum per element is the
+    same collective on the same values, so results equal the unchunked form."""
 
     def __init__(self, weight, weight_scale, bias: Optional[torch.Tensor] = None, group=None,
                  linear_fn: Callable = _default_linear, reduce_results: bool = True, already_sharded: bool = False,
-                 overlap_chunks: int = 1):
+                 overlap_chunks: int = 1, all_reduce=None):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -83,20 +87,36 @@ class RowParallelBlockFp8Linear:
         self._linear = linear_fn
         self.overlap_chunks = max(1, int(overlap_chunks))
         self._comm_stream = None
+        self.all_reduce = all_reduce
+
+    def _reduce(self, t: torch.Tensor) -> torch.Tensor:
+        if self.all_reduce is not None:
+            return self.all_reduce.all_reduce(t)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
+        return t
+
+    def _out_buffer(self, M: int, x: torch.Tensor) -> torch.Tensor:
+        N = self.weight.shape[0]
+        if self.all_reduce is not None:
+            return self.all_reduce.buffer((M, N), x.dtype)
+        return torch.empty((M, N), dtype=x.dtype, device=x.device)
 
     def forward(self, x_shard: torch.Tensor) -> torch.Tensor:
         bias = self.bias if self.rank == 0 else None   # added once, before the sum
         reduce = self.reduce_results and self.world > 1
         M = x_shard.shape[0] if x_shard.dim() == 2 else 0
-        if not (reduce and self.overlap_chunks > 1 and x_shard.is_cuda and M >= 256 * self.overlap_chunks):
-            out = self._linear(x_shard, self.weight, self.weight_scale, bias)
-            if reduce:
-                dist.all_reduce(out, op=dist.ReduceOp.SUM, group=self.group)
-            return out
+        if not reduce:
+            return self._linear(x_shard, self.weight, self.weight_scale, bias)
+        if not (self.overlap_chunks > 1 and x_shard.is_cuda and M >= 256 * self.overlap_chunks):
+            if self.all_reduce is not None and x_shard.dim() == 2:
+                out = self._linear(x_shard, self.weight, self.weight_scale, bias, out=self._out_buffer(M, x_shard))
+            else:
+                out = self._linear(x_shard, self.weight, self.weight_scale, bias)
+            return self._reduce(out)
         if self._comm_stream is None:
             self._comm_stream = torch.cuda.Stream(device=x_shard.device)
         main = torch.cuda.current_stream(x_shard.device)
-        out = torch.empty((M, self.weight.shape[0]), dtype=x_shard.dtype, device=x_shard.device)
+        out = self._out_buffer(M, x_shard)
         rows = (M + self.overlap_chunks - 1) // self.overlap_chunks
         rows = (rows + 127) // 128 * 128
         for lo in range(0, M, rows):
@@ -106,7 +126,10 @@ class RowParallelBlockFp8Linear:
             ready.record(main)
             with torch.cuda.stream(self._comm_stream):
                 self._comm_stream.wait_event(ready)
-                dist.all_reduce(out[lo:hi], op=dist.ReduceOp.SUM, group=self.group)
+                if self.all_reduce is not None:
+                    self.all_reduce.all_reduce_(out[lo:hi])
+                else:
+                    dist.all_reduce(out[lo:hi], op=dist.ReduceOp.SUM, group=self.group)
         main.wait_stream(self._comm_stream)
         return out
 

@@ -11,7 +11,29 @@ from typing import Callable, List, Optional
 import torch
 
 from ...sgl_kernel import fp8_blockwise_scaled_mm
-from .fp8_kernel import sglang_per_token_group_quant_fp8, w8a8_block_fp8_matmul_deepgemm
+from .fp8_kernel import sglang_per_token_group_quant_fp8, w8a8_block_fp8_matmul, w8a8_block_fp8_matmul_deepgemm
+
+
+def ragged_w8a8_block_fp8_linear(input: torch.Tensor, weight: torch.Tensor, block_size: List[int],
+                                 weight_scale: torch.Tensor, input_scale: Optional[torch.Tensor] = None,
+                                 bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Weights whose N or K is not a multiple of 128 (DeepSeek-V3's kv_a_proj_with_mqa has N = 576) with
+    ceil-sized block scales: row-major activation scales and the [N, K]-weight entry of the same CUDA kernel,
+    which masks the ragged last block.  Takes the place of the reference's triton_w8a8_block_fp8_linear
+    (python/sglang/srt/layers/quantization/fp8_utils.py:289-309), the branch its CUTLASS linear falls back
+    to for such shapes (:190-197)."""
+    assert input_scale is None
+    input_2d = input.view(-1, input.shape[-1])
+    output_shape = [*input.shape[:-1], weight.shape[0]]
+    q_input, x_scale = sglang_per_token_group_quant_fp8(input_2d, block_size[1], column_major_scales=False)
+    output = w8a8_block_fp8_matmul(q_input, weight, x_scale, weight_scale, block_size, output_dtype=input_2d.dtype)
+    if bias is not None:
+        output += bias
+    return output.to(dtype=input_2d.dtype).view(*output_shape)
+
+
+# the name the reference's callers import for this branch
+triton_w8a8_block_fp8_linear = ragged_w8a8_block_fp8_linear
 
 
 def w8a8_block_fp8_linear(input: torch.Tensor, weight: torch.Tensor, block_size: List[int],
@@ -20,6 +42,12 @@ def w8a8_block_fp8_linear(input: torch.Tensor, weight: torch.Tensor, block_size:
     """`out` (extension): a row-major [tokens, N] tensor of the input dtype to write into."""
     assert input_scale is None
     assert list(block_size) == [128, 128]
+    if weight.shape[0] % 128 != 0 or weight.shape[1] % 128 != 0:
+        y = ragged_w8a8_block_fp8_linear(input, weight, block_size, weight_scale, input_scale, bias)
+        if out is not None:
+            out.copy_(y.view(out.shape))
+            return out.view(y.shape)
+        return y
     input_2d = input.view(-1, input.shape[-1])
     output_shape = [*input.shape[:-1], weight.shape[0]]
     q_input, x_scale = sglang_per_token_group_quant_fp8(

@@ -75,25 +75,140 @@ def _ep_worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
-def _run(worker):
-    world, port = 2, _free_port()
+def _ar_worker(rank, world, port, q):
+    """The library's own all-reduce kernels: two-shot in place (multicast when the machine offers it, and the
+    peer-pointer form), one-shot, on a ragged-looking size; every element must be the fp32 sum rounded once,
+    identical on both ranks, and a second call must work on the same flags."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from sglang_b200.distributed.custom_all_reduce import SymmetricAllReduce
+        results = {}
+        for use_mc in (True, False):
+            ar = SymmetricAllReduce(8 << 20, use_multicast=use_mc)
+            results[f"multicast_{use_mc}"] = ar.multicast
+            for it, (rows, cols, dtype) in enumerate([(512, 7168, torch.bfloat16), (48, 1024, torch.float16),
+                                                       (512, 7168, torch.bfloat16)]):
+                g = torch.Generator(device="cuda").manual_seed(100 * it + rank)
+                mine = torch.randn(rows, cols, generator=g, device="cuda").to(dtype)
+                parts = [torch.empty_like(mine) for _ in range(world)]
+                dist.all_gather(parts, mine)
+                want = sum(p_.float() for p_ in parts).to(dtype)
+                buf = ar.buffer((rows, cols), dtype)
+                buf.copy_(mine)
+                got2 = ar.all_reduce_(buf).clone()
+                buf.copy_(mine)
+                torch.cuda.synchronize(); dist.barrier()
+                got1 = ar.all_reduce_small(buf[:16])     # one-shot over the first rows
+                # a row slice in the middle of the buffer (what the chunked row-parallel linear reduces)
+                buf.copy_(mine)
+                torch.cuda.synchronize(); dist.barrier()
+                ar.all_reduce_(buf[rows // 2:])
+                got_half = buf[rows // 2:].clone()
+                untouched = torch.equal(buf[:rows // 2], mine[:rows // 2])
+                ar.check()
+                key = f"mc{int(use_mc)}_{it}"
+                results[key] = (bool(torch.equal(got2, want)), bool(torch.equal(got1, want[:16])),
+                                bool(torch.equal(got_half, want[rows // 2:])), bool(untouched))
+            del ar
+        gathered = [None] * world
+        dist.all_gather_object(gathered, results)
+        if rank == 0:
+            q.put(gathered)
+    finally:
+        dist.destroy_process_group()
+
+
+def _tp_custom_worker(rank, world, port, q):
+    """Row-parallel linear with the custom all-reduce, whole and in overlapped row chunks, against the
+    unsharded linear; NCCL-reduced overlapped chunks against NCCL unchunked (bias on rank 0 only)."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from sglang_b200.distributed import RowParallelBlockFp8Linear
+        from sglang_b200.distributed.custom_all_reduce import SymmetricAllReduce
+        from sglang_b200.layers.quantization.fp8_utils import w8a8_block_fp8_linear
+        M, K, N = 640, 2048, 1024
+        x = O.gen_activation(M, K, seed=11).cuda()
+        wq, ws = O.gen_weight(N, K, seed=12)
+        wq, ws = wq.cuda(), ws.cuda()
+        bias = torch.randn(N, generator=torch.Generator().manual_seed(13)).to(torch.bfloat16).cuda()
+        full = w8a8_block_fp8_linear(x, wq, [128, 128], ws, bias=bias)
+        kp = K // world
+        xs = x[:, rank * kp:(rank + 1) * kp].contiguous()
+        ar = SymmetricAllReduce(M * N * 2)
+        y_nccl = RowParallelBlockFp8Linear(wq, ws, bias)(xs).clone()
+        y_nccl_chunked = RowParallelBlockFp8Linear(wq, ws, bias, overlap_chunks=2)(xs).clone()
+        y_custom = RowParallelBlockFp8Linear(wq, ws, bias, all_reduce=ar)(xs).clone()
+        y_custom_chunked = RowParallelBlockFp8Linear(wq, ws, bias, all_reduce=ar, overlap_chunks=2)(xs).clone()
+        torch.cuda.synchronize()
+        ar.check()
+        both = [torch.empty_like(y_custom) for _ in range(world)]
+        dist.all_gather(both, y_custom)
+        if rank == 0:
+            q.put({"nccl_chunked_equal": bool(torch.equal(y_nccl, y_nccl_chunked)),
+                   "custom_chunked_equal": bool(torch.equal(y_custom, y_custom_chunked)),
+                   "custom_same_on_ranks": bool(torch.equal(both[0], both[1])),
+                   "custom_err": O.rel_l2(y_custom.float().cpu(), full.float().cpu()),
+                   "nccl_err": O.rel_l2(y_nccl.float().cpu(), full.float().cpu())})
+    finally:
+        dist.destroy_process_group()
+
+
+def _run(worker, world=2, timeout=240):
+    port = _free_port()
     ctx = mp.get_context("spawn")
-    q = ctx.SimpleQueue()
+    q = ctx.Queue()
     procs = [ctx.Process(target=worker, args=(r, world, port, q)) for r in range(world)]
-    for p in procs: p.start()
     for p in procs:
-        p.join(180)
-    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
-    return q.get()
+        p.start()
+    try:
+        for p in procs:
+            p.join(timeout)
+        codes = [p.exitcode for p in procs]
+        assert all(c == 0 for c in codes), f"rank exit codes {codes} (None = still running after {timeout} s)"
+        return q.get(timeout=30)
+    finally:
+        # never leave a rank behind holding a GPU: a stalled collective or kernel ends here
+        for p in procs:
+            if p.exitcode is None:
+                p.terminate()
+                p.join(10)
+            if p.exitcode is None:
+                p.kill()
+                p.join(10)
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+needs2 = pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+
+
+@needs2
 def test_tp2_nccl():
     col_equal, row_err = _run(_tp_worker)
     assert col_equal                      # column-parallel: the same columns, bit for bit
     assert row_err < 1e-2                 # row-parallel: bf16 partials summed in bf16
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@needs2
+def test_allreduce_kernels_2gpu():
+    per_rank = _run(_ar_worker)
+    for res in per_rank:
+        assert res["multicast_False"] is False
+        for key, val in res.items():
+            if key.startswith("mc"):
+                assert val == (True, True, True, True), (key, val, res)
+
+
+@needs2
+def test_tp2_custom_all_reduce_and_overlapped_chunks():
+    r = _run(_tp_custom_worker)
+    assert r["nccl_chunked_equal"] and r["custom_chunked_equal"] and r["custom_same_on_ranks"], r
+    # two bf16 partial outputs summed: each carries its own rounding (about 2^-9 relative)
+    assert r["custom_err"] < 5e-3 and r["nccl_err"] < 5e-3, r
+
+
+@needs2
 def test_ep2_nccl_bitwise():
     assert _run(_ep_worker)
