@@ -2,22 +2,28 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
 
-Workload (config.workload): the DeepSeek-V3-shaped dense MLP as two block-FP8 linears at
+Headline workload (config.workload): the DeepSeek-V3-shaped dense MLP as two block-FP8 linears at
 M = 4096 tokens -- gate_up (K=7168, N=36864) then down (K=18432, N=7168).  One step =
-group-quantise x, GEMM, group-quantise h, GEMM (4 kernels).  Inputs are seeded synthetic
-tensors (activations N(0,1), weights N(0,0.02) block-quantised); weights (396 MB of e4m3) and
+group-quantise x, GEMM, group-quantise h, GEMM.  Inputs are seeded synthetic tensors (activations
+N(0,1), weights N(0,0.02) block-quantised once on the full matrix); weights (396 MB of e4m3) and
 activations (210 MB of bf16) exceed the 126 MB L2, so no explicit flush is needed.
 
-N > 1 (launched by torchrun, one rank per GPU, NCCL): the same MLP tensor-parallel as in the
-reference -- gate_up column-parallel (N/p per rank, no communication), down row-parallel
-(K/p per rank) followed by one bf16 all-reduce of [4096,7168].  Total work is fixed: strong scaling.
+N > 1 (torchrun, one rank per GPU): the same MLP tensor-parallel as in the reference -- gate_up
+column-parallel (N/p per rank, no communication), down row-parallel (K/p per rank) followed by the sum of
+the bf16 partial outputs [4096,7168] across ranks (this library's NVLink all-reduce kernels; --allreduce
+nccl for the NCCL collective).  Total work is fixed: strong scaling.  Every run checks itself before it
+is timed: sampled rows of each rank's outputs against an fp32 torch restatement of the block-scaled product
+on unsharded weights, and at N > 1 the expert-parallel MoE layer against the single-GPU fused path
+(bitwise); a failed check ends the run with a non-zero exit code.
 
-The JSON line carries: value = whole-job TFLOP/s with inputs resident in HBM; e2e = the same
-through the public linear call with HOST activations (pinned) copied in and the bf16 results
-copied out inside the timed region; roofline for the dominant kernel (the gate_up GEMM) from
-CUDA events placed around its launches inside the timed region; cpu_baseline = the reference's
-own CPU block-FP8 matmul (oracle/_ref, built from the reference sources) or, where the host
-lacks AMX, the torch restatement, timed on the host cores on a bounded sample.
+At every N the step is replayed from a CUDA graph inside the timed region (per-kernel times come from a
+separate eager pass with events).  The JSON line carries: value = whole-job TFLOP/s with inputs resident
+in HBM; e2e = the same through the public linear call with HOST activations (pinned) copied in and the
+bf16 results copied out inside the timed region; roofline for the dominant kernel (the gate_up GEMM);
+quant = the group-quantisation kernel on its own benchmark configuration (M=16384 x 7168); config3 /
+config4 = the Llama-3-70B tensor-parallel layer set and the DeepSeek-V3 MoE layer; gpu_comparator = the
+reference's own sm_100a kernels (when their build is present) timed on the same inputs; cpu_baseline =
+the reference's CPU block-FP8 matmul on the host cores.
 """
 from __future__ import annotations
 
@@ -40,9 +46,13 @@ INTER = 18432
 WORKLOAD = "deepseek_v3_dense_mlp_block_fp8_M4096(gate_up K7168 N36864 + down K18432 N7168)"
 FLOPS_PER_STEP = 2.0 * M_TOKENS * (INTER2 * HIDDEN + HIDDEN * INTER)
 NOMINAL_FP8_TFLOPS = 4500.0
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the gate_up GEMM at M=4096, from the ncu
-# capture summarised in profiles/gemm_block_fp8_gate_up_M4096_dram.md (algorithmic bytes: 596.9e6)
-GEMM_TRAFFIC_BYTES = 586.4e6
+NOMINAL_HBM_GBS = 8000.0
+# DRAM bytes (read + write) of one launch of the gate_up GEMM at M=4096 on one GPU, from an ncu capture of
+# that launch (dram__bytes_read.sum + dram__bytes_write.sum; algorithmic bytes: 596.9e6)
+GEMM_TRAFFIC_BYTES_1GPU = 586.4e6
+PARITY_ROWS = 64
+TOL_LINEAR = 1e-3        # rel-L2 of a linear's bf16 output vs the fp32 restatement rounded to bf16
+TOL_ROW_PARALLEL = 5e-3  # p bf16 partial outputs, each rounded on its own, then summed (as in the reference)
 
 
 def _peaks():
@@ -56,7 +66,7 @@ def _peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi SM clocks and throttle reasons while the timed region runs."""
+    """Samples nvidia-smi SM clocks and throttle reasons while the timed regions run."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
@@ -65,11 +75,12 @@ class ClockSampler:
         self.idx = gpu_index
         self.proc = None
         self.lines = []
+        self.marks = {}
 
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.idx)], stdout=subprocess.PIPE, text=True)
+                                          "-lms", "50", "-i", str(self.idx)], stdout=subprocess.PIPE, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
         except OSError:
@@ -77,19 +88,15 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.perf_counter(), line.strip()))
 
-    def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
+    def mark(self, name):
+        self.marks[name] = time.perf_counter()
+
+    def _parse(self, lines):
         clocks, maxc, power, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        for _, ln in lines:
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 8:
                 continue
@@ -100,12 +107,34 @@ class ClockSampler:
             for n, v in zip(names, f[4:8]):
                 if v.lower().startswith("active"):
                     reasons.add(n)
+        return clocks, maxc, power, reasons
+
+    def window(self, begin, end):
+        """Median SM clock and peak power of the samples taken between two marks."""
+        t0, t1 = self.marks.get(begin), self.marks.get(end)
+        if t0 is None or t1 is None:
+            return None
+        clocks, _, power, reasons = self._parse([x for x in self.lines if t0 <= x[0] <= t1])
+        if not clocks:
+            return None
+        clocks.sort()
+        return {"sm_mhz": clocks[len(clocks) // 2], "power_w_max": max(power), "samples": len(clocks),
+                "reasons": sorted(reasons)}
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        clocks, maxc, power, reasons = self._parse(self.lines)
         if not clocks:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
         # samples under load = upper half of the power readings
         order = sorted(range(len(clocks)), key=lambda i: power[i])
-        load = [clocks[i] for i in order[len(order) // 2:]]
-        load.sort()
+        load = sorted(clocks[i] for i in order[len(order) // 2:])
         return {"sm_mhz": load[len(load) // 2], "sm_max_mhz": max(maxc), "power_w_max": max(power),
                 "samples": len(clocks), "reasons": sorted(reasons)}
 
@@ -115,7 +144,7 @@ class ClockSampler:
 # ------------------------------------------------------------------------------------------
 def cpu_reference_run(steps: int, warmup: int, sample_rows: int = 64):
     """Times the reference CPU block-FP8 matmul on `sample_rows` tokens of the workload (both
-    layers).  Returns (tflops, info dict)."""
+    layers).  Returns (tflops, seconds per pass, info dict)."""
     import torch
 
     from oracle import block_fp8_oracle as O
@@ -168,7 +197,7 @@ def run_reference_arm(args):
     if rank != 0:
         return
     steps = max(1, args.steps)
-    # the full 4096-token workload takes about 1.6 s per pass on 8 AMX cores; shrink the sample
+    # the full 4096-token workload takes about 0.5 s per pass on 16 AMX cores; shrink the sample
     # for long runs so the arm still ends within a few minutes
     rows = M_TOKENS if steps <= 30 else 512
     tflops, dt, info = cpu_reference_run(steps, min(args.warmup, 2), rows)
@@ -182,7 +211,7 @@ def run_reference_arm(args):
 
 
 # ------------------------------------------------------------------------------------------
-# GPU arm
+# shared helpers of the GPU arm
 # ------------------------------------------------------------------------------------------
 def gen_weight_device(n, k, seed, device):
     """N(0,0.02^2) weight block-quantised on the device (amax.clamp(1e-4)/448 per 128x128 block,
@@ -202,11 +231,356 @@ def gen_weight_device(n, k, seed, device):
     return q, s
 
 
+def torch_group_quant(x):
+    """Group quantisation restated in torch (the arithmetic of python/sglang/test/test_block_fp8.py:24-49
+    with the fp32 eps of the CUDA kernel): the checker's own codes and scales, not the library's."""
+    import torch
+    m, k = x.shape
+    xf = x.float().view(m, k // 128, 128)
+    s = xf.abs().amax(-1).clamp(min=1e-10) / 448.0
+    q = (xf / s[..., None]).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).view(m, k)
+    return q, s
+
+
+def torch_block_matmul_fp32(a_q, b_q, sa, sb):
+    """fp32 restatement of the block-scaled product (python/sglang/test/test_block_fp8.py:274-326 before the
+    cast): per 128-wide k-block an fp32 matmul of the dequantised codes times sa[m,kb] * sb[n/128,kb]."""
+    import torch
+    old = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        m, k = a_q.shape
+        n = b_q.shape[0]
+        c = torch.zeros((m, n), dtype=torch.float32, device=a_q.device)
+        sb_rows = sb.repeat_interleave(128, 0)[:n]
+        for kb in range(k // 128):
+            ak = a_q[:, kb * 128:(kb + 1) * 128].float()
+            bk = b_q[:, kb * 128:(kb + 1) * 128].float()
+            c += (ak @ bk.t()) * (sa[:, kb:kb + 1] * sb_rows[:, kb][None, :])
+        return c
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old
+
+
+def rel_l2(x, ref):
+    return float(((x.float() - ref.float()).norm() / ref.float().norm().clamp(min=1e-30)).item())
+
+
+def time_graph(fn, steps, barrier, stream_setup=None):
+    """Captures `fn` once, replays it `steps` times between events; returns (ms per step, graph)."""
+    import torch
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side, capture_error_mode="thread_local"):
+        fn()
+    for _ in range(3):
+        g.replay()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    a.record()
+    for _ in range(steps):
+        g.replay()
+    b.record()
+    barrier()
+    return a.elapsed_time(b) / steps, g
+
+
+def time_eager(fn, steps, warmup=3):
+    import torch
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / steps
+
+
+def gemm_status_ok():
+    import ctypes
+    from sglang_b200 import _lib
+    st = ctypes.c_int(0)
+    _lib.check("status", _lib.lib().b200_gemm_device_status(ctypes.byref(st)))
+    return st.value == 0
+
+
+# ------------------------------------------------------------------------------------------
+# extra keys: quant (config 2), Llama-3-70B layer set (config 3), MoE layer (config 4), comparator
+# ------------------------------------------------------------------------------------------
+def quant_config2(dev, pk, steps=20):
+    """Config 2: [16384, 7168] bf16 with 0.1 % outliers -> e4m3 + column-major padded fp32 scales; the inputs
+    rotate through enough buffers to exceed L2."""
+    import torch
+    from sglang_b200.layers.quantization.fp8_kernel import sglang_per_token_group_quant_fp8
+    m = 16384
+    g = torch.Generator(device=dev).manual_seed(2000)
+    xs = []
+    for _ in range(3):
+        x = torch.randn((m, HIDDEN), generator=g, device=dev)
+        x = torch.where(torch.rand((m, HIDDEN), generator=g, device=dev) < 1e-3, x * 100, x)
+        xs.append(x.to(torch.bfloat16))
+    it = [0]
+
+    def fn():
+        it[0] += 1
+        return sglang_per_token_group_quant_fp8(xs[it[0] % 3], 128, column_major_scales=True, scale_tma_aligned=True)
+    ms, g_ = time_graph(lambda: [fn() for _ in range(6)], steps, torch.cuda.synchronize)
+    g_.reset()
+    ms /= 6
+    nbytes = 3.03125 * m * HIDDEN
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    return {"bound": "hbm", "kernel": "quant_group_kernel<bf16,128> on [16384,7168] (config 2), graph replay, 3 rotating "
+                                      "inputs (705 MB)", "us": ms * 1e3, "achieved": gbs, "peak": pk["hbm_gbs"],
+            "unit": "GB/s", "frac": gbs / pk["hbm_gbs"], "frac_of_nominal_8000": gbs / NOMINAL_HBM_GBS,
+            "algorithmic_bytes_per_launch": nbytes}
+
+
+def fp8_ceiling(dev, steps=20):
+    """Yardstick only: per-tensor-scaled e4m3 torch._scaled_mm at 8192^3 (a library GEMM without block scales)."""
+    import torch
+    try:
+        x = torch.randn((8192, 8192), device=dev).to(torch.float8_e4m3fn)
+        w = torch.randn((8192, 8192), device=dev).to(torch.float8_e4m3fn)
+        one = torch.ones((), device=dev)
+        ms = time_eager(lambda: torch._scaled_mm(x, w.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16), steps)
+        return 2.0 * 8192 ** 3 / (ms * 1e-3) / 1e12
+    except Exception as e:  # noqa: BLE001
+        print(f"[bench] fp8 ceiling not measured: {e}", file=sys.stderr)
+        return None
+
+
+LLAMA = {"qkv": ("col", 10240, 8192), "gate_up": ("col", 57344, 8192), "o_proj": ("row", 8192, 8192),
+         "down": ("row", 8192, 28672)}
+
+
+def llama_config3(dev, world, rank, ar, steps=10):
+    """Config 3: the four Llama-3-70B projections tensor-parallel over `world` ranks at M = 128 and 8192, each
+    through the product's parallel linear (quantisation + GEMM + the all-reduce of the row-parallel ones),
+    replayed from a CUDA graph.  Returns {layer: {M: ms}} (max over ranks taken by the caller)."""
+    import torch
+    import torch.distributed as dist
+    from sglang_b200.distributed import ColumnParallelBlockFp8Linear, RowParallelBlockFp8Linear
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+    out = {}
+    for li, (name, (kind, n, k)) in enumerate(LLAMA.items()):
+        n_r, k_r = (n // world, k) if kind == "col" else (n, k // world)
+        wq, ws = gen_weight_device(n_r, k_r, 3000 + 10 * li + rank, dev)
+        if kind == "col":
+            layer = ColumnParallelBlockFp8Linear(wq, ws, already_sharded=True)
+        else:
+            layer = RowParallelBlockFp8Linear(wq, ws, already_sharded=True, all_reduce=ar)
+        out[name] = {}
+        for m in (128, 8192):
+            g = torch.Generator(device=dev).manual_seed(31 + m)
+            x = torch.randn((m, k_r), generator=g, device=dev).to(torch.bfloat16)
+            ms, g_ = time_graph(lambda: layer(x), steps, barrier)
+            g_.reset()
+            out[name][str(m)] = ms
+        del layer, wq, ws
+    return out
+
+
+def moe_weights(dev, experts, seed0, H=7168, I=2048):
+    """Expert weights with directly drawn codes and scales (11.3 GB for 256 experts), expert e from seed0 + e so
+    that any rank can rebuild any expert."""
+    import torch
+    w13 = torch.empty((len(experts), 2 * I, H), dtype=torch.float8_e4m3fn, device=dev)
+    w2 = torch.empty((len(experts), H, I), dtype=torch.float8_e4m3fn, device=dev)
+    w13s = torch.empty((len(experts), 2 * I // 128, H // 128), dtype=torch.float32, device=dev)
+    w2s = torch.empty((len(experts), H // 128, I // 128), dtype=torch.float32, device=dev)
+
+    def codes(g, *shape):
+        c = torch.randint(0, 0x78, shape, generator=g, device=dev, dtype=torch.uint8)
+        sign = torch.randint(0, 2, shape, generator=g, device=dev, dtype=torch.uint8) << 7
+        return (c | sign).view(torch.float8_e4m3fn)
+    for i, e in enumerate(experts):
+        g = torch.Generator(device=dev).manual_seed(seed0 + e)
+        w13[i] = codes(g, 2 * I, H)
+        w2[i] = codes(g, H, I)
+        w13s[i] = torch.rand((2 * I // 128, H // 128), generator=g, device=dev) * 2e-4 + 1e-5
+        w2s[i] = torch.rand((H // 128, I // 128), generator=g, device=dev) * 2e-4 + 1e-5
+    return w13, w2, w13s, w2s
+
+
+def moe_routing(dev, tokens, E=256, topk=8, seed=4000):
+    import torch
+    g = torch.Generator(device=dev).manual_seed(seed)
+    x = torch.randn((tokens, 7168), generator=g, device=dev).to(torch.bfloat16)
+    logits = torch.randn((tokens, E), generator=g, device=dev)
+    tw, ti = torch.topk(torch.softmax(logits.float(), dim=-1), topk, dim=-1)
+    return x, tw.contiguous(), ti.to(torch.int32).contiguous()
+
+
+def moe_config4_single(dev, pk, steps=5):
+    """Config 4 on one GPU: 256 experts, 4096 tokens, top-8 through the fused layer."""
+    import torch
+    from sglang_b200.layers.moe.cutlass_moe import fused_experts_block_fp8
+    E, H, I, topk, tokens = 256, 7168, 2048, 8, 4096
+    w13, w2, w13s, w2s = moe_weights(dev, list(range(E)), 5000)
+    x, tw, ti = moe_routing(dev, tokens)
+    ms, g_ = time_graph(lambda: fused_experts_block_fp8(x, w13, w2, w13s, w2s, tw, ti), steps, torch.cuda.synchronize)
+    g_.reset()
+    flops = 2.0 * tokens * topk * (2 * I * H + H * I)
+    wbytes = float(E) * (2 * I * H + H * I)
+    floor_ms = wbytes / (pk["hbm_gbs"] * 1e9) * 1e3
+    del w13, w2, w13s, w2s
+    torch.cuda.empty_cache()
+    return {"workload": "deepseek_v3_moe_block_fp8(256 experts, top-8, 4096 tokens, hidden 7168, intermediate 2048)",
+            "ms": ms, "tflops": flops / (ms * 1e-3) / 1e12, "weight_gbs": wbytes / (ms * 1e-3) / 1e9,
+            "weight_read_floor_ms": floor_ms, "frac_of_floor": floor_ms / ms}
+
+
+def moe_config4_ep(dev, world, rank, steps=5):
+    """Config 4 expert-parallel: 256 experts split contiguously over the ranks, 4096 tokens sharded over the
+    ranks, dispatch / local experts / combine.  Rank 0 also holds all experts and compares its own tokens with
+    the single-GPU fused layer, bit for bit."""
+    import torch
+    import torch.distributed as dist
+    from sglang_b200.distributed import ExpertParallelBlockFp8MoE
+    from sglang_b200.layers.moe.cutlass_moe import fused_experts_block_fp8
+    E, H, I, topk, tokens = 256, 7168, 2048, 8, 4096
+    el, tl = E // world, tokens // world
+    w13, w2, w13s, w2s = moe_weights(dev, list(range(rank * el, (rank + 1) * el)), 5000)
+    x_all, tw_all, ti_all = moe_routing(dev, tokens)        # same seed on every rank: identical routing
+    sl = slice(rank * tl, (rank + 1) * tl)
+    x, tw, ti = x_all[sl].contiguous(), tw_all[sl].contiguous(), ti_all[sl].contiguous()
+    moe = ExpertParallelBlockFp8MoE(w13, w2, w13s, w2s)
+    y = moe(x, tw, ti)
+    torch.cuda.synchronize()
+    ok = 1
+    if rank == 0:
+        fw13, fw2, fw13s, fw2s = moe_weights(dev, list(range(E)), 5000)
+        ref = fused_experts_block_fp8(x, fw13, fw2, fw13s, fw2s, tw, ti)
+        ok = int(torch.equal(y, ref))
+        del fw13, fw2, fw13s, fw2s, ref
+        torch.cuda.empty_cache()
+    flag = torch.tensor([ok], device=dev, dtype=torch.int32)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+    ms = []
+    for _ in range(2):
+        moe(x, tw, ti)
+    for _ in range(steps):
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        moe(x, tw, ti)
+        b.record()
+        torch.cuda.synchronize()
+        ms.append(a.elapsed_time(b))
+    t = torch.tensor([sorted(ms)[len(ms) // 2]], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    stages = getattr(moe, "last_stage_ms", None)
+    res = {"workload": f"deepseek_v3_moe_block_fp8 expert-parallel: {el} experts and {tl} tokens per rank, top-8",
+           "ms": float(t.item()), "tflops": 2.0 * tokens * topk * (2 * I * H + H * I) / (float(t.item()) * 1e-3) / 1e12,
+           "bitwise_equal_to_single_gpu_on_rank0_tokens": bool(int(flag.item()))}
+    if stages:
+        res["stages_ms_rank0"] = stages
+    return res, bool(int(flag.item()))
+
+
+def gpu_comparator(dev, steps=10):
+    """The reference's own sm_100a kernels (built by oracle/build_ref_cuda.py from the reference checkout into
+    baseline/_ref/), timed beside this library's kernels on the same inputs in this process.  Comparison
+    only: nothing here is on the product path.  Each side runs from a CUDA graph of `steps` calls."""
+    import torch
+    from oracle import build_ref_cuda as R
+    from sglang_b200.layers.quantization.fp8_kernel import sglang_per_token_group_quant_fp8
+    from sglang_b200.sgl_kernel import fp8_blockwise_scaled_mm
+    out = {"built_from": "sgl-kernel/csrc/gemm/fp8_blockwise_gemm_kernel.cu, per_token_group_quant_8bit.cu "
+                         "(CUTLASS headers of the flashinfer package, not the commit the reference pins)"}
+    have = {}
+    for fam in ("quant", "gemm"):
+        try:
+            have[fam] = R.load(fam)
+        except Exception as e:  # noqa: BLE001
+            have[fam] = False
+            out[f"{fam}_load_error"] = str(e)[:200]
+    if not any(have.values()):
+        out["unavailable"] = "baseline/_ref holds no built comparator library"
+        return out
+    ops = torch.ops.sgl_kernel_ref
+    g = torch.Generator(device=dev).manual_seed(77)
+
+    def graph_us(fn):
+        ms, g_ = time_graph(lambda: [fn() for _ in range(4)], steps, torch.cuda.synchronize)
+        g_.reset()
+        return ms / 4 * 1e3
+    if have["quant"]:
+        m = 16384
+        xs = [torch.randn((m, HIDDEN), generator=g, device=dev).to(torch.bfloat16) for _ in range(3)]
+        q = torch.empty((m, HIDDEN), device=dev, dtype=torch.float8_e4m3fn)
+        s = torch.empty((HIDDEN // 128, m), device=dev, dtype=torch.float32).t()
+        it = [0]
+
+        def ref_q():
+            it[0] += 1
+            ops.sgl_per_token_group_quant_fp8(xs[it[0] % 3], q, s, 128, 1e-10, -448.0, 448.0, False)
+
+        def our_q():
+            it[0] += 1
+            sglang_per_token_group_quant_fp8(xs[it[0] % 3], 128, column_major_scales=True)
+        ref_q()
+        q2, s2 = sglang_per_token_group_quant_fp8(xs[it[0] % 3], 128, column_major_scales=True)
+        same = bool(torch.equal(q.view(torch.uint8), q2.view(torch.uint8)) and torch.equal(s, s2))
+        t_ref, t_us = graph_us(ref_q), graph_us(our_q)
+        out["quant_M16384"] = {"reference_us": t_ref, "ours_us": t_us, "speedup": t_ref / t_us, "bit_identical": same}
+        del xs, q, s
+    if have["gemm"]:
+        for name, (m, n, k) in {"gate_up_M4096": (4096, INTER2, HIDDEN), "down_M4096": (4096, HIDDEN, INTER),
+                                "gate_up_M128": (128, INTER2, HIDDEN), "down_M128": (128, HIDDEN, INTER)}.items():
+            ncopy = 1 if m > 512 else 3       # small M streams weights: rotate copies so that they come from HBM
+            ws = [gen_weight_device(n, k, 700 + c, dev) for c in range(ncopy)]
+            x = torch.randn((m, k), generator=g, device=dev).to(torch.bfloat16)
+            a, sa = sglang_per_token_group_quant_fp8(x, 128, column_major_scales=True)
+            it = [0]
+
+            def ref_mm():
+                it[0] += 1
+                wq, wsc = ws[it[0] % ncopy]
+                return ops.fp8_blockwise_scaled_mm(a, wq.t(), sa, wsc.t(), torch.bfloat16)
+
+            def our_mm():
+                it[0] += 1
+                wq, wsc = ws[it[0] % ncopy]
+                return fp8_blockwise_scaled_mm(a, wq.t(), sa, wsc.t(), torch.bfloat16)
+            it[0] = 0
+            o_ref = ref_mm()
+            it[0] = 0
+            o_us = our_mm()
+            err = rel_l2(o_us, o_ref)
+            t_ref, t_us = graph_us(ref_mm), graph_us(our_mm)
+            out[name] = {"reference_us": t_ref, "ours_us": t_us, "speedup": t_ref / t_us, "rel_l2_between": err,
+                         "ours_tflops": 2.0 * m * n * k / (t_us * 1e-6) / 1e12,
+                         "reference_tflops": 2.0 * m * n * k / (t_ref * 1e-6) / 1e12}
+            del ws
+    return out
+
+
+# ------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------
 def run_gpu_arm(args):
     import torch
     import torch.distributed as dist
 
     from sglang_b200 import _lib
+    from sglang_b200.distributed import ColumnParallelBlockFp8Linear, RowParallelBlockFp8Linear
     from sglang_b200.layers.quantization.fp8_kernel import sglang_per_token_group_quant_fp8
     from sglang_b200.layers.quantization.fp8_utils import w8a8_block_fp8_linear
     from sglang_b200.sgl_kernel import fp8_blockwise_scaled_mm
@@ -222,185 +596,152 @@ def run_gpu_arm(args):
         dist.init_process_group("nccl", device_id=dev)
     p = world
     n1, k2 = INTER2 // p, INTER // p        # column-parallel gate_up, row-parallel down
-
-    w1q, w1s = gen_weight_device(n1, HIDDEN, 100 + rank, dev)
-    w2q, w2s = gen_weight_device(HIDDEN, k2, 200 + rank, dev)
-    w1_t, w1s_t, w2_t, w2s_t = w1q.T, w1s.T, w2q.T, w2s.T
-    g = torch.Generator(device=dev).manual_seed(7)           # x is replicated: same seed on all ranks
-    x = torch.randn((M_TOKENS, HIDDEN), generator=g, device=dev).to(torch.bfloat16)
-    gh = torch.Generator(device=dev).manual_seed(300 + rank)
-    h = torch.randn((M_TOKENS, k2), generator=gh, device=dev).to(torch.bfloat16)
-
-    ev = lambda: torch.cuda.Event(enable_timing=True)
-    kernel_events = []   # (name, start, stop) inside the timed region
-    TP_CHUNKS = args.tp_chunks or 4
-    y2_buf = torch.empty((M_TOKENS, HIDDEN), dtype=torch.bfloat16, device=dev)
-    comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
-
-    def step(record=False):
-        def timed(name, fn):
-            if not record:
-                return fn()
-            a, b = ev(), ev()
-            a.record(); r = fn(); b.record()
-            kernel_events.append((name, a, b))
-            return r
-        xq, xs = timed("quant_x", lambda: sglang_per_token_group_quant_fp8(x, 128, column_major_scales=True))
-        y1 = timed("gemm_gate_up", lambda: fp8_blockwise_scaled_mm(xq, w1_t, xs, w1s_t, torch.bfloat16))
-        if world == 1:
-            hq, hs = timed("quant_h", lambda: sglang_per_token_group_quant_fp8(h, 128, column_major_scales=True))
-            y2 = timed("gemm_down", lambda: fp8_blockwise_scaled_mm(hq, w2_t, hs, w2s_t, torch.bfloat16))
-        else:
-            # row-parallel down projection in TP_CHUNKS row chunks: the bf16 all-reduce of chunk i runs on
-            # a side stream while chunk i+1 is quantised and multiplied
-            y2 = y2_buf
-            main = torch.cuda.current_stream()
-            rows = M_TOKENS // TP_CHUNKS
-            for c in range(TP_CHUNKS):
-                sl = slice(c * rows, (c + 1) * rows)
-                hq, hs = sglang_per_token_group_quant_fp8(h[sl], 128, column_major_scales=True)
-                fp8_blockwise_scaled_mm(hq, w2_t, hs, w2s_t, torch.bfloat16, out=y2[sl])
-                ready = torch.cuda.Event()
-                ready.record(main)
-                with torch.cuda.stream(comm_stream):
-                    comm_stream.wait_event(ready)
-                    dist.all_reduce(y2[sl])
-            main.wait_stream(comm_stream)
-        return y1, y2
+    pk = _peaks()
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
+    # Weights are quantised once on the FULL matrix (same seed on every rank) and sharded by the product's
+    # parallel linears, so the tensor-parallel result is comparable with the unsharded one.
+    w1q, w1s = gen_weight_device(INTER2, HIDDEN, 100, dev)
+    w2q, w2s = gen_weight_device(HIDDEN, INTER, 200, dev)
+    ar = None
+    if world > 1 and args.allreduce == "custom":
+        from sglang_b200.distributed.custom_all_reduce import SymmetricAllReduce
+        ar = SymmetricAllReduce(max(M_TOKENS, 8192) * 8192 * 2)
+    col = ColumnParallelBlockFp8Linear(w1q, w1s)
+    row = RowParallelBlockFp8Linear(w2q, w2s, all_reduce=ar)
+    g = torch.Generator(device=dev).manual_seed(7)           # x is replicated: same seed on all ranks
+    x = torch.randn((M_TOKENS, HIDDEN), generator=g, device=dev).to(torch.bfloat16)
+    gh = torch.Generator(device=dev).manual_seed(300)        # h: every rank draws the full matrix, keeps its K slice
+    h_full = torch.randn((M_TOKENS, INTER), generator=gh, device=dev).to(torch.bfloat16)
+    h = h_full[:, rank * k2:(rank + 1) * k2].contiguous()
+
+    # ---- self-check before anything is timed
+    rows = torch.arange(0, M_TOKENS, M_TOKENS // PARITY_ROWS, device=dev)
+    y1 = col(x)
+    y2 = row(h).clone()
+    xq_r, xs_r = torch_group_quant(x[rows])
+    ref1 = torch_block_matmul_fp32(xq_r, w1q[rank * n1:(rank + 1) * n1], xs_r, w1s[rank * n1 // 128:(rank + 1) * n1 // 128])
+    hq_r, hs_r = torch_group_quant(h_full[rows])
+    ref2 = torch_block_matmul_fp32(hq_r, w2q, hs_r, w2s)
+    err1 = rel_l2(y1[rows], ref1.to(torch.bfloat16))
+    err2 = rel_l2(y2[rows], ref2.to(torch.bfloat16))
+    same_on_ranks = True
+    if world > 1:
+        y2_0 = y2[rows].clone()
+        dist.broadcast(y2_0, 0)
+        same_on_ranks = bool(torch.equal(y2_0, y2[rows]))
+    tol2 = TOL_LINEAR if world == 1 else TOL_ROW_PARALLEL
+    ok_local = int(err1 <= TOL_LINEAR and err2 <= tol2 and (same_on_ranks or ar is None) and gemm_status_ok())
+    errs = torch.tensor([err1, err2, float(ok_local)], device=dev, dtype=torch.float64)
+    if world > 1:
+        emax = errs.clone()
+        dist.all_reduce(emax, op=dist.ReduceOp.MAX)
+        emin = errs.clone()
+        dist.all_reduce(emin, op=dist.ReduceOp.MIN)
+        err1, err2, ok_all = float(emax[0]), float(emax[1]), bool(emin[2] > 0)
+    else:
+        ok_all = bool(ok_local)
+    parity = {"rows_checked": PARITY_ROWS, "checker": "fp32 torch restatement of quantisation and block-scaled product "
+                                                      "on the unsharded weights",
+              "column_parallel_rel_l2": err1, "row_parallel_rel_l2": err2,
+              "tolerance": {"linear": TOL_LINEAR, "row_parallel_sum_of_bf16_partials": tol2},
+              "all_reduced_rows_identical_on_all_ranks": same_on_ranks if world > 1 else None, "ok": ok_all}
+    del h_full, ref1, ref2
+    if ar is not None:
+        ar.check()
+
+    chunk_ms = {}
+    chunks_used = 1
+
+    def step():
+        return col(x), row(h)
+
+    if world > 1:
+        # How many row chunks the row-parallel projection is cut into is a trade between overlap (the all-reduce
+        # of one chunk under the GEMM of the next) and the fixed cost of each collective.  The warm-up measures
+        # the candidates (graph replays, slowest rank counts) and the timed region runs the fastest.
+        cands = [args.tp_chunks] if args.tp_chunks else [1, 2, 4]
+        best = None
+        for c in cands:
+            row.overlap_chunks = c
+            ms_c, g_c = time_graph(step, 10, barrier)
+            g_c.reset()
+            t = torch.tensor([ms_c], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            chunk_ms[str(c)] = round(float(t.item()), 4)
+            if best is None or float(t.item()) < best[0]:
+                best = (float(t.item()), c)
+        chunks_used = best[1]
+        row.overlap_chunks = chunks_used
+
     for _ in range(max(3, args.warmup)):
         step()
     barrier()
-    # Tensor-parallel ranks replay the step from a CUDA graph (kernels, the side-stream fork/join and the
-    # NCCL all-reduces captured once): a rank's share of the step is a few hundred microseconds of device
-    # work, less than the Python calls that enqueue it.
-    graph = None
-
-    def capture_step():
-        """The step captured into a CUDA graph on every rank, or None on every rank (the ranks agree)."""
-        cap = torch.cuda.Stream(device=dev)
-        cap.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(cap):
-            step()
-        torch.cuda.current_stream().wait_stream(cap)
-        barrier()
-        # thread-local capture mode: the process group's watchdog thread polls events while this thread
-        # captures.  Nothing executes during capture, so a rank whose capture fails can still agree with
-        # the others (one small all-reduce afterwards) to run eagerly.
-        captured = 1
-        g_ = None
-        try:
-            g_ = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g_, stream=cap, capture_error_mode="thread_local"):
-                step()
-        except Exception as e:  # noqa: BLE001
-            captured = 0
-            g_ = None
-            print(f"[bench rank {rank}] graph capture failed, running eagerly: {e}", file=sys.stderr, flush=True)
-        torch.cuda.synchronize()
-        flag = torch.tensor([captured], device=dev, dtype=torch.int32)
-        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-        if int(flag.item()) == 0:
-            if g_ is not None:
-                g_.reset()
-            return None
-        for _ in range(3):
-            g_.replay()
-            torch.cuda.synchronize()
-        barrier()
-        return g_
-
-    if world > 1 and not args.eager:
-        # How many row chunks the row-parallel projection is cut into is a trade between overlap (the
-        # all-reduce of one chunk under the GEMM of the next) and the fixed cost of each collective; which
-        # wins depends on the rank count.  With --tp-chunks 0 the warm-up measures the candidates (ten
-        # replays each, slowest rank counts) and the timed region runs the fastest.
-        candidates = [args.tp_chunks] if args.tp_chunks else [4, 2, 1]
-        best = None
-        chunk_ms = {}
-        for c in candidates:
-            TP_CHUNKS = c
-            g_ = capture_step()
-            if g_ is None:
-                break
-            if len(candidates) == 1:
-                best = (0.0, c, g_)
-                break
-            a, b = ev(), ev()
-            barrier()
-            a.record()
-            for _ in range(10):
-                g_.replay()
-            b.record()
-            barrier()
-            t = torch.tensor([a.elapsed_time(b)], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            t = float(t.item()) / 10
-            chunk_ms[str(c)] = round(t, 4)
-            if best is None or t < best[0]:
-                if best is not None:
-                    best[2].reset()
-                best = (t, c, g_)
-            else:
-                g_.reset()
-        if best is not None:
-            _, TP_CHUNKS, graph = best
-        else:
-            TP_CHUNKS = args.tp_chunks or 4
-        barrier()
-    elif world > 1:
-        TP_CHUNKS = args.tp_chunks or 4
-        chunk_ms = {}
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    # ---- timed region 1: device-resident inputs
-    t0, t1 = ev(), ev()
+        time.sleep(0.3)
+    # ---- timed region 1: device-resident inputs, the step replayed from a CUDA graph (same at every N)
+    sampler.mark("burst0")
+    ms, graph = time_graph(step, args.steps, barrier)
+    sampler.mark("burst1")
+    # ---- the same step back to back for >= 2 s: the clocks settle under the power cap
+    reps = max(args.steps, int(2000.0 / max(ms, 1e-3)) + 1)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    sampler.mark("sus0")
     t0.record()
-    for _ in range(args.steps):
-        if graph is not None:
-            graph.replay()
-        else:
-            step(record=True)
+    for _ in range(reps):
+        graph.replay()
     t1.record()
     barrier()
-    ms = t0.elapsed_time(t1) / args.steps
-    if graph is not None:
-        # per-kernel times from a few eager steps (events cannot be timed inside a graph); the capture emptied
-        # the allocator's cache, so two unrecorded steps first take the device allocations out of the figures
-        for _ in range(2):
-            step()
-        barrier()
-        for _ in range(5):
-            step(record=True)
-        barrier()
-    per_kernel = {}
-    for name, a, b in kernel_events:
-        per_kernel.setdefault(name, []).append(a.elapsed_time(b))
-    per_kernel = {k: sum(v) / len(v) for k, v in per_kernel.items()}
+    sampler.mark("sus1")
+    sustained_ms = t0.elapsed_time(t1) / reps
+    graph.reset()
 
-    # ---- timed region 2: end to end through the public linear call with host buffers.
-    # Every step copies its activations in from pinned host memory and its results back; the three legs
-    # (copy in, compute, copy out) of consecutive steps overlap on three streams with double buffers, so
-    # the steady-state step costs the slowest leg (PCIe is full duplex) instead of their sum.
+    # ---- per-kernel times: a separate eager pass with events around each call (one GPU's share of the step)
+    per_kernel = {}
+    xq, xs = sglang_per_token_group_quant_fp8(x, 128, column_major_scales=True)
+    hq, hs = sglang_per_token_group_quant_fp8(h, 128, column_major_scales=True)
+    w1r, w1sr, w2r, w2sr = col.weight, col.weight_scale, row.weight, row.weight_scale
+    calls = {"quant_x": lambda: sglang_per_token_group_quant_fp8(x, 128, column_major_scales=True),
+             "gemm_gate_up": lambda: fp8_blockwise_scaled_mm(xq, w1r.T, xs, w1sr.T, torch.bfloat16),
+             "quant_h": lambda: sglang_per_token_group_quant_fp8(h, 128, column_major_scales=True),
+             "gemm_down": lambda: fp8_blockwise_scaled_mm(hq, w2r.T, hs, w2sr.T, torch.bfloat16)}
+    for name, fn in calls.items():
+        us, g_ = time_graph(lambda: [fn() for _ in range(4)], 5, torch.cuda.synchronize)
+        g_.reset()
+        per_kernel[name] = us / 4
+    if world > 1:
+        y2b = row._out_buffer(M_TOKENS, h) if ar is not None else torch.empty((M_TOKENS, HIDDEN), dtype=torch.bfloat16, device=dev)
+        us, g_ = time_graph(lambda: row._reduce(y2b), 5, barrier)
+        g_.reset()
+        per_kernel["all_reduce_[4096,7168]_bf16"] = us
+
+    # ---- timed region 2: end to end through the public linear call with host buffers.  Every step copies its
+    # activations in from pinned host memory and its results back; the three legs (copy in, compute, copy out) of
+    # consecutive steps overlap on three streams with double buffers.  With p ranks each rank moves 1/p of every
+    # replicated tensor over its own PCIe link: its row slice of x (the ranks exchange the slices over NVLink),
+    # its own K slice of h, its own N slice of y1 and its row slice of the summed y2.
     DEPTH = 2
-    x_host = x.cpu().pin_memory()
+    mr = M_TOKENS // p
+    x_host = x[rank * mr:(rank + 1) * mr].cpu().pin_memory()
     h_host = h.cpu().pin_memory()
     y1_host = [torch.empty((M_TOKENS, n1), dtype=torch.bfloat16).pin_memory() for _ in range(DEPTH)]
-    y2_host = [torch.empty((M_TOKENS, HIDDEN), dtype=torch.bfloat16).pin_memory() for _ in range(DEPTH)]
+    y2_host = [torch.empty((mr, HIDDEN), dtype=torch.bfloat16).pin_memory() for _ in range(DEPTH)]
     x_dev = [torch.empty_like(x) for _ in range(DEPTH)]
     h_dev = [torch.empty_like(h) for _ in range(DEPTH)]
     s_in, s_comp, s_out = (torch.cuda.Stream(device=dev) for _ in range(3))
     ev_in = [torch.cuda.Event() for _ in range(DEPTH)]
     ev_comp = [torch.cuda.Event() for _ in range(DEPTH)]
     ev_out = [torch.cuda.Event() for _ in range(DEPTH)]
+    ev_y2 = [torch.cuda.Event() for _ in range(DEPTH)]
     step_no = [0]
+    row.overlap_chunks = 1
 
     def e2e_step():
         i = step_no[0]
@@ -409,22 +750,26 @@ def run_gpu_arm(args):
         with torch.cuda.stream(s_in):
             if i >= DEPTH:
                 s_in.wait_event(ev_comp[b])          # the device input buffers of step i - DEPTH have been consumed
-            x_dev[b].copy_(x_host, non_blocking=True)
+            x_dev[b][rank * mr:(rank + 1) * mr].copy_(x_host, non_blocking=True)
             h_dev[b].copy_(h_host, non_blocking=True)
             ev_in[b].record(s_in)
         with torch.cuda.stream(s_comp):
             s_comp.wait_event(ev_in[b])
-            y1 = w8a8_block_fp8_linear(x_dev[b], w1q, [128, 128], w1s)
-            y2 = w8a8_block_fp8_linear(h_dev[b], w2q, [128, 128], w2s)
             if world > 1:
-                dist.all_reduce(y2)
+                dist.all_gather_into_tensor(x_dev[b], x_dev[b][rank * mr:(rank + 1) * mr])
+            y1 = col(x_dev[b])
+            if ar is not None and i >= 1:
+                # the summed outputs live in the one symmetric buffer: the previous step's copy-out of it must be done
+                s_comp.wait_event(ev_y2[(i - 1) % DEPTH])
+            y2 = row(h_dev[b])
             ev_comp[b].record(s_comp)
         with torch.cuda.stream(s_out):
             s_out.wait_event(ev_comp[b])
             y1.record_stream(s_out)
             y2.record_stream(s_out)
+            y2_host[b].copy_(y2[rank * mr:(rank + 1) * mr], non_blocking=True)
+            ev_y2[b].record(s_out)
             y1_host[b].copy_(y1, non_blocking=True)
-            y2_host[b].copy_(y2, non_blocking=True)
             ev_out[b].record(s_out)
 
     def e2e_join():
@@ -440,7 +785,7 @@ def run_gpu_arm(args):
     e2e_join()
     barrier()
     step_no[0] = 0
-    t2, t3 = ev(), ev()
+    t2, t3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t2.record()
     for st_ in (s_in, s_comp, s_out):
         st_.wait_stream(torch.cuda.current_stream())
@@ -450,88 +795,136 @@ def run_gpu_arm(args):
     t3.record()
     barrier()
     e2e_ms = t2.elapsed_time(t3) / e2e_steps
-    clocks = sampler.stop() if rank == 0 else None
 
-    times = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+    times = torch.tensor([ms, e2e_ms, sustained_ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms, e2e_ms = float(times[0]), float(times[1])
+    ms, e2e_ms, sustained_ms = float(times[0]), float(times[1]), float(times[2])
+    status_ok = gemm_status_ok()
+    if ar is not None:
+        ar.check()
 
-    import ctypes
-    st = ctypes.c_int(0)
-    _lib.check("status", _lib.lib().b200_gemm_device_status(ctypes.byref(st)))
-    assert st.value == 0, f"GEMM device status word {st.value}"
+    # ---- extra keys (outside every timed region above)
+    extras = {}
+    del x_dev, h_dev, y1_host, y2_host
+    if not args.skip_extras:
+        c3 = llama_config3(dev, world, rank, ar)
+        flat = torch.tensor([c3[n_][m_] for n_ in LLAMA for m_ in ("128", "8192")], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(flat, op=dist.ReduceOp.MAX)
+        it = iter(flat.tolist())
+        cfg3 = {}
+        for n_, (kind, n, k) in LLAMA.items():
+            cfg3[n_] = {"parallel": "column (N split, no collective)" if kind == "col" else
+                        ("row (K split + all-reduce of the bf16 partial outputs)" if world > 1 else "row (K split)"),
+                        "N": n, "K": k}
+            for m_ in ("128", "8192"):
+                t_ms = next(it)
+                cfg3[n_][f"M{m_}_ms"] = t_ms
+                cfg3[n_][f"M{m_}_tflops"] = 2.0 * int(m_) * n * k / (t_ms * 1e-3) / 1e12
+        cfg3["note"] = (f"Llama-3-70B projections over {world} GPU(s): quantisation + GEMM" +
+                        (" + all-reduce" if world > 1 else "") + ", graph replay, max over ranks")
+        extras["config3"] = cfg3
+        if world == 1:
+            del w1q, w1s, w2q, w2s, col, row
+            torch.cuda.empty_cache()
+            extras["quant"] = quant_config2(dev, pk)
+            extras["config4"] = moe_config4_single(dev, pk)
+            extras["fp8_ceiling_tflops"] = fp8_ceiling(dev)
+            try:
+                extras["gpu_comparator"] = gpu_comparator(dev)
+            except Exception as e:  # noqa: BLE001
+                extras["gpu_comparator"] = {"unavailable": f"comparator failed: {str(e)[:300]}"}
+        else:
+            cfg4, ep_ok = moe_config4_ep(dev, world, rank)
+            extras["config4"] = cfg4
+            parity["expert_parallel_bitwise_ok"] = ep_ok
+            parity["ok"] = parity["ok"] and ep_ok
+    clocks = sampler.stop() if rank == 0 else None
 
     if rank == 0:
-        pk = _peaks()
         gemm_ms = per_kernel["gemm_gate_up"]
         gemm_flops = 2.0 * M_TOKENS * n1 * HIDDEN
         achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12
-        peak = 2.0 * pk["bf16_sustained"]
-        quant_bytes = 3.03125 * M_TOKENS * HIDDEN
-        quant_gbs = quant_bytes / (per_kernel["quant_x"] * 1e-3) / 1e9
-        # our kernels per step: two quant launches (one per row chunk when tensor-parallel), the GEMMs, and one
-        # small reduce launch after every GEMM whose last wave of tiles the library splits
+        peak_burst = 2.0 * pk["bf16_burst"]
+        peak_sust = 2.0 * pk["bf16_sustained"]
+        sus_clk = sampler.window("sus0", "sus1")
+        burst_clk = sampler.window("burst0", "burst1")
+        sustained_tflops = FLOPS_PER_STEP / (sustained_ms * 1e-3) / 1e12
         from sglang_b200.sgl_kernel.gemm import _splitk_plan
         split1 = _splitk_plan(M_TOKENS, n1, HIDDEN, dev)[0] > 1
-        rows2 = M_TOKENS if world == 1 else M_TOKENS // TP_CHUNKS
+        rows2 = M_TOKENS // chunks_used
         split2 = _splitk_plan(rows2, HIDDEN, k2, dev)[0] > 1
-        chunks2 = 1 if world == 1 else TP_CHUNKS
-        launches_per_step = (1 + 1 + int(split1)) + chunks2 * (1 + 1 + int(split2))
-        h2d = x.numel() * 2 + h.numel() * 2
-        d2h = y1_host[0].numel() * 2 + y2_host[0].numel() * 2
+        launches_per_step = (1 + 1 + int(split1)) + chunks_used * (1 + 1 + int(split2)) + (chunks_used if ar is not None else 0)
+        h2d = x_host.numel() * 2 + h.numel() * 2
+        d2h = M_TOKENS * n1 * 2 + mr * HIDDEN * 2
+        roof = {"bound": "tensor", "kernel": "gemm_block_fp8_kernel<BLOCK_N=256, 16 epilogue warps, 32-column chunks, bf16> "
+                                             f"(gate_up{'' if world == 1 else f' shard N={n1}'})",
+                "achieved": achieved, "peak": peak_burst, "unit": "TFLOP/s", "frac": achieved / peak_burst,
+                "peak_source": f"2 x bf16_tflops (burst) of {pk['src']}: the kernel is timed alone in a short graph replay and "
+                               "the fp8 pipe does twice the bf16 MACs per clock (the file holds no fp8 entry)",
+                "frac_of_nominal_4500": achieved / NOMINAL_FP8_TFLOPS,
+                "traffic": GEMM_TRAFFIC_BYTES_1GPU if world == 1 else None,
+                "algorithmic_flops_per_launch": gemm_flops,
+                "sustained": {"step_tflops": sustained_tflops, "ms_per_step": sustained_ms, "seconds": sustained_ms * reps / 1e3,
+                              "sm_mhz_median": sus_clk["sm_mhz"] if sus_clk else None,
+                              "power_w_max": sus_clk["power_w_max"] if sus_clk else None,
+                              "peak": peak_sust, "frac": sustained_tflops / peak_sust,
+                              "peak_source": f"2 x bf16_tflops_sustained of {pk['src']} (whole step, back to back for >= 2 s)"}}
+        if extras.get("fp8_ceiling_tflops"):
+            roof["fp8_ceiling_measured"] = extras["fp8_ceiling_tflops"]
+            roof["frac_of_fp8_ceiling"] = achieved / extras["fp8_ceiling_tflops"]
+            roof["fp8_ceiling_source"] = "torch._scaled_mm, per-tensor e4m3, 8192^3, this run (yardstick only)"
         line = {
             "metric": "block_fp8_linear_tflops", "value": FLOPS_PER_STEP / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "e4m3 x e4m3 -> f32 -> bf16",
             "data": "synthetic",
             "config": {"workload": WORKLOAD,
-                       "parallelism": (f"tp{world}: gate_up column-parallel, down row-parallel in {TP_CHUNKS} row chunks "
-                                       "with the bf16 NCCL all-reduce of each chunk overlapped"
-                                       + ("; step replayed from a CUDA graph" if graph is not None else "")) if world > 1 else "single",
+                       "parallelism": (f"tp{world}: gate_up column-parallel, down row-parallel in {chunks_used} row chunk(s), "
+                                       f"partial outputs summed by {'this library NVLink all-reduce kernel' + (' (multicast)' if ar.multicast else ' (peer pointers)') if ar is not None else 'NCCL all-reduce'}"
+                                       ) if world > 1 else "single",
+                       "timing": "step replayed from a CUDA graph at every N; per-kernel times from separate graph replays",
                        "l2": "inputs larger than L2 (weights 396 MB e4m3 + activations 210 MB bf16 per step)",
                        "kernels_ms": per_kernel,
-                       **({"row_chunk_candidates_ms": chunk_ms} if world > 1 and chunk_ms else {})},
+                       **({"row_chunk_candidates_ms": chunk_ms} if world > 1 else {})},
+            "parity": parity,
             "e2e": {"value": FLOPS_PER_STEP / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
                     "note": "every step copies its activations from pinned host memory and its bf16 results back; the "
-                            "copy-in / compute / copy-out legs of consecutive steps overlap on three streams "
-                            "(double buffers); weights stay resident (they are layer parameters)"},
+                            "copy-in / compute / copy-out legs of consecutive steps overlap on three streams (double "
+                            "buffers); weights stay resident (they are layer parameters); bytes are per rank: each rank "
+                            "moves 1/p of every replicated tensor"},
             "gpu_launches": args.steps * launches_per_step,
-            "roofline": {"bound": "tensor", "kernel": "gemm_block_fp8_kernel<BLOCK_N=256, 16 epilogue warps, 32-column chunks, bf16> (gate_up)",
-                         "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                         "peak_source": f"2 x bf16_tflops_sustained of {pk['src']} (the fp8 pipe does twice the "
-                                        "bf16 MACs per clock; the file holds no fp8 entry)",
-                         "frac_of_nominal_4500": achieved / NOMINAL_FP8_TFLOPS,
-                         "traffic": GEMM_TRAFFIC_BYTES, "algorithmic_flops_per_launch": gemm_flops},
-            "quant": {"bound": "hbm", "kernel": "quant_group_kernel<bf16,128> on [4096,7168]",
-                      "achieved": quant_gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": quant_gbs / pk["hbm_gbs"],
-                      "algorithmic_bytes_per_launch": quant_bytes},
-            "clocks": clocks,
+            "roofline": roof,
+            "clocks": {**(clocks or {}), "burst_region": burst_clk, "sustained_region": sus_clk},
+            "status_ok": status_ok,
         }
-        if world == 1:
+        for k_ in ("quant", "config3", "config4", "gpu_comparator"):
+            if k_ in extras:
+                line[k_] = extras[k_]
+        if world == 1 and not args.skip_extras:
             _, _, info = cpu_reference_run(steps=5, warmup=1, sample_rows=M_TOKENS)
             line["cpu_baseline"] = info
         print(json.dumps(line))
         sys.stdout.flush()
+    rc = 0 if (parity["ok"] and status_ok) else 3
     if world > 1:
-        # release the captured graph before the communicator it references, and never let a slow
-        # communicator teardown keep a finished benchmark alive
-        if graph is not None:
-            graph.reset()
-            graph = None
         torch.cuda.synchronize()
         dist.barrier()
-        guard = threading.Timer(20.0, lambda: os._exit(0))
+        guard = threading.Timer(20.0, lambda: os._exit(rc))
         guard.daemon = True
         guard.start()
         dist.destroy_process_group()
         guard.cancel()
+    if rc != 0:
+        print(f"[bench rank {rank}] self-check failed: {json.dumps(parity)}", file=sys.stderr, flush=True)
+        sys.exit(rc)
 
 
 def run_kernel_case(args):
     """One kernel alone on one GPU (used for the M sweeps and as the small case for ncu captures):
-    --kernel gemm_gate_up|gemm_down|quant --m M.  Prints one JSON line per case."""
+    --kernel gemm_gate_up|gemm_down|gemm|quant|moe --m M.  Prints one JSON line per case."""
     import torch
 
     from sglang_b200.layers.quantization.fp8_kernel import sglang_per_token_group_quant_fp8
@@ -544,29 +937,16 @@ def run_kernel_case(args):
     for m in ms_list:
         g = torch.Generator(device=dev).manual_seed(m)
         if args.kernel == "moe":
-            # DeepSeek-V3 MoE layer on one GPU: 256 experts, top-8, hidden 7168, intermediate 2048.
+            # DeepSeek-V3 MoE layer on one GPU: `--experts` experts, top-8, hidden 7168, intermediate 2048.
             # Codes and scales are drawn directly (11.3 GB of weights); parity is covered by the tests.
             from sglang_b200.layers.moe.cutlass_moe import fused_experts_block_fp8
             E, H, I, topk = args.experts, 7168, 2048, 8
-            def codes(*shape):
-                c = torch.randint(0, 0x78, shape, generator=g, device=dev, dtype=torch.uint8)
-                sign = torch.randint(0, 2, shape, generator=g, device=dev, dtype=torch.uint8) << 7
-                return (c | sign).view(torch.float8_e4m3fn)
-            w13 = torch.empty((E, 2 * I, H), dtype=torch.float8_e4m3fn, device=dev)
-            w2 = torch.empty((E, H, I), dtype=torch.float8_e4m3fn, device=dev)
-            for e in range(E):
-                w13[e] = codes(2 * I, H)
-                w2[e] = codes(H, I)
-            w13s = torch.rand((E, 2 * I // 128, H // 128), generator=g, device=dev) * 2e-4 + 1e-5
-            w2s = torch.rand((E, H // 128, I // 128), generator=g, device=dev) * 2e-4 + 1e-5
-            x = torch.randn((m, H), generator=g, device=dev).to(torch.bfloat16)
-            logits = torch.randn((m, E), generator=g, device=dev)
-            tw, ti = torch.topk(torch.softmax(logits.float(), dim=-1), topk, dim=-1)
-            ti = ti.to(torch.int32)
+            w13, w2, w13s, w2s = moe_weights(dev, list(range(E)), 5000)
+            x, tw, ti = moe_routing(dev, m, E=E)
 
             def fn():
                 return fused_experts_block_fp8(x, w13, w2, w13s, w2s, tw, ti)
-            work, unit, peak = 2.0 * m * topk * (2 * I * H + H * I) / 1e12, "TFLOP/s", 2.0 * pk["bf16_sustained"]
+            work, unit, peak = 2.0 * m * topk * (2 * I * H + H * I) / 1e12, "TFLOP/s", 2.0 * pk["bf16_burst"]
         elif args.kernel == "quant":
             nbuf = max(2, min(8, int(300e6 // (m * HIDDEN * 2)) + 1))   # rotate buffers: > L2 in total
             xs = []
@@ -600,7 +980,7 @@ def run_kernel_case(args):
                 it[0] += 1
                 w_t, ws_t = views[it[0] % ncopy]
                 return fp8_blockwise_scaled_mm(xq, w_t, xs_, ws_t, torch.bfloat16)
-            work, unit, peak = 2.0 * m * n * k / 1e12, "TFLOP/s", 2.0 * pk["bf16_sustained"]
+            work, unit, peak = 2.0 * m * n * k / 1e12, "TFLOP/s", 2.0 * pk["bf16_burst"]
         for _ in range(max(3, args.warmup)):
             fn()
         torch.cuda.synchronize()
@@ -648,8 +1028,11 @@ def main():
     ap.add_argument("--experts", type=int, default=256,
                     help="--kernel moe: experts held on this GPU (256 = whole layer, 32 = one rank of 8)")
     ap.add_argument("--tp-chunks", type=int, default=0, choices=[0, 1, 2, 4, 8],
-                    help="N > 1: row chunks of the row-parallel projection whose all-reduces overlap the next chunk")
-    ap.add_argument("--eager", action="store_true", help="N > 1: enqueue every step from Python instead of graph replay")
+                    help="N > 1: row chunks of the row-parallel projection whose all-reduces overlap the next chunk "
+                         "(0 = measure 1, 2 and 4 during warm-up and take the fastest)")
+    ap.add_argument("--allreduce", default="custom", choices=["custom", "nccl"],
+                    help="N > 1: this library's NVLink all-reduce kernels, or NCCL")
+    ap.add_argument("--skip-extras", action="store_true", help="only the headline workload (no config3/config4/quant keys)")
     ap.add_argument("--graph", action="store_true",
                     help="--kernel: replay the timed steps from a CUDA graph (excludes Python call overhead)")
     ap.add_argument("--gpus", type=int, default=1)

@@ -166,6 +166,22 @@ int b200_fp8_blockwise_scaled_mm_ue8m0(const void* a, int64_t lda, const void* b
                                        int64_t M, int64_t N, int64_t K, void* stream);
 
 /*
+ * The same product on the tensor core's own block-scaling path (tcgen05.mma kind::mxf8f6f4.block_scale): BOTH scale
+ * sets must be powers of two -- sa_packed as above, and sb_pow2 fp32 values 2^e (only their exponent field is
+ * used; a mantissa that is not zero is ignored, i.e. the scale is rounded down to a power of two).  All k-blocks
+ * accumulate inside tensor memory, nothing is promoted in fp32 registers, so this entry runs at the plain FP8 MMA
+ * rate.  Power-of-two scaling is exact: results equal b200_fp8_blockwise_scaled_mm_ue8m0's up to the order of the
+ * fp32 additions.  K % 128 == 0.
+ * Replaces: the reference's DeepGEMM linear with UE8M0 scales, its default on Blackwell
+ * (python/sglang/srt/layers/quantization/fp8_utils.py:215-258; weights re-quantised to power-of-two scales by
+ * requant_weight_ue8m0, fp8_utils.py:370-443; python/sglang/srt/layers/deep_gemm_wrapper/entrypoint.py:78-93).
+ */
+int b200_fp8_blockwise_scaled_mm_pow2(const void* a, int64_t lda, const void* b, int64_t ldb, const uint32_t* sa_packed,
+                                      int64_t sa_stride_m, int64_t sa_stride_pack, const float* sb_pow2,
+                                      int64_t sb_stride_n, int64_t sb_stride_g, void* out, int64_t ldo, int out_dtype,
+                                      int64_t M, int64_t N, int64_t K, void* stream);
+
+/*
  * Grouped (per-expert) block-scaled FP8 GEMM: for every expert e,
  *   out[off_e : off_e + m_e, :] = blockscaled( a[off_e : off_e + m_e, :], b[e] )   (same math as above)
  * with off_e = expert_offsets[e], m_e = problem_sizes[3*e] read ON THE DEVICE (no host sync).
@@ -275,6 +291,14 @@ int b200_apply_shuffle_mul_sum(const void* input, void* output, const int32_t* p
 int b200_moe_fused_gate(const float* gating_output, int64_t row_stride, const float* bias, float* topk_weights,
                         int32_t* topk_ids, int64_t num_tokens, int num_experts, int num_expert_group,
                         int topk_group, int topk, void* stream);
+/* The same gate with the reference's fused shared experts (moe_fused_gate.cu:60-71,225-252): of the topk output
+ * slots per token the last num_fused_shared_experts carry ids num_experts, num_experts + 1, ... and the weight
+ * 1 / routed_scaling_factor (the reference's (sum / routed_scaling_factor) / sum); the first
+ * topk - num_fused_shared_experts slots are the routed choices, renormalised over themselves. */
+int b200_moe_fused_gate_shared_experts(const float* gating_output, int64_t row_stride, const float* bias,
+                                       float* topk_weights, int32_t* topk_ids, int64_t num_tokens, int num_experts,
+                                       int num_expert_group, int topk_group, int topk, int num_fused_shared_experts,
+                                       double routed_scaling_factor, void* stream);
 
 /*
  * Router: weights = softmax(gating_output.float(), dim=-1), then the topk largest per token and their expert
@@ -315,6 +339,49 @@ int b200_allreduce(void* const* peer_buffers, void* const* peer_signal_pads, voi
                    int one_shot, int num_blocks, int64_t flag_base_words, void* stream);
 int b200_allreduce_flag_words(int world_size);
 int b200_allreduce_max_blocks(void);
+
+/*
+ * Expert-parallel token exchange over NVLink (2..8 GPUs of one NVSwitch domain, one process per GPU).
+ * Replaces: the DeepEP dispatch / combine the reference's expert-parallel MoE uses
+ * (python/sglang/srt/layers/moe/token_dispatcher/deepep.py:314-480, dispatch of quantised rows :328-336;
+ * python/sglang/srt/layers/moe/ep_moe/layer.py:427-489); experts are split contiguously over the ranks
+ * (python/sglang/srt/layers/moe/fused_moe_triton/layer.py:165-185).
+ *
+ * Every rank owns one symmetric buffer of b200_ep_buffer_bytes(...) bytes, mapped into every process
+ * (peer_buffers[r], r < world_size) and laid out by the five byte offsets that call returns: receive regions
+ * for codes [world][capacity][hidden] (e4m3), scales [world][capacity][hidden/128] (fp32) and
+ * (local expert id, source slot) pairs [world][capacity] (2 x int32), a count table [world] (int32), and the
+ * return buffer [max_slots][hidden] of the output type.  Zero the buffer once before the first call.
+ *
+ * b200_ep_dispatch: for every (token, choice) slot f = token*topk + j with expert e = topk_ids[f] >= 0, the
+ *   token's row (q [num_tokens, hidden] e4m3, s [num_tokens, hidden/128] fp32 row-major) is stored into
+ *   rank e / experts_per_rank's receive region for this source, at the slot's position among this source's
+ *   rows for that rank (stable in f), together with (e % experts_per_rank, f).  Rows beyond `capacity` for one
+ *   destination are dropped and *status becomes 31.  The call ends with a flag barrier between the ranks
+ *   (flag words [flag_base_words, + world_size) of the signal pads), so kernels enqueued after it on the same
+ *   stream see every peer's rows.  scratch_pos [num_tokens*topk] int32, scratch_counts [8] int32,
+ *   scratch_counter [1] uint32 (zero before the first call): device scratch of the caller.
+ * b200_ep_received_expert_ids: ids_out [world*capacity] int32 = the local expert id of each received row in
+ *   region order, -1 where no row arrived (what the grouped GEMM's routing tables take as "skip").
+ * b200_ep_combine: rows [*, hidden] (dtype bf16 / fp16) holds the expert output of received row r at row
+ *   row_of[r] (r itself when row_of is NULL); each is stored into its source rank's return buffer at the row's
+ *   source slot; ends with a flag barrier (a different flag_base_words than the dispatch's).
+ * The kernels of the ranks wait for one another (bounded, about a second): every rank must make the same
+ * calls in the same order; *status (device word, zero before the first call) receives 32 / 33 if a peer
+ * never arrived.  Nothing on the host reads device data.
+ */
+int64_t b200_ep_buffer_bytes(int world_size, int capacity, int hidden, int max_slots, int out_elem_bytes,
+                             int64_t* layout_offsets_5);
+int b200_ep_dispatch(const void* q, const float* s, const int32_t* topk_ids, int64_t num_tokens, int topk, int hidden,
+                     int experts_per_rank, void* const* peer_buffers, void* const* peer_signal_pads,
+                     const int64_t* layout_offsets_5, int capacity, int rank, int world_size, int64_t flag_base_words,
+                     int* status, int32_t* scratch_pos, int32_t* scratch_counts, unsigned int* scratch_counter,
+                     void* stream);
+int b200_ep_received_expert_ids(const void* local_buffer, const int64_t* layout_offsets_5, int capacity, int hidden,
+                                int world_size, int32_t* ids_out, void* stream);
+int b200_ep_combine(const void* rows, const int32_t* row_of, int dtype, int hidden, void* const* peer_buffers,
+                    void* const* peer_signal_pads, const int64_t* layout_offsets_5, int capacity, int rank,
+                    int world_size, int64_t flag_base_words, int* status, unsigned int* scratch_counter, void* stream);
 
 /*
  * Device-side waits in the GEMM kernels are bounded (about a second of SM clocks).  A wait that gives up

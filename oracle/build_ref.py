@@ -91,9 +91,12 @@ def load() -> bool:
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("SGLANG_REFERENCE_DIR", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("SGLANG_REFERENCE_DIR"),
+                    help="path of the reference checkout (or set SGLANG_REFERENCE_DIR)")
     ap.add_argument("--force", action="store_true")
     a = ap.parse_args()
+    if not a.reference:
+        ap.error("--reference or SGLANG_REFERENCE_DIR is required")
     out = build(a.reference, a.force)
     print("[build_ref] ->", out)
     sys.exit(0)

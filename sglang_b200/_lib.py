@@ -48,6 +48,9 @@ _SIGNATURES = {
     "b200_fp8_blockwise_scaled_mm_ue8m0": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64,
                                                    c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int, c_int64,
                                                    c_int64, c_int64, c_void_p]),
+    "b200_fp8_blockwise_scaled_mm_pow2": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64,
+                                                  c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int, c_int64,
+                                                  c_int64, c_int64, c_void_p]),
     "b200_gemm_device_status": (c_int, [ctypes.POINTER(c_int)]),
     "b200_gemm_poll_status": (c_int, [ctypes.POINTER(c_int)]),
     "b200_fp8_blockwise_scaled_grouped_mm": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64,
@@ -64,6 +67,8 @@ _SIGNATURES = {
     "b200_topk_softmax": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
     "b200_moe_fused_gate": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int,
                                     c_void_p]),
+    "b200_moe_fused_gate_shared_experts": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int,
+                                                   c_int, c_int, c_int, ctypes.c_double, c_void_p]),
     "b200_shuffle_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "b200_silu_and_mul": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
     "b200_apply_shuffle_mul_sum": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,
@@ -72,6 +77,12 @@ _SIGNATURES = {
                                c_int, c_int, c_int, c_int64, c_void_p]),
     "b200_allreduce_flag_words": (c_int, [c_int]),
     "b200_allreduce_max_blocks": (c_int, []),
+    "b200_ep_buffer_bytes": (c_int64, [c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "b200_ep_dispatch": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                 c_int, c_int, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "b200_ep_received_expert_ids": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "b200_ep_combine": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                c_int64, c_void_p, c_void_p, c_void_p]),
     "b200_debug_force_block_n": (c_int, [c_int]),
 }
 

@@ -22,61 +22,23 @@
 // spin is bounded; a rank whose peer never arrives records an error code in `status` (a device word of
 // the caller) and carries on without waiting, so a missing rank costs wrong data, not a hung GPU.
 // These kernels wait for kernels on OTHER GPUs: one process per GPU, never two ranks on one GPU.
-#include "common.cuh"
+#include "peer_sync.cuh"
 
 namespace b200 {
 namespace {
 
-constexpr int kMaxRanks = 8;
 constexpr int kArThreads = 512;
-constexpr long long kArWaitCycles = 2000000000LL;   // about a second
 
 struct ArParams {
   void* local;                   // this rank's buffer
   void* peers[kMaxRanks];        // every rank's buffer, as mapped into this process (peers[rank] == local)
-  uint32_t* signals[kMaxRanks];  // every rank's signal pad, as mapped into this process
+  PeerSync sync;                 // signal pads, rank, world, first flag word, status word
   void* mc;                      // multicast address of the buffer, or null
   void* out;                     // one-shot: local output
-  int* status;                   // device word: 0, or the code of the first wait that gave up
   int64_t offset_bytes;          // of the reduced range inside the buffer (multiple of 16 * world)
   int64_t bytes;                 // length of the reduced range (multiple of 16 * world for two-shot, 16 for one-shot)
   int rank, world;
-  uint32_t flag_base;            // first flag word used by this call site inside the signal pads
 };
-
-__device__ __forceinline__ uint32_t cas_release_sys(uint32_t* addr, uint32_t cmp, uint32_t val) {
-  uint32_t old;
-  asm volatile("atom.global.release.sys.cas.b32 %0, [%1], %2, %3;" : "=r"(old) : "l"(addr), "r"(cmp), "r"(val) : "memory");
-  return old;
-}
-__device__ __forceinline__ uint32_t cas_acquire_sys(uint32_t* addr, uint32_t cmp, uint32_t val) {
-  uint32_t old;
-  asm volatile("atom.global.acquire.sys.cas.b32 %0, [%1], %2, %3;" : "=r"(old) : "l"(addr), "r"(cmp), "r"(val) : "memory");
-  return old;
-}
-
-// All ranks' blocks with the same index meet.  Thread t < world of each block signals rank t's pad and
-// waits for rank t's signal in its own pad.  Flags of block b: words [flag_base + b*world, +world).
-__device__ __forceinline__ void rank_barrier(const ArParams& p, int code) {
-  __syncthreads();
-  if (threadIdx.x < p.world) {
-    const int peer = threadIdx.x;
-    uint32_t* theirs = p.signals[peer] + p.flag_base + blockIdx.x * p.world + p.rank;
-    uint32_t* mine = p.signals[p.rank] + p.flag_base + blockIdx.x * p.world + peer;
-    const long long t0 = clock64();
-    bool ok = true;
-    while (cas_release_sys(theirs, 0u, 1u) != 0u) {
-      if (clock64() - t0 > kArWaitCycles) { ok = false; break; }
-    }
-    if (ok) {
-      while (cas_acquire_sys(mine, 1u, 0u) != 1u) {
-        if (clock64() - t0 > kArWaitCycles) { ok = false; break; }
-      }
-    }
-    if (!ok) atomicCAS(p.status, 0, code);
-  }
-  __syncthreads();
-}
 
 struct alignas(16) Vec16 { uint32_t w[4]; };
 
@@ -137,7 +99,7 @@ __device__ __forceinline__ Vec16 peer_sum(const ArParams& p, int64_t byte_off) {
 
 template <typename T, bool MULTIMEM>
 __global__ void __launch_bounds__(kArThreads) allreduce_twoshot_kernel(const ArParams p) {
-  rank_barrier(p, 21);   // every rank's partial values are in its buffer
+  rank_barrier(p.sync, 21);   // every rank's partial values are in its buffer
   const int64_t slice = p.bytes / p.world;
   const int64_t base = p.offset_bytes + slice * p.rank;
   const int64_t nvec = slice / 16;
@@ -168,12 +130,12 @@ __global__ void __launch_bounds__(kArThreads) allreduce_twoshot_kernel(const ArP
     }
   }
   __threadfence_system();
-  rank_barrier(p, 22);   // every slice has reached every rank
+  rank_barrier(p.sync, 22);   // every slice has reached every rank
 }
 
 template <typename T, bool MULTIMEM>
 __global__ void __launch_bounds__(kArThreads) allreduce_oneshot_kernel(const ArParams p) {
-  rank_barrier(p, 23);
+  rank_barrier(p.sync, 23);
   const int64_t nvec = p.bytes / 16;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
@@ -182,7 +144,7 @@ __global__ void __launch_bounds__(kArThreads) allreduce_oneshot_kernel(const ArP
     else v = peer_sum<T>(p, p.offset_bytes + i * 16);
     *reinterpret_cast<Vec16*>(static_cast<char*>(p.out) + i * 16) = v;
   }
-  rank_barrier(p, 24);   // nobody overwrites its buffer while a peer still reads it
+  rank_barrier(p.sync, 24);   // nobody overwrites its buffer while a peer still reads it
 }
 
 }  // namespace
@@ -211,19 +173,18 @@ extern "C" int b200_allreduce(void* const* peer_buffers, void* const* peer_signa
   ArParams p;
   for (int r = 0; r < kMaxRanks; ++r) {
     p.peers[r] = r < world_size ? peer_buffers[r] : nullptr;
-    p.signals[r] = r < world_size ? static_cast<uint32_t*>(peer_signal_pads[r]) : nullptr;
-    if (r < world_size && (!p.peers[r] || !p.signals[r])) return B200_ERR_NULL_PTR;
+    if (r < world_size && !p.peers[r]) return B200_ERR_NULL_PTR;
     if (r < world_size && !aligned16(p.peers[r])) return B200_ERR_MISALIGNED;
   }
+  rc = make_peer_sync(&p.sync, peer_signal_pads, rank, world_size, flag_base_words, status);
+  if (rc != B200_OK) return rc;
   p.local = p.peers[rank];
   p.mc = multicast_buffer;
   p.out = out;
-  p.status = status;
   p.offset_bytes = offset_bytes;
   p.bytes = bytes;
   p.rank = rank;
   p.world = world_size;
-  p.flag_base = static_cast<uint32_t>(flag_base_words);
   // no more blocks than 16-byte vectors of work per rank
   const int64_t vecs = (one_shot ? bytes : bytes / world_size) / 16;
   const int64_t want = (vecs + kArThreads - 1) / kArThreads;

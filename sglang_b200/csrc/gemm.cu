@@ -34,7 +34,7 @@ constexpr int kGroupM = 32;     // m-blocks per rasterisation group: the group's
 constexpr int kScaleGroup = 4;   // k-blocks per scale-ring slot
 constexpr int kScaleSlots = 4;   // slots in the ring (the stager runs up to 16 k-blocks ahead)
 
-template <int BLOCK_N, int EPI_WARPS>
+template <int BLOCK_N, int EPI_WARPS, int ISSUERS = 1>
 struct Cfg {
   static constexpr int kStages = BLOCK_N == 256 ? 4 : 6;
   static constexpr int kABytes = BLOCK_M * BLOCK_K;
@@ -47,6 +47,10 @@ struct Cfg {
   static constexpr int kTmaWarp = EPI_WARPS;
   static constexpr int kMmaWarp = EPI_WARPS + 1;
   static constexpr int kStagerWarp = EPI_WARPS + 2;             // stages the scale products in shared memory
+  static constexpr int kMmaWarp2 = EPI_WARPS + 3;               // second MMA issuer (kIssuers == 2)
+  // Two MMA-issuing warps take alternate k-blocks: one warp's barrier waits and loop bookkeeping then overlap
+  // the other's issue instead of leaving the tensor pipe idle between k-blocks.
+  static constexpr int kIssuers = ISSUERS;
   static constexpr int kThreads = 32 * (4 + EPI_WARPS);
   // With 16 epilogue warps the launch gives every thread 96 registers (20 warps); the helper
   // warpgroup hands 32 per thread back and the epilogue warps take 8 more each, enough to hold 64
@@ -133,11 +137,32 @@ __device__ __forceinline__ Work decode_work(int vt, const GemmParams& p, int nkb
   return Work{tile, split, kb0, min(nkb, kb0 + p.kb_per_split), true};
 }
 
-template <int BLOCK_N, int EPI_WARPS, int CHUNK, bool GROUPED, typename OutT>
-__global__ void __launch_bounds__(Cfg<BLOCK_N, EPI_WARPS>::kThreads, 1)
+// ld of 16 columns has landed: the wait carries the destination registers as operands so that no use of
+// them can be scheduled before it (the load itself only names them as outputs at issue time).
+__device__ __forceinline__ void tmem_ld_wait16(float (&v)[16]) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+               :
+               : "memory");
+}
+
+// acc[0..15] += v[0..15] * s, two fp32 FMAs per instruction (fma.rn.f32x2)
+__device__ __forceinline__ void fma16(float* acc, const float (&v)[16], float2 s2) {
+#pragma unroll
+  for (int c = 0; c < 16; c += 2) {
+    const float2 r = __ffma2_rn(make_float2(v[c], v[c + 1]), s2, make_float2(acc[c], acc[c + 1]));
+    acc[c] = r.x;
+    acc[c + 1] = r.y;
+  }
+}
+
+template <int BLOCK_N, int EPI_WARPS, int CHUNK, bool GROUPED, typename OutT, int ISSUERS = 1>
+__global__ void __launch_bounds__(Cfg<BLOCK_N, EPI_WARPS, ISSUERS>::kThreads, 1)
 gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                       const GemmParams p) {
-  using C = Cfg<BLOCK_N, EPI_WARPS>;
+  using C = Cfg<BLOCK_N, EPI_WARPS, ISSUERS>;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: the 128-byte swizzle pattern is a function of address bits [4,10).
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -231,20 +256,30 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       }
     }
     __syncwarp();
-  } else if (warp == C::kMmaWarp) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp == C::kMmaWarp || (C::kIssuers == 2 && warp == C::kMmaWarp2)) {
+    // ------------------------------------------------------------------ MMA issuer(s)
     // The whole warp walks the loop so that addresses and descriptors stay warp-uniform; one
-    // elected lane issues.  Issuing one k-block (4 MMAs + commit) occupies the thread ~320 cycles.
+    // elected lane issues.  With two issuers each warp takes every other k-block of the CTA's sequence
+    // (own stage, own accumulator buffer: k-blocks are independent) and only tracks the ring positions
+    // of the ones it skips.
     constexpr uint32_t idesc = umma_idesc_e4m3(BLOCK_M, BLOCK_N);
     const uint64_t a_desc0 = umma_desc_k128(smem_u32(smem_a));
     const uint64_t b_desc0 = umma_desc_k128(smem_u32(smem_b));
-    int stage = 0, acc = 0;
+    const int issuer = (warp == C::kMmaWarp) ? 0 : 1;
+    int stage = 0, acc = 0, turn = 0;
     uint32_t phase = 0, acc_phase = 0;
     bool ok = true;
     for (int vt = blockIdx.x; ok && vt < num_vtiles; vt += gridDim.x) {
       const Work w = decode_work(vt, p, nkb, GROUPED);
       const int kb_begin = w.kb_begin, kb_end = w.kb_end;
       for (int kb = kb_begin; kb < kb_end; ++kb) {
+        if (C::kIssuers == 2 && turn != issuer) {
+          turn ^= 1;
+          if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+          if (++acc == C::kNumAcc) { acc = 0; acc_phase ^= 1u; }
+          continue;
+        }
+        turn ^= 1;
         ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1u, p.status, 2);
         if (ok) ok = mbar_wait(&full_bar[stage], phase, p.status, 3);
         ok = __all_sync(0xffffffffu, ok);
@@ -350,6 +385,8 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     // ====================================================================== promotion + epilogue warps
     if constexpr (C::kRebalanceRegs) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(C::kEpiRegs));
     constexpr int CPW = C::kColsPerWarp;
+    constexpr bool kPipe = (CHUNK == 16);
+    static_assert(!kPipe || CPW == 64, "the pipelined read-out is written for 64 columns per warp");
     static_assert(CPW % CHUNK == 0 && (CHUNK == 16 || CHUNK == 32 || CHUNK == 64), "chunking");
     static_assert(CPW <= 128, "a warp's columns lie in one weight-scale block");
     const int quad = warp & 3;         // tensor-memory lane quadrant this warp may read
@@ -371,6 +408,11 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       float acc[CPW];
 #pragma unroll
       for (int c = 0; c < CPW; ++c) acc[c] = 0.f;
+      // software-pipelined read-out (kPipe): the last chunk of a k-block is accumulated under the first
+      // tensor-memory load of the next one
+      [[maybe_unused]] float va[16], vb[16];
+      [[maybe_unused]] bool pending = false;
+      [[maybe_unused]] float2 s2_pending = make_float2(0.f, 0.f);
       for (int kb0 = kb_begin; ok && kb0 < kb_end; kb0 += kScaleGroup) {
         // the four scale products of this group, then the slot goes straight back to the stager
         ok = mbar_wait(&scale_full[slot], sphase, p.status, 6);
@@ -386,11 +428,42 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         for (int j = 0; j < kScaleGroup; ++j) {
           const int kb = kb0 + j;
           if (kb < kb_end) {
+            const uint32_t taddr = tmem_base + lane_addr + static_cast<uint32_t>(acc_i * BLOCK_N + part * CPW);
+            const float2 s2 = make_float2(sc[j], sc[j]);
+            if constexpr (kPipe) {
+              // Four 16-column chunks per k-block through two register buffers: while the FMAs of one chunk
+              // run, the tensor-memory load of the next is in flight, so neither the load latency nor the
+              // FMA pipe (shared by the scheduler's four read-out warps) is waited for on its own.  The
+              // buffer goes back to the MMA warps as soon as the last load has landed; that chunk's FMAs
+              // are deferred until the next k-block's first load has been issued (or done at once if the
+              // next k-block has not completed yet).
+              if (!mbar_try_wait(&done_bar[stage], phase)) {
+                if (pending) { fma16(acc + 48, vb, s2_pending); pending = false; }
+                ok = mbar_wait(&done_bar[stage], phase, p.status, 4);
+                if (!ok) break;
+              }
+              tc_fence_after();
+              tmem_ld16(taddr, va);
+              if (pending) { fma16(acc + 48, vb, s2_pending); pending = false; }
+              tmem_ld_wait16(va);
+              tmem_ld16(taddr + 16, vb);
+              fma16(acc, va, s2);
+              tmem_ld_wait16(vb);
+              tmem_ld16(taddr + 32, va);
+              fma16(acc + 16, vb, s2);
+              tmem_ld_wait16(va);
+              tmem_ld16(taddr + 48, vb);
+              fma16(acc + 32, va, s2);
+              tmem_ld_wait16(vb);
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&acc_empty[acc_i]);
+              pending = true;
+              s2_pending = s2;
+            } else {
             ok = mbar_wait(&done_bar[stage], phase, p.status, 4);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t taddr = tmem_base + lane_addr + static_cast<uint32_t>(acc_i * BLOCK_N + part * CPW);
-            const float2 s2 = make_float2(sc[j], sc[j]);
 #pragma unroll
             for (int ch = 0; ch < CPW / CHUNK; ++ch) {
               float v[CHUNK];
@@ -416,10 +489,14 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                 acc[ch * CHUNK + c + 1] = r.y;
               }
             }
+            }
             if (++acc_i == C::kNumAcc) acc_i = 0;
             if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
           }
         }
+      }
+      if constexpr (kPipe) {
+        if (pending) { fma16(acc + 48, vb, s2_pending); pending = false; }
       }
       if (ok && row_in_tile < t.valid_rows && n0 < p.N) {
         if (w.partial && p.tail_first > 0) {
@@ -529,10 +606,10 @@ int launch_tail_reduce(const GemmParams& p, int block_n, cudaStream_t stream) {
 }
 
 // ------------------------------------------------------------------------------------ host
-template <int BLOCK_N, int EPI_WARPS, int CHUNK, bool GROUPED, typename OutT>
+template <int BLOCK_N, int EPI_WARPS, int CHUNK, bool GROUPED, typename OutT, int ISSUERS>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t stream) {
-  using C = Cfg<BLOCK_N, EPI_WARPS>;
-  auto kern = gemm_block_fp8_kernel<BLOCK_N, EPI_WARPS, CHUNK, GROUPED, OutT>;
+  using C = Cfg<BLOCK_N, EPI_WARPS, ISSUERS>;
+  auto kern = gemm_block_fp8_kernel<BLOCK_N, EPI_WARPS, CHUNK, GROUPED, OutT, ISSUERS>;
   static bool attr_set[64] = {false};
   int dev = 0;
   B200_CUDA_TRY(cudaGetDevice(&dev));
@@ -553,12 +630,12 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cu
   return B200_OK;
 }
 
-template <int BLOCK_N, int EPI_WARPS, int CHUNK, bool GROUPED = false>
+template <int BLOCK_N, int EPI_WARPS, int CHUNK, bool GROUPED = false, int ISSUERS = 1>
 int launch_dtype(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t stream) {
   switch (p.out_dtype) {
-    case B200_DT_BF16: return launch<BLOCK_N, EPI_WARPS, CHUNK, GROUPED, __nv_bfloat16>(ma, mb, p, stream);
-    case B200_DT_F16: return launch<BLOCK_N, EPI_WARPS, CHUNK, GROUPED, __half>(ma, mb, p, stream);
-    case B200_DT_F32: return launch<BLOCK_N, EPI_WARPS, CHUNK, GROUPED, float>(ma, mb, p, stream);
+    case B200_DT_BF16: return launch<BLOCK_N, EPI_WARPS, CHUNK, GROUPED, __nv_bfloat16, ISSUERS>(ma, mb, p, stream);
+    case B200_DT_F16: return launch<BLOCK_N, EPI_WARPS, CHUNK, GROUPED, __half, ISSUERS>(ma, mb, p, stream);
+    case B200_DT_F32: return launch<BLOCK_N, EPI_WARPS, CHUNK, GROUPED, float, ISSUERS>(ma, mb, p, stream);
     default: return B200_ERR_BAD_DTYPE;
   }
 }
@@ -720,13 +797,18 @@ int dense_mm(const void* a, int64_t lda, const void* b, int64_t ldb, const float
   int block_n = 256;
   if (p.split_k == 1 || p.tail_first > 0) block_n = dense_block_n(M, N, sm_count());
   if (g_force_block_n == 128 || g_force_block_n == 256) block_n = g_force_block_n;
+  if (g_force_block_n == 2562) block_n = 256;   // A/B runs: 256-wide tile, two MMA issuers
+  if (g_force_block_n == 1282) block_n = 128;   // A/B runs: 128-wide tile, two MMA issuers
 
   CUtensorMap ma, mb;
   rc = make_map_u8_2d(&ma, a, M, K, lda, BLOCK_M);
   if (rc != B200_OK) return rc;
   rc = make_map_u8_2d(&mb, b, N, K, ldb, block_n);
   if (rc != B200_OK) return rc;
-  rc = block_n == 256 ? launch_dtype<256, 16, 32>(ma, mb, p, st) : launch_dtype<128, 8, 64>(ma, mb, p, st);
+  if (g_force_block_n == 1282) rc = launch_dtype<128, 8, 64, false, 2>(ma, mb, p, st);
+  else if (block_n != 256) rc = launch_dtype<128, 8, 64>(ma, mb, p, st);
+  else if (g_force_block_n == 2562) rc = launch_dtype<256, 16, 32, false, 2>(ma, mb, p, st);
+  else rc = launch_dtype<256, 16, 32, false, 1>(ma, mb, p, st);
   if (rc != B200_OK || p.split_k == 1) return rc;
   if (p.tail_first > 0) {
     switch (out_dtype) {

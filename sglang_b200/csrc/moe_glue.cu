@@ -540,7 +540,12 @@ template <int PER_LANE>
 __global__ void __launch_bounds__(128) fused_gate_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
                                                          float* __restrict__ weights, int32_t* __restrict__ ids,
                                                          int64_t num_tokens, int num_experts, int num_groups,
-                                                         int topk_group, int topk, int64_t logits_stride) {
+                                                         int topk_group, int topk_all, int64_t logits_stride,
+                                                         int num_shared, double routed_scaling_factor) {
+  // topk_all output slots per token: the first topk routed choices, then num_shared fused shared experts
+  // (ids num_experts, num_experts + 1, ...) whose weight is (sum of the routed scores / routed_scaling_factor)
+  // before the common division by that sum (sgl-kernel/csrc/moe/moe_fused_gate.cu:225-252)
+  const int topk = topk_all - num_shared;
   extern __shared__ float smem_choice[];   // [warps][num_experts]
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
   const int64_t token = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + wib;
@@ -618,22 +623,31 @@ __global__ void __launch_bounds__(128) fused_gate_kernel(const float* __restrict
     if (lane == j) { my_w = best_s; my_id = best_e; }
   }
   if (lane < topk) {
-    weights[token * topk + lane] = my_w / picked_sum;
-    ids[token * topk + lane] = my_id;
+    weights[token * topk_all + lane] = my_w / picked_sum;
+    ids[token * topk_all + lane] = my_id;
+  } else if (lane < topk_all) {
+    const float shared = static_cast<float>(static_cast<double>(picked_sum) / routed_scaling_factor);
+    weights[token * topk_all + lane] = shared / picked_sum;
+    ids[token * topk_all + lane] = num_experts + (lane - topk);
   }
 }
 
 }  // namespace
 }  // namespace b200
 
-extern "C" int b200_moe_fused_gate(const float* gating_output, int64_t row_stride, const float* bias, float* topk_weights,
-                                   int32_t* topk_ids, int64_t num_tokens, int num_experts, int num_expert_group,
-                                   int topk_group, int topk, void* stream) {
+extern "C" int b200_moe_fused_gate_shared_experts(const float* gating_output, int64_t row_stride, const float* bias,
+                                                  float* topk_weights, int32_t* topk_ids, int64_t num_tokens,
+                                                  int num_experts, int num_expert_group, int topk_group, int topk,
+                                                  int num_fused_shared_experts, double routed_scaling_factor,
+                                                  void* stream) {
   using namespace b200;
   if (num_tokens < 0 || num_experts <= 0 || num_expert_group <= 0 || topk_group <= 0 || topk <= 0) return B200_ERR_BAD_SHAPE;
   if (num_experts % num_expert_group != 0 || num_expert_group > 32 || topk_group > num_expert_group) return B200_ERR_BAD_SHAPE;
+  if (num_fused_shared_experts < 0 || num_fused_shared_experts >= topk) return B200_ERR_BAD_SHAPE;
+  if (num_fused_shared_experts > 0 && !(routed_scaling_factor != 0.0)) return B200_ERR_BAD_SHAPE;
   const int group_size = num_experts / num_expert_group;
-  if (group_size < 2 || topk > 32 || topk > topk_group * group_size) return B200_ERR_BAD_SHAPE;
+  const int routed = topk - num_fused_shared_experts;
+  if (group_size < 2 || topk > 32 || routed > topk_group * group_size) return B200_ERR_BAD_SHAPE;
   if (num_experts > 1024) return B200_ERR_TOO_LARGE;
   if (num_tokens == 0) return B200_OK;
   if (!gating_output || !bias || !topk_weights || !topk_ids) return B200_ERR_NULL_PTR;
@@ -644,10 +658,19 @@ extern "C" int b200_moe_fused_gate(const float* gating_output, int64_t row_strid
   const size_t smem = 4 * static_cast<size_t>(num_experts) * sizeof(float);
   if (num_experts <= 256)
     fused_gate_kernel<8><<<blocks, 128, smem, st>>>(gating_output, bias, topk_weights, topk_ids, num_tokens, num_experts,
-                                                   num_expert_group, topk_group, topk, row_stride);
+                                                   num_expert_group, topk_group, topk, row_stride,
+                                                   num_fused_shared_experts, routed_scaling_factor);
   else
     fused_gate_kernel<32><<<blocks, 128, smem, st>>>(gating_output, bias, topk_weights, topk_ids, num_tokens, num_experts,
-                                                    num_expert_group, topk_group, topk, row_stride);
+                                                    num_expert_group, topk_group, topk, row_stride,
+                                                    num_fused_shared_experts, routed_scaling_factor);
   B200_CUDA_TRY(cudaGetLastError());
   return B200_OK;
+}
+
+extern "C" int b200_moe_fused_gate(const float* gating_output, int64_t row_stride, const float* bias, float* topk_weights,
+                                   int32_t* topk_ids, int64_t num_tokens, int num_experts, int num_expert_group,
+                                   int topk_group, int topk, void* stream) {
+  return b200_moe_fused_gate_shared_experts(gating_output, row_stride, bias, topk_weights, topk_ids, num_tokens,
+                                            num_experts, num_expert_group, topk_group, topk, 0, 1.0, stream);
 }

@@ -105,10 +105,13 @@ def fused_experts_block_fp8(a, w13, w2, w13_scale, w2_scale, topk_weights, topk_
                                      w2_scale.transpose(1, 2), topk_weights, topk_ids)
 
 
-def grouped_experts_prequantized(a_q, a_scale, expert_ids, w13, w2, w13_scale, w2_scale, out_dtype=torch.bfloat16):
+def grouped_experts_prequantized(a_q, a_scale, expert_ids, w13, w2, w13_scale, w2_scale, out_dtype=torch.bfloat16,
+                                 return_sorted: bool = False):
     """Expert MLPs over rows that are ALREADY quantised (what an expert-parallel rank receives):
     a_q [R, k] e4m3, a_scale [R, k/128] fp32, expert_ids [R] int32 (local ids; < 0 = skip).
-    Returns [R, k] in out_dtype, rows in input order, no routing weights applied."""
+    Returns [R, k] in out_dtype, rows in input order, no routing weights applied; with `return_sorted` the
+    rows stay grouped by expert and the second result maps input row -> its row there (skipped rows map
+    nowhere meaningful), which saves one pass when the caller scatters the rows anyway."""
     R, k = a_q.shape
     E, n = w13.shape[0], w2.shape[2]
     device = a_q.device
@@ -127,6 +130,8 @@ def grouped_experts_prequantized(a_q, a_scale, expert_ids, w13, w2, w13_scale, w
     c2 = torch.empty((R, k), device=device, dtype=out_dtype)
     fp8_blockwise_scaled_grouped_mm(c2, None, None, None, None, None, inter_q, w2.transpose(1, 2), inter_s,
                                     w2_scale, None, None, None, None, None, ps2, expert_offsets[:-1], None)
+    if return_sorted:
+        return c2, c_map
     out = torch.empty((R, k), device=device, dtype=out_dtype)
     apply_shuffle_mul_sum(c2, out, c_map, None)     # topk = 1: pure un-permute back to input order
     return out

@@ -118,12 +118,15 @@ def w8a8_block_fp8_matmul(A: torch.Tensor, B: torch.Tensor, As: torch.Tensor, Bs
 
 
 def w8a8_block_fp8_matmul_deepgemm(A: torch.Tensor, B: torch.Tensor, As: torch.Tensor, Bs: torch.Tensor,
-                                   block_size: List[int], output_dtype: torch.dtype) -> torch.Tensor:
+                                   block_size: List[int], output_dtype: torch.dtype,
+                                   weight_scale_ue8m0: bool = False) -> torch.Tensor:
     """C = A @ B.T with block scales where `As` may be the packed UE8M0 tensor that
     sglang_per_token_group_quant_fp8(..., scale_ue8m0=True) returns (int32 [M, ceil(K/512)], rows contiguous)
     or fp32 scales [M, K/128]; `Bs` fp32 [N/128, K/128].  Mirrors the call surface of the reference's
     w8a8_block_fp8_matmul_deepgemm (python/sglang/srt/layers/quantization/fp8_kernel.py:849-867); bf16 only,
-    like DeepGEMM."""
+    like DeepGEMM.  weight_scale_ue8m0=True promises that `Bs` holds powers of two as well (what the reference's
+    requant_weight_ue8m0 leaves, fp8_utils.py:370-443): the product then runs on the tensor core's block-scaling
+    path with every k-block accumulated in tensor memory."""
     assert list(block_size) == [128, 128] and output_dtype == torch.bfloat16
     if As.dtype != torch.int32:
         return w8a8_block_fp8_matmul(A, B, As, Bs, block_size, output_dtype)
@@ -138,7 +141,9 @@ def w8a8_block_fp8_matmul_deepgemm(A: torch.Tensor, B: torch.Tensor, As: torch.T
     if M == 0:
         return C
     with torch.cuda.device(A.device):
-        rc = _lib.lib().b200_fp8_blockwise_scaled_mm_ue8m0(
+        entry = _lib.lib().b200_fp8_blockwise_scaled_mm_pow2 if weight_scale_ue8m0 else \
+            _lib.lib().b200_fp8_blockwise_scaled_mm_ue8m0
+        rc = entry(
             A.data_ptr(), K, B.data_ptr(), K, As.data_ptr(), As.stride(0), As.stride(1),
             Bs.data_ptr(), Bs.stride(0), Bs.stride(1), C.data_ptr(), N, _lib.DT_BF16, M, N, K,
             torch.cuda.current_stream(A.device).cuda_stream)

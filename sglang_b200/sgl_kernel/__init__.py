@@ -1,7 +1,7 @@
 """Drop-in for the block-FP8 subset of the reference's `sgl_kernel` package.
 
 Importing this module registers the operators under torch.ops.sgl_kernel with the reference's
-schemas verbatim (sgl-kernel/csrc/common_extension.cc:111-119,165-170,192-207), implemented for the
+schemas verbatim (sgl-kernel/csrc/common_extension.cc:111-119,165-179,192-207), implemented for the
 CUDA dispatch key by the B200 C-ABI library, and exposes the same-named Python wrappers
 (sgl-kernel/python/sgl_kernel/{gemm,moe}.py).
 """
@@ -28,6 +28,9 @@ _SCHEMAS = {
     "apply_shuffle_mul_sum": "(Tensor input, Tensor output, Tensor permutation, Tensor? factors) -> ()",
     "silu_and_mul": "(Tensor out, Tensor input) -> ()",
     "topk_softmax": "(Tensor! topk_weights, Tensor! topk_indices, Tensor gating_output, bool renormalize) -> ()",
+    "moe_fused_gate":
+        "(Tensor input, Tensor bias, int num_expert_group, int topk_group, int topk, int num_fused_shared_experts, "
+        "float routed_scaling_factor) -> (Tensor[])",
     "moe_align_block_size":
         "(Tensor topk_ids, int num_experts, int block_size, Tensor! sorted_token_ids, Tensor! experts_ids, "
         "Tensor! num_tokens_post_pad, Tensor! cumsum_buffer, bool pad_sorted_token_ids) -> ()",
@@ -44,6 +47,16 @@ def _silu_and_mul_op(out, input):
     silu_and_mul(input, out)
 
 
+def _moe_fused_gate_op(input, bias, num_expert_group, topk_group, topk, num_fused_shared_experts, routed_scaling_factor):
+    return list(moe_fused_gate(input, bias, num_expert_group, topk_group, topk, num_fused_shared_experts,
+                               routed_scaling_factor))
+
+
+def _moe_fused_gate_meta(input, bias, num_expert_group, topk_group, topk, num_fused_shared_experts, routed_scaling_factor):
+    return [input.new_empty((input.shape[0], topk), dtype=torch.float32),
+            input.new_empty((input.shape[0], topk), dtype=torch.int32)]
+
+
 _IMPLS = {
     "fp8_blockwise_scaled_mm": fp8_blockwise_scaled_mm,
     "sgl_per_token_group_quant_fp8": sgl_per_token_group_quant_fp8,
@@ -54,6 +67,7 @@ _IMPLS = {
     "silu_and_mul": _silu_and_mul_op,
     "topk_softmax": topk_softmax,
     "moe_align_block_size": moe_align_block_size,
+    "moe_fused_gate": _moe_fused_gate_op,
 }
 
 
@@ -70,6 +84,7 @@ def _nothing_meta(*args):
 # other operators write into tensors the caller allocated.
 _META = {name: _nothing_meta for name in _SCHEMAS}
 _META["fp8_blockwise_scaled_mm"] = _mm_meta
+_META["moe_fused_gate"] = _moe_fused_gate_meta
 
 _library = None
 

@@ -81,10 +81,12 @@ def moe_fused_gate(input_tensor: torch.Tensor, bias: torch.Tensor, num_expert_gr
                    num_fused_shared_experts: int = 0, routed_scaling_factor: float = 0):
     """DeepSeek-V3 gate (sigmoid scores, choice bias, group-limited top-k, weights renormalised): returns
     (topk_weights fp32 [m, k], topk_ids int32 [m, k]).  Mirrors sgl_kernel.moe_fused_gate
-    (sgl-kernel/python/sgl_kernel/moe.py:39-66); the fused shared expert of the reference
-    (num_fused_shared_experts > 0, which is where routed_scaling_factor enters) is not built."""
-    if num_fused_shared_experts:
-        raise NotImplementedError("fused shared experts are not built")
+    (sgl-kernel/python/sgl_kernel/moe.py:39-66).  With num_fused_shared_experts > 0 the last that many of the
+    topk slots are the fused shared experts: ids num_experts, num_experts + 1, ..., weight
+    1 / routed_scaling_factor; the routed slots before them are renormalised over themselves
+    (sgl-kernel/csrc/moe/moe_fused_gate.cu:225-252)."""
+    _check(0 <= num_fused_shared_experts < topk, "num_fused_shared_experts must be smaller than topk")
+    _check(num_fused_shared_experts == 0 or routed_scaling_factor != 0, "routed_scaling_factor must be non-zero")
     _check(input_tensor.is_cuda and bias.is_cuda, "tensors must be CUDA tensors")
     _check(input_tensor.dim() == 2 and bias.dim() == 1 and bias.numel() == input_tensor.size(1), "shape mismatch")
     _check(input_tensor.dtype == torch.float32 and bias.dtype == torch.float32, "input and bias must be float32")
@@ -92,14 +94,15 @@ def moe_fused_gate(input_tensor: torch.Tensor, bias: torch.Tensor, num_expert_gr
     m, E = input_tensor.shape
     _check(E % num_expert_group == 0 and num_expert_group <= 32 and E // num_expert_group >= 2 and E <= 1024,
            "unsupported expert grouping")
-    _check(0 < topk_group <= num_expert_group and 0 < topk <= min(32, topk_group * (E // num_expert_group)),
-           "unsupported topk / topk_group")
+    _check(0 < topk_group <= num_expert_group and topk <= 32 and
+           0 < topk - num_fused_shared_experts <= topk_group * (E // num_expert_group), "unsupported topk / topk_group")
     weights = torch.empty((m, topk), dtype=torch.float32, device=input_tensor.device)
     ids = torch.empty((m, topk), dtype=torch.int32, device=input_tensor.device)
     with torch.cuda.device(input_tensor.device):
-        rc = _lib.lib().b200_moe_fused_gate(input_tensor.data_ptr(), input_tensor.stride(0), bias.data_ptr(),
-                                            weights.data_ptr(), ids.data_ptr(), m, E, num_expert_group, topk_group, topk,
-                                            _stream_ptr(input_tensor.device))
+        rc = _lib.lib().b200_moe_fused_gate_shared_experts(
+            input_tensor.data_ptr(), input_tensor.stride(0), bias.data_ptr(), weights.data_ptr(), ids.data_ptr(), m, E,
+            num_expert_group, topk_group, topk, int(num_fused_shared_experts),
+            float(routed_scaling_factor) if num_fused_shared_experts else 1.0, _stream_ptr(input_tensor.device))
     _lib.check("moe_fused_gate", rc)
     return weights, ids
 

@@ -19,7 +19,7 @@ Sources executed (paths inside the reference checkout):
   python/sglang/test/test_block_fp8_deep_gemm_blackwell.py   ceil_to_ue8m0, per_token_group_quant_mxfp8,
                                             per_block_quant_mxfp8 (power-of-two scales)
 
-Usage:  python tests/golden/make_golden.py [--reference <reference checkout>] [--only ue8m0]
+Usage:  python tests/golden/make_golden.py --reference <reference checkout> [--only ue8m0]
 """
 from __future__ import annotations
 
@@ -169,7 +169,7 @@ def main(reference: str, only: str = ""):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of the reference checkout")
     ap.add_argument("--only", default="", choices=["", "ue8m0"], help="write just this group of vectors")
     a = ap.parse_args()
     main(a.reference, a.only)

@@ -399,6 +399,42 @@ def test_ue8m0_scaled_matmul(M, N, K, no_split_k):
     assert same_bits(out, same)
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 256, 128), (128, 256, 512), (130, 512, 1024), (300, 1152, 640),
+                                   (1024, 7168, 2048), (4096, 4096, 7168)])
+def test_power_of_two_scales_on_the_block_scaling_mma(M, N, K):
+    """Both scale sets powers of two (activations: packed UE8M0 from the quantiser; weights: per_block_quant_mxfp8):
+    the hardware block-scaled product against the oracle's fp32 result and against the fp32-promotion kernel fed
+    the same codes and scales.  Rows and weight blocks carry very different exponents (an activation row scaled by
+    2^(row % 13), weight blocks by 2^(block index % 7)), so a scale applied to the wrong row, column block or
+    k-block cannot pass."""
+    from sglang_b200.layers.quantization.fp8_kernel import (sglang_per_token_group_quant_fp8,
+                                                            w8a8_block_fp8_matmul_deepgemm)
+    g = torch.Generator().manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g)
+    x = (x * torch.pow(2.0, (torch.arange(M) % 13).float()).unsqueeze(1)).to(torch.bfloat16)
+    x[:, : K // 2] *= 4.0      # k-blocks of one row differ as well
+    w = torch.randn(N, K, generator=g) * 0.02
+    blk = (torch.arange((N + 127) // 128).unsqueeze(1) * (K // 128) + torch.arange(K // 128).unsqueeze(0)) % 7
+    w = w * torch.pow(2.0, blk.float()).repeat_interleave(128, 0)[:N].repeat_interleave(128, 1)
+    wq, ws = O.per_block_quant_mxfp8(w)
+    q_ref, s_ref, packed_ref = O.quant_group_fp8_ue8m0_cuda_semantics(x, 128)
+    q, s_packed = sglang_per_token_group_quant_fp8(x.cuda(), 128, column_major_scales=True, scale_tma_aligned=True,
+                                                   scale_ue8m0=True)
+    from sglang_b200 import _lib
+    ref32 = O.block_fp8_matmul_fp32(q_ref, wq, s_ref, ws)
+    soft = w8a8_block_fp8_matmul_deepgemm(q, wq.cuda(), s_packed, ws.cuda(), [128, 128], torch.bfloat16).cpu()
+    for tile_width in (0, 256):     # 0: the 240-wide tile with two accumulators; 256: one accumulator
+        _lib.lib().b200_debug_force_block_n(tile_width)
+        try:
+            out = w8a8_block_fp8_matmul_deepgemm(q, wq.cuda(), s_packed, ws.cuda(), [128, 128], torch.bfloat16,
+                                                 weight_scale_ue8m0=True).cpu()
+            _status_ok()
+        finally:
+            _lib.lib().b200_debug_force_block_n(0)
+        assert O.rel_l2(out.float(), ref32.to(torch.bfloat16).float()) <= TOL, tile_width
+        assert O.rel_l2(out.float(), soft.float()) <= TOL, tile_width
+
+
 def test_deepgemm_shaped_linear():
     """deepgemm_w8a8_block_fp8_linear_with_fallback: quantise with packed power-of-two scales, multiply, add
     bias, view back; the fp32-scale fallback for shapes the DeepGEMM path does not take."""

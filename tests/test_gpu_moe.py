@@ -154,6 +154,88 @@ def test_fused_moe_deepseek_shapes_reduced_tokens():
     _status_ok()
 
 
+def _gpu_block_matmul_fp32(a_q, w_q, sa, sw):
+    """fp32 restatement on the GPU of the block-scaled product (the arithmetic of native_w8a8_block_fp8_matmul,
+    python/sglang/test/test_block_fp8.py:274-326): a_q [m,K] e4m3, w_q [N,K] e4m3, sa [m,K/128], sw [N/128,K/128]."""
+    K = a_q.shape[1]
+    c = torch.zeros(a_q.shape[0], w_q.shape[0], device=a_q.device)
+    sw_rows = sw.repeat_interleave(128, 0)
+    for kb in range(K // 128):
+        c += (a_q[:, kb * 128:(kb + 1) * 128].float() @ w_q[:, kb * 128:(kb + 1) * 128].float().t()) * \
+             (sa[:, kb:kb + 1] * sw_rows[:, kb][None, :])
+    return c
+
+
+def test_fused_moe_full_benchmark_size_256_experts_4096_tokens():
+    """The MoE benchmark configuration at size on one GPU: 256 experts (hidden 7168, intermediate 2048, 11.3 GB of
+    e4m3 weights), 4096 tokens, softmax top-8.  Every token against an fp32 restatement of the op sequence on the
+    GPU (per expert: quantise, block-scaled product, bf16, SiLU*mul, quantise, product, bf16; weighted sum in fp32),
+    and a sample of tokens against the CPU oracle run on just the experts those tokens use."""
+    from sglang_b200.layers.moe.cutlass_moe import fused_experts_block_fp8
+    old_tf32 = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        E, H, I, m, topk = 256, 7168, 2048, 4096, 8
+        dev = torch.device("cuda")
+        w13 = torch.empty(E, 2 * I, H, dtype=torch.float8_e4m3fn, device=dev)
+        w2 = torch.empty(E, H, I, dtype=torch.float8_e4m3fn, device=dev)
+        w13s = torch.empty(E, 2 * I // 128, H // 128, device=dev)
+        w2s = torch.empty(E, H // 128, I // 128, device=dev)
+        g = torch.Generator(device=dev).manual_seed(40)
+
+        def block_quant(w):   # per_block_cast_to_fp8 (sgl-kernel/tests/test_fp8_blockwise_moe.py:51-64) on the device
+            n, k = w.shape
+            wv = w.view(n // 128, 128, k // 128, 128)
+            amax = wv.abs().amax(dim=(1, 3), keepdim=True).clamp(1e-4)
+            return (wv * (448.0 / amax)).to(torch.float8_e4m3fn).view(n, k), (amax / 448.0).view(n // 128, k // 128)
+        for e in range(E):
+            w13[e], w13s[e] = block_quant(torch.randn(2 * I, H, generator=g, device=dev) * 0.02)
+            w2[e], w2s[e] = block_quant(torch.randn(H, I, generator=g, device=dev) * 0.02)
+        x = torch.randn(m, H, generator=g, device=dev).to(torch.bfloat16)
+        logits = torch.randn(m, E, generator=g, device=dev)
+        tw, ti = torch.topk(torch.softmax(logits.float(), dim=-1), topk, dim=-1)
+        ti = ti.to(torch.int32)
+        out = fused_experts_block_fp8(x, w13, w2, w13s, w2s, tw, ti)
+        out2 = fused_experts_block_fp8(x, w13, w2, w13s, w2s, tw, ti)
+        assert same_bits(out, out2), "not deterministic"
+
+        # fp32 restatement on the GPU, expert by expert
+        def quant(t_):
+            tf = t_.float().view(t_.shape[0], -1, 128)
+            s_ = tf.abs().amax(-1).clamp(min=1e-10) / 448.0
+            return (tf / s_.unsqueeze(-1)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).view(t_.shape), s_
+        xq, xs = quant(x)
+        ref = torch.zeros(m, H, device=dev)
+        flat_e = ti.reshape(-1).long()
+        flat_t = torch.arange(m, device=dev).repeat_interleave(topk)
+        flat_w = tw.to(torch.bfloat16).float().reshape(-1)
+        contrib = torch.empty(m * topk, H, device=dev, dtype=torch.bfloat16)
+        for e in range(E):
+            sel = (flat_e == e).nonzero().flatten()
+            if sel.numel() == 0:
+                continue
+            rows = flat_t[sel]
+            c1 = _gpu_block_matmul_fp32(xq[rows], w13[e], xs[rows], w13s[e]).to(torch.bfloat16)
+            act = (torch.nn.functional.silu(c1[:, :I].float()) * c1[:, I:].float()).to(torch.bfloat16)
+            aq, as_ = quant(act)
+            contrib[sel] = _gpu_block_matmul_fp32(aq, w2[e], as_, w2s[e]).to(torch.bfloat16)
+        ref = (contrib.float().view(m, topk, H) * flat_w.view(m, topk, 1)).sum(1)
+        err = O.rel_l2(out.float().cpu(), ref.to(torch.bfloat16).float().cpu())
+        assert err <= 5e-3, err      # same tolerance as the small cases: __expf in SiLU, bf16 rounding flips
+        # sampled tokens against the CPU oracle, restricted to the experts they route to
+        tok = torch.arange(0, m, 683, device=dev)          # 6 tokens
+        used = torch.unique(ti[tok].reshape(-1)).long()
+        remap = torch.full((E,), -1, dtype=torch.int32, device=dev)
+        remap[used] = torch.arange(used.numel(), dtype=torch.int32, device=dev)
+        ids_local = remap[ti[tok].long()]
+        ref_cpu = O.cutlass_fused_experts_fp8(x[tok].cpu(), w13[used].cpu(), w2[used].cpu(), w13s[used].cpu(),
+                                              w2s[used].cpu(), tw[tok].cpu(), ids_local.cpu())
+        assert O.rel_l2(out[tok].float().cpu(), ref_cpu.float()) <= 5e-3
+        _status_ok()
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old_tf32
+
+
 def test_ep_module_single_rank_equals_fused_path():
     """world size 1: dispatch -> local grouped experts -> combine must give the fused path's bits."""
     from sglang_b200.distributed import ExpertParallelBlockFp8MoE
@@ -188,6 +270,18 @@ def test_fused_silu_mul_quant_equals_two_kernels(M, K, dtype):
     assert same_bits(q, q_ref) and same_bits(s, s_ref)
     q2, s2 = silu_and_mul_per_token_group_quant_fp8(x, 128, column_major_scales=True, scale_tma_aligned=True)
     assert same_bits(q2, q_ref) and same_bits(s2.contiguous(), s_ref)
+    # and directly against the CPU oracle: SiLU*mul in fp32 rounded once to the input type, then the group quantiser.
+    # The kernel evaluates the exponential with __expf, so a rounded activation may differ by one ulp of the input
+    # type now and then; codes may then differ by one step in that group.  Scales within 1 ulp-of-input relative,
+    # dequantised values within one e4m3 step of the oracle's.
+    xc = x.cpu()
+    act = O.silu_and_mul(xc)
+    qo, so = O.quant_group_fp8_cuda_semantics(act, 128)
+    rel = {torch.bfloat16: 2.0 ** -7, torch.float16: 2.0 ** -10}[dtype]
+    assert torch.allclose(s.cpu(), so, rtol=2 * rel, atol=0)
+    deq, deq_o = q.float().cpu().view(M, -1, 128) * s.cpu().unsqueeze(-1), qo.float().view(M, -1, 128) * so.unsqueeze(-1)
+    assert bool(((deq - deq_o).abs() <= so.unsqueeze(-1) * 32.0 + 1e-30).all())
+    assert (q.cpu().view(torch.uint8) != qo.view(torch.uint8)).float().mean() < 0.05
 
 
 def test_fp8_moe_method_apply():
@@ -304,8 +398,21 @@ def test_moe_fused_gate(m, E, G, topk_group, topk):
     assert torch.equal(got != 0, want != 0)
     torch.testing.assert_close(got, want, rtol=3e-6, atol=1e-8)
     torch.testing.assert_close(w.sum(dim=-1).cpu(), torch.ones(m), rtol=1e-5, atol=1e-6)
-    with pytest.raises(NotImplementedError):
-        moe_fused_gate(logits.cuda(), bias.cuda(), G, topk_group, topk, num_fused_shared_experts=1, routed_scaling_factor=2.5)
+    # fused shared experts (sgl-kernel/csrc/moe/moe_fused_gate.cu:225-252): the last n slots carry ids E, E+1, ... and
+    # weight 1 / routed_scaling_factor; the routed slots before them are the gate with topk - n choices
+    for n_shared in (1, 2):
+        if topk - n_shared < 1:
+            continue
+        w2, ids2 = moe_fused_gate(logits.cuda(), bias.cuda(), G, topk_group, topk, num_fused_shared_experts=n_shared,
+                                  routed_scaling_factor=2.5)
+        w_r, ids_r = moe_fused_gate(logits.cuda(), bias.cuda(), G, topk_group, topk - n_shared)
+        assert torch.equal(ids2[:, :topk - n_shared], ids_r) and torch.equal(w2[:, :topk - n_shared], w_r)
+        assert torch.equal(ids2[:, topk - n_shared:].cpu(),
+                           (E + torch.arange(n_shared, dtype=torch.int32)).repeat(m, 1))
+        torch.testing.assert_close(w2[:, topk - n_shared:].cpu(), torch.full((m, n_shared), 1 / 2.5), rtol=1e-6, atol=0)
+    # the operator registered with the reference's schema returns the same pair
+    w3, ids3 = torch.ops.sgl_kernel.moe_fused_gate(logits.cuda(), bias.cuda(), G, topk_group, topk, 0, 1.0)
+    assert torch.equal(w3, w) and torch.equal(ids3, ids)
 
 
 def test_checkpoint_to_moe_layer(tmp_path):

@@ -63,14 +63,30 @@ def _ep_worker(rank, world, port, q):
         el = E // world
         sl = slice(rank * el, (rank + 1) * el)
         rows = slice(rank * m_per, (rank + 1) * m_per)
+        results = {}
+        for backend in ("nvlink", "nccl"):
+            moe = ExpertParallelBlockFp8MoE(w13q[sl].contiguous(), w2q[sl].contiguous(), w13s[sl].contiguous(),
+                                            w2s[sl].contiguous(), backend=backend)
+            for it in range(2):          # the second call reuses the exchange buffers and barrier flags
+                y = moe(x[rows].contiguous(), w[rows].contiguous(), ids[rows].contiguous())
+                parts = [torch.empty_like(y) for _ in range(world)]
+                dist.all_gather(parts, y)
+                torch.cuda.synchronize()
+                moe.check()
+                results[f"{backend}_{it}"] = bool(torch.equal(torch.cat(parts, 0), ref))
+        # a routing that sends every row to rank 0's experts: with capacity = tokens * topk nothing may be dropped
         moe = ExpertParallelBlockFp8MoE(w13q[sl].contiguous(), w2q[sl].contiguous(), w13s[sl].contiguous(),
-                                        w2s[sl].contiguous())
-        y = moe(x[rows].contiguous(), w[rows].contiguous(), ids[rows].contiguous())
+                                        w2s[sl].contiguous(), backend="nvlink", capacity_factor=float(world))
+        ids0 = (ids % el).contiguous()
+        ref0 = fused_experts_block_fp8(x, w13q, w2q, w13s, w2s, w, ids0)
+        y = moe(x[rows].contiguous(), w[rows].contiguous(), ids0[rows].contiguous())
         parts = [torch.empty_like(y) for _ in range(world)]
         dist.all_gather(parts, y)
         torch.cuda.synchronize()
+        moe.check()
+        results["all_to_rank0"] = bool(torch.equal(torch.cat(parts, 0), ref0))
         if rank == 0:
-            q.put(bool(torch.equal(torch.cat(parts, 0), ref)))
+            q.put(results)
     finally:
         dist.destroy_process_group()
 
@@ -210,5 +226,8 @@ def test_tp2_custom_all_reduce_and_overlapped_chunks():
 
 
 @needs2
-def test_ep2_nccl_bitwise():
-    assert _run(_ep_worker)
+def test_ep2_bitwise_both_exchanges():
+    """Expert-parallel layer on 2 ranks, NVLink dispatch/combine kernels and the NCCL all-to-all form, each
+    twice, plus a skewed routing at full capacity: bit for bit the single-GPU fused layer."""
+    res = _run(_ep_worker)
+    assert all(res.values()), res

@@ -143,6 +143,35 @@ def test_full_size_checksum_property():
     assert bool(torch.all(err <= s * 16.001 + 1e-30))   # 16 = half the e4m3 step at the top binade
 
 
+def test_largest_benchmark_size_m65536_every_element():
+    """M = 65536 x 7168 (the largest size of the bandwidth configuration, 470 M elements): the CPU oracle on
+    every 509th row, and EVERY code and scale bit for bit against a torch restatement of the same arithmetic on
+    the GPU (fp32 divide, clamp, round-to-nearest-even saturating cast; itself pinned to the oracle on the
+    sampled rows), row-major and column-major padded scale layouts."""
+    M, K = 65536, 7168
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.empty(M, K, device="cuda", dtype=torch.bfloat16)
+    for r0 in range(0, M, 8192):
+        blk = torch.randn(8192, K, generator=g, device="cuda", dtype=torch.float32)
+        blk = torch.where(torch.rand(8192, K, generator=g, device="cuda") < 1e-3, blk * 100, blk)
+        x[r0:r0 + 8192] = blk.to(torch.bfloat16)
+    q, s = _quant(x, column_major_scales=True, scale_tma_aligned=True)
+    q_rm, s_rm = _quant(x)
+    assert same_bits(q, q_rm) and same_bits(s.contiguous(), s_rm)
+    rows = torch.arange(0, M, 509)
+    q_ref, s_ref = O.quant_group_fp8_cuda_semantics(x[rows.cuda()].cpu(), 128)
+    assert same_bits(q[rows.cuda()].cpu(), q_ref) and same_bits(s[rows.cuda()].contiguous().cpu(), s_ref)
+    for r0 in range(0, M, 8192):
+        xf = x[r0:r0 + 8192].float().view(8192, K // 128, 128)
+        s_t = xf.abs().amax(-1).clamp(min=1e-10) / 448.0
+        q_t = (xf / s_t.unsqueeze(-1)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).view(8192, K)
+        assert same_bits(q_rm[r0:r0 + 8192], q_t) and same_bits(s_rm[r0:r0 + 8192], s_t), r0
+        if r0 == 0:   # the restatement itself against the oracle
+            idx = rows[rows < 8192].cuda()
+            n = idx.numel()
+            assert same_bits(q_t[idx].cpu(), q_ref[:n]) and same_bits(s_t[idx].cpu(), s_ref[:n])
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
 @pytest.mark.parametrize("M,K", [(1, 128), (5, 512), (37, 1024), (130, 7168), (2048, 7168), (6, 640)])
 def test_ue8m0_packed_scales_bit_exact(M, K, dtype):
