@@ -17,7 +17,7 @@ on unsharded weights, and at N > 1 the expert-parallel MoE layer against the sin
 (bitwise); a failed check ends the run with a non-zero exit code.
 
 At every N the step is replayed from a CUDA graph inside the timed region (per-kernel times come from a
-separate eager pass with events).  The JSON line carries: value = whole-job TFLOP/s with inputs resident
+separate eager pass with events around each call).  The JSON line carries: value = whole-job TFLOP/s with inputs resident
 in HBM; e2e = the same through the public linear call with HOST activations (pinned) copied in and the
 bf16 results copied out inside the timed region; roofline for the dominant kernel (the gate_up GEMM);
 quant = the group-quantisation kernel on its own benchmark configuration (M=16384 x 7168); config3 /
@@ -237,7 +237,8 @@ def torch_group_quant(x):
     import torch
     m, k = x.shape
     xf = x.float().view(m, k // 128, 128)
-    s = xf.abs().amax(-1).clamp(min=1e-10) / 448.0
+    amax = xf.abs().amax(-1).clamp(min=1e-10)
+    s = amax / torch.full_like(amax, 448.0)   # tensor / tensor: torch divides by a Python scalar with a reciprocal multiply on CUDA
     q = (xf / s[..., None]).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).view(m, k)
     return q, s
 
@@ -355,6 +356,50 @@ def fp8_ceiling(dev, steps=20):
     except Exception as e:  # noqa: BLE001
         print(f"[bench] fp8 ceiling not measured: {e}", file=sys.stderr)
         return None
+
+
+def ue8m0_mlp(dev, ceiling, steps=10):
+    """The headline MLP step with POWER-OF-TWO scales (the reference's DeepGEMM / UE8M0 mode, its default on
+    Blackwell): weights re-quantised to power-of-two block scales, activations quantised with packed UE8M0 scales,
+    products on the tensor core's block-scaling path (no fp32 promotion).  Same shapes and FLOPs as the headline."""
+    import torch
+    from sglang_b200.layers.quantization.fp8_kernel import sglang_per_token_group_quant_fp8, w8a8_block_fp8_matmul_deepgemm
+    from sglang_b200.layers.quantization.fp8_utils import deepgemm_w8a8_block_fp8_linear_with_fallback, requant_weight_ue8m0
+    w1q, w1s = gen_weight_device(INTER2, HIDDEN, 100, dev)
+    w2q, w2s = gen_weight_device(HIDDEN, INTER, 200, dev)
+    w1q, w1s = requant_weight_ue8m0(w1q, w1s, [128, 128])
+    w2q, w2s = requant_weight_ue8m0(w2q, w2s, [128, 128])
+    g = torch.Generator(device=dev).manual_seed(7)
+    x = torch.randn((M_TOKENS, HIDDEN), generator=g, device=dev).to(torch.bfloat16)
+    h = torch.randn((M_TOKENS, INTER), generator=g, device=dev).to(torch.bfloat16)
+
+    def step():
+        y1 = deepgemm_w8a8_block_fp8_linear_with_fallback(x, w1q, [128, 128], w1s, weight_scale_ue8m0=True)
+        y2 = deepgemm_w8a8_block_fp8_linear_with_fallback(h, w2q, [128, 128], w2s, weight_scale_ue8m0=True)
+        return y1, y2
+    ms, g_ = time_graph(step, steps, torch.cuda.synchronize)
+    g_.reset()
+    q, sp = sglang_per_token_group_quant_fp8(x, 128, column_major_scales=True, scale_tma_aligned=True, scale_ue8m0=True)
+    hw = w8a8_block_fp8_matmul_deepgemm(q, w1q, sp, w1s, [128, 128], torch.bfloat16, weight_scale_ue8m0=True)
+    sw = w8a8_block_fp8_matmul_deepgemm(q, w1q, sp, w1s, [128, 128], torch.bfloat16)
+    err = rel_l2(hw, sw)
+    us, g_ = time_graph(lambda: [w8a8_block_fp8_matmul_deepgemm(q, w1q, sp, w1s, [128, 128], torch.bfloat16,
+                                                                weight_scale_ue8m0=True) for _ in range(4)], 5,
+                        torch.cuda.synchronize)
+    g_.reset()
+    gemm_ms = us / 4
+    gemm_tf = 2.0 * M_TOKENS * INTER2 * HIDDEN / (gemm_ms * 1e-3) / 1e12
+    out = {"workload": WORKLOAD + " with power-of-two (UE8M0) activation and weight scales",
+           "kernel": "gemm_mx_kernel (tcgen05.mma kind::mxf8f6f4.block_scale, all k-blocks accumulated in tensor memory)",
+           "ms_per_step": ms, "step_tflops": FLOPS_PER_STEP / (ms * 1e-3) / 1e12,
+           "gemm_gate_up_ms": gemm_ms, "gemm_gate_up_tflops": gemm_tf,
+           "frac_of_nominal_4500": gemm_tf / NOMINAL_FP8_TFLOPS,
+           "rel_l2_vs_fp32_promotion_kernel_on_the_same_codes": err}
+    if ceiling:
+        out["frac_of_fp8_ceiling"] = gemm_tf / ceiling
+    del w1q, w1s, w2q, w2s
+    torch.cuda.empty_cache()
+    return out
 
 
 LLAMA = {"qkv": ("col", 10240, 8192), "gate_up": ("col", 57344, 8192), "o_proj": ("row", 8192, 8192),
@@ -603,6 +648,13 @@ def run_gpu_arm(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    t_start = time.time()
+
+    def dbg(msg):
+        if os.environ.get("B200_BENCH_DEBUG"):
+            torch.cuda.synchronize()
+            print(f"[bench r{rank} +{time.time() - t_start:.2f}s] {msg}", file=sys.stderr, flush=True)
+
     # Weights are quantised once on the FULL matrix (same seed on every rank) and sharded by the product's
     # parallel linears, so the tensor-parallel result is comparable with the unsharded one.
     w1q, w1s = gen_weight_device(INTER2, HIDDEN, 100, dev)
@@ -621,8 +673,11 @@ def run_gpu_arm(args):
 
     # ---- self-check before anything is timed
     rows = torch.arange(0, M_TOKENS, M_TOKENS // PARITY_ROWS, device=dev)
+    dbg("inputs ready")
     y1 = col(x)
+    dbg("column-parallel done")
     y2 = row(h).clone()
+    dbg("row-parallel done")
     xq_r, xs_r = torch_group_quant(x[rows])
     ref1 = torch_block_matmul_fp32(xq_r, w1q[rank * n1:(rank + 1) * n1], xs_r, w1s[rank * n1 // 128:(rank + 1) * n1 // 128])
     hq_r, hs_r = torch_group_quant(h_full[rows])
@@ -712,10 +767,22 @@ def run_gpu_arm(args):
              "gemm_gate_up": lambda: fp8_blockwise_scaled_mm(xq, w1r.T, xs, w1sr.T, torch.bfloat16),
              "quant_h": lambda: sglang_per_token_group_quant_fp8(h, 128, column_major_scales=True),
              "gemm_down": lambda: fp8_blockwise_scaled_mm(hq, w2r.T, hs, w2sr.T, torch.bfloat16)}
-    for name, fn in calls.items():
-        us, g_ = time_graph(lambda: [fn() for _ in range(4)], 5, torch.cuda.synchronize)
-        g_.reset()
-        per_kernel[name] = us / 4
+    # one call of each per pass, in the order of the step, events around every call (eager): the clocks a kernel
+    # sees are those of the step it is part of, not those of a kernel repeated back to back under the power cap
+    for _ in range(2):
+        for fn in calls.values():
+            fn()
+    torch.cuda.synchronize()
+    evs = []
+    for _ in range(5):
+        for name, fn in calls.items():
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b.record()
+            evs.append((name, a, b))
+    torch.cuda.synchronize()
+    for name, a, b in evs:
+        per_kernel.setdefault(name, []).append(a.elapsed_time(b))
+    per_kernel = {k_: sum(v_) / len(v_) for k_, v_ in per_kernel.items()}
     if world > 1:
         y2b = row._out_buffer(M_TOKENS, h) if ar is not None else torch.empty((M_TOKENS, HIDDEN), dtype=torch.bfloat16, device=dev)
         us, g_ = time_graph(lambda: row._reduce(y2b), 5, barrier)
@@ -832,6 +899,10 @@ def run_gpu_arm(args):
             extras["config4"] = moe_config4_single(dev, pk)
             extras["fp8_ceiling_tflops"] = fp8_ceiling(dev)
             try:
+                extras["ue8m0_path"] = ue8m0_mlp(dev, extras["fp8_ceiling_tflops"])
+            except Exception as e:  # noqa: BLE001
+                extras["ue8m0_path"] = {"unavailable": str(e)[:300]}
+            try:
                 extras["gpu_comparator"] = gpu_comparator(dev)
             except Exception as e:  # noqa: BLE001
                 extras["gpu_comparator"] = {"unavailable": f"comparator failed: {str(e)[:300]}"}
@@ -861,8 +932,8 @@ def run_gpu_arm(args):
         roof = {"bound": "tensor", "kernel": "gemm_block_fp8_kernel<BLOCK_N=256, 16 epilogue warps, 32-column chunks, bf16> "
                                              f"(gate_up{'' if world == 1 else f' shard N={n1}'})",
                 "achieved": achieved, "peak": peak_burst, "unit": "TFLOP/s", "frac": achieved / peak_burst,
-                "peak_source": f"2 x bf16_tflops (burst) of {pk['src']}: the kernel is timed alone in a short graph replay and "
-                               "the fp8 pipe does twice the bf16 MACs per clock (the file holds no fp8 entry)",
+                "peak_source": f"2 x bf16_tflops (burst) of {pk['src']}: the kernel is timed with events inside a short eager pass "
+                               "of the step, and the fp8 pipe does twice the bf16 MACs per clock (the file holds no fp8 entry)",
                 "frac_of_nominal_4500": achieved / NOMINAL_FP8_TFLOPS,
                 "traffic": GEMM_TRAFFIC_BYTES_1GPU if world == 1 else None,
                 "algorithmic_flops_per_launch": gemm_flops,
@@ -884,7 +955,7 @@ def run_gpu_arm(args):
                        "parallelism": (f"tp{world}: gate_up column-parallel, down row-parallel in {chunks_used} row chunk(s), "
                                        f"partial outputs summed by {'this library NVLink all-reduce kernel' + (' (multicast)' if ar.multicast else ' (peer pointers)') if ar is not None else 'NCCL all-reduce'}"
                                        ) if world > 1 else "single",
-                       "timing": "step replayed from a CUDA graph at every N; per-kernel times from separate graph replays",
+                       "timing": "step replayed from a CUDA graph at every N; per-kernel times from a separate eager pass with events around each call, at every N",
                        "l2": "inputs larger than L2 (weights 396 MB e4m3 + activations 210 MB bf16 per step)",
                        "kernels_ms": per_kernel,
                        **({"row_chunk_candidates_ms": chunk_ms} if world > 1 else {})},
@@ -900,7 +971,7 @@ def run_gpu_arm(args):
             "clocks": {**(clocks or {}), "burst_region": burst_clk, "sustained_region": sus_clk},
             "status_ok": status_ok,
         }
-        for k_ in ("quant", "config3", "config4", "gpu_comparator"):
+        for k_ in ("quant", "config3", "config4", "ue8m0_path", "gpu_comparator"):
             if k_ in extras:
                 line[k_] = extras[k_]
         if world == 1 and not args.skip_extras:

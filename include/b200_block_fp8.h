@@ -327,7 +327,7 @@ int b200_topk_softmax(const void* gating_output, int dtype, int64_t row_stride, 
  *                 bytes % (16 * world_size) == 0.
  *   one_shot = 1: into `out` (local memory, bytes long); bytes % 16 == 0.  For small buffers.
  * Every element is the fp32 sum over ranks rounded once: identical bits on all ranks, run to run.
- * The kernels of the ranks wait for one another at flag barriers (bounded, about a second): every rank
+ * The kernels of the ranks wait for one another at flag barriers (bounded, about five seconds): every rank
  * must call with the same arguments, in the same order, and nothing else may use the flag words
  * [flag_base_words, + b200_allreduce_flag_words(world_size)) of the signal pads meanwhile.  *status
  * (device memory, zero before the first call) receives a non-zero code if a peer never arrived; the
@@ -366,7 +366,7 @@ int b200_allreduce_max_blocks(void);
  * b200_ep_combine: rows [*, hidden] (dtype bf16 / fp16) holds the expert output of received row r at row
  *   row_of[r] (r itself when row_of is NULL); each is stored into its source rank's return buffer at the row's
  *   source slot; ends with a flag barrier (a different flag_base_words than the dispatch's).
- * The kernels of the ranks wait for one another (bounded, about a second): every rank must make the same
+ * The kernels of the ranks wait for one another (bounded, about five seconds): every rank must make the same
  * calls in the same order; *status (device word, zero before the first call) receives 32 / 33 if a peer
  * never arrived.  Nothing on the host reads device data.
  */

@@ -15,7 +15,8 @@
 //   one-shot, out of place  every rank sums the whole buffer into a local output; one pass and two
 //                        barriers, for buffers of a few hundred kilobytes where latency is everything.
 // Either way every element is the fp32 sum of all ranks' values rounded once -- the same bits on every
-// rank, independent of timing.
+// rank, independent of timing.  (The peer-pointer forms round to nearest-even; the switch's own rounding of
+// its fp32 sum differs from that by one unit in the last place now and then.)
 //
 // Ranks meet at flag barriers in the peers' signal pads (one 32-bit flag per block and peer,
 // compare-and-swap 0 -> 1 by the sender, 1 -> 0 by the receiver, so the flags need no epoch).  Every
@@ -104,7 +105,7 @@ __global__ void __launch_bounds__(kArThreads) allreduce_twoshot_kernel(const ArP
   const int64_t base = p.offset_bytes + slice * p.rank;
   const int64_t nvec = slice / 16;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  constexpr int U = 4;
+  constexpr int U = 8;   // 16-byte vectors in flight per thread: NVLink round trips are microseconds long
   for (int64_t i0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < nvec; i0 += stride * U) {
     Vec16 v[U];
 #pragma unroll
@@ -166,7 +167,7 @@ extern "C" int b200_allreduce(void* const* peer_buffers, void* const* peer_signa
   if (one_shot ? (bytes % 16 != 0) : (bytes % (16 * world_size) != 0)) return B200_ERR_BAD_SHAPE;
   if (offset_bytes % 16 != 0) return B200_ERR_MISALIGNED;
   if (one_shot && !out) return B200_ERR_NULL_PTR;
-  if (num_blocks <= 0) num_blocks = 32;
+  if (num_blocks <= 0) num_blocks = 64;
   if (num_blocks > b200_allreduce_max_blocks()) num_blocks = b200_allreduce_max_blocks();
   int rc = require_sm100();
   if (rc != B200_OK) return rc;

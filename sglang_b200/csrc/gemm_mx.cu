@@ -12,15 +12,17 @@
 //  python/sglang/srt/layers/deep_gemm_wrapper/entrypoint.py:78-93 gemm_nt_f8f8bf16,
 //  weights re-quantised to power-of-two scales by requant_weight_ue8m0, fp8_utils.py:370-443).
 //
-// One persistent CTA per SM, 128 x 256 tiles, 8 warps:
-//   warps 0-3  epilogue: after a tile's last k-block, each reads its 32 rows x 256 columns from tensor memory,
+// One persistent CTA per SM, 128 x 256 (or 256 x 240) tiles, 8 warps:
+//   warps 0-3  epilogue: after a tile's last k-block, each reads its rows of the accumulator(s) from tensor memory,
 //              converts and stores; then hands the accumulator back.
-//   warp 4     TMA producer: A box (128 x 128 B) + B box (256 x 128 B) per k-block, 128-byte swizzle, no multicast.
-//   warp 5     MMA issuer: per k-block copies the stage's scale-factor tiles from shared to tensor memory
-//              (tcgen05.cp 32x128b.warpx4) and issues 4 x tcgen05.mma (K = 32 each, scale-factor ids 0..3).
-//   warp 6     scale stager: builds the stage's scale-factor tiles in the layout the MMA expects -- per 128 rows
-//              a 512-byte tile, row r's four K-group bytes at (r % 32) * 16 + (r / 32) * 4 -- from the packed
-//              activation exponents and the weights' fp32 power-of-two scales (exponent field taken as the byte).
+//   warp 4     TMA producer: A box + B box per k-block, 128-byte swizzle, no multicast.
+//   warp 5     MMA issuer: 4 x tcgen05.mma per k-block and 128-row half (K = 32 each).  A row's (column's) 32-bit
+//              scale word holds the exponent bytes of FOUR consecutive k-blocks; the instruction's scale-factor id
+//              picks the k-block's byte, so the scale tiles are copied from shared to tensor memory
+//              (tcgen05.cp 32x128b.warpx4) once per four k-blocks.
+//   warp 6     scale stager: builds those tiles in the layout the MMA expects -- per 128 rows a 512-byte tile,
+//              row r's word at (r % 32) * 16 + (r / 32) * 4 -- from the packed activation exponents (the
+//              quantiser's words, as they are) and the weights' fp32 power-of-two scales (exponent fields).
 // Every mbarrier wait is bounded (common.cuh); a wait that gives up records a code and all roles drain.
 #include "gemm_common.cuh"
 
@@ -28,27 +30,34 @@ namespace b200 {
 namespace {
 
 constexpr int BM = 128, BK = 128;
-constexpr int kStagesMx = 4;
 constexpr int kSfSlots = 3;                             // scale-factor ring: one slot serves four k-blocks
-constexpr int kABytesMx = BM * BK;
-constexpr int kSfaBytes = 512, kSfbBytes = 1024;       // one 128-row tile for A, two for the (up to 256) columns of B
-constexpr int kSfBytes = kSfaBytes + kSfbBytes;
+constexpr int kSfaBytes = 512, kSfbBytes = 1024;       // one 512-byte tile per 128 rows of A, two for the (up to 256) columns of B
 constexpr int kThreadsMx = 256;
 constexpr int kGroupMMx = 32;
 
-// Tile width BN = 240 leaves room in tensor memory for TWO accumulators (columns [0,240) and [256,496)) next to the
-// scale factors ([240,252)), so a tile's read-out overlaps the next tile's MMAs; BN = 256 has one accumulator
-// ([0,256), scale factors at [256,268)) and is kept for comparison.
-template <int BN>
+// Tile shapes (rows x columns per CTA) and their tensor-memory maps:
+//   128 x 256  one accumulator [0,256), scale factors at [256,268).
+//   128 x 240  two accumulators [0,240) and [256,496), scale factors at [240,252): a tile's read-out overlaps the
+//              next tile's MMAs.
+//   256 x 240  (MSUB = 2) two 128-row halves that share every B stage: accumulators [0,240) and [256,496), scale
+//              factors of the two halves and of B at [240,256).  One CTA per SM moves 188 bytes of shared memory per
+//              clock at full MMA rate with a 128-row tile (TMA writes plus operand reads); sharing B between two
+//              halves brings that to 125.
+template <int BN, int MSUB>
 struct MxCfg {
-  static constexpr int kNumAcc = BN <= 240 ? 2 : 1;
+  static_assert(MSUB == 1 || BN <= 240, "two 128-row halves need the 240-wide tile");
+  static constexpr int kStages = MSUB == 2 ? 3 : 4;
+  static constexpr int kNumAcc = (BN <= 240 && MSUB == 1) ? 2 : 1;   // accumulator double buffering across tiles
+  static constexpr int kABytes = MSUB * BM * BK;
   static constexpr int kBBytes = BN * BK;
-  static constexpr int kStageBytes = kABytesMx + kBBytes;
-  static constexpr uint32_t kSfaCol = BN <= 240 ? 240 : 256;
-  static constexpr uint32_t kSfbCol = kSfaCol + 4;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr uint32_t kSfaCol = BN <= 240 ? 240 : 256;          // 4 columns per 128-row half
+  static constexpr uint32_t kSfbCol = kSfaCol + 4 * MSUB;
   static constexpr uint32_t kAccStride = 256;
-  static constexpr int kSmem = kStagesMx * kStageBytes + kSfSlots * kSfBytes + 1024 + 256;
+  static constexpr int kSfBytes = MSUB * kSfaBytes + kSfbBytes;
+  static constexpr int kSmem = kStages * kStageBytes + kSfSlots * kSfBytes + 1024 + 256;
   static_assert(kBBytes % 1024 == 0, "stage bases must keep the 1024-byte alignment of the swizzle pattern");
+  static_assert(kSmem <= 227 * 1024, "shared memory");
 };
 
 struct MxParams {
@@ -104,10 +113,14 @@ __device__ __forceinline__ void mx_tile_coords(int tile, int m_blocks, int n_blo
   n_blk = in_group / rows;
 }
 
-template <int BN, typename OutT>
+template <int BN, int MSUB, typename OutT>
 __global__ void __launch_bounds__(kThreadsMx, 1)
 gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const MxParams p) {
-  using C = MxCfg<BN>;
+  using C = MxCfg<BN, MSUB>;
+  constexpr int kStagesMx = C::kStages;
+  constexpr int kABytesMx = C::kABytes;
+  constexpr int kSfBytes = C::kSfBytes;
+  constexpr int kTileM = BM * MSUB;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_a = smem;
@@ -124,7 +137,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int m_blocks = (p.M + BM - 1) / BM;
+  const int m_blocks = (p.M + kTileM - 1) / kTileM;
   const int n_blocks = (p.N + BN - 1) / BN;
   const int nkb = (p.K + BK - 1) / BK;
   const int num_tiles = m_blocks * n_blocks;
@@ -171,7 +184,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (!ok) break;
         if (elect_one()) {
           mbar_expect_tx(&full_bar[stage], C::kStageBytes);
-          tma_load_2d(smem_a + stage * kABytesMx, &map_a, &full_bar[stage], kb * BK, m_blk * BM);
+          tma_load_2d(smem_a + stage * kABytesMx, &map_a, &full_bar[stage], kb * BK, m_blk * kTileM);
           tma_load_2d(smem_b + stage * C::kBBytes, &map_b, &full_bar[stage], kb * BK, n_blk * BN);
         }
         __syncwarp();
@@ -219,20 +232,26 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (elected) {
           if (j == 0) {
             const uint32_t sf_addr = smem_u32(smem_sf + slot * kSfBytes);
-            tmem_cp_sf(tmem_base + C::kSfaCol, sf_desc(sf_addr));
-            tmem_cp_sf(tmem_base + C::kSfbCol, sf_desc(sf_addr + kSfaBytes));
-            tmem_cp_sf(tmem_base + C::kSfbCol + 4, sf_desc(sf_addr + kSfaBytes + 512));
+#pragma unroll
+            for (int h = 0; h < MSUB; ++h) tmem_cp_sf(tmem_base + C::kSfaCol + 4 * h, sf_desc(sf_addr + h * kSfaBytes));
+            tmem_cp_sf(tmem_base + C::kSfbCol, sf_desc(sf_addr + MSUB * kSfaBytes));
+            tmem_cp_sf(tmem_base + C::kSfbCol + 4, sf_desc(sf_addr + MSUB * kSfaBytes + 512));
           }
 #pragma unroll
-          for (int k = 0; k < 3; ++k)
-            umma_mx(d_tmem, a_desc + static_cast<uint64_t>(2 * k), b_desc + static_cast<uint64_t>(2 * k), idesc,
-                    tmem_base + C::kSfaCol, tmem_base + C::kSfbCol, (kb > 0 || k > 0) ? 1u : 0u);
+          for (int i = 0; i < 4 * MSUB - 1; ++i) {
+            const int k = i / MSUB, h = i % MSUB;      // K step, 128-row half
+            umma_mx(d_tmem + h * C::kAccStride, a_desc + static_cast<uint64_t>(2 * k + h * ((BM * BK) >> 4)),
+                    b_desc + static_cast<uint64_t>(2 * k), idesc, tmem_base + C::kSfaCol + 4 * h, tmem_base + C::kSfbCol,
+                    (kb > 0 || k > 0) ? 1u : 0u);
+          }
         }
         // all lanes test (warp-uniform outcome); a tile's last k-block is followed by another tile's first
         next_ready = mbar_try_wait(&full_bar[nstage], nphase, 1);
         next_ready = __all_sync(0xffffffffu, next_ready);
         if (elected) {
-          umma_mx(d_tmem, a_desc + 6, b_desc + 6, idesc, tmem_base + C::kSfaCol, tmem_base + C::kSfbCol, 1u);
+          constexpr int h = MSUB - 1;
+          umma_mx(d_tmem + h * C::kAccStride, a_desc + static_cast<uint64_t>(6 + h * ((BM * BK) >> 4)), b_desc + 6, idesc,
+                  tmem_base + C::kSfaCol + 4 * h, tmem_base + C::kSfbCol, 1u);
           umma_commit(&empty_bar[stage]);
           if (j == 3 || last_kb) umma_commit(&sf_empty[slot]);
           if (last_kb) umma_commit(&acc_full[acc]);
@@ -259,11 +278,11 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
       int m_blk, n_blk;
       mx_tile_coords(tile, m_blocks, n_blocks, m_blk, n_blk);
-      const int row0 = m_blk * BM;
+      const int row0 = m_blk * kTileM;
       for (int kb0 = 0; kb0 < nkb; kb0 += 4) {
-        uint32_t w[4];
+        uint32_t w[4 * MSUB];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < 4 * MSUB; ++j) {
           const int row = row0 + lane + 32 * j;
           w[j] = (row < p.M) ? __ldg(p.sa + static_cast<int64_t>(kb0 >> 2) * p.sa_stride_pack + row * p.sa_stride_m) : 0u;
         }
@@ -284,9 +303,11 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         ok = mbar_wait_warp(&sf_empty[slot], sphase ^ 1u, p.status, 45);
         if (!ok) break;
         uint8_t* sf = smem_sf + slot * kSfBytes;
-        *reinterpret_cast<uint4*>(sf + lane * 16) = make_uint4(w[0], w[1], w[2], w[3]);
-        *reinterpret_cast<uint4*>(sf + kSfaBytes + lane * 16) = make_uint4(wb[0], wb[1], wb[2], wb[3]);
-        *reinterpret_cast<uint4*>(sf + kSfaBytes + 512 + lane * 16) = make_uint4(wb[4], wb[5], wb[6], wb[7]);
+#pragma unroll
+        for (int h = 0; h < MSUB; ++h)
+          *reinterpret_cast<uint4*>(sf + h * kSfaBytes + lane * 16) = make_uint4(w[4 * h], w[4 * h + 1], w[4 * h + 2], w[4 * h + 3]);
+        *reinterpret_cast<uint4*>(sf + MSUB * kSfaBytes + lane * 16) = make_uint4(wb[0], wb[1], wb[2], wb[3]);
+        *reinterpret_cast<uint4*>(sf + MSUB * kSfaBytes + 512 + lane * 16) = make_uint4(wb[4], wb[5], wb[6], wb[7]);
         fence_proxy_async_smem();     // generic-proxy writes -> visible to the tensor core's copy
         __syncwarp();
         if (lane == 0) mbar_arrive(&sf_full[slot]);
@@ -305,26 +326,30 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
       int m_blk, n_blk;
       mx_tile_coords(tile, m_blocks, n_blocks, m_blk, n_blk);
-      const int m = m_blk * BM + warp * 32 + lane;
       ok = mbar_wait(&acc_full[acc], acc_phase[acc], p.status, 46);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t taddr = tmem_base + lane_addr + static_cast<uint32_t>(acc) * C::kAccStride;
       constexpr int kChunks = BN / 16;
 #pragma unroll 1
-      for (int ch = 0; ch < kChunks; ch += 2) {
-        float v[32];
-        tmem_ld16(taddr + ch * 16, *reinterpret_cast<float(*)[16]>(v));
-        if (ch + 1 < kChunks) tmem_ld16(taddr + (ch + 1) * 16, *reinterpret_cast<float(*)[16]>(v + 16));
-        tmem_ld_wait();
-        if (ch + 2 >= kChunks) {
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      for (int h = 0; h < MSUB; ++h) {
+        const int m = m_blk * kTileM + h * BM + warp * 32 + lane;
+        const uint32_t taddr = tmem_base + lane_addr + static_cast<uint32_t>(MSUB == 2 ? h : acc) * C::kAccStride;
+#pragma unroll 1
+        for (int ch = 0; ch < kChunks; ch += 2) {
+          float v[32];
+          tmem_ld16(taddr + ch * 16, *reinterpret_cast<float(*)[16]>(v));
+          if (ch + 1 < kChunks) tmem_ld16(taddr + (ch + 1) * 16, *reinterpret_cast<float(*)[16]>(v + 16));
+          tmem_ld_wait();
+          if (h == MSUB - 1 && ch + 2 >= kChunks) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[acc]);
+          }
+          const int n0 = n_blk * BN + ch * 16;
+          const int width = (ch + 1 < kChunks) ? 32 : 16;
+          if (m < p.M && n0 < p.N)
+            store_row<32>(out + static_cast<int64_t>(m) * p.ldo + n0, v, min(p.N - n0, width), vec_ok && width == 32);
         }
-        const int n0 = n_blk * BN + ch * 16;
-        const int width = (ch + 1 < kChunks) ? 32 : 16;
-        if (m < p.M && n0 < p.N) store_row<32>(out + static_cast<int64_t>(m) * p.ldo + n0, v, min(p.N - n0, width), vec_ok && width == 32);
       }
       acc_phase[acc] ^= 1u;
       if (C::kNumAcc == 2) acc ^= 1;
@@ -342,10 +367,10 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
 }
 
-template <int BN, typename OutT>
+template <int BN, int MSUB, typename OutT>
 int launch_mx(const CUtensorMap& ma, const CUtensorMap& mb, const MxParams& p, cudaStream_t stream) {
-  using C = MxCfg<BN>;
-  auto kern = gemm_mx_kernel<BN, OutT>;
+  using C = MxCfg<BN, MSUB>;
+  auto kern = gemm_mx_kernel<BN, MSUB, OutT>;
   static bool attr_set[64] = {false};
   int dev = 0;
   B200_CUDA_TRY(cudaGetDevice(&dev));
@@ -353,24 +378,24 @@ int launch_mx(const CUtensorMap& ma, const CUtensorMap& mb, const MxParams& p, c
     B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem));
     attr_set[dev & 63] = true;
   }
-  const long long tiles = static_cast<long long>((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const long long tiles = static_cast<long long>((p.M + BM * MSUB - 1) / (BM * MSUB)) * ((p.N + BN - 1) / BN);
   const int grid = tiles < sm_count() ? static_cast<int>(tiles) : sm_count();
   kern<<<grid, kThreadsMx, C::kSmem, stream>>>(ma, mb, p);
   B200_CUDA_TRY(cudaGetLastError());
   return B200_OK;
 }
 
-template <int BN>
+template <int BN, int MSUB>
 int launch_mx_dtype(const void* a, int64_t lda, const void* b, int64_t ldb, const MxParams& p, cudaStream_t st) {
   CUtensorMap ma, mb;
-  int rc = make_map_u8_2d(&ma, a, p.M, p.K, lda, BM);
+  int rc = make_map_u8_2d(&ma, a, p.M, p.K, lda, BM * MSUB);
   if (rc != B200_OK) return rc;
   rc = make_map_u8_2d(&mb, b, p.N, p.K, ldb, BN);
   if (rc != B200_OK) return rc;
   switch (p.out_dtype) {
-    case B200_DT_BF16: return launch_mx<BN, __nv_bfloat16>(ma, mb, p, st);
-    case B200_DT_F16: return launch_mx<BN, __half>(ma, mb, p, st);
-    default: return launch_mx<BN, float>(ma, mb, p, st);
+    case B200_DT_BF16: return launch_mx<BN, MSUB, __nv_bfloat16>(ma, mb, p, st);
+    case B200_DT_F16: return launch_mx<BN, MSUB, __half>(ma, mb, p, st);
+    default: return launch_mx<BN, MSUB, float>(ma, mb, p, st);
   }
 }
 
@@ -407,8 +432,13 @@ extern "C" int b200_fp8_blockwise_scaled_mm_pow2(const void* a, int64_t lda, con
   p.status = gemm_status_ptr();
   if (!p.status) return B200_ERR_CUDA;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // 240-wide tiles (two accumulators, read-out overlapped with the next tile's MMAs); the test hook's value 256
-  // selects the single-accumulator 256-wide form
-  if (g_force_block_n == 256) return launch_mx_dtype<256>(a, lda, b, ldb, p, st);
-  return launch_mx_dtype<240>(a, lda, b, ldb, p, st);
+  // Tile choice.  Measured (us; 4096 x 36864 x 7168 / 4096 x 7168 x 18432 / 16384 x 7168 x 18432): 128 x 256 tiles
+  // 875 / 491 / 1813, 256 x 240 tiles 879 / 479 / 1801, 128 x 240 tiles (two accumulators) 940 / 502 / 1948.  The
+  // two-half tile pays off on long K (fewer, longer tiles amortise its unoverlapped read-out); the 128 x 240 tile
+  // never did and is reachable only through the test hook (values 256 / 240 / 2240 select a tile directly).
+  if (g_force_block_n == 256) return launch_mx_dtype<256, 1>(a, lda, b, ldb, p, st);
+  if (g_force_block_n == 240) return launch_mx_dtype<240, 1>(a, lda, b, ldb, p, st);
+  if (g_force_block_n == 2240) return launch_mx_dtype<240, 2>(a, lda, b, ldb, p, st);
+  if (M >= 2048 && K >= 12288) return launch_mx_dtype<240, 2>(a, lda, b, ldb, p, st);
+  return launch_mx_dtype<256, 1>(a, lda, b, ldb, p, st);
 }

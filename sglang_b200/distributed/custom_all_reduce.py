@@ -58,11 +58,14 @@ class SymmetricAllReduce:
         self.nbytes = (int(max_bytes) + granule - 1) // granule * granule
         self._buf = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=self.device)
         self._hdl = symm_mem.rendezvous(self._buf, self.group)
-        self._peer_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in self._hdl.buffer_ptrs])
+        # The handle's pointers address the start of the symmetric ALLOCATION on every rank; the tensor may sit at
+        # an offset inside it (the same offset on every rank).
+        self.base_offset = int(self._buf.data_ptr()) - int(self._hdl.buffer_ptrs[self.rank])
+        self._peer_ptrs = (ctypes.c_void_p * self.world)(*[int(p) + self.base_offset for p in self._hdl.buffer_ptrs])
         self._signal_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in self._hdl.signal_pad_ptrs])
         mc = int(self._hdl.multicast_ptr) if use_multicast else 0
         self.multicast = mc != 0
-        self._mc = ctypes.c_void_p(mc if mc else None)
+        self._mc = ctypes.c_void_p(mc + self.base_offset if mc else None)
         self._status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.num_blocks = int(num_blocks)
         self._hdl.barrier()   # every rank's flags are zero before the first kernel touches them

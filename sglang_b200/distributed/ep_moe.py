@@ -75,7 +75,8 @@ class _NvlinkExchange:
         self.buf = symm_mem.empty(int(nbytes), dtype=torch.uint8, device=device)
         self.buf.zero_()
         self.hdl = symm_mem.rendezvous(self.buf, group)
-        self.peer_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in self.hdl.buffer_ptrs])
+        base_offset = int(self.buf.data_ptr()) - int(self.hdl.buffer_ptrs[self.rank])   # tensor inside the allocation
+        self.peer_ptrs = (ctypes.c_void_p * self.world)(*[int(p) + base_offset for p in self.hdl.buffer_ptrs])
         self.signal_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in self.hdl.signal_pad_ptrs])
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self.pos = torch.empty(self.max_slots, dtype=torch.int32, device=device)

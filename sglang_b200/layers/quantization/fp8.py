@@ -21,7 +21,8 @@ from typing import Any, Dict, List, Optional
 
 import torch
 
-from .fp8_utils import dispatch_w8a8_block_fp8_linear
+from .fp8_utils import (deepgemm_w8a8_block_fp8_linear_with_fallback, dispatch_w8a8_block_fp8_linear,
+                        requant_weight_ue8m0_inplace)
 
 ACTIVATION_SCHEMES = ["static", "dynamic"]
 FP8 = torch.float8_e4m3fn
@@ -95,10 +96,15 @@ def _require_block_quant(cfg: Fp8Config) -> None:
 class Fp8LinearMethod:
     """Linear method for block-quantised FP8 (fp8.py:187-488)."""
 
-    def __init__(self, quant_config: Fp8Config):
+    def __init__(self, quant_config: Fp8Config, scale_ue8m0: bool = False):
+        """scale_ue8m0: the reference's DeepGEMM mode with power-of-two scales, its default on Blackwell
+        (DEEPGEMM_SCALE_UE8M0; fp8.py:345-357 re-quantises the weights after loading, fp8_utils.py:215-258 is the
+        linear): weights get power-of-two block scales, activations are quantised with packed UE8M0 scales, and
+        the product runs on the tensor core's block-scaling path."""
         _require_block_quant(quant_config)
         self.quant_config = quant_config
         self.block_quant = True
+        self.scale_ue8m0 = bool(scale_ue8m0)
         self.w8a8_block_fp8_linear = dispatch_w8a8_block_fp8_linear()
 
     def create_weights(self, layer: torch.nn.Module, input_size_per_partition: int, output_partition_sizes: List[int],
@@ -138,8 +144,16 @@ class Fp8LinearMethod:
         """Block-quantised weights are used as loaded (fp8.py:334-358); only the wrappers are renewed."""
         layer.weight = torch.nn.Parameter(layer.weight.data, requires_grad=False)
         layer.weight_scale_inv = torch.nn.Parameter(layer.weight_scale_inv.data, requires_grad=False)
+        if self.scale_ue8m0 and layer.weight.shape[0] % 128 == 0 and layer.weight.shape[1] % 128 == 0:
+            requant_weight_ue8m0_inplace(layer.weight, layer.weight_scale_inv, self.quant_config.weight_block_size)
+            layer.weight_scale_is_ue8m0 = True
 
     def apply(self, layer: torch.nn.Module, x: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if getattr(layer, "weight_scale_is_ue8m0", False):
+            return deepgemm_w8a8_block_fp8_linear_with_fallback(
+                input=x, weight=layer.weight, block_size=self.quant_config.weight_block_size,
+                weight_scale=layer.weight_scale_inv, input_scale=None, bias=bias, scale_ue8m0=True,
+                weight_scale_ue8m0=True)
         return self.w8a8_block_fp8_linear(input=x, weight=layer.weight, block_size=self.quant_config.weight_block_size,
                                           weight_scale=layer.weight_scale_inv, input_scale=None, bias=bias)
 

@@ -423,7 +423,7 @@ def test_power_of_two_scales_on_the_block_scaling_mma(M, N, K):
     from sglang_b200 import _lib
     ref32 = O.block_fp8_matmul_fp32(q_ref, wq, s_ref, ws)
     soft = w8a8_block_fp8_matmul_deepgemm(q, wq.cuda(), s_packed, ws.cuda(), [128, 128], torch.bfloat16).cpu()
-    for tile_width in (0, 256):     # 0: the 240-wide tile with two accumulators; 256: one accumulator
+    for tile_width in (0, 240, 2240):     # 128 x 256 (one accumulator), 128 x 240 (two), 256 x 240 (two row halves)
         _lib.lib().b200_debug_force_block_n(tile_width)
         try:
             out = w8a8_block_fp8_matmul_deepgemm(q, wq.cuda(), s_packed, ws.cuda(), [128, 128], torch.bfloat16,
@@ -433,6 +433,33 @@ def test_power_of_two_scales_on_the_block_scaling_mma(M, N, K):
             _lib.lib().b200_debug_force_block_n(0)
         assert O.rel_l2(out.float(), ref32.to(torch.bfloat16).float()) <= TOL, tile_width
         assert O.rel_l2(out.float(), soft.float()) <= TOL, tile_width
+
+
+def test_fp8_linear_method_ue8m0_mode():
+    """Fp8LinearMethod(scale_ue8m0=True): the weights are re-quantised to power-of-two block scales after loading
+    (the arithmetic of the reference's requant_weight_ue8m0, pinned here by the oracle's per_block_quant_mxfp8 on
+    the dequantised weight) and apply() runs the block-scaling MMA; against the oracle on the re-quantised weight."""
+    from sglang_b200.layers.quantization.fp8 import Fp8Config, Fp8LinearMethod
+    cfg = Fp8Config.from_config({"quant_method": "fp8", "activation_scheme": "dynamic", "weight_block_size": [128, 128]})
+    method = Fp8LinearMethod(cfg, scale_ue8m0=True)
+    layer = torch.nn.Module()
+    N, K, M = 512, 1024, 96
+    method.create_weights(layer, K, [N], K, N, torch.bfloat16, tp_size=1, device="cuda")
+    wq, ws = O.gen_weight(N, K, seed=51)
+    layer.weight.data.copy_(wq.cuda())
+    layer.weight_scale_inv.data.copy_(ws.cuda())
+    method.process_weights_after_loading(layer)
+    w_deq = (wq.float() * ws.repeat_interleave(128, 0).repeat_interleave(128, 1)).to(torch.bfloat16)
+    wq2, ws2 = O.per_block_quant_mxfp8(w_deq)
+    assert same_bits(layer.weight.data.cpu(), wq2) and torch.equal(layer.weight_scale_inv.data.cpu(), ws2)
+    assert bool((torch.log2(ws2) == torch.log2(ws2).round()).all())
+    x = O.gen_activation(M, K, seed=52)
+    bias = torch.randn(N, generator=torch.Generator().manual_seed(53)).to(torch.bfloat16)
+    out = method.apply(layer, x.cuda(), bias.cuda()).cpu()
+    q_ref, s_ref, _ = O.quant_group_fp8_ue8m0_cuda_semantics(x, 128)
+    ref = O.block_fp8_matmul_fp32(q_ref, wq2, s_ref, ws2).to(torch.bfloat16) + bias
+    assert O.rel_l2(out.float(), ref.float()) <= TOL
+    _status_ok()
 
 
 def test_deepgemm_shaped_linear():

@@ -202,7 +202,8 @@ def test_fused_moe_full_benchmark_size_256_experts_4096_tokens():
         # fp32 restatement on the GPU, expert by expert
         def quant(t_):
             tf = t_.float().view(t_.shape[0], -1, 128)
-            s_ = tf.abs().amax(-1).clamp(min=1e-10) / 448.0
+            amax_ = tf.abs().amax(-1).clamp(min=1e-10)
+            s_ = amax_ / torch.full_like(amax_, 448.0)   # tensor / tensor: an IEEE division on CUDA too
             return (tf / s_.unsqueeze(-1)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).view(t_.shape), s_
         xq, xs = quant(x)
         ref = torch.zeros(m, H, device=dev)

@@ -163,7 +163,8 @@ def test_largest_benchmark_size_m65536_every_element():
     assert same_bits(q[rows.cuda()].cpu(), q_ref) and same_bits(s[rows.cuda()].contiguous().cpu(), s_ref)
     for r0 in range(0, M, 8192):
         xf = x[r0:r0 + 8192].float().view(8192, K // 128, 128)
-        s_t = xf.abs().amax(-1).clamp(min=1e-10) / 448.0
+        amax_t = xf.abs().amax(-1).clamp(min=1e-10)
+        s_t = amax_t / torch.full_like(amax_t, 448.0)   # tensor / tensor: an IEEE division (a Python-scalar divisor becomes a reciprocal multiply on CUDA)
         q_t = (xf / s_t.unsqueeze(-1)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).view(8192, K)
         assert same_bits(q_rm[r0:r0 + 8192], q_t) and same_bits(s_rm[r0:r0 + 8192], s_t), r0
         if r0 == 0:   # the restatement itself against the oracle
