@@ -480,11 +480,23 @@ def moe_config4_single(dev, pk, steps=5):
     flops = 2.0 * tokens * topk * (2 * I * H + H * I)
     wbytes = float(E) * (2 * I * H + H * I)
     floor_ms = wbytes / (pk["hbm_gbs"] * 1e9) * 1e3
+    # the same layer with power-of-two scales on both sides (the reference's DeepGEMM expert path on Blackwell):
+    # the codes stay, the drawn weight scales are rounded up to powers of two
+    from sglang_b200.layers.moe.cutlass_moe import fused_experts_block_fp8_ue8m0
+    w13s.copy_(torch.exp2(torch.ceil(torch.log2(w13s))))
+    w2s.copy_(torch.exp2(torch.ceil(torch.log2(w2s))))
+    ms2, g_ = time_graph(lambda: fused_experts_block_fp8_ue8m0(x, w13, w2, w13s, w2s, tw, ti), steps,
+                         torch.cuda.synchronize)
+    g_.reset()
     del w13, w2, w13s, w2s
     torch.cuda.empty_cache()
     return {"workload": "deepseek_v3_moe_block_fp8(256 experts, top-8, 4096 tokens, hidden 7168, intermediate 2048)",
             "ms": ms, "tflops": flops / (ms * 1e-3) / 1e12, "weight_gbs": wbytes / (ms * 1e-3) / 1e9,
-            "weight_read_floor_ms": floor_ms, "frac_of_floor": floor_ms / ms}
+            "weight_read_floor_ms": floor_ms, "frac_of_floor": floor_ms / ms,
+            "ue8m0_path": {"kernel": "gemm_mx_kernel<grouped> (tcgen05.mma kind::mxf8f6f4.block_scale), power-of-two "
+                                     "activation and weight scales",
+                           "ms": ms2, "tflops": flops / (ms2 * 1e-3) / 1e12, "weight_gbs": wbytes / (ms2 * 1e-3) / 1e9,
+                           "frac_of_floor": floor_ms / ms2}}
 
 
 def moe_config4_ep(dev, world, rank, steps=5):
@@ -649,17 +661,25 @@ def run_gpu_arm(args):
         torch.cuda.synchronize()
 
     t_start = time.time()
+    ar = None
+
+    snaps = []
 
     def dbg(msg):
+        if os.environ.get("B200_BENCH_TRACE") and ar is not None:
+            # stage marker without a host synchronisation: a stream-ordered copy of the all-reduce status word
+            h_ = torch.empty(1, dtype=torch.int32).pin_memory()
+            h_.copy_(ar._status, non_blocking=True)
+            snaps.append((msg, h_))
         if os.environ.get("B200_BENCH_DEBUG"):
             torch.cuda.synchronize()
-            print(f"[bench r{rank} +{time.time() - t_start:.2f}s] {msg}", file=sys.stderr, flush=True)
+            st_ = f" all-reduce status {int(ar._status.item())}" if ar is not None else ""
+            print(f"[bench r{rank} +{time.time() - t_start:.2f}s] {msg}{st_}", file=sys.stderr, flush=True)
 
     # Weights are quantised once on the FULL matrix (same seed on every rank) and sharded by the product's
     # parallel linears, so the tensor-parallel result is comparable with the unsharded one.
     w1q, w1s = gen_weight_device(INTER2, HIDDEN, 100, dev)
     w2q, w2s = gen_weight_device(HIDDEN, INTER, 200, dev)
-    ar = None
     if world > 1 and args.allreduce == "custom":
         from sglang_b200.distributed.custom_all_reduce import SymmetricAllReduce
         ar = SymmetricAllReduce(max(M_TOKENS, 8192) * 8192 * 2)
@@ -728,6 +748,7 @@ def run_gpu_arm(args):
             t = torch.tensor([ms_c], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             chunk_ms[str(c)] = round(float(t.item()), 4)
+            dbg(f"row chunks {c}: {chunk_ms[str(c)]} ms")
             if best is None or float(t.item()) < best[0]:
                 best = (float(t.item()), c)
         chunks_used = best[1]
@@ -744,19 +765,34 @@ def run_gpu_arm(args):
     sampler.mark("burst0")
     ms, graph = time_graph(step, args.steps, barrier)
     sampler.mark("burst1")
+    dbg("timed region done")
     # ---- the same step back to back for >= 2 s: the clocks settle under the power cap
-    reps = max(args.steps, int(2000.0 / max(ms, 1e-3)) + 1)
+    ms_all = torch.tensor([ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(ms_all, op=dist.ReduceOp.MAX)      # every rank must replay the SAME number of steps
+    reps = max(args.steps, int(2000.0 / max(float(ms_all.item()), 1e-3)) + 1)
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     sampler.mark("sus0")
     t0.record()
-    for _ in range(reps):
+    trace_replays = bool(os.environ.get("B200_BENCH_TRACE"))
+    worst, worst_i, tprev = 0.0, -1, time.perf_counter()
+    for i_ in range(reps):
         graph.replay()
+        if trace_replays:
+            tn = time.perf_counter()
+            if tn - tprev > worst:
+                worst, worst_i = tn - tprev, i_
+            tprev = tn
     t1.record()
     barrier()
+    if trace_replays:
+        print(f"[bench r{rank}] sustained loop: {reps} replays, longest host-side gap between two launches "
+              f"{worst * 1e3:.1f} ms at replay {worst_i}, device time {t0.elapsed_time(t1):.1f} ms", file=sys.stderr, flush=True)
     sampler.mark("sus1")
     sustained_ms = t0.elapsed_time(t1) / reps
     graph.reset()
+    dbg("sustained loop done")
 
     # ---- per-kernel times: a separate eager pass with events around each call (one GPU's share of the step)
     per_kernel = {}
@@ -788,6 +824,7 @@ def run_gpu_arm(args):
         us, g_ = time_graph(lambda: row._reduce(y2b), 5, barrier)
         g_.reset()
         per_kernel["all_reduce_[4096,7168]_bf16"] = us
+    dbg("per-kernel pass done")
 
     # ---- timed region 2: end to end through the public linear call with host buffers.  Every step copies its
     # activations in from pinned host memory and its results back; the three legs (copy in, compute, copy out) of
@@ -862,12 +899,16 @@ def run_gpu_arm(args):
     t3.record()
     barrier()
     e2e_ms = t2.elapsed_time(t3) / e2e_steps
+    dbg("end-to-end region done")
 
     times = torch.tensor([ms, e2e_ms, sustained_ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms, e2e_ms, sustained_ms = float(times[0]), float(times[1]), float(times[2])
     status_ok = gemm_status_ok()
+    if snaps:
+        print(f"[bench r{rank}] all-reduce status after each stage: " + "; ".join(f"{m_}={int(h_[0])}" for m_, h_ in snaps),
+              file=sys.stderr, flush=True)
     if ar is not None:
         ar.check()
 
@@ -1015,6 +1056,11 @@ def run_kernel_case(args):
             w13, w2, w13s, w2s = moe_weights(dev, list(range(E)), 5000)
             x, tw, ti = moe_routing(dev, m, E=E)
 
+            if args.scales == "pow2":
+                from sglang_b200.layers.moe.cutlass_moe import fused_experts_block_fp8_ue8m0 as fused_experts_block_fp8
+                w13s.copy_(torch.exp2(torch.ceil(torch.log2(w13s))))
+                w2s.copy_(torch.exp2(torch.ceil(torch.log2(w2s))))
+
             def fn():
                 return fused_experts_block_fp8(x, w13, w2, w13s, w2s, tw, ti)
             work, unit, peak = 2.0 * m * topk * (2 * I * H + H * I) / 1e12, "TFLOP/s", 2.0 * pk["bf16_burst"]
@@ -1043,14 +1089,28 @@ def run_kernel_case(args):
             ncopy = 1 if m > 512 else max(2, int(300e6 // (n * k)) + 1)
             copies = [gen_weight_device(n, k, 1 + c, dev) for c in range(ncopy)]
             x = torch.randn((m, k), generator=g, device=dev).to(torch.bfloat16)
-            xq, xs_ = sglang_per_token_group_quant_fp8(x, 128, column_major_scales=True)
-            views = [(wq.T, ws.T) for wq, ws in copies]
             it = [0]
+            if args.scales == "pow2":
+                # power-of-two scales on both sides: the block-scaling MMA (gemm_mx.cu)
+                from sglang_b200.layers.quantization.fp8_kernel import w8a8_block_fp8_matmul_deepgemm
+                from sglang_b200.layers.quantization.fp8_utils import requant_weight_ue8m0
+                copies = [requant_weight_ue8m0(wq, ws, [128, 128]) for wq, ws in copies]
+                xq, xs_ = sglang_per_token_group_quant_fp8(x, 128, column_major_scales=True, scale_tma_aligned=True,
+                                                           scale_ue8m0=True)
 
-            def fn():
-                it[0] += 1
-                w_t, ws_t = views[it[0] % ncopy]
-                return fp8_blockwise_scaled_mm(xq, w_t, xs_, ws_t, torch.bfloat16)
+                def fn():
+                    it[0] += 1
+                    wq, ws = copies[it[0] % ncopy]
+                    return w8a8_block_fp8_matmul_deepgemm(xq, wq, xs_, ws, [128, 128], torch.bfloat16,
+                                                          weight_scale_ue8m0=True)
+            else:
+                xq, xs_ = sglang_per_token_group_quant_fp8(x, 128, column_major_scales=True)
+                views = [(wq.T, ws.T) for wq, ws in copies]
+
+                def fn():
+                    it[0] += 1
+                    w_t, ws_t = views[it[0] % ncopy]
+                    return fp8_blockwise_scaled_mm(xq, w_t, xs_, ws_t, torch.bfloat16)
             work, unit, peak = 2.0 * m * n * k / 1e12, "TFLOP/s", 2.0 * pk["bf16_burst"]
         for _ in range(max(3, args.warmup)):
             fn()
@@ -1080,7 +1140,8 @@ def run_kernel_case(args):
             b.record()
         torch.cuda.synchronize()
         sec = a.elapsed_time(b) / args.steps * 1e-3
-        rec = {"kernel": args.kernel if args.kernel != "gemm" else f"gemm N={args.n} K={args.k}", "M": m,
+        rec = {"kernel": (args.kernel if args.kernel != "gemm" else f"gemm N={args.n} K={args.k}") +
+               (" (power-of-two scales)" if args.scales == "pow2" and args.kernel != "quant" else ""), "M": m,
                "us": sec * 1e6, "achieved": work / sec, "unit": unit,
                "frac_of_measured_peak": work / sec / peak, "graph": bool(args.graph)}
         if args.kernel == "moe":
@@ -1096,6 +1157,8 @@ def main():
     ap.add_argument("--n", type=int, default=0, help="--kernel gemm: output features (multiple of 128)")
     ap.add_argument("--k", type=int, default=0, help="--kernel gemm: input features (multiple of 128)")
     ap.add_argument("--m", default="4096", help="token count(s) for --kernel, comma separated")
+    ap.add_argument("--scales", default="fp32", choices=["fp32", "pow2"],
+                    help="--kernel gemm*: fp32 scales (promotion kernels) or power-of-two scales (block-scaling MMA)")
     ap.add_argument("--experts", type=int, default=256,
                     help="--kernel moe: experts held on this GPU (256 = whole layer, 32 = one rank of 8)")
     ap.add_argument("--tp-chunks", type=int, default=0, choices=[0, 1, 2, 4, 8],

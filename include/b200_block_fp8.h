@@ -99,6 +99,30 @@ int b200_silu_mul_per_token_group_quant_fp8(const void* x, int x_dtype, void* q,
                                             float fp8_max, void* stream);
 
 /*
+ * The same fusion with power-of-two scales in the packed layout of b200_per_token_group_quant_fp8_ue8m0: the input
+ * of the second expert GEMM on the block-scaling path.  Bit-identical to b200_silu_and_mul followed by
+ * b200_per_token_group_quant_fp8_ue8m0.  Replaces silu_and_mul + sglang_per_token_group_quant_fp8(scale_ue8m0=True)
+ * at python/sglang/srt/layers/moe/ep_moe/layer.py:606-628.
+ */
+int b200_silu_mul_per_token_group_quant_fp8_ue8m0(const void* x, int x_dtype, void* q, uint32_t* s_packed, int64_t M,
+                                                  int64_t K, int64_t s_stride_pack, float eps, float fp8_min,
+                                                  float fp8_max, void* stream);
+
+/*
+ * Per-token-group (128) quantisation with a row gather: row r of q / s = the quantisation of row src_rows[r] of
+ * x [x_rows, K] (indices clamped into the rows of x).  Same bits as quantising x and gathering codes and scales
+ * afterwards.  scale_ue8m0 == 0: fp32 scales, element (r, g) at s[r * s_stride_row + g * s_stride_grp];
+ * != 0: s is the packed exponent tensor of b200_per_token_group_quant_fp8_ue8m0 with s_stride_grp the stride between
+ * packed words (>= R) and s_stride_row ignored.
+ * Replaces: sglang_per_token_group_quant_fp8 + shuffle_rows (codes) + shuffle_rows (scales) at
+ * python/sglang/srt/layers/moe/cutlass_moe.py:141-150; the quantise-then-ep_scatter pair of the reference's DeepGEMM
+ * expert path (python/sglang/srt/layers/moe/ep_moe/layer.py:575-590).
+ */
+int b200_gather_per_token_group_quant_fp8(const void* x, int x_dtype, int64_t x_rows, const int32_t* src_rows, void* q,
+                                          void* s, int64_t R, int64_t K, int64_t s_stride_row, int64_t s_stride_grp,
+                                          int scale_ue8m0, float eps, float fp8_min, float fp8_max, void* stream);
+
+/*
  * Dense block-scaled FP8 GEMM:  out[m,n] = cast( sum_kb ( sum_{k in kb} a[m,k]*b[n,k] )
  *                                               * sa[m,kb] * sb[n/128,kb] ),  fp32 accumulation.
  * Replaces: fp8_blockwise_scaled_mm
@@ -182,6 +206,32 @@ int b200_fp8_blockwise_scaled_mm_pow2(const void* a, int64_t lda, const void* b,
                                       int64_t M, int64_t N, int64_t K, void* stream);
 
 /*
+ * Grouped form of the block-scaling product, driven by a device-resident problem table: problem i multiplies rows
+ * [problem_offsets[i], problem_offsets[i] + problem_rows[i * problem_rows_stride]) of a [total_rows, K] with weight
+ * slice e = problem_experts[i] (i itself when problem_experts is NULL; a slice outside [0, num_weight_experts)
+ * skips the problem) of b [num_weight_experts * N, K]; weight scales sb_pow2[e * sb_stride_e + (n/128) * sb_stride_n +
+ * kb * sb_stride_g] are fp32 powers of two.  Packed activation exponents: word (row, g4) at
+ * sa_packed[g4 * sa_stride_pack + row * sa_stride_m] with `row` the global row of a (sa_stride_problem < 0), or at
+ * sa_packed[i * sa_stride_problem + g4 * sa_stride_pack + (row - problem_offsets[i]) * sa_stride_m] (>= 0).
+ * Rows outside every problem are neither computed nor written.  At most 2048 problems; N % 128 == 0, K % 128 == 0.
+ * Offsets and counts are clamped into the row range on the device.  Covers, with nothing read on the host:
+ *   - the MoE expert GEMMs over rows packed without padding (problem_offsets / problem_rows = expert_offsets /
+ *     column 0 of problem_sizes as b200_moe_prepare writes them),
+ *   - DeepGEMM's CONTIGUOUS layout (one problem per 128-row block, problem_experts[i] = m_indices[128 * i]),
+ *   - DeepGEMM's MASKED layout (problem i = expert i, problem_offsets[i] = i * max_m, problem_rows = masked_m,
+ *     sa_stride_problem = the expert stride of the packed scales).
+ * Replaces: deep_gemm.m_grouped_fp8_gemm_nt_contiguous / fp8_m_grouped_gemm_nt_masked behind
+ * python/sglang/srt/layers/quantization/deep_gemm_wrapper/entrypoint.py:39-75 (callers
+ * python/sglang/srt/layers/moe/ep_moe/layer.py:246-253,302-309,603-637).
+ */
+int b200_fp8_blockwise_scaled_grouped_mm_pow2(
+    const void* a, int64_t lda, int64_t total_rows, const void* b, int64_t ldb, const uint32_t* sa_packed,
+    int64_t sa_stride_m, int64_t sa_stride_pack, int64_t sa_stride_problem, const float* sb_pow2, int64_t sb_stride_e,
+    int64_t sb_stride_n, int64_t sb_stride_g, void* out, int64_t ldo, int out_dtype, const int32_t* problem_offsets,
+    const int32_t* problem_rows, int64_t problem_rows_stride, const int32_t* problem_experts, int num_problems,
+    int num_weight_experts, int64_t N, int64_t K, void* stream);
+
+/*
  * Grouped (per-expert) block-scaled FP8 GEMM: for every expert e,
  *   out[off_e : off_e + m_e, :] = blockscaled( a[off_e : off_e + m_e, :], b[e] )   (same math as above)
  * with off_e = expert_offsets[e], m_e = problem_sizes[3*e] read ON THE DEVICE (no host sync).
@@ -262,6 +312,16 @@ int b200_moe_prepare_noalloc(const int32_t* topk_ids, int64_t num_tokens, int to
                              int32_t* problem_sizes2, int32_t* input_permutation, int32_t* output_permutation,
                              void* stream);
 
+/*
+ * Row gather of PACKED power-of-two scales (the layout of b200_per_token_group_quant_fp8_ue8m0: word w of row r at
+ * [w * stride_pack + r]): output word (w, r) = input word (w, dst2src_map[r]), indices clamped into the source rows.
+ * The companion of b200_shuffle_rows for the scales of the block-scaling expert path (the reference scatters codes
+ * and scales together in ep_scatter, python/sglang/srt/layers/moe/ep_moe/kernels.py).
+ */
+int b200_shuffle_packed_scales(const uint32_t* input, int64_t input_stride_pack, int64_t num_src_rows,
+                               const int32_t* dst2src_map, uint32_t* output, int64_t output_stride_pack,
+                               int64_t num_dst_rows, int words_per_row, void* stream);
+
 /* output[d, :] = input[dst2src_map[d], :] for rows of row_bytes bytes (128-bit copies when rows and
  * bases are 16-byte aligned, narrower ones otherwise).
  * Replaces: shuffle_rows (sgl-kernel/csrc/moe/prepare_moe_input.cu:169-256, schema :204-205). */
@@ -327,7 +387,7 @@ int b200_topk_softmax(const void* gating_output, int dtype, int64_t row_stride, 
  *                 bytes % (16 * world_size) == 0.
  *   one_shot = 1: into `out` (local memory, bytes long); bytes % 16 == 0.  For small buffers.
  * Every element is the fp32 sum over ranks rounded once: identical bits on all ranks, run to run.
- * The kernels of the ranks wait for one another at flag barriers (bounded, about five seconds): every rank
+ * The kernels of the ranks wait for one another at flag barriers (bounded, about ten seconds): every rank
  * must call with the same arguments, in the same order, and nothing else may use the flag words
  * [flag_base_words, + b200_allreduce_flag_words(world_size)) of the signal pads meanwhile.  *status
  * (device memory, zero before the first call) receives a non-zero code if a peer never arrived; the
@@ -366,7 +426,7 @@ int b200_allreduce_max_blocks(void);
  * b200_ep_combine: rows [*, hidden] (dtype bf16 / fp16) holds the expert output of received row r at row
  *   row_of[r] (r itself when row_of is NULL); each is stored into its source rank's return buffer at the row's
  *   source slot; ends with a flag barrier (a different flag_base_words than the dispatch's).
- * The kernels of the ranks wait for one another (bounded, about five seconds): every rank must make the same
+ * The kernels of the ranks wait for one another (bounded, about ten seconds): every rank must make the same
  * calls in the same order; *status (device word, zero before the first call) receives 32 / 33 if a peer
  * never arrived.  Nothing on the host reads device data.
  */

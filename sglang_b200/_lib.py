@@ -51,6 +51,15 @@ _SIGNATURES = {
     "b200_fp8_blockwise_scaled_mm_pow2": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64,
                                                   c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int, c_int64,
                                                   c_int64, c_int64, c_void_p]),
+    "b200_fp8_blockwise_scaled_grouped_mm_pow2": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64,
+                                                          c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64,
+                                                          c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int64,
+                                                          c_void_p, c_int, c_int, c_int64, c_int64, c_void_p]),
+    "b200_silu_mul_per_token_group_quant_fp8_ue8m0": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64,
+                                                              c_int64, c_float, c_float, c_float, c_void_p]),
+    "b200_gather_per_token_group_quant_fp8": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_int64,
+                                                      c_int64, c_int64, c_int64, c_int, c_float, c_float, c_float,
+                                                      c_void_p]),
     "b200_gemm_device_status": (c_int, [ctypes.POINTER(c_int)]),
     "b200_gemm_poll_status": (c_int, [ctypes.POINTER(c_int)]),
     "b200_fp8_blockwise_scaled_grouped_mm": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64,
@@ -69,6 +78,8 @@ _SIGNATURES = {
                                     c_void_p]),
     "b200_moe_fused_gate_shared_experts": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int,
                                                    c_int, c_int, c_int, ctypes.c_double, c_void_p]),
+    "b200_shuffle_packed_scales": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_int,
+                                           c_void_p]),
     "b200_shuffle_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "b200_silu_and_mul": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
     "b200_apply_shuffle_mul_sum": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,

@@ -660,21 +660,35 @@ inline int forced_token_tile() {
 namespace b200 {
 namespace {
 
-// Which kernel a dense problem gets: up to 64 tokens the weight-streaming kernel (gemm_swapab.cu,
-// 128 weight rows x tokens per tile) measured 10-30 % faster on every DeepSeek-V3 projection; above
-// that the 128-token x 128/256-column tiles of this file.
-inline bool dense_uses_swapab(int64_t M) { return M <= 64; }
+// Which kernel a dense problem gets: up to 192 tokens the weight-streaming kernel (gemm_swapab.cu,
+// 128 weight rows x up to 64 tokens per tile).  Measured against this file's tiles on the DeepSeek-V3 and
+// Llama-3-70B projections: 10-30 % faster up to 64 tokens, 0-25 % faster for 65-192 (two or three token tiles per
+// weight tile, the second and third reading the weights from L2), slower from 256 on.
+inline bool dense_uses_swapab(int64_t M) { return M <= 192; }
+inline int dense_token_tile(int64_t M) { return M <= 32 ? 32 : 64; }
 
 // Split count for small M (up to 512 rows): when the output has too few tiles for the SMs, the k-blocks of
 // each tile are spread over several CTAs so that the weights stream through all SMs at once.
 int plan_split_k(int64_t M, int64_t N, int64_t K, int sms) {
   if (M > 4 * BLOCK_M || (N % 4) != 0) return 1;   // beyond 512 rows the tile count is never that small
   const int64_t m_blocks = (M + BLOCK_M - 1) / BLOCK_M;
-  const int64_t tiles = dense_uses_swapab(M) ? (N + 127) / 128 : m_blocks * ((N + 255) / 256);
+  const int64_t tt = dense_token_tile(M);
+  const int64_t tiles = dense_uses_swapab(M) ? ((M + tt - 1) / tt) * ((N + 127) / 128) : m_blocks * ((N + 255) / 256);
   const int64_t nkb = (K + BLOCK_K - 1) / BLOCK_K;
   // measured on DeepSeek-V3 shapes: below 32 k-blocks the launch and pipeline ramp dominate and the
   // extra reduce kernel costs more than the idle SMs
-  if (tiles * 2 > sms || nkb < 32) return 1;
+  if (nkb < 32) return 1;
+  if (tiles * 2 > sms) {
+    // More tiles than half the SMs.  The weight-streaming kernel with two or three token tiles per weight tile can
+    // still leave most of its last wave empty (DeepSeek-V3 down projection at 129-192 tokens: 168 tiles on 148 SMs;
+    // measured 63.9 us unsplit, 55.5 us split in two): split only to fill such a wave.
+    if (!dense_uses_swapab(M)) return 1;
+    auto fill = [sms](int64_t t) { return static_cast<double>(t) / static_cast<double>(((t + sms - 1) / sms) * sms); };
+    if (fill(tiles) >= 0.7) return 1;
+    for (int s2 = 2; s2 <= 4; ++s2)
+      if (nkb / s2 >= 8 && fill(tiles * s2) >= 0.75) return s2;
+    return 1;
+  }
   int64_t s = sms / tiles;
   if (s > nkb / 8) s = nkb / 8;  // at least eight k-blocks per CTA
   if (s > 16) s = 16;
@@ -749,7 +763,7 @@ int dense_mm(const void* a, int64_t lda, const void* b, int64_t ldb, const float
     split_k = plan_split_k(M, N, K, sm_count());
     if (split_k > 1 && (!workspace || !aligned16(workspace) || workspace_bytes < splitk_workspace_bytes(split_k, M, N)))
       split_k = 1;
-    if (split_k == 1 && M > BLOCK_M && g_force_block_n == 0 && workspace && aligned16(workspace)) {
+    if (split_k == 1 && M > BLOCK_M && !dense_uses_swapab(M) && g_force_block_n == 0 && workspace && aligned16(workspace)) {
       tail = plan_tail(M, N, K, dense_block_n(M, N, sm_count()), sm_count());
       if (tail.split_k > 1 && workspace_bytes < tail.bytes) tail = TailPlan();
     }
@@ -784,7 +798,7 @@ int dense_mm(const void* a, int64_t lda, const void* b, int64_t ldb, const float
   // waves of half-size tiles take as long), else 128 x 128.
   if (g_force_block_n == 3 || forced_token_tile() != 0 || (g_force_block_n == 0 && dense_uses_swapab(M))) {
     int tt = forced_token_tile();
-    if (tt == 0) tt = M <= 32 ? 32 : (M <= 64 ? 64 : 128);
+    if (tt == 0) tt = dense_token_tile(M);
     rc = launch_gemm_swapab(a, lda, M, b, ldb, N, p, false, tt, st);
     if (rc != B200_OK || p.split_k == 1) return rc;
     switch (out_dtype) {
@@ -861,7 +875,7 @@ extern "C" int b200_fp8_blockwise_scaled_mm_splitk_plan(int64_t M, int64_t N, in
   const int s = (M == 0 || N == 0) ? 1 : b200::plan_split_k(M, N, K, sms);
   *split_k = s;
   *workspace_bytes = s > 1 ? b200::splitk_workspace_bytes(s, M, N) : 0;
-  if (s == 1 && M > 128 && N > 0) {   // large M: split of the last, mostly empty wave of tiles
+  if (s == 1 && M > 128 && !b200::dense_uses_swapab(M) && N > 0) {   // large M: split of the last, mostly empty wave of tiles
     const b200::TailPlan t = b200::plan_tail(M, N, K, b200::dense_block_n(M, N, sms), sms);
     if (t.split_k > 1) {
       *split_k = t.split_k;
@@ -921,7 +935,11 @@ extern "C" int b200_fp8_blockwise_scaled_grouped_mm(const void* a, int64_t lda, 
     if (tt == 0) tt = avg_rows <= 20 ? 32 : 64;
     return launch_gemm_swapab(a, lda, total_rows, b, ldb, N * num_experts, p, true, tt, st);
   }
-  const int block_n = (N % 256 == 0 && g_force_block_n != 128) ? 256 : 128;
+  // Up to 256 rows per expert the 128-wide tile (four accumulators, twice as many tiles to balance over the SMs)
+  // measured faster than the 256-wide one: 256 experts x 128 rows, 1.92 / 1.18 ms against 2.29 / 1.28 ms for the
+  // two expert GEMMs of the DeepSeek-V3 layer.
+  const bool wide = N % 256 == 0 && g_force_block_n != 128 && (avg_rows > 256 || g_force_block_n == 256);
+  const int block_n = wide ? 256 : 128;
   CUtensorMap ma, mb;
   rc = make_map_u8_2d(&ma, a, total_rows, K, lda, BLOCK_M);
   if (rc != B200_OK) return rc;

@@ -68,6 +68,25 @@ struct MxParams {
   int M, N, K;
   int out_dtype;
   int* status;
+  // grouped form: problem i multiplies rows [offsets[i], offsets[i] + rows[i * rows_stride]) of A with weight slice
+  // experts[i] (i itself when experts is null): weight rows [e * N, (e + 1) * N), scales at sb + e * sb_stride_e.
+  const int* offsets;
+  const int* rows;
+  const int* experts;
+  int64_t rows_stride, sb_stride_e;
+  // packed activation exponents of problem i: indexed by the GLOBAL row of A (sa_stride_problem < 0; DeepGEMM's
+  // contiguous layout), or per problem by the row inside it at sa + i * sa_stride_problem (its masked layout)
+  int64_t sa_stride_problem;
+  int num_problems, num_weight_experts;
+  int prefetch_ahead;   // grouped: weight boxes requested into L2 this many k-blocks ahead of the shared-memory ring
+};
+
+constexpr int kMaxProblems = 2048;
+
+// One output tile: rows [row0, row0 + valid) of A / out, column block n_blk of weight slice e_w.
+struct MxTile {
+  int row0, valid, n_blk, e_w;
+  int64_t sa_base;   // word (row, g4) of the packed exponents sits at sa[sa_base + g4 * sa_stride_pack + row * sa_stride_m]
 };
 
 // Shared-memory descriptor of a scale-factor tile for tcgen05.cp: 32 rows x 16 bytes, rows contiguous, no
@@ -113,7 +132,43 @@ __device__ __forceinline__ void mx_tile_coords(int tile, int m_blocks, int n_blo
   n_blk = in_group / rows;
 }
 
-template <int BN, int MSUB, typename OutT>
+// Dense: groups of 32 row blocks x all column blocks.  Grouped: the row tiles of all problems laid end to end
+// (prefix table `tile_start`, built once per CTA), column blocks fastest, so the one or two row tiles of an expert
+// run at the same time on neighbouring SMs and its weights are fetched from HBM once.  Offsets and counts come from
+// device memory and are clamped into the row range: a table that does not match the buffers cannot send a load or a
+// store out of bounds.
+template <bool GROUPED, int TILE_M>
+__device__ __forceinline__ MxTile mx_get_tile(int tile, const MxParams& p, int m_blocks, int n_blocks,
+                                              const int* tile_start) {
+  MxTile t;
+  if constexpr (!GROUPED) {
+    int m_blk;
+    mx_tile_coords(tile, m_blocks, n_blocks, m_blk, t.n_blk);
+    t.row0 = m_blk * TILE_M;
+    t.valid = min(TILE_M, p.M - t.row0);
+    t.e_w = 0;
+    t.sa_base = 0;
+  } else {
+    const int vt = tile / n_blocks;
+    t.n_blk = tile - vt * n_blocks;
+    int lo = 0, hi = p.num_problems;            // last problem whose first tile is <= vt
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (tile_start[mid] <= vt) lo = mid; else hi = mid;
+    }
+    const int sub = vt - tile_start[lo];
+    const int rows = __ldg(p.rows + static_cast<int64_t>(lo) * p.rows_stride);
+    const int off = __ldg(p.offsets + lo);
+    t.row0 = min(max(off + sub * TILE_M, 0), p.M - 1);
+    t.sa_base = p.sa_stride_problem < 0 ? 0 : lo * p.sa_stride_problem - off * p.sa_stride_m;
+    t.valid = max(1, min(min(TILE_M, rows - sub * TILE_M), p.M - t.row0));
+    const int e = p.experts ? __ldg(p.experts + lo) : lo;
+    t.e_w = min(max(e, 0), p.num_weight_experts - 1);
+  }
+  return t;
+}
+
+template <int BN, int MSUB, bool GROUPED, typename OutT>
 __global__ void __launch_bounds__(kThreadsMx, 1)
 gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const MxParams p) {
   using C = MxCfg<BN, MSUB>;
@@ -140,7 +195,33 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int m_blocks = (p.M + kTileM - 1) / kTileM;
   const int n_blocks = (p.N + BN - 1) / BN;
   const int nkb = (p.K + BK - 1) / BK;
-  const int num_tiles = m_blocks * n_blocks;
+  __shared__ int tile_start[GROUPED ? kMaxProblems + 1 : 1];
+  if constexpr (GROUPED) {
+    // row tiles per problem (none for an empty problem or one whose weight slice does not exist) ...
+    for (int i = threadIdx.x; i < p.num_problems; i += kThreadsMx) {
+      const int rows = __ldg(p.rows + static_cast<int64_t>(i) * p.rows_stride);
+      const int e = p.experts ? __ldg(p.experts + i) : i;
+      tile_start[i + 1] = (rows > 0 && e >= 0 && e < p.num_weight_experts) ? (min(rows, p.M) + kTileM - 1) / kTileM : 0;
+    }
+    __syncthreads();
+    // ... and their running sum, by one warp
+    if (warp == 0) {
+      int carry = 0;
+      for (int base = 0; base < p.num_problems; base += 32) {
+        int v = (base + lane < p.num_problems) ? tile_start[base + lane + 1] : 0;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+          const int u = __shfl_up_sync(0xffffffffu, v, off);
+          if (lane >= off) v += u;
+        }
+        if (base + lane < p.num_problems) tile_start[base + lane + 1] = carry + v;
+        carry += __shfl_sync(0xffffffffu, v, 31);
+      }
+      if (lane == 0) tile_start[0] = 0;
+    }
+    __syncthreads();
+  }
+  const int num_tiles = GROUPED ? tile_start[p.num_problems] * n_blocks : m_blocks * n_blocks;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStagesMx; ++i) {
@@ -176,16 +257,45 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
+    // Grouped: every weight byte comes from HBM exactly once and the ring (4 stages, 192 KB) covers only ~2 us of
+    // latency at the rate one SM must sustain.  A second cursor runs `prefetch_ahead` k-blocks in front of the
+    // loads -- across tile boundaries -- and asks for the weight boxes in L2, so that the loads into shared memory
+    // find them there.
+    int pf_tile = blockIdx.x, pf_kb = 0, pf_row = 0;
+    bool pf_live = false;
+    auto pf_step = [&]() {
+      if (!pf_live) return;
+      if (elect_one()) tma_prefetch_l2_2d(&map_b, pf_kb * BK, pf_row);
+      __syncwarp();
+      if (++pf_kb == nkb) {
+        pf_kb = 0;
+        pf_tile += gridDim.x;
+        pf_live = pf_tile < num_tiles;
+        if (pf_live) {
+          const MxTile t = mx_get_tile<GROUPED, kTileM>(pf_tile, p, m_blocks, n_blocks, tile_start);
+          pf_row = t.e_w * p.N + t.n_blk * BN;
+        }
+      }
+    };
+    if constexpr (GROUPED) {
+      pf_live = p.prefetch_ahead > 0 && pf_tile < num_tiles;
+      if (pf_live) {
+        const MxTile t = mx_get_tile<GROUPED, kTileM>(pf_tile, p, m_blocks, n_blocks, tile_start);
+        pf_row = t.e_w * p.N + t.n_blk * BN;
+      }
+      for (int i = 0; i < p.prefetch_ahead; ++i) pf_step();
+    }
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-      int m_blk, n_blk;
-      mx_tile_coords(tile, m_blocks, n_blocks, m_blk, n_blk);
+      const MxTile t = mx_get_tile<GROUPED, kTileM>(tile, p, m_blocks, n_blocks, tile_start);
+      const int w_row0 = t.e_w * p.N + t.n_blk * BN;
       for (int kb = 0; kb < nkb; ++kb) {
         ok = mbar_wait_warp(&empty_bar[stage], phase ^ 1u, p.status, 41);
         if (!ok) break;
+        if constexpr (GROUPED) pf_step();
         if (elect_one()) {
           mbar_expect_tx(&full_bar[stage], C::kStageBytes);
-          tma_load_2d(smem_a + stage * kABytesMx, &map_a, &full_bar[stage], kb * BK, m_blk * kTileM);
-          tma_load_2d(smem_b + stage * C::kBBytes, &map_b, &full_bar[stage], kb * BK, n_blk * BN);
+          tma_load_2d(smem_a + stage * kABytesMx, &map_a, &full_bar[stage], kb * BK, t.row0);
+          tma_load_2d(smem_b + stage * C::kBBytes, &map_b, &full_bar[stage], kb * BK, w_row0);
         }
         __syncwarp();
         if (++stage == kStagesMx) { stage = 0; phase ^= 1u; }
@@ -276,22 +386,22 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint32_t sphase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-      int m_blk, n_blk;
-      mx_tile_coords(tile, m_blocks, n_blocks, m_blk, n_blk);
-      const int row0 = m_blk * kTileM;
+      const MxTile t = mx_get_tile<GROUPED, kTileM>(tile, p, m_blocks, n_blocks, tile_start);
+      const int row0 = t.row0, n_blk = t.n_blk, row_end = t.row0 + t.valid;
+      const float* sb_e = p.sb + (GROUPED ? static_cast<int64_t>(t.e_w) * p.sb_stride_e : 0);
       for (int kb0 = 0; kb0 < nkb; kb0 += 4) {
         uint32_t w[4 * MSUB];
 #pragma unroll
         for (int j = 0; j < 4 * MSUB; ++j) {
           const int row = row0 + lane + 32 * j;
-          w[j] = (row < p.M) ? __ldg(p.sa + static_cast<int64_t>(kb0 >> 2) * p.sa_stride_pack + row * p.sa_stride_m) : 0u;
+          w[j] = (row < row_end) ? __ldg(p.sa + t.sa_base + static_cast<int64_t>(kb0 >> 2) * p.sa_stride_pack + row * p.sa_stride_m) : 0u;
         }
         uint32_t wb[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           // column (i / 4) * 128 + (i % 4) * 32 + lane of the tile
           const int col = min(n_blk * BN + (i >> 2) * 128 + (i & 3) * 32 + lane, p.N - 1);
-          const float* sp = p.sb + static_cast<int64_t>(col >> 7) * p.sb_stride_n;
+          const float* sp = sb_e + static_cast<int64_t>(col >> 7) * p.sb_stride_n;
           uint32_t word = 0;
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
@@ -324,15 +434,16 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint32_t acc_phase[2] = {0, 0};
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-      int m_blk, n_blk;
-      mx_tile_coords(tile, m_blocks, n_blocks, m_blk, n_blk);
+      const MxTile t = mx_get_tile<GROUPED, kTileM>(tile, p, m_blocks, n_blocks, tile_start);
+      const int n_blk = t.n_blk;
+      const int m_end = t.row0 + t.valid;
       ok = mbar_wait(&acc_full[acc], acc_phase[acc], p.status, 46);
       if (!ok) break;
       tc_fence_after();
       constexpr int kChunks = BN / 16;
 #pragma unroll 1
       for (int h = 0; h < MSUB; ++h) {
-        const int m = m_blk * kTileM + h * BM + warp * 32 + lane;
+        const int m = t.row0 + h * BM + warp * 32 + lane;
         const uint32_t taddr = tmem_base + lane_addr + static_cast<uint32_t>(MSUB == 2 ? h : acc) * C::kAccStride;
 #pragma unroll 1
         for (int ch = 0; ch < kChunks; ch += 2) {
@@ -347,7 +458,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
           const int n0 = n_blk * BN + ch * 16;
           const int width = (ch + 1 < kChunks) ? 32 : 16;
-          if (m < p.M && n0 < p.N)
+          if (m < m_end && n0 < p.N)
             store_row<32>(out + static_cast<int64_t>(m) * p.ldo + n0, v, min(p.N - n0, width), vec_ok && width == 32);
         }
       }
@@ -367,10 +478,10 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
 }
 
-template <int BN, int MSUB, typename OutT>
+template <int BN, int MSUB, bool GROUPED, typename OutT>
 int launch_mx(const CUtensorMap& ma, const CUtensorMap& mb, const MxParams& p, cudaStream_t stream) {
   using C = MxCfg<BN, MSUB>;
-  auto kern = gemm_mx_kernel<BN, MSUB, OutT>;
+  auto kern = gemm_mx_kernel<BN, MSUB, GROUPED, OutT>;
   static bool attr_set[64] = {false};
   int dev = 0;
   B200_CUDA_TRY(cudaGetDevice(&dev));
@@ -378,24 +489,26 @@ int launch_mx(const CUtensorMap& ma, const CUtensorMap& mb, const MxParams& p, c
     B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem));
     attr_set[dev & 63] = true;
   }
-  const long long tiles = static_cast<long long>((p.M + BM * MSUB - 1) / (BM * MSUB)) * ((p.N + BN - 1) / BN);
+  // grouped: the tile count lives on the device; row tiles <= ceil(rows / tile) + problems bounds the grid
+  const long long m_tiles = (p.M + BM * MSUB - 1) / (BM * MSUB) + (GROUPED ? p.num_problems : 0);
+  const long long tiles = m_tiles * ((p.N + BN - 1) / BN);
   const int grid = tiles < sm_count() ? static_cast<int>(tiles) : sm_count();
   kern<<<grid, kThreadsMx, C::kSmem, stream>>>(ma, mb, p);
   B200_CUDA_TRY(cudaGetLastError());
   return B200_OK;
 }
 
-template <int BN, int MSUB>
+template <int BN, int MSUB, bool GROUPED = false>
 int launch_mx_dtype(const void* a, int64_t lda, const void* b, int64_t ldb, const MxParams& p, cudaStream_t st) {
   CUtensorMap ma, mb;
   int rc = make_map_u8_2d(&ma, a, p.M, p.K, lda, BM * MSUB);
   if (rc != B200_OK) return rc;
-  rc = make_map_u8_2d(&mb, b, p.N, p.K, ldb, BN);
+  rc = make_map_u8_2d(&mb, b, GROUPED ? static_cast<int64_t>(p.N) * p.num_weight_experts : p.N, p.K, ldb, BN);
   if (rc != B200_OK) return rc;
   switch (p.out_dtype) {
-    case B200_DT_BF16: return launch_mx<BN, MSUB, __nv_bfloat16>(ma, mb, p, st);
-    case B200_DT_F16: return launch_mx<BN, MSUB, __half>(ma, mb, p, st);
-    default: return launch_mx<BN, MSUB, float>(ma, mb, p, st);
+    case B200_DT_BF16: return launch_mx<BN, MSUB, GROUPED, __nv_bfloat16>(ma, mb, p, st);
+    case B200_DT_F16: return launch_mx<BN, MSUB, GROUPED, __half>(ma, mb, p, st);
+    default: return launch_mx<BN, MSUB, GROUPED, float>(ma, mb, p, st);
   }
 }
 
@@ -429,6 +542,9 @@ extern "C" int b200_fp8_blockwise_scaled_mm_pow2(const void* a, int64_t lda, con
   p.sb_stride_n = sb_stride_n; p.sb_stride_g = sb_stride_g; p.ldo = ldo;
   p.M = static_cast<int>(M); p.N = static_cast<int>(N); p.K = static_cast<int>(K);
   p.out_dtype = out_dtype;
+  p.offsets = nullptr; p.rows = nullptr; p.experts = nullptr;
+  p.rows_stride = 0; p.sb_stride_e = 0; p.sa_stride_problem = -1; p.num_problems = 0; p.num_weight_experts = 1;
+  p.prefetch_ahead = 0;
   p.status = gemm_status_ptr();
   if (!p.status) return B200_ERR_CUDA;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -441,4 +557,48 @@ extern "C" int b200_fp8_blockwise_scaled_mm_pow2(const void* a, int64_t lda, con
   if (g_force_block_n == 2240) return launch_mx_dtype<240, 2>(a, lda, b, ldb, p, st);
   if (M >= 2048 && K >= 12288) return launch_mx_dtype<240, 2>(a, lda, b, ldb, p, st);
   return launch_mx_dtype<256, 1>(a, lda, b, ldb, p, st);
+}
+
+
+// Grouped form (MoE experts; DeepGEMM's contiguous and masked layouts are special cases of the problem table, see
+// the header).  Weights are one [num_weight_experts * N, K] matrix, weight scales [expert][N/128][K/128] fp32 powers
+// of two with strides (sb_stride_e, sb_stride_n, sb_stride_g); the packed activation exponents are indexed by the
+// GLOBAL row of `a` like the codes (sa_stride_problem < 0), or by the row inside the problem with each problem's
+// words starting at sa_packed + i * sa_stride_problem.  Everything the tile schedule needs is read on the device.
+extern "C" int b200_fp8_blockwise_scaled_grouped_mm_pow2(
+    const void* a, int64_t lda, int64_t total_rows, const void* b, int64_t ldb, const uint32_t* sa_packed,
+    int64_t sa_stride_m, int64_t sa_stride_pack, int64_t sa_stride_problem, const float* sb_pow2, int64_t sb_stride_e, int64_t sb_stride_n,
+    int64_t sb_stride_g, void* out, int64_t ldo, int out_dtype, const int32_t* problem_offsets,
+    const int32_t* problem_rows, int64_t problem_rows_stride, const int32_t* problem_experts, int num_problems,
+    int num_weight_experts, int64_t N, int64_t K, void* stream) {
+  using namespace b200;
+  if (total_rows < 0 || N < 0 || K <= 0 || num_problems < 0 || num_weight_experts <= 0) return B200_ERR_BAD_SHAPE;
+  if (total_rows == 0 || N == 0 || num_problems == 0) return B200_OK;
+  if (num_problems > kMaxProblems) return B200_ERR_TOO_LARGE;
+  if (total_rows > 0x7fffff00LL || K > 0x7fffff00LL || N * num_weight_experts > 0x7fffff00LL) return B200_ERR_TOO_LARGE;
+  if (!a || !b || !sa_packed || !sb_pow2 || !out || !problem_offsets || !problem_rows) return B200_ERR_NULL_PTR;
+  if (out_dtype != B200_DT_BF16 && out_dtype != B200_DT_F16 && out_dtype != B200_DT_F32) return B200_ERR_BAD_DTYPE;
+  if (lda < K || ldb < K || ldo < N) return B200_ERR_BAD_STRIDE;
+  if ((lda % 16) != 0 || (ldb % 16) != 0 || !aligned16(a) || !aligned16(b)) return B200_ERR_MISALIGNED;
+  if (sa_stride_m < 0 || sa_stride_pack < 0 || sb_stride_e < 0 || sb_stride_n < 0 || sb_stride_g < 0 ||
+      problem_rows_stride < 0)
+    return B200_ERR_BAD_STRIDE;
+  if (K % 128 != 0) return B200_ERR_BAD_SHAPE;
+  if (N % 128 != 0) return B200_ERR_UNSUPPORTED;   // a column block of scales must not straddle two experts
+  int rc = require_sm100();
+  if (rc != B200_OK) return rc;
+  if (gemm_sticky_status() != 0) return B200_ERR_DEVICE_TIMEOUT;
+  MxParams p;
+  p.sa = sa_packed; p.sb = sb_pow2; p.out = out;
+  p.sa_stride_m = sa_stride_m; p.sa_stride_pack = sa_stride_pack;
+  p.sb_stride_n = sb_stride_n; p.sb_stride_g = sb_stride_g; p.ldo = ldo;
+  p.M = static_cast<int>(total_rows); p.N = static_cast<int>(N); p.K = static_cast<int>(K);
+  p.out_dtype = out_dtype;
+  p.offsets = problem_offsets; p.rows = problem_rows; p.experts = problem_experts;
+  p.rows_stride = problem_rows_stride; p.sb_stride_e = sb_stride_e; p.sa_stride_problem = sa_stride_problem;
+  p.num_problems = num_problems; p.num_weight_experts = num_weight_experts;
+  p.prefetch_ahead = (g_force_block_n >= 9000 && g_force_block_n <= 9064) ? g_force_block_n - 9000 : 8;
+  p.status = gemm_status_ptr();
+  if (!p.status) return B200_ERR_CUDA;
+  return launch_mx_dtype<256, 1, true>(a, lda, b, ldb, p, static_cast<cudaStream_t>(stream));
 }

@@ -88,39 +88,61 @@ prep_scan_kernel(int32_t* __restrict__ scratch, int num_chunks, int num_experts,
 __global__ void __launch_bounds__(kPrepThreads)
 prep_scatter_kernel(const int32_t* __restrict__ topk_ids, int64_t n_ids, int topk, int num_experts,
                     const int32_t* __restrict__ scratch, int32_t* __restrict__ input_permutation,
-                    int32_t* __restrict__ output_permutation) {
+                    int32_t* __restrict__ output_permutation, int walk_warps) {
   extern __shared__ int32_t s_mem[];
-  int32_t* s_next = s_mem;                 // [E] next free slot of each expert inside this chunk
-  int32_t* s_ids = s_mem + num_experts;    // [kPrepChunk]
+  int32_t* s_ids = s_mem;                          // [kPrepChunk]
+  int32_t* s_wnext = s_mem + kPrepChunk;           // [walk_warps][E] next free slot of each expert for each walking warp
+  const int kWarps = walk_warps;                   // 1, 2, 4 or 8 (as many as the per-warp tables leave room for)
+  const int kSeg = kPrepChunk / kWarps;            // ids per warp: contiguous, so the order stays the flat index
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int32_t* chunk_base = scratch + static_cast<int64_t>(blockIdx.x) * num_experts;
-  for (int e = threadIdx.x; e < num_experts; e += kPrepThreads) s_next[e] = chunk_base[e];
   const int64_t base = static_cast<int64_t>(blockIdx.x) * kPrepChunk;
-  for (int i = threadIdx.x; i < kPrepChunk; i += kPrepThreads) {
-    const int64_t idx = base + i;
-    s_ids[i] = idx < n_ids ? topk_ids[idx] : -1;
+  const int64_t left = n_ids - base;
+  const int n_here = left < kPrepChunk ? static_cast<int>(left < 0 ? 0 : left) : kPrepChunk;
+  for (int i = threadIdx.x; i < kWarps * num_experts; i += kPrepThreads) s_wnext[i] = 0;
+  for (int i = threadIdx.x; i < kPrepChunk; i += kPrepThreads) s_ids[i] = i < n_here ? topk_ids[base + i] : -1;
+  __syncthreads();
+  // per-warp histograms of the warps' segments
+  if (warp < kWarps) {
+    for (int i = lane; i < kSeg; i += 32) {
+      const int e = s_ids[warp * kSeg + i];
+      if (e >= 0 && e < num_experts) atomicAdd(&s_wnext[warp * num_experts + e], 1);
+    }
   }
   __syncthreads();
-  // One warp walks the chunk in order, 32 ids at a time; equal experts inside the 32 are ranked
-  // with a match mask, so slots follow ascending flat index exactly.
-  if (threadIdx.x < 32) {
-    const int lane = threadIdx.x;
-    for (int i0 = 0; i0 < kPrepChunk; i0 += 32) {
-      const int64_t idx = base + i0 + lane;
-      const int e = s_ids[i0 + lane];
-      const bool valid = e >= 0 && e < num_experts;
-      const unsigned peers = __match_any_sync(0xffffffffu, valid ? e : -1 - lane);
-      if (valid) {
-        const int rank = __popc(peers & ((1u << lane) - 1u));
-        const int slot = s_next[e] + rank;
-        input_permutation[slot] = static_cast<int32_t>(idx / topk);
-        output_permutation[idx] = slot;
-      } else if (idx < n_ids) {
-        output_permutation[idx] = -1;   // no slot: masked expert (the weighted sum skips it)
-      }
-      __syncwarp();
-      if (valid && (peers >> lane) <= 1u) s_next[e] += __popc(peers);   // highest lane of each group
-      __syncwarp();
+  // per expert: exclusive scan over the warps on top of the chunk's first slot
+  for (int e = threadIdx.x; e < num_experts; e += kPrepThreads) {
+    int run = chunk_base[e];
+    for (int w = 0; w < kWarps; ++w) {
+      const int c = s_wnext[w * num_experts + e];
+      s_wnext[w * num_experts + e] = run;
+      run += c;
     }
+  }
+  __syncthreads();
+  // Every warp walks its own segment in order, 32 ids at a time; equal experts inside the 32 are ranked with a
+  // match mask, so slots follow the ascending flat index exactly.  (One warp walking the whole chunk took 17 us
+  // even for a few dozen ids: a match step costs ~650 cycles, so the depth of the walk is what matters.)
+  if (warp >= kWarps) return;
+  int32_t* my_next = s_wnext + warp * num_experts;
+  const int seg_end = min(kSeg, n_here - warp * kSeg);
+  for (int i0 = 0; i0 < seg_end; i0 += 32) {
+    const int i = warp * kSeg + i0 + lane;
+    const int64_t idx = base + i;
+    const int e = s_ids[i];
+    const bool valid = e >= 0 && e < num_experts;
+    const unsigned peers = __match_any_sync(0xffffffffu, valid ? e : -1 - lane);
+    if (valid) {
+      const int rank = __popc(peers & ((1u << lane) - 1u));
+      const int slot = my_next[e] + rank;
+      input_permutation[slot] = static_cast<int32_t>(idx / topk);
+      output_permutation[idx] = slot;
+    } else if (idx < n_ids) {
+      output_permutation[idx] = -1;   // no slot: masked expert (the weighted sum skips it)
+    }
+    __syncwarp();
+    if (valid && (peers >> lane) <= 1u) my_next[e] += __popc(peers);   // highest lane of each group
+    __syncwarp();
   }
 }
 
@@ -236,8 +258,12 @@ int moe_prepare_launch(const int32_t* topk_ids, int64_t n_ids, int topk, int num
   prep_scan_kernel<<<1, 1024, num_experts * sizeof(int32_t), st>>>(scratch, nch, num_experts, expert_offsets,
                                                                    blockscale_offsets, problem_sizes1,
                                                                    problem_sizes2, n, k);
-  prep_scatter_kernel<<<nch, kPrepThreads, (num_experts + kPrepChunk) * sizeof(int32_t), st>>>(
-      topk_ids, n_ids, topk, num_experts, scratch, input_permutation, output_permutation);
+  // walking warps: as many (a power of two up to 8) as fit their per-expert tables into 48 KB of shared memory
+  int walk_warps = 8;
+  while (walk_warps > 1 && (static_cast<size_t>(walk_warps) * num_experts + kPrepChunk) * sizeof(int32_t) > 48 * 1024)
+    walk_warps >>= 1;
+  prep_scatter_kernel<<<nch, kPrepThreads, (static_cast<size_t>(walk_warps) * num_experts + kPrepChunk) * sizeof(int32_t), st>>>(
+      topk_ids, n_ids, topk, num_experts, scratch, input_permutation, output_permutation, walk_warps);
   B200_CUDA_TRY(cudaGetLastError());
   return B200_OK;
 }
@@ -319,6 +345,41 @@ extern "C" int b200_moe_prepare_noalloc(const int32_t* topk_ids, int64_t num_tok
   return moe_prepare_launch(topk_ids, n_ids, topk, num_experts, n, k, expert_offsets, blockscale_offsets,
                             problem_sizes1, problem_sizes2, input_permutation, output_permutation, scratch,
                             static_cast<cudaStream_t>(stream));
+}
+
+namespace b200 {
+namespace {
+// Column gather of a [words][rows] table: dst[w][r] = src[w][clamp(map[r])].  The packed power-of-two scales are
+// stored with the rows contiguous, so copying a token's scale words to the rows of its experts is a gather along
+// the contiguous dimension: coalesced stores, reads from a table that sits in L2.
+__global__ void __launch_bounds__(256) packed_scales_gather_kernel(const uint32_t* __restrict__ src, int64_t src_ld,
+                                                                    int64_t src_rows, const int32_t* __restrict__ map,
+                                                                    uint32_t* __restrict__ dst, int64_t dst_ld,
+                                                                    int64_t num_dst_rows) {
+  const int64_t r = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (r >= num_dst_rows) return;
+  const int64_t c = min(max(static_cast<int64_t>(__ldg(map + r)), int64_t(0)), src_rows - 1);
+  dst[blockIdx.y * dst_ld + r] = __ldg(src + blockIdx.y * src_ld + c);
+}
+}  // namespace
+}  // namespace b200
+
+extern "C" int b200_shuffle_packed_scales(const uint32_t* input, int64_t input_stride_pack, int64_t num_src_rows,
+                                          const int32_t* dst2src_map, uint32_t* output, int64_t output_stride_pack,
+                                          int64_t num_dst_rows, int words_per_row, void* stream) {
+  using namespace b200;
+  if (num_dst_rows < 0 || num_src_rows < 0 || words_per_row < 0) return B200_ERR_BAD_SHAPE;
+  if (num_dst_rows == 0 || words_per_row == 0) return B200_OK;
+  if (num_src_rows == 0) return B200_ERR_BAD_SHAPE;
+  if (!input || !dst2src_map || !output) return B200_ERR_NULL_PTR;
+  if (input_stride_pack < num_src_rows || output_stride_pack < num_dst_rows) return B200_ERR_BAD_STRIDE;
+  const int64_t blocks = (num_dst_rows + 255) / 256;
+  if (blocks > 0x7fffffffLL || words_per_row > 65535) return B200_ERR_TOO_LARGE;
+  packed_scales_gather_kernel<<<dim3(static_cast<unsigned>(blocks), static_cast<unsigned>(words_per_row)), 256, 0,
+                                static_cast<cudaStream_t>(stream)>>>(input, input_stride_pack, num_src_rows, dst2src_map,
+                                                                     output, output_stride_pack, num_dst_rows);
+  B200_CUDA_TRY(cudaGetLastError());
+  return B200_OK;
 }
 
 extern "C" int b200_shuffle_rows(const void* input, const int32_t* dst2src_map, void* output, int64_t num_dst_rows,

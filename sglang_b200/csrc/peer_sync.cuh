@@ -5,7 +5,7 @@
 // Every rank owns a signal pad (zero-initialised 32-bit flags) that every other rank has mapped.  Flag
 // [block][peer] of a rank's pad is set (compare-and-swap 0 -> 1, release) by that peer's block with the
 // same index and cleared (1 -> 0, acquire) by the owner, so the flags need no epoch and a pad is reused
-// call after call.  Every spin is bounded (about five seconds): a rank whose peer never arrives records a code in its status
+// call after call.  Every spin is bounded (about ten seconds): a rank whose peer never arrives records a code in its status
 // word and carries on, so a missing rank costs wrong data, never a hung GPU.
 #pragma once
 #include "common.cuh"
@@ -14,8 +14,8 @@ namespace b200 {
 
 constexpr int kMaxRanks = 8;
 // Ranks reach a meeting point at different times (one may still be loading a module or running a longer kernel),
-// so the limit is generous: about five seconds of SM clocks.
-constexpr long long kPeerWaitCycles = 10000000000LL;
+// so the limit is generous: about ten seconds of SM clocks.
+constexpr long long kPeerWaitCycles = 20000000000LL;
 
 struct PeerSync {
   uint32_t* signals[kMaxRanks];  // every rank's signal pad, as mapped into this process

@@ -108,7 +108,8 @@ __device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float 
 // contiguous).  The tile writes whole words; groups past K/GROUP inside the last word are zero bytes.
 template <typename T, int GROUP, int PASSES, bool IEEE_DIV, bool FUSE_SILU = false, bool UE8M0 = false>
 __global__ void __launch_bounds__(kThreads, (PASSES >= 8 || sizeof(T) == 4) ? 2 : 4)   // 4 blocks/SM: <= 64 registers
-quant_group_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ s, int64_t M, int64_t K,
+quant_group_kernel(const T* __restrict__ x, const int32_t* __restrict__ src_rows, int64_t x_rows, uint8_t* __restrict__ q,
+                   float* __restrict__ s, int64_t M, int64_t K,
                    int64_t s_stride_row, int64_t s_stride_grp, float eps, float fp8_min, float fp8_max,
                    int tiles_k) {
   constexpr int TPG = GROUP / kVec;              // lanes cooperating on one group
@@ -134,10 +135,13 @@ quant_group_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* __re
   for (int p = 0; p < PASSES; ++p) {
     const int64_t row = row0 + p * ROWS_PER_PASS;
     if (col_ok && row < M) {
+      // src_rows (optional): output row `row` quantises input row src_rows[row] (a routed copy of a token)
+      // (clamped into the input's rows: a table that does not match the buffer cannot send a load out of bounds)
+      const int64_t srow = src_rows ? min(max(static_cast<int64_t>(__ldg(src_rows + row)), int64_t(0)), x_rows - 1) : row;
       if constexpr (FUSE_SILU) {
         Vec16<T> gate, up;
-        gate.load(x + row * 2 * K + col);
-        up.load(x + row * 2 * K + K + col);
+        gate.load(x + srow * 2 * K + col);
+        up.load(x + srow * 2 * K + K + col);
         float f[kVec];
 #pragma unroll
         for (int i = 0; i < kVec; ++i) {
@@ -146,7 +150,7 @@ quant_group_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* __re
         }
         data[p].from_floats(f);
       } else {
-        data[p].load(x + row * K + col);
+        data[p].load(x + srow * K + col);
       }
     } else {
       data[p].zero();
@@ -254,7 +258,7 @@ quant_group_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* __re
 
 template <typename T, int GROUP, bool IEEE_DIV, bool FUSE_SILU = false, bool UE8M0 = false>
 int launch_group(const void* x, void* q, float* s, int64_t M, int64_t K, int64_t ssr, int64_t ssg, float eps,
-                 float fmin_, float fmax_, cudaStream_t stream) {
+                 float fmin_, float fmax_, cudaStream_t stream, const int32_t* src_rows = nullptr, int64_t x_rows = 0) {
   const int tiles_k = static_cast<int>((K + kTileW - 1) / kTileW);
   const int sms = sm_count();
   if (sms <= 0) return B200_ERR_CUDA;
@@ -270,7 +274,7 @@ int launch_group(const void* x, void* q, float* s, int64_t M, int64_t K, int64_t
   const T* xp = static_cast<const T*>(x);
   uint8_t* qp = static_cast<uint8_t*>(q);
 #define B200_LAUNCH_Q(P)                                                                                       \
-  quant_group_kernel<T, GROUP, P, IEEE_DIV, FUSE_SILU, UE8M0><<<grid, kThreads, 0, stream>>>(xp, qp, s, M, K, ssr, ssg, eps, fmin_, \
+  quant_group_kernel<T, GROUP, P, IEEE_DIV, FUSE_SILU, UE8M0><<<grid, kThreads, 0, stream>>>(xp, src_rows, x_rows, qp, s, M, K, ssr, ssg, eps, fmin_, \
                                                                            fmax_, tiles_k)
   switch (passes) {
     case 8:
@@ -383,4 +387,68 @@ extern "C" int b200_per_token_group_quant_fp8_ue8m0(const void* x, int x_dtype, 
     default:
       return B200_ERR_BAD_DTYPE;
   }
+}
+
+// SiLU(gate) * up followed by the power-of-two quantisation, in one pass: what the second expert GEMM of the
+// block-scaling path consumes (the reference runs silu_and_mul, then sglang_per_token_group_quant_fp8 with
+// scale_ue8m0=True: python/sglang/srt/layers/moe/ep_moe/layer.py:606-628).  x is [M, 2K] (gate | up).
+extern "C" int b200_silu_mul_per_token_group_quant_fp8_ue8m0(const void* x, int x_dtype, void* q, uint32_t* s_packed,
+                                                             int64_t M, int64_t K, int64_t s_stride_pack, float eps,
+                                                             float fp8_min, float fp8_max, void* stream) {
+  using namespace b200;
+  if (M < 0 || K < 0) return B200_ERR_BAD_SHAPE;
+  if (K % 128 != 0) return B200_ERR_BAD_SHAPE;
+  if (M == 0 || K == 0) return B200_OK;
+  if (!x || !q || !s_packed) return B200_ERR_NULL_PTR;
+  if (!aligned16(x) || !aligned16(q)) return B200_ERR_MISALIGNED;
+  if (s_stride_pack < M) return B200_ERR_BAD_STRIDE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  float* s = reinterpret_cast<float*>(s_packed);
+  switch (x_dtype) {
+    case B200_DT_BF16:
+      return launch_group<__nv_bfloat16, 128, false, true, true>(x, q, s, M, K, 1, s_stride_pack, eps, fp8_min, fp8_max, st);
+    case B200_DT_F16:
+      return launch_group<__half, 128, false, true, true>(x, q, s, M, K, 1, s_stride_pack, eps, fp8_min, fp8_max, st);
+    default:
+      return B200_ERR_BAD_DTYPE;
+  }
+}
+
+// Row gather fused into the quantisation: output row r holds the codes and scale(s) of input row src_rows[r].
+// One launch in place of quantise + gather codes + gather scales when every token is copied to the rows of its
+// experts (the reference's ep_scatter after the quantisation, python/sglang/srt/layers/moe/ep_moe/kernels.py;
+// shuffle_rows in cutlass_moe.py:144-150): same bits as quantising first and gathering afterwards.  x has `x_rows`
+// rows; indices are clamped into [0, x_rows).  scale_ue8m0 != 0: s is the packed exponent tensor
+// (s_stride_grp = the stride between packed words, s_stride_row ignored).
+extern "C" int b200_gather_per_token_group_quant_fp8(const void* x, int x_dtype, int64_t x_rows, const int32_t* src_rows,
+                                                     void* q, void* s, int64_t R, int64_t K, int64_t s_stride_row,
+                                                     int64_t s_stride_grp, int scale_ue8m0, float eps, float fp8_min,
+                                                     float fp8_max, void* stream) {
+  using namespace b200;
+  if (R < 0 || K < 0 || x_rows < 0) return B200_ERR_BAD_SHAPE;
+  if (K % 128 != 0) return B200_ERR_BAD_SHAPE;
+  if (R == 0 || K == 0) return B200_OK;
+  if (x_rows == 0) return B200_ERR_BAD_SHAPE;
+  if (!x || !q || !s || !src_rows) return B200_ERR_NULL_PTR;
+  if (!aligned16(x) || !aligned16(q)) return B200_ERR_MISALIGNED;
+  if (scale_ue8m0) {
+    if (s_stride_grp < R) return B200_ERR_BAD_STRIDE;
+    s_stride_row = 1;
+  } else if (s_stride_row < 0 || s_stride_grp < 0 || (s_stride_row == 0 && R > 1) || (s_stride_grp == 0 && K / 128 > 1)) {
+    return B200_ERR_BAD_STRIDE;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  float* sp = static_cast<float*>(s);
+#define B200_GQ(T)                                                                                                  \
+  (scale_ue8m0 ? launch_group<T, 128, false, false, true>(x, q, sp, R, K, s_stride_row, s_stride_grp, eps, fp8_min, \
+                                                          fp8_max, st, src_rows, x_rows)                           \
+               : launch_group<T, 128, false, false, false>(x, q, sp, R, K, s_stride_row, s_stride_grp, eps, fp8_min, \
+                                                           fp8_max, st, src_rows, x_rows))
+  switch (x_dtype) {
+    case B200_DT_BF16: return B200_GQ(__nv_bfloat16);
+    case B200_DT_F16: return B200_GQ(__half);
+    case B200_DT_F32: return B200_GQ(float);
+    default: return B200_ERR_BAD_DTYPE;
+  }
+#undef B200_GQ
 }

@@ -57,7 +57,8 @@ def sglang_per_token_group_quant_fp8(x: torch.Tensor, group_size: int, eps: floa
 
 
 def silu_and_mul_per_token_group_quant_fp8(x: torch.Tensor, group_size: int = 128, eps: float = 1e-10,
-                                           column_major_scales: bool = False, scale_tma_aligned: bool = False):
+                                           column_major_scales: bool = False, scale_tma_aligned: bool = False,
+                                           scale_ue8m0: bool = False):
     """x [..., 2K] (gate | up) -> codes [..., K], scales as in sglang_per_token_group_quant_fp8.
     Bit-identical to silu_and_mul followed by sglang_per_token_group_quant_fp8; one kernel, and the
     [..., K] intermediate is never written.  (The reference has this fusion only as a Triton kernel
@@ -67,18 +68,52 @@ def silu_and_mul_per_token_group_quant_fp8(x: torch.Tensor, group_size: int = 12
     assert x.dtype in (torch.bfloat16, torch.float16)
     K = x.shape[-1] // 2
     out_shape = x.shape[:-1] + (K,)
+    M = x.numel() // (2 * K)
     x_q = torch.empty(out_shape, device=x.device, dtype=fp8_dtype)
+    dt = {torch.float16: _lib.DT_F16, torch.bfloat16: _lib.DT_BF16}[x.dtype]
+    if scale_ue8m0:
+        x_s = create_per_token_group_quant_fp8_output_scale((M, K), x.device, group_size, True, True, True)
+        if M > 0:
+            with torch.cuda.device(x.device):
+                rc = _lib.lib().b200_silu_mul_per_token_group_quant_fp8_ue8m0(
+                    x.data_ptr(), dt, x_q.data_ptr(), x_s.data_ptr(), M, K, x_s.stride(1), eps, fp8_min, fp8_max,
+                    torch.cuda.current_stream(x.device).cuda_stream)
+            _lib.check("silu_and_mul_per_token_group_quant_fp8", rc)
+        return x_q, x_s
     x_s = create_per_token_group_quant_fp8_output_scale(out_shape, x.device, group_size, column_major_scales,
                                                         scale_tma_aligned, False)
-    M = x.numel() // (2 * K)
     if M > 0:
         s2 = x_s.reshape(M, K // 128) if x_s.dim() != 2 else x_s
-        dt = {torch.float16: _lib.DT_F16, torch.bfloat16: _lib.DT_BF16}[x.dtype]
         with torch.cuda.device(x.device):
             rc = _lib.lib().b200_silu_mul_per_token_group_quant_fp8(
                 x.data_ptr(), dt, x_q.data_ptr(), s2.data_ptr(), M, K, s2.stride(0), s2.stride(1), eps, fp8_min,
                 fp8_max, torch.cuda.current_stream(x.device).cuda_stream)
         _lib.check("silu_and_mul_per_token_group_quant_fp8", rc)
+    return x_q, x_s
+
+
+def gather_per_token_group_quant_fp8(x: torch.Tensor, src_rows: torch.Tensor, group_size: int = 128, eps: float = 1e-10,
+                                     column_major_scales: bool = False, scale_tma_aligned: bool = False,
+                                     scale_ue8m0: bool = False):
+    """Row r of the result = codes and scales of x[src_rows[r]]: sglang_per_token_group_quant_fp8 followed by a row
+    gather of codes and scales (shuffle_rows in the reference's cutlass_moe.py:144-150; ep_scatter in its EP path),
+    in one kernel and with the same bits.  x [M, K] bf16/fp16/fp32 contiguous, src_rows [R] int32."""
+    assert group_size == 128, "the fused form is built for 128-wide groups"
+    assert x.dim() == 2 and x.is_contiguous() and x.shape[1] % 128 == 0
+    assert src_rows.dtype == torch.int32 and src_rows.is_contiguous()
+    M, K = x.shape
+    R = src_rows.numel()
+    x_q = torch.empty((R, K), device=x.device, dtype=fp8_dtype)
+    x_s = create_per_token_group_quant_fp8_output_scale((R, K), x.device, group_size, column_major_scales,
+                                                        scale_tma_aligned, scale_ue8m0)
+    if R > 0:
+        dt = {torch.float32: _lib.DT_F32, torch.float16: _lib.DT_F16, torch.bfloat16: _lib.DT_BF16}[x.dtype]
+        with torch.cuda.device(x.device):
+            rc = _lib.lib().b200_gather_per_token_group_quant_fp8(
+                x.data_ptr(), dt, M, src_rows.data_ptr(), x_q.data_ptr(), x_s.data_ptr(), R, K, x_s.stride(0),
+                x_s.stride(1), 1 if scale_ue8m0 else 0, eps, fp8_min, fp8_max,
+                torch.cuda.current_stream(x.device).cuda_stream)
+        _lib.check("gather_per_token_group_quant_fp8", rc)
     return x_q, x_s
 
 

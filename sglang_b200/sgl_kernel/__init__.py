@@ -9,7 +9,8 @@ import torch
 
 from .gemm import fp8_blockwise_scaled_mm, sgl_per_token_group_quant_fp8
 from .moe import (apply_shuffle_mul_sum, fp8_blockwise_scaled_grouped_mm, prepare_moe_input, shuffle_rows,
-                  shuffle_rows_into, silu_and_mul, topk_softmax, moe_fused_gate, moe_align_block_size)
+                  shuffle_rows_into, shuffle_packed_scales, silu_and_mul, topk_softmax, moe_fused_gate,
+                  moe_align_block_size)
 
 _SCHEMAS = {
     "fp8_blockwise_scaled_mm":
@@ -107,5 +108,5 @@ def register_torch_ops() -> None:
 register_torch_ops()
 
 __all__ = ["fp8_blockwise_scaled_mm", "sgl_per_token_group_quant_fp8", "fp8_blockwise_scaled_grouped_mm",
-           "prepare_moe_input", "shuffle_rows", "apply_shuffle_mul_sum", "silu_and_mul", "topk_softmax",
+           "prepare_moe_input", "shuffle_rows", "shuffle_packed_scales", "apply_shuffle_mul_sum", "silu_and_mul", "topk_softmax",
            "moe_fused_gate", "moe_align_block_size", "register_torch_ops"]

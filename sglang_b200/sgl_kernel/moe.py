@@ -155,6 +155,24 @@ def shuffle_rows(input_tensor, dst2src_map, output_tensor_shape):
     return output_tensor
 
 
+def shuffle_packed_scales(packed: torch.Tensor, dst2src_map: torch.Tensor) -> torch.Tensor:
+    """Row gather of the packed power-of-two scales that sglang_per_token_group_quant_fp8(scale_ue8m0=True) returns
+    (int32 [M, W], rows contiguous): result [R, W] in the same layout with row r = packed[dst2src_map[r]]."""
+    _check(packed.dtype == torch.int32 and packed.dim() == 2, "packed scales must be int32 [rows, words]")
+    _check(packed.stride(0) == 1 or packed.size(0) == 1, "packed scales must have their rows contiguous")
+    _check(dst2src_map.dtype == torch.int32 and dst2src_map.is_contiguous(), "dst2src_map must be int32")
+    M, W = packed.shape
+    R = dst2src_map.numel()
+    aligned = (R + 3) // 4 * 4
+    out = torch.zeros((W, aligned), dtype=torch.int32, device=packed.device).transpose(0, 1)[:R, :]
+    if R > 0:
+        with torch.cuda.device(packed.device):
+            rc = _lib.lib().b200_shuffle_packed_scales(packed.data_ptr(), packed.stride(1), M, dst2src_map.data_ptr(),
+                                                       out.data_ptr(), out.stride(1), R, W, _stream_ptr(packed.device))
+        _lib.check("shuffle_packed_scales", rc)
+    return out
+
+
 def apply_shuffle_mul_sum(input, output, permutation, factors):
     """output[i] = sum_j factors[i,j] * input[permutation[i*topk+j]] (fp32 accumulate)."""
     _check(input.dim() == 2, "input_tensor must be 2D [m * topk, row_stride]")

@@ -76,7 +76,7 @@ def test_argument_checks_return_before_any_device_work(lib):
 
 
 def test_split_k_plan_needs_no_device(lib):
-    """Decode-size batches on narrow, deep projections split; wide or shallow ones and M > 128 do not."""
+    """Decode-size batches on narrow, deep projections split; wide or shallow ones do not."""
     def plan(M, N, K, sms=148):
         s, b = ctypes.c_int(-1), ctypes.c_size_t(1)
         assert lib.b200_fp8_blockwise_scaled_mm_splitk_plan(M, N, K, sms, ctypes.byref(s), ctypes.byref(b)) == 0
@@ -84,11 +84,13 @@ def test_split_k_plan_needs_no_device(lib):
             assert b.value == (s.value * M * N * 4 if s.value > 1 else 0)
         return s.value
     assert plan(16, 7168, 18432) == 2          # <= 64 tokens: 56 tiles of 128 weight rows on 148 SMs
-    assert plan(128, 7168, 18432) == 5         # 65..128 tokens: 28 tiles of 128 x 256
+    assert plan(128, 7168, 18432) == 1         # 65..128 tokens: two token tiles x 56 weight tiles, 76 % of one wave
     assert plan(1, 1536, 7168) == 7            # capped at eight k-blocks per CTA
     assert plan(16, 36864, 7168) == 1          # already more tiles than SMs
     assert plan(16, 7168, 2048) == 1           # too few k-blocks to pay for the reduce kernel
-    assert plan(129, 7168, 18432) == 2         # two row blocks x 28: 56 tiles of 128 x 256
+    assert plan(129, 7168, 18432) == 2         # three token tiles x 56: 168 tiles, a nearly empty second wave
+    assert plan(192, 10240, 8192) == 1         # 240 tiles: 81 % of two waves
+    assert plan(256, 7168, 18432) == 2         # beyond 192 tokens 128 x 256 tiles: 56 of them
     assert plan(512, 7168, 18432) == 1         # 112 tiles: most SMs busy already
     assert plan(0, 7168, 18432) == 1
     assert plan(16, 7168, 18432, sms=0) == 2   # <= 0 means a 148-SM part

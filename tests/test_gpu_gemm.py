@@ -152,7 +152,9 @@ def test_split_k_auto_decode_shapes(M, N, K):
     assert O.rel_l2(cbf.float(), ref32.to(torch.bfloat16).float()) <= TOL
     s, nb = ctypes.c_int(0), ctypes.c_size_t(0)
     assert _lib.lib().b200_fp8_blockwise_scaled_mm_splitk_plan(M, N, K, 148, ctypes.byref(s), ctypes.byref(nb)) == 0
-    assert (s.value > 1) == (N <= 148 * 128) and nb.value == (s.value * M * N * 4 if s.value > 1 else 0)
+    assert nb.value == (s.value * M * N * 4 if s.value > 1 else 0)
+    if M <= 64:          # one token tile: narrow projections leave SMs idle and are split
+        assert (s.value > 1) == (N <= 148 * 128)
 
 
 def test_split_k_argument_errors():
