@@ -683,6 +683,7 @@ def run_gpu_arm(args):
     if world > 1 and args.allreduce == "custom":
         from sglang_b200.distributed.custom_all_reduce import SymmetricAllReduce
         ar = SymmetricAllReduce(max(M_TOKENS, 8192) * 8192 * 2)
+        ar_forms_us = ar.autotune(M_TOKENS * HIDDEN * 2)       # multicast or peer pointers: whichever is faster here
     col = ColumnParallelBlockFp8Linear(w1q, w1s)
     row = RowParallelBlockFp8Linear(w2q, w2s, all_reduce=ar)
     g = torch.Generator(device=dev).manual_seed(7)           # x is replicated: same seed on all ranks
@@ -999,7 +1000,8 @@ def run_gpu_arm(args):
                        "timing": "step replayed from a CUDA graph at every N; per-kernel times from a separate eager pass with events around each call, at every N",
                        "l2": "inputs larger than L2 (weights 396 MB e4m3 + activations 210 MB bf16 per step)",
                        "kernels_ms": per_kernel,
-                       **({"row_chunk_candidates_ms": chunk_ms} if world > 1 else {})},
+                       **({"row_chunk_candidates_ms": chunk_ms} if world > 1 else {}),
+                       **({"all_reduce_forms_us": ar_forms_us} if ar is not None else {})},
             "parity": parity,
             "e2e": {"value": FLOPS_PER_STEP / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,

@@ -46,7 +46,7 @@ constexpr int kGroupMMx = 32;
 template <int BN, int MSUB>
 struct MxCfg {
   static_assert(MSUB == 1 || BN <= 240, "two 128-row halves need the 240-wide tile");
-  static constexpr int kStages = MSUB == 2 ? 3 : 4;
+  static constexpr int kStages = MSUB == 2 ? 3 : (BN <= 192 ? 5 : 4);
   static constexpr int kNumAcc = (BN <= 240 && MSUB == 1) ? 2 : 1;   // accumulator double buffering across tiles
   static constexpr int kABytes = MSUB * BM * BK;
   static constexpr int kBBytes = BN * BK;
@@ -78,7 +78,6 @@ struct MxParams {
   // contiguous layout), or per problem by the row inside it at sa + i * sa_stride_problem (its masked layout)
   int64_t sa_stride_problem;
   int num_problems, num_weight_experts;
-  int prefetch_ahead;   // grouped: weight boxes requested into L2 this many k-blocks ahead of the shared-memory ring
 };
 
 constexpr int kMaxProblems = 2048;
@@ -257,41 +256,12 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    // Grouped: every weight byte comes from HBM exactly once and the ring (4 stages, 192 KB) covers only ~2 us of
-    // latency at the rate one SM must sustain.  A second cursor runs `prefetch_ahead` k-blocks in front of the
-    // loads -- across tile boundaries -- and asks for the weight boxes in L2, so that the loads into shared memory
-    // find them there.
-    int pf_tile = blockIdx.x, pf_kb = 0, pf_row = 0;
-    bool pf_live = false;
-    auto pf_step = [&]() {
-      if (!pf_live) return;
-      if (elect_one()) tma_prefetch_l2_2d(&map_b, pf_kb * BK, pf_row);
-      __syncwarp();
-      if (++pf_kb == nkb) {
-        pf_kb = 0;
-        pf_tile += gridDim.x;
-        pf_live = pf_tile < num_tiles;
-        if (pf_live) {
-          const MxTile t = mx_get_tile<GROUPED, kTileM>(pf_tile, p, m_blocks, n_blocks, tile_start);
-          pf_row = t.e_w * p.N + t.n_blk * BN;
-        }
-      }
-    };
-    if constexpr (GROUPED) {
-      pf_live = p.prefetch_ahead > 0 && pf_tile < num_tiles;
-      if (pf_live) {
-        const MxTile t = mx_get_tile<GROUPED, kTileM>(pf_tile, p, m_blocks, n_blocks, tile_start);
-        pf_row = t.e_w * p.N + t.n_blk * BN;
-      }
-      for (int i = 0; i < p.prefetch_ahead; ++i) pf_step();
-    }
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
       const MxTile t = mx_get_tile<GROUPED, kTileM>(tile, p, m_blocks, n_blocks, tile_start);
       const int w_row0 = t.e_w * p.N + t.n_blk * BN;
       for (int kb = 0; kb < nkb; ++kb) {
         ok = mbar_wait_warp(&empty_bar[stage], phase ^ 1u, p.status, 41);
         if (!ok) break;
-        if constexpr (GROUPED) pf_step();
         if (elect_one()) {
           mbar_expect_tx(&full_bar[stage], C::kStageBytes);
           tma_load_2d(smem_a + stage * kABytesMx, &map_a, &full_bar[stage], kb * BK, t.row0);
@@ -544,7 +514,6 @@ extern "C" int b200_fp8_blockwise_scaled_mm_pow2(const void* a, int64_t lda, con
   p.out_dtype = out_dtype;
   p.offsets = nullptr; p.rows = nullptr; p.experts = nullptr;
   p.rows_stride = 0; p.sb_stride_e = 0; p.sa_stride_problem = -1; p.num_problems = 0; p.num_weight_experts = 1;
-  p.prefetch_ahead = 0;
   p.status = gemm_status_ptr();
   if (!p.status) return B200_ERR_CUDA;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -597,8 +566,11 @@ extern "C" int b200_fp8_blockwise_scaled_grouped_mm_pow2(
   p.offsets = problem_offsets; p.rows = problem_rows; p.experts = problem_experts;
   p.rows_stride = problem_rows_stride; p.sb_stride_e = sb_stride_e; p.sa_stride_problem = sa_stride_problem;
   p.num_problems = num_problems; p.num_weight_experts = num_weight_experts;
-  p.prefetch_ahead = (g_force_block_n >= 9000 && g_force_block_n <= 9064) ? g_force_block_n - 9000 : 8;
   p.status = gemm_status_ptr();
   if (!p.status) return B200_ERR_CUDA;
+  // Tile width.  128 x 256 with one accumulator is the default; the test hook reaches the narrower tiles with two
+  // accumulators (a tile's read-out overlaps the next tile's MMAs): 9240 -> 128 x 240, 9192 -> 128 x 192.
+  if (g_force_block_n == 9240) return launch_mx_dtype<240, 1, true>(a, lda, b, ldb, p, static_cast<cudaStream_t>(stream));
+  if (g_force_block_n == 9192) return launch_mx_dtype<192, 1, true>(a, lda, b, ldb, p, static_cast<cudaStream_t>(stream));
   return launch_mx_dtype<256, 1, true>(a, lda, b, ldb, p, static_cast<cudaStream_t>(stream));
 }

@@ -34,6 +34,7 @@ ONE_SHOT_MAX_BYTES = 512 * 1024
 class SymmetricAllReduce:
     """A symmetric buffer of `max_bytes` on every rank of `group` plus the all-reduce over it.
 
+    autotune(nbytes)          times the multicast and the peer-pointer form and keeps the faster one
     buffer(shape, dtype)      a view of the buffer's start to write partial results into
     all_reduce_(t)            in place over a row-contiguous view of the buffer (two-shot)
     all_reduce_small(t, out)  one-shot into a local tensor (small buffers)
@@ -64,11 +65,54 @@ class SymmetricAllReduce:
         self._peer_ptrs = (ctypes.c_void_p * self.world)(*[int(p) + self.base_offset for p in self._hdl.buffer_ptrs])
         self._signal_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in self._hdl.signal_pad_ptrs])
         mc = int(self._hdl.multicast_ptr) if use_multicast else 0
+        self._mc_addr = mc + self.base_offset if mc else 0
         self.multicast = mc != 0
-        self._mc = ctypes.c_void_p(mc + self.base_offset if mc else None)
+        self._mc = ctypes.c_void_p(self._mc_addr if mc else None)
         self._status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.num_blocks = int(num_blocks)
         self._hdl.barrier()   # every rank's flags are zero before the first kernel touches them
+
+    def set_form(self, form: str) -> None:
+        """"multicast": sums come out of the NVSwitch (multimem.ld_reduce / multimem.st); "peer": plain loads from and
+        stores to every rank's buffer.  Every rank must choose the same form."""
+        if form == "multicast":
+            if not self._mc_addr:
+                raise ValueError("no multicast address for this buffer")
+            self.multicast, self._mc = True, ctypes.c_void_p(self._mc_addr)
+        elif form == "peer":
+            self.multicast, self._mc = False, ctypes.c_void_p(None)
+        else:
+            raise ValueError(form)
+
+    def autotune(self, nbytes: int, iters: int = 10) -> dict:
+        """Times the two-shot all-reduce of `nbytes` in both forms (max over ranks) and keeps the faster one; every
+        rank must call it.  Which form wins depends on the rank count: through the switch every rank's own slice
+        crosses NVLink too, with peer pointers only remote data does, but every SM's loads pay the NVLink latency.
+        The buffer's contents are overwritten.  Returns {form: microseconds}."""
+        granule = 16 * self.world
+        nbytes = min(self.nbytes, (int(nbytes) + granule - 1) // granule * granule)
+        view = self._buf[:nbytes].view(torch.bfloat16)
+        forms = (["multicast"] if self._mc_addr else []) + ["peer"]
+        times = {}
+        for form in forms:
+            self.set_form(form)
+            view.zero_()
+            for _ in range(2):
+                self.all_reduce_(view)
+            torch.cuda.synchronize(self.device)
+            dist.barrier(self.group)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(iters):
+                self.all_reduce_(view)
+            b.record()
+            torch.cuda.synchronize(self.device)
+            t = torch.tensor([a.elapsed_time(b) / iters * 1e3], device=self.device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+            times[form] = float(t.item())
+        self.check()
+        self.set_form(min(times, key=times.get))      # same numbers on every rank, so the same choice
+        return times
 
     def buffer(self, shape, dtype: torch.dtype) -> torch.Tensor:
         n = 1

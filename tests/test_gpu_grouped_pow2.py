@@ -104,9 +104,10 @@ def _rows(R, K, seed):
     return x
 
 
+@pytest.mark.parametrize("tile_hook", [0, 9240, 9192])      # 128 x 256 (default), 128 x 240, 128 x 192 tiles
 @pytest.mark.parametrize("sizes,N,K", [([5], 256, 128), ([0, 1, 127, 128, 129, 300, 0, 64], 512, 1024),
                                        ([130] * 20, 1152, 640), ([256, 3, 700], 4096, 7168)])
-def test_grouped_block_scaling_gemm_problem_table(sizes, N, K):
+def test_grouped_block_scaling_gemm_problem_table(sizes, N, K, tile_hook):
     """Problems of ragged sizes packed without padding (what b200_moe_prepare writes), including empty ones: every
     expert's rows against the oracle's fp32 product and, bit for bit, against the dense block-scaling entry run on
     that expert alone; rows between problems and a skipped problem stay untouched."""
@@ -132,9 +133,14 @@ def test_grouped_block_scaling_gemm_problem_table(sizes, N, K):
     skipped = E - 1 if E > 2 else -1
     if skipped >= 0:
         experts[skipped] = -1
+    from sglang_b200 import _lib
     out = torch.full((R, N), 7.0, dtype=torch.bfloat16, device="cuda")
-    grouped_gemm_pow2(q, sp, wq.cuda(), ws.cuda(), out, off_t, ps[:, 0], experts)
-    _status_ok()
+    _lib.lib().b200_debug_force_block_n(tile_hook)
+    try:
+        grouped_gemm_pow2(q, sp, wq.cuda(), ws.cuda(), out, off_t, ps[:, 0], experts)
+        _status_ok()
+    finally:
+        _lib.lib().b200_debug_force_block_n(0)
     out = out.cpu()
     owned = torch.zeros(R, dtype=torch.bool)
     for e, (o, sz) in enumerate(zip(offsets, sizes)):

@@ -143,6 +143,22 @@ def _ar_worker(rank, world, port, q):
                                                 f"equals own input: {bool(torch.equal(got2, mine))}, one-shot max|diff| "
                                                 f"{(got1.float() - want[:16].float()).abs().max().item():.4g}, "
                                                 f"ranks agree: {bool(torch.equal(both[0], both[1]))}")
+            if use_mc and ar.multicast:
+                # autotune keeps one of the two forms (the same on every rank) and the buffer still reduces right
+                times = ar.autotune(4 << 20, iters=3)
+                picked = "multicast" if ar.multicast else "peer"
+                g = torch.Generator(device="cuda").manual_seed(900 + rank)
+                mine = torch.randn(256, 4096, generator=g, device="cuda").to(torch.bfloat16)
+                parts = [torch.empty_like(mine) for _ in range(world)]
+                dist.all_gather(parts, mine)
+                want = sum(p_.float() for p_ in parts).to(torch.bfloat16)
+                buf = ar.buffer((256, 4096), torch.bfloat16)
+                buf.copy_(mine)
+                torch.cuda.synchronize(); dist.barrier()
+                got = ar.all_reduce_(buf).clone()
+                ar.check()
+                close = bool(((got.float() - want.float()).abs() <= 2.0 ** -7 * want.float().abs() + 1e-6).all())
+                results["autotune"] = (sorted(times) == ["multicast", "peer"], picked == min(times, key=times.get), close)
             del ar
         gathered = [None] * world
         dist.all_gather_object(gathered, results)
@@ -228,6 +244,7 @@ def test_allreduce_kernels_2gpu():
     per_rank = _run(_ar_worker)
     for res in per_rank:
         assert res["multicast_False"] is False
+        assert res.get("autotune", (True, True, True)) == (True, True, True), res.get("autotune")
         bad = {k: v for k, v in res.items() if k.startswith("mc") and v != (True, True, True, True)}
         assert not bad, {k: v for k, v in res.items() if not (k.startswith("mc") and k not in bad)}
 
