@@ -731,7 +731,7 @@ def run_gpu_arm(args):
         ar.check()
 
     chunk_ms = {}
-    chunks_used = 1
+    chunks_used, reserve_used = 1, 0
 
     def step():
         return col(x), row(h)
@@ -740,20 +740,27 @@ def run_gpu_arm(args):
         # How many row chunks the row-parallel projection is cut into is a trade between overlap (the all-reduce
         # of one chunk under the GEMM of the next) and the fixed cost of each collective.  The warm-up measures
         # the candidates (graph replays, slowest rank counts) and the timed region runs the fastest.
-        cands = [args.tp_chunks] if args.tp_chunks else [1, 2, 4]
+        # A candidate is (row chunks, SMs left to the all-reduce): with SMs reserved the chunk GEMMs run on the rest
+        # and the all-reduce runs in its multicast form beside them; with none the two kernels compete for the SMs.
+        cands = [(args.tp_chunks, 0)] if args.tp_chunks else [(1, 0), (2, 0), (4, 0)]
+        if not args.tp_chunks and ar is not None and ar.has_multicast:
+            cands += [(2, 16), (4, 16), (8, 16)]
         best = None
-        for c in cands:
-            row.overlap_chunks = c
+        for c, r in cands:
+            row.overlap_chunks, row.reserve_sms = c, r
             ms_c, g_c = time_graph(step, 10, barrier)
             g_c.reset()
             t = torch.tensor([ms_c], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            chunk_ms[str(c)] = round(float(t.item()), 4)
-            dbg(f"row chunks {c}: {chunk_ms[str(c)]} ms")
+            name = str(c) if r == 0 else f"{c} (+{r} SMs reserved)"
+            chunk_ms[name] = round(float(t.item()), 4)
+            dbg(f"row chunks {name}: {chunk_ms[name]} ms")
             if best is None or float(t.item()) < best[0]:
-                best = (float(t.item()), c)
-        chunks_used = best[1]
-        row.overlap_chunks = chunks_used
+                best = (float(t.item()), c, r)
+        chunks_used, reserve_used = best[1], best[2]
+        row.overlap_chunks, row.reserve_sms = chunks_used, reserve_used
+        if ar is not None:
+            ar.check()
 
     for _ in range(max(3, args.warmup)):
         step()
@@ -982,8 +989,9 @@ def run_gpu_arm(args):
                 "sustained": {"step_tflops": sustained_tflops, "ms_per_step": sustained_ms, "seconds": sustained_ms * reps / 1e3,
                               "sm_mhz_median": sus_clk["sm_mhz"] if sus_clk else None,
                               "power_w_max": sus_clk["power_w_max"] if sus_clk else None,
-                              "peak": peak_sust, "frac": sustained_tflops / peak_sust,
-                              "peak_source": f"2 x bf16_tflops_sustained of {pk['src']} (whole step, back to back for >= 2 s)"}}
+                              "peak": peak_sust * world, "frac": sustained_tflops / (peak_sust * world),
+                              "peak_source": f"{world} GPU(s) x 2 x bf16_tflops_sustained of {pk['src']} (whole step, all "
+                                             "ranks, back to back for >= 2 s)"}}
         if extras.get("fp8_ceiling_tflops"):
             roof["fp8_ceiling_measured"] = extras["fp8_ceiling_tflops"]
             roof["frac_of_fp8_ceiling"] = achieved / extras["fp8_ceiling_tflops"]
@@ -995,7 +1003,7 @@ def run_gpu_arm(args):
             "data": "synthetic",
             "config": {"workload": WORKLOAD,
                        "parallelism": (f"tp{world}: gate_up column-parallel, down row-parallel in {chunks_used} row chunk(s), "
-                                       f"partial outputs summed by {'this library NVLink all-reduce kernel' + (' (multicast)' if ar.multicast else ' (peer pointers)') if ar is not None else 'NCCL all-reduce'}"
+                                       f"partial outputs summed by {'this library NVLink all-reduce kernel' + (' (multicast, on ' + str(reserve_used) + ' SMs the GEMMs leave free)' if reserve_used else (' (multicast)' if ar.multicast else ' (peer pointers)')) if ar is not None else 'NCCL all-reduce'}"
                                        ) if world > 1 else "single",
                        "timing": "step replayed from a CUDA graph at every N; per-kernel times from a separate eager pass with events around each call, at every N",
                        "l2": "inputs larger than L2 (weights 396 MB e4m3 + activations 210 MB bf16 per step)",

@@ -373,6 +373,15 @@ int b200_topk_softmax(const void* gating_output, int dtype, int64_t row_stride, 
                       void* stream);
 
 /*
+ * Upper bound on the SMs the persistent kernels of this library occupy (their grids are sized by the SM count), for
+ * the calling process; 0 = all.  Returns the previous value.  A row-parallel linear that overlaps the all-reduce of
+ * one row chunk with the GEMM of the next leaves a few SMs to the all-reduce kernel this way (the reference reaches
+ * the same end with deep_gemm.set_num_sms, python/sglang/srt/layers/quantization/deep_gemm_wrapper/entrypoint.py:100-110).
+ * The value is read when a kernel is launched (or captured into a graph).
+ */
+int b200_set_sm_limit(int sms);
+
+/*
  * Sum of bf16 / fp16 buffers across 2..8 GPUs of one NVSwitch domain, one process per GPU.
  * Replaces: the reference's custom all-reduce (sgl-kernel/csrc/allreduce/custom_all_reduce.cuh, one-shot
  * and two-shot kernels over IPC peer pointers; registered as `all_reduce` in

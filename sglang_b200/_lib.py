@@ -28,6 +28,7 @@ _SIGNATURES = {
     "b200_strerror": (ctypes.c_char_p, [c_int]),
     "b200_last_cuda_error": (c_int, []),
     "b200_abi_version": (c_int, []),
+    "b200_set_sm_limit": (c_int, [c_int]),
     "b200_per_token_group_quant_fp8": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                                c_int64, c_int64, c_float, c_float, c_float, c_void_p]),
     "b200_per_token_group_quant_fp8_ieee_div": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64,

@@ -29,10 +29,15 @@ int query_device(int* dev_out) {
 }
 }  // namespace
 
+namespace {
+int g_sm_limit = 0;   // 0 = all SMs
+}
+
 int sm_count() {
   int dev = 0;
   if (query_device(&dev) != B200_OK) return -1;
-  return g_sm_count[dev];
+  const int sms = g_sm_count[dev];
+  return (g_sm_limit > 0 && g_sm_limit < sms) ? g_sm_limit : sms;
 }
 
 int require_sm100() {
@@ -43,6 +48,12 @@ int require_sm100() {
 }
 
 }  // namespace b200
+
+extern "C" int b200_set_sm_limit(int sms) {
+  const int old = b200::g_sm_limit;
+  b200::g_sm_limit = sms > 0 ? sms : 0;
+  return old;
+}
 
 extern "C" const char* b200_strerror(int code) {
   switch (code) {

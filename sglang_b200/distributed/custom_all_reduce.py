@@ -67,6 +67,7 @@ class SymmetricAllReduce:
         mc = int(self._hdl.multicast_ptr) if use_multicast else 0
         self._mc_addr = mc + self.base_offset if mc else 0
         self.multicast = mc != 0
+        self.has_multicast = mc != 0
         self._mc = ctypes.c_void_p(self._mc_addr if mc else None)
         self._status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.num_blocks = int(num_blocks)

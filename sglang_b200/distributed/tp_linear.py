@@ -70,11 +70,15 @@ class RowParallelBlockFp8Linear:
 
     overlap_chunks > 1: the rows are processed in that many chunks and the all-reduce of chunk i runs on
     a side stream while chunk i+1 is quantised and multiplied (CUDA only).  The sum per element is the
-    same collective on the same values, so results equal the unchunked form."""
+    same collective on the same values, so results equal the unchunked form.
+    reserve_sms > 0 (with overlap_chunks > 1 and a SymmetricAllReduce that has a multicast address): the GEMMs of
+    the chunks leave that many SMs free and the all-reduce runs in its multicast form on that many blocks -- the
+    form whose speed does not depend on the block count -- so the two really run side by side; without it a
+    persistent GEMM holds every SM and the collective waits for its last wave."""
 
     def __init__(self, weight, weight_scale, bias: Optional[torch.Tensor] = None, group=None,
                  linear_fn: Callable = _default_linear, reduce_results: bool = True, already_sharded: bool = False,
-                 overlap_chunks: int = 1, all_reduce=None):
+                 overlap_chunks: int = 1, all_reduce=None, reserve_sms: int = 0):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -88,6 +92,7 @@ class RowParallelBlockFp8Linear:
         self.overlap_chunks = max(1, int(overlap_chunks))
         self._comm_stream = None
         self.all_reduce = all_reduce
+        self.reserve_sms = max(0, int(reserve_sms))
 
     def _reduce(self, t: torch.Tensor) -> torch.Tensor:
         if self.all_reduce is not None:
@@ -119,17 +124,32 @@ class RowParallelBlockFp8Linear:
         out = self._out_buffer(M, x_shard)
         rows = (M + self.overlap_chunks - 1) // self.overlap_chunks
         rows = (rows + 127) // 128 * 128
-        for lo in range(0, M, rows):
-            hi = min(M, lo + rows)
-            self._linear(x_shard[lo:hi], self.weight, self.weight_scale, bias, out=out[lo:hi])
-            ready = torch.cuda.Event()
-            ready.record(main)
-            with torch.cuda.stream(self._comm_stream):
-                self._comm_stream.wait_event(ready)
-                if self.all_reduce is not None:
-                    self.all_reduce.all_reduce_(out[lo:hi])
-                else:
-                    dist.all_reduce(out[lo:hi], op=dist.ReduceOp.SUM, group=self.group)
+        ar = self.all_reduce
+        split = self.reserve_sms > 0 and ar is not None and getattr(ar, "has_multicast", False)
+        if split:
+            from ..sgl_kernel.gemm import set_sm_limit
+            sms = torch.cuda.get_device_properties(x_shard.device).multi_processor_count
+            old_limit = set_sm_limit(max(1, sms - self.reserve_sms))
+            old_form, old_blocks = ("multicast" if ar.multicast else "peer"), ar.num_blocks
+            ar.set_form("multicast")
+            ar.num_blocks = self.reserve_sms
+        try:
+            for lo in range(0, M, rows):
+                hi = min(M, lo + rows)
+                self._linear(x_shard[lo:hi], self.weight, self.weight_scale, bias, out=out[lo:hi])
+                ready = torch.cuda.Event()
+                ready.record(main)
+                with torch.cuda.stream(self._comm_stream):
+                    self._comm_stream.wait_event(ready)
+                    if ar is not None:
+                        ar.all_reduce_(out[lo:hi])
+                    else:
+                        dist.all_reduce(out[lo:hi], op=dist.ReduceOp.SUM, group=self.group)
+        finally:
+            if split:
+                set_sm_limit(old_limit)
+                ar.set_form(old_form)
+                ar.num_blocks = old_blocks
         main.wait_stream(self._comm_stream)
         return out
 

@@ -40,6 +40,16 @@ SPLIT_K_MODE = "auto"
 
 
 _PLAN: dict = {}
+_SM_LIMIT = 0
+
+
+def set_sm_limit(sms: int) -> int:
+    """At most `sms` SMs for the persistent kernels launched from now on (0 = all); returns the previous limit.
+    The counterpart of the reference's configure_deep_gemm_num_sms (deep_gemm_wrapper/entrypoint.py:100-110)."""
+    global _SM_LIMIT
+    old = _lib.lib().b200_set_sm_limit(int(sms))
+    _SM_LIMIT = max(0, int(sms))
+    return old
 
 
 def _splitk_plan(M: int, N: int, K: int, device: torch.device):
@@ -49,13 +59,15 @@ def _splitk_plan(M: int, N: int, K: int, device: torch.device):
     if SPLIT_K_MODE != "auto":
         return 1, 0
     idx = device.index if device.index is not None else torch.cuda.current_device()
-    key = (M, N, K, idx)
+    key = (M, N, K, idx, _SM_LIMIT)
     hit = _PLAN.get(key)
     if hit is not None:
         return hit
     sms = _SM_COUNT.get(idx)
     if sms is None:
         sms = _SM_COUNT[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    if _SM_LIMIT > 0:
+        sms = min(sms, _SM_LIMIT)
     import ctypes
     s, b = ctypes.c_int(1), ctypes.c_size_t(0)
     _lib.check("fp8_blockwise_scaled_mm_splitk_plan",

@@ -191,12 +191,23 @@ def _tp_custom_worker(rank, world, port, q):
         y_nccl_chunked = RowParallelBlockFp8Linear(wq, ws, bias, overlap_chunks=2)(xs).clone()
         y_custom = RowParallelBlockFp8Linear(wq, ws, bias, all_reduce=ar)(xs).clone()
         y_custom_chunked = RowParallelBlockFp8Linear(wq, ws, bias, all_reduce=ar, overlap_chunks=2)(xs).clone()
+        # chunks with SMs reserved for the collective: GEMMs on the remaining SMs, multicast all-reduce beside them;
+        # the limit and the all-reduce's form must be back to what they were afterwards
+        from sglang_b200 import _lib
+        form_before = ar.multicast
+        y_reserved = RowParallelBlockFp8Linear(wq, ws, bias, all_reduce=ar, overlap_chunks=2, reserve_sms=16)(xs).clone()
+        limit_after = _lib.lib().b200_set_sm_limit(0)
         torch.cuda.synchronize()
         ar.check()
+        ulp_ok = bool(((y_reserved.float() - y_custom.float()).abs() <= 2.0 ** -7 * y_custom.float().abs() + 1e-6).all())
         both = [torch.empty_like(y_custom) for _ in range(world)]
         dist.all_gather(both, y_custom)
+        both_r = [torch.empty_like(y_reserved) for _ in range(world)]
+        dist.all_gather(both_r, y_reserved)
         if rank == 0:
             q.put({"nccl_chunked_equal": bool(torch.equal(y_nccl, y_nccl_chunked)),
+                   "reserved_ok": ulp_ok and bool(torch.equal(both_r[0], both_r[1])) and limit_after == 0
+                                  and ar.multicast == form_before,
                    "custom_chunked_equal": bool(torch.equal(y_custom, y_custom_chunked)),
                    "custom_same_on_ranks": bool(torch.equal(both[0], both[1])),
                    "custom_err": O.rel_l2(y_custom.float().cpu(), full.float().cpu()),
@@ -252,7 +263,7 @@ def test_allreduce_kernels_2gpu():
 @needs2
 def test_tp2_custom_all_reduce_and_overlapped_chunks():
     r = _run(_tp_custom_worker)
-    assert r["nccl_chunked_equal"] and r["custom_chunked_equal"] and r["custom_same_on_ranks"], r
+    assert r["nccl_chunked_equal"] and r["custom_chunked_equal"] and r["custom_same_on_ranks"] and r["reserved_ok"], r
     # two bf16 partial outputs summed: each carries its own rounding (about 2^-9 relative)
     assert r["custom_err"] < 5e-3 and r["nccl_err"] < 5e-3, r
 
