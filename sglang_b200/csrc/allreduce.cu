@@ -98,6 +98,43 @@ __device__ __forceinline__ Vec16 peer_sum(const ArParams& p, int64_t byte_off) {
   return o;
 }
 
+// U 16-byte vectors of this rank's slice, summed over the ranks (through the switch or from every peer).
+template <typename T, bool MULTIMEM, int U>
+__device__ __forceinline__ void twoshot_load(const ArParams& p, int64_t base, int64_t i0, int64_t stride, int64_t nvec,
+                                             Vec16 (&v)[U]) {
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const int64_t i = i0 + u * stride;
+    if (i < nvec) {
+      if constexpr (MULTIMEM) v[u] = multimem_ld_reduce<T>(static_cast<const char*>(p.mc) + base + i * 16);
+      else v[u] = peer_sum<T>(p, base + i * 16);
+    }
+  }
+}
+// ... and stored to every rank.
+template <bool MULTIMEM, int U>
+__device__ __forceinline__ void twoshot_store(const ArParams& p, int64_t base, int64_t i0, int64_t stride, int64_t nvec,
+                                              const Vec16 (&v)[U]) {
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const int64_t i = i0 + u * stride;
+    if (i < nvec) {
+      if constexpr (MULTIMEM) {
+        multimem_st(static_cast<char*>(p.mc) + base + i * 16, v[u]);
+      } else {
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r)
+          if (r < p.world) *reinterpret_cast<Vec16*>(static_cast<char*>(p.peers[r]) + base + i * 16) = v[u];
+      }
+    }
+  }
+}
+
+// The loads of a rank's slice travel one way over NVLink (every rank SENDS its contribution to the sums), the stores
+// the other way (every rank RECEIVES every slice).  A loop that loads, waits and then stores uses the two directions
+// in turn -- and all blocks of all ranks leave the opening barrier in step, so the whole machine alternates.  The
+// loop is therefore software-pipelined: the loads of batch i+1 are issued before the stores of batch i, and both
+// directions carry data at the same time.
 template <typename T, bool MULTIMEM>
 __global__ void __launch_bounds__(kArThreads) allreduce_twoshot_kernel(const ArParams p) {
   rank_barrier(p.sync, 21);   // every rank's partial values are in its buffer
@@ -105,30 +142,21 @@ __global__ void __launch_bounds__(kArThreads) allreduce_twoshot_kernel(const ArP
   const int64_t base = p.offset_bytes + slice * p.rank;
   const int64_t nvec = slice / 16;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  constexpr int U = 8;   // 16-byte vectors in flight per thread: NVLink round trips are microseconds long
-  for (int64_t i0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < nvec; i0 += stride * U) {
-    Vec16 v[U];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int64_t i = i0 + u * stride;
-      if (i < nvec) {
-        if constexpr (MULTIMEM) v[u] = multimem_ld_reduce<T>(static_cast<const char*>(p.mc) + base + i * 16);
-        else v[u] = peer_sum<T>(p, base + i * 16);
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int64_t i = i0 + u * stride;
-      if (i < nvec) {
-        if constexpr (MULTIMEM) {
-          multimem_st(static_cast<char*>(p.mc) + base + i * 16, v[u]);
-        } else {
-#pragma unroll
-          for (int r = 0; r < kMaxRanks; ++r)
-            if (r < p.world) *reinterpret_cast<Vec16*>(static_cast<char*>(p.peers[r]) + base + i * 16) = v[u];
-        }
-      }
-    }
+  // 16-byte vectors per batch and thread; two batches are live at a time (the peer form holds one vector per rank
+  // for each of them while it sums)
+  constexpr int U = MULTIMEM ? 4 : 2;
+  const int64_t step = stride * U;
+  int64_t i0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  Vec16 a[U], b[U];
+  if (i0 < nvec) twoshot_load<T, MULTIMEM, U>(p, base, i0, stride, nvec, a);
+  while (i0 < nvec) {
+    if (i0 + step < nvec) twoshot_load<T, MULTIMEM, U>(p, base, i0 + step, stride, nvec, b);
+    twoshot_store<MULTIMEM, U>(p, base, i0, stride, nvec, a);
+    i0 += step;
+    if (i0 >= nvec) break;
+    if (i0 + step < nvec) twoshot_load<T, MULTIMEM, U>(p, base, i0 + step, stride, nvec, a);
+    twoshot_store<MULTIMEM, U>(p, base, i0, stride, nvec, b);
+    i0 += step;
   }
   __threadfence_system();
   rank_barrier(p.sync, 22);   // every slice has reached every rank

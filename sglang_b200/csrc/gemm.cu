@@ -689,6 +689,9 @@ int plan_split_k(int64_t M, int64_t N, int64_t K, int sms) {
       if (nkb / s2 >= 8 && fill(tiles * s2) >= 0.75) return s2;
     return 1;
   }
+  // (A byte model that picks the count with the best fill of the SMs' wave slots -- 5 for 56 tiles, 3 for 80 -- was
+  // measured no better than this rule: 31.5 against 30.1 us on the 56-tile down projection at 64 tokens, 23.8 against
+  // 22.5 us on the 80-tile qkv projection; fewer CTAs each pull more than their share of the HBM bandwidth.)
   int64_t s = sms / tiles;
   if (s > nkb / 8) s = nkb / 8;  // at least eight k-blocks per CTA
   if (s > 16) s = 16;

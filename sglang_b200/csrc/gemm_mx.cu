@@ -12,7 +12,8 @@
 //  python/sglang/srt/layers/deep_gemm_wrapper/entrypoint.py:78-93 gemm_nt_f8f8bf16,
 //  weights re-quantised to power-of-two scales by requant_weight_ue8m0, fp8_utils.py:370-443).
 //
-// One persistent CTA per SM, 128 x 256 (or 256 x 240) tiles, 8 warps:
+// Three forms: 128 x 256 and 256 x 240 tiles on one CTA per SM (below), and 256 x 256 tiles on a CTA pair
+// (cta_group::2, further down).  One persistent CTA per SM, 8 warps:
 //   warps 0-3  epilogue: after a tile's last k-block, each reads its rows of the accumulator(s) from tensor memory,
 //              converts and stores; then hands the accumulator back.
 //   warp 4     TMA producer: A box + B box per k-block, 128-byte swizzle, no multicast.
@@ -482,6 +483,342 @@ int launch_mx_dtype(const void* a, int64_t lda, const void* b, int64_t ldb, cons
   }
 }
 
+
+// ============================================================================================ CTA-pair form
+// Two CTAs of a cluster work on one 256 x 256 tile (tcgen05 cta_group::2): each CTA loads its own 128 rows of A
+// and HALF of the weight tile (128 of the 256 columns) per k-block, the leader CTA's elected thread issues
+// M256 x N256 x K32 MMAs that both SMs execute, each on its own rows with the weight halves of both.  Per SM and
+// k-block that is 32 KB written to and 32 KB read from shared memory and 32 KB fetched from L2 for 512 tensor
+// cycles -- the single-CTA form moves 48 + 48 + 48 KB -- so the operand feed no longer sets the pace.
+// Scale factors: every CTA's stager builds the tile of its OWN rows and the tile of ALL 256 columns in its own
+// shared memory; the leader's tcgen05.cp.cta_group::2 copies, in each CTA, that CTA's tiles into its tensor memory
+// (like the MMA, the copy acts on both CTAs with the same shared-memory offset and the same tensor-memory address).
+// Barriers: operands -> the leader's full barrier (both CTAs' loads credit it); scale tiles -> the leader's
+// sf_full (one arrival per CTA, cluster-scope release); completions are committed to both CTAs at once
+// (stage reusable, scale slot reusable, accumulator ready); accumulator drained -> the leader's acc_empty
+// (four epilogue warps of each CTA).
+constexpr int kPairStages = 6;
+constexpr int kPairABytes = BM * BK;            // 128 rows of A per CTA
+constexpr int kPairBBytes = 128 * BK;           // 128 of the tile's 256 weight rows per CTA
+constexpr int kPairStageBytes = kPairABytes + kPairBBytes;
+constexpr int kPairSfBytes = kSfaBytes + kSfbBytes;
+constexpr int kPairSmem = kPairStages * kPairStageBytes + kSfSlots * kPairSfBytes + 1024 + 256;
+constexpr uint32_t kPairSfaCol = 256, kPairSfbCol = 260;
+static_assert(kPairSmem <= 227 * 1024, "shared memory");
+
+__device__ __forceinline__ void tmem_cp_sf_pair(uint32_t taddr, uint64_t desc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void umma_mx_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], %1, %2, %3, [%4], [%5], p;\n\t}\n"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+      : "memory");
+}
+// Arrival on the leader CTA's barrier that publishes this CTA's shared-memory writes to the cluster.
+__device__ __forceinline__ void mbar_arrive_leader_release(uint64_t* bar) {
+  asm volatile(
+      "{\n\t.reg .b32 remote;\n\t"
+      "mapa.shared::cluster.u32 remote, %0, 0;\n\t"
+      "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [remote];\n\t}\n"
+      ::"r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 P, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, P;\n\t}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, int* status, int code) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (!mbar_try_wait_cluster(bar, parity)) {
+    if ((++spins & 0xffu) == 0) {
+      if (*reinterpret_cast<volatile int*>(status) != 0) return false;
+      if (clock64() - t0 > kWaitLimitCycles) {
+        report_wait_failure(status, code);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(kThreadsMx, 1)
+gemm_mx_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const MxParams p) {
+  constexpr int kTileM = 2 * BM, kTileN = 256;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + kPairStages * kPairABytes;
+  uint8_t* smem_sf = smem + kPairStages * kPairStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_sf + kSfSlots * kPairSfBytes);
+  uint64_t* full_bar = bars;                        // leader's copy is live: operands of both CTAs landed
+  uint64_t* empty_bar = full_bar + kPairStages;     // per CTA: the k-block's MMAs completed
+  uint64_t* sf_full = empty_bar + kPairStages;      // leader's copy is live: both CTAs' scale tiles written
+  uint64_t* sf_empty = sf_full + kSfSlots;          // per CTA: the slot's k-blocks completed
+  uint64_t* acc_full = sf_empty + kSfSlots;         // per CTA: the tile's last MMA completed
+  uint64_t* acc_empty = acc_full + 1;               // leader's copy is live: both CTAs have read their accumulators
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair_id = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int m_blocks = (p.M + kTileM - 1) / kTileM;
+  const int n_blocks = (p.N + kTileN - 1) / kTileN;
+  const int nkb = (p.K + BK - 1) / BK;
+  const int num_tiles = m_blocks * n_blocks;
+
+  cluster_sync_all();   // both CTAs are resident before tensor memory is paired
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kPairStages; ++i) {
+      mbar_init(&full_bar[i], 2);    // one arrival per CTA's producer (+ both CTAs' bytes)
+      mbar_init(&empty_bar[i], 1);   // the leader's commit, delivered to both CTAs
+    }
+    for (int i = 0; i < kSfSlots; ++i) {
+      mbar_init(&sf_full[i], 2);     // one arrival per CTA's stager
+      mbar_init(&sf_empty[i], 1);
+    }
+    mbar_init(acc_full, 1);
+    mbar_init(acc_empty, 8);         // four epilogue warps in each CTA
+    fence_mbar_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 4 && lane == 0) {
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+  }
+  if (warp == 5) {
+    tmem_alloc_pair(tmem_slot, 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ TMA producer (each CTA)
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = pair_id; ok && tile < num_tiles; tile += num_pairs) {
+      int m_blk, n_blk;
+      mx_tile_coords(tile, m_blocks, n_blocks, m_blk, n_blk);
+      const int row_a = m_blk * kTileM + static_cast<int>(rank) * BM;
+      const int row_b = n_blk * kTileN + static_cast<int>(rank) * 128;
+      for (int kb = 0; kb < nkb; ++kb) {
+        ok = mbar_wait_warp(&empty_bar[stage], phase ^ 1u, p.status, 51);
+        if (!ok) break;
+        if (elect_one()) {
+          if (leader) mbar_expect_tx(&full_bar[stage], 2 * kPairStageBytes);
+          tma_load_2d_pair(smem_a + stage * kPairABytes, &map_a, &full_bar[stage], kb * BK, row_a);
+          tma_load_2d_pair(smem_b + stage * kPairBBytes, &map_b, &full_bar[stage], kb * BK, row_b);
+          if (!leader) mbar_arrive_cluster(&full_bar[stage], 0);
+        }
+        __syncwarp();
+        if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (leader) {
+      const uint64_t a_desc0 = umma_desc_k128(smem_u32(smem_a));
+      const uint64_t b_desc0 = umma_desc_k128(smem_u32(smem_b));
+      int stage = 0, slot = 0;
+      uint32_t phase = 0, sphase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int tile = pair_id; ok && tile < num_tiles; tile += num_pairs) {
+        ok = mbar_wait(acc_empty, acc_phase ^ 1u, p.status, 52);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        for (int kb = 0; kb < nkb; ++kb) {
+          ok = mbar_wait(&full_bar[stage], phase, p.status, 53);
+          const int j = kb & 3;
+          if (ok && j == 0) ok = mbar_wait_cluster(&sf_full[slot], sphase, p.status, 54);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+          const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(stage * (kPairABytes >> 4));
+          const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(stage * (kPairBBytes >> 4));
+          const uint32_t idesc = idesc_mx(kTileM, kTileN, static_cast<uint32_t>(j));
+          const bool last_kb = (kb == nkb - 1);
+          if (elect_one()) {
+            if (j == 0) {
+              const uint32_t sf_addr = smem_u32(smem_sf + slot * kPairSfBytes);
+              tmem_cp_sf_pair(tmem_base + kPairSfaCol, sf_desc(sf_addr));
+              tmem_cp_sf_pair(tmem_base + kPairSfbCol, sf_desc(sf_addr + kSfaBytes));
+              tmem_cp_sf_pair(tmem_base + kPairSfbCol + 4, sf_desc(sf_addr + kSfaBytes + 512));
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              umma_mx_pair(tmem_base, a_desc + static_cast<uint64_t>(2 * k), b_desc + static_cast<uint64_t>(2 * k), idesc,
+                           tmem_base + kPairSfaCol, tmem_base + kPairSfbCol, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_commit_pair(&empty_bar[stage], 3);
+            if (j == 3 || last_kb) umma_commit_pair(&sf_empty[slot], 3);
+            if (last_kb) umma_commit_pair(acc_full, 3);
+          }
+          __syncwarp();
+          if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+          if (j == 3 || last_kb) {
+            if (++slot == kSfSlots) { slot = 0; sphase ^= 1u; }
+          }
+        }
+        acc_phase ^= 1u;
+      }
+    }
+    __syncwarp();
+  } else if (warp == 6) {
+    // ------------------------------------------------------------------ scale-factor stager (each CTA)
+    int slot = 0;
+    uint32_t sphase = 0;
+    bool ok = true;
+    for (int tile = pair_id; ok && tile < num_tiles; tile += num_pairs) {
+      int m_blk, n_blk;
+      mx_tile_coords(tile, m_blocks, n_blocks, m_blk, n_blk);
+      const int row0 = m_blk * kTileM + static_cast<int>(rank) * BM;
+      for (int kb0 = 0; kb0 < nkb; kb0 += 4) {
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int row = row0 + lane + 32 * j;
+          w[j] = (row < p.M) ? __ldg(p.sa + static_cast<int64_t>(kb0 >> 2) * p.sa_stride_pack + row * p.sa_stride_m) : 0u;
+        }
+        uint32_t wb[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int col = min(n_blk * kTileN + (i >> 2) * 128 + (i & 3) * 32 + lane, p.N - 1);
+          const float* sp = p.sb + static_cast<int64_t>(col >> 7) * p.sb_stride_n;
+          uint32_t word = 0;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int kb = min(kb0 + k, nkb - 1);
+            word |= ((__float_as_uint(__ldg(sp + static_cast<int64_t>(kb) * p.sb_stride_g)) >> 23) & 0xffu) << (8 * k);
+          }
+          wb[i] = word;
+        }
+        ok = mbar_wait_warp(&sf_empty[slot], sphase ^ 1u, p.status, 55);
+        if (!ok) break;
+        uint8_t* sf = smem_sf + slot * kPairSfBytes;
+        *reinterpret_cast<uint4*>(sf + lane * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(sf + kSfaBytes + lane * 16) = make_uint4(wb[0], wb[1], wb[2], wb[3]);
+        *reinterpret_cast<uint4*>(sf + kSfaBytes + 512 + lane * 16) = make_uint4(wb[4], wb[5], wb[6], wb[7]);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_leader_release(&sf_full[slot]);
+        if (++slot == kSfSlots) { slot = 0; sphase ^= 1u; }
+      }
+    }
+    __syncwarp();
+  } else if (warp < 4) {
+    // ------------------------------------------------------------------ epilogue (each CTA, its own 128 rows)
+    OutT* out = static_cast<OutT*>(p.out);
+    const bool vec_ok = (p.ldo % (16 / (int)sizeof(OutT)) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15u) == 0);
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = pair_id; ok && tile < num_tiles; tile += num_pairs) {
+      int m_blk, n_blk;
+      mx_tile_coords(tile, m_blocks, n_blocks, m_blk, n_blk);
+      ok = mbar_wait(acc_full, acc_phase, p.status, 56);
+      if (!ok) break;
+      tc_fence_after();
+      const int m = m_blk * kTileM + static_cast<int>(rank) * BM + warp * 32 + lane;
+      const uint32_t taddr = tmem_base + lane_addr;
+      constexpr int kChunks = kTileN / 16;
+#pragma unroll 1
+      for (int ch = 0; ch < kChunks; ch += 2) {
+        float v[32];
+        tmem_ld16(taddr + ch * 16, *reinterpret_cast<float(*)[16]>(v));
+        tmem_ld16(taddr + (ch + 1) * 16, *reinterpret_cast<float(*)[16]>(v + 16));
+        tmem_ld_wait();
+        if (ch + 2 >= kChunks) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(acc_empty, 0);
+        }
+        const int n0 = n_blk * kTileN + ch * 16;
+        if (m < p.M && n0 < p.N) store_row<32>(out + static_cast<int64_t>(m) * p.ldo + n0, v, min(p.N - n0, 32), vec_ok);
+      }
+      acc_phase ^= 1u;
+    }
+  }
+
+  tc_fence_before();
+  cluster_sync_all();
+  if (*reinterpret_cast<volatile int*>(p.status) != 0) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, 512);
+  }
+}
+
+template <typename OutT>
+int launch_mx_pair(const CUtensorMap& ma, const CUtensorMap& mb, const MxParams& p, cudaStream_t stream) {
+  auto kern = gemm_mx_pair_kernel<OutT>;
+  static int max_pairs[64] = {0};
+  int dev = 0;
+  B200_CUDA_TRY(cudaGetDevice(&dev));
+  dev &= 63;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(kThreadsMx);
+  cfg.dynamicSmemBytes = kPairSmem;
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (max_pairs[dev] == 0) {
+    B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmem));
+    cfg.gridDim = dim3(2 * 74);
+    int n = 0;
+    B200_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, kern, &cfg));
+    if (n <= 0) return B200_ERR_UNSUPPORTED;
+    max_pairs[dev] = n;
+  }
+  const long long tiles = static_cast<long long>((p.M + 255) / 256) * ((p.N + 255) / 256);
+  int pairs = sm_count() / 2;
+  if (pairs > max_pairs[dev]) pairs = max_pairs[dev];
+  if (tiles < pairs) pairs = static_cast<int>(tiles);
+  cfg.gridDim = dim3(2 * pairs);
+  B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ma, mb, p));
+  return B200_OK;
+}
+
+int launch_mx_pair_dtype(const void* a, int64_t lda, const void* b, int64_t ldb, const MxParams& p, cudaStream_t st) {
+  CUtensorMap ma, mb;
+  int rc = make_map_u8_2d(&ma, a, p.M, p.K, lda, BM);
+  if (rc != B200_OK) return rc;
+  rc = make_map_u8_2d(&mb, b, p.N, p.K, ldb, 128);
+  if (rc != B200_OK) return rc;
+  switch (p.out_dtype) {
+    case B200_DT_BF16: return launch_mx_pair<__nv_bfloat16>(ma, mb, p, st);
+    case B200_DT_F16: return launch_mx_pair<__half>(ma, mb, p, st);
+    default: return launch_mx_pair<float>(ma, mb, p, st);
+  }
+}
+
 }  // namespace
 
 extern int g_force_block_n;
@@ -517,14 +854,21 @@ extern "C" int b200_fp8_blockwise_scaled_mm_pow2(const void* a, int64_t lda, con
   p.status = gemm_status_ptr();
   if (!p.status) return B200_ERR_CUDA;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // Tile choice.  Measured (us; 4096 x 36864 x 7168 / 4096 x 7168 x 18432 / 16384 x 7168 x 18432): 128 x 256 tiles
-  // 875 / 491 / 1813, 256 x 240 tiles 879 / 479 / 1801, 128 x 240 tiles (two accumulators) 940 / 502 / 1948.  The
-  // two-half tile pays off on long K (fewer, longer tiles amortise its unoverlapped read-out); the 128 x 240 tile
-  // never did and is reachable only through the test hook (values 256 / 240 / 2240 select a tile directly).
+  // Tile choice.  Measured (us; 1024 / 4096 x 36864 x 7168, then 1024 / 4096 / 16384 x 7168 x 18432):
+  //   128 x 256, one CTA        252 / 873    171 / 541 / 1793
+  //   256 x 240, one CTA        261 / 876    136 / 543 / 1640
+  //   256 x 256 on a CTA pair   226 / 848    172 / 566 / 1973
+  // (128 x 240 with two accumulators: 940 on the second shape, never ahead.)  Long K favours the two-half tile
+  // (fewer, longer tiles amortise its unoverlapped read-out), wide N with K up to 8192 the CTA pair (half the
+  // operand bytes per SM).  With every SM issuing MMAs back to back and nothing else the chip settles at 1.5 GHz
+  // under its power cap (3.7 PFLOP/s); these kernels reach 2.5-2.7 and slow down the longer they run.
+  // The test hook selects a form directly: 256 / 240 / 2240 / 2256.
+  if (g_force_block_n == 2256) return launch_mx_pair_dtype(a, lda, b, ldb, p, st);
   if (g_force_block_n == 256) return launch_mx_dtype<256, 1>(a, lda, b, ldb, p, st);
   if (g_force_block_n == 240) return launch_mx_dtype<240, 1>(a, lda, b, ldb, p, st);
   if (g_force_block_n == 2240) return launch_mx_dtype<240, 2>(a, lda, b, ldb, p, st);
-  if (M >= 2048 && K >= 12288) return launch_mx_dtype<240, 2>(a, lda, b, ldb, p, st);
+  if (M >= 1024 && K >= 12288) return launch_mx_dtype<240, 2>(a, lda, b, ldb, p, st);
+  if (M >= 512 && N >= 4096) return launch_mx_pair_dtype(a, lda, b, ldb, p, st);
   return launch_mx_dtype<256, 1>(a, lda, b, ldb, p, st);
 }
 

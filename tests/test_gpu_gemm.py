@@ -425,7 +425,8 @@ def test_power_of_two_scales_on_the_block_scaling_mma(M, N, K):
     from sglang_b200 import _lib
     ref32 = O.block_fp8_matmul_fp32(q_ref, wq, s_ref, ws)
     soft = w8a8_block_fp8_matmul_deepgemm(q, wq.cuda(), s_packed, ws.cuda(), [128, 128], torch.bfloat16).cpu()
-    for tile_width in (0, 240, 2240):     # 128 x 256 (one accumulator), 128 x 240 (two), 256 x 240 (two row halves)
+    # 128 x 256 (one accumulator), 128 x 240 (two), 256 x 240 (two row halves), 256 x 256 on a CTA pair
+    for tile_width in (0, 240, 2240, 2256):
         _lib.lib().b200_debug_force_block_n(tile_width)
         try:
             out = w8a8_block_fp8_matmul_deepgemm(q, wq.cuda(), s_packed, ws.cuda(), [128, 128], torch.bfloat16,
