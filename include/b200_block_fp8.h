@@ -109,6 +109,25 @@ int b200_silu_mul_per_token_group_quant_fp8_ue8m0(const void* x, int x_dtype, vo
                                                   float fp8_max, void* stream);
 
 /*
+ * RMSNorm fused with the per-token-group (128) FP8 quantisation of its output -- the producer-side fusion of the
+ * linear's quant stage.  y = T((x * rsqrt(mean(x^2) + norm_eps)) * weight) in fp32, rounded to x's type T exactly
+ * as a separate norm kernel stores it, then quantised like b200_per_token_group_quant_fp8: codes and scales equal the
+ * two-kernel sequence bit for bit, the [M, K] activation makes one trip through HBM instead of three.
+ * residual != NULL: x + residual (fp32) is normalised and written back to residual rounded to T (fused_add_rmsnorm).
+ * y != NULL: the normalised row is also stored.  q == s == NULL: the norm alone (y required).
+ * scale_ue8m0 != 0: s is the packed exponent tensor (s_stride_grp = stride between packed words >= M).
+ * x, residual, y: [M, K] contiguous bf16 / fp16; weight [K]; K % 128 == 0, K <= 16384.
+ * Replaces: RMSNorm.forward (python/sglang/srt/layers/layernorm.py:78-171; sgl_kernel.rmsnorm /
+ * fused_add_rmsnorm, sgl-kernel/python/sgl_kernel/elementwise.py:9-82) followed by
+ * sglang_per_token_group_quant_fp8 at the head of w8a8_block_fp8_linear
+ * (python/sglang/srt/layers/quantization/fp8_utils.py:199-201).
+ */
+int b200_rmsnorm_per_token_group_quant_fp8(const void* x, int x_dtype, void* residual, const void* weight, float norm_eps,
+                                           void* y, void* q, void* s, int64_t M, int64_t K, int64_t s_stride_row,
+                                           int64_t s_stride_grp, int scale_ue8m0, float eps, float fp8_min,
+                                           float fp8_max, void* stream);
+
+/*
  * Per-token-group (128) quantisation with a row gather: row r of q / s = the quantisation of row src_rows[r] of
  * x [x_rows, K] (indices clamped into the rows of x).  Same bits as quantising x and gathering codes and scales
  * afterwards.  scale_ue8m0 == 0: fp32 scales, element (r, g) at s[r * s_stride_row + g * s_stride_grp];

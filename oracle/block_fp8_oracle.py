@@ -269,6 +269,24 @@ def block_fp8_linear(x, w_q, w_s, bias=None, out_dtype=torch.bfloat16):
 
 
 # --------------------------------------------------------------------------------------
+# Producer of the linear's input
+# --------------------------------------------------------------------------------------
+def rmsnorm_native(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, residual: Optional[torch.Tensor] = None):
+    """RMSNorm.forward_native (python/sglang/srt/layers/layernorm.py:135-171): fp32 throughout --
+    x (+ residual, which is returned rounded to the input type), x * rsqrt(mean(x^2) + eps), * weight -- and one
+    rounding to the input type at the end.  Returns y, or (y, residual_out)."""
+    orig = x.dtype
+    xf = x.to(torch.float32)
+    res_out = None
+    if residual is not None:
+        xf = xf + residual.to(torch.float32)
+        res_out = xf.to(orig)
+    var = xf.pow(2).mean(dim=-1, keepdim=True)
+    y = ((xf * torch.rsqrt(var + eps)) * weight).to(orig)
+    return y if residual is None else (y, res_out)
+
+
+# --------------------------------------------------------------------------------------
 # MoE glue
 # --------------------------------------------------------------------------------------
 def silu_and_mul(x: torch.Tensor) -> torch.Tensor:

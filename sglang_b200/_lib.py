@@ -61,6 +61,9 @@ _SIGNATURES = {
     "b200_gather_per_token_group_quant_fp8": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_int64,
                                                       c_int64, c_int64, c_int64, c_int, c_float, c_float, c_float,
                                                       c_void_p]),
+    "b200_rmsnorm_per_token_group_quant_fp8": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
+                                                       c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_float,
+                                                       c_float, c_float, c_void_p]),
     "b200_gemm_device_status": (c_int, [ctypes.POINTER(c_int)]),
     "b200_gemm_poll_status": (c_int, [ctypes.POINTER(c_int)]),
     "b200_fp8_blockwise_scaled_grouped_mm": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64,

@@ -42,6 +42,15 @@ struct Vec16<__nv_bfloat16> {
     v[1] = __ldcs(p4 + 1);
   }
   __device__ __forceinline__ void zero() { v[0] = v[1] = make_uint4(0, 0, 0, 0); }
+  __device__ __forceinline__ void load_cached(const __nv_bfloat16* p) {   // reused data: default caching
+    const uint4* p4 = reinterpret_cast<const uint4*>(p);
+    v[0] = __ldg(p4);
+    v[1] = __ldg(p4 + 1);
+  }
+  __device__ __forceinline__ void store(__nv_bfloat16* p) const {
+    reinterpret_cast<uint4*>(p)[0] = v[0];
+    reinterpret_cast<uint4*>(p)[1] = v[1];
+  }
   __device__ __forceinline__ float get(int i) const {
     const uint32_t* w = reinterpret_cast<const uint32_t*>(v);
     const uint32_t word = w[i >> 1];
@@ -62,6 +71,15 @@ struct Vec16<__half> {
     v[1] = __ldcs(p4 + 1);
   }
   __device__ __forceinline__ void zero() { v[0] = v[1] = make_uint4(0, 0, 0, 0); }
+  __device__ __forceinline__ void load_cached(const __half* p) {
+    const uint4* p4 = reinterpret_cast<const uint4*>(p);
+    v[0] = __ldg(p4);
+    v[1] = __ldg(p4 + 1);
+  }
+  __device__ __forceinline__ void store(__half* p) const {
+    reinterpret_cast<uint4*>(p)[0] = v[0];
+    reinterpret_cast<uint4*>(p)[1] = v[1];
+  }
   __device__ __forceinline__ float get(int i) const {
     const __half2* h = reinterpret_cast<const __half2*>(v);
     const float2 f = __half22float2(h[i >> 1]);
@@ -96,6 +114,58 @@ __device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float 
   const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
   const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
   return lo | (hi << 16);
+}
+
+// The 16 codes of one thread: x / scale correctly rounded, clamped, converted (see the file header).
+template <typename T, bool IEEE_DIV>
+__device__ __forceinline__ uint4 quantise_vec16(const Vec16<T>& data, float scale, float fp8_min, float fp8_max) {
+  const bool std_range = (fp8_max == 448.0f) && (fp8_min == -448.0f);
+  bool fast = !IEEE_DIV && std_range;
+  if (fast) {
+    const uint32_t bits = __float_as_uint(scale);
+    // all-ones significand or Inf/NaN scale: leave the fast form
+    fast = ((bits & 0x007fffffu) != 0x007fffffu) && ((bits & 0x7f800000u) != 0x7f800000u);
+  }
+  uint4 out;
+  bool need_slow = !fast;
+  if (fast) {
+    // Correctly rounded x/scale from the correctly rounded reciprocal (Markstein): q0 = x*r,
+    // t = fma(q0, scale, -x) = -(x - q0*scale) exactly, q = fma(-t, r, q0).  Written with t = -rem so
+    // that a zero x keeps its sign through both fmas (-0 stays -0, +0 stays +0), as x/scale does.
+    // |q| <= 448*(1 + 2^-23): the saturating conversion clamps that, so no explicit clamp is needed;
+    // only a NaN input must become fp8_min (fmaxf(NaN, lo) = lo in the reference): NaN survives the
+    // arithmetic and converts to code 0x7f / 0xff, which is detected on the packed codes below.
+    const float r = __frcp_rn(scale);
+    float y[kVec];
+#pragma unroll
+    for (int i = 0; i < kVec; ++i) {
+      const float v = data.get(i);
+      const float q0 = __fmul_rn(v, r);
+      const float t = __fmaf_rn(q0, scale, -v);
+      y[i] = __fmaf_rn(-t, r, q0);
+    }
+    out.x = pack4_e4m3(y[0], y[1], y[2], y[3]);
+    out.y = pack4_e4m3(y[4], y[5], y[6], y[7]);
+    out.z = pack4_e4m3(y[8], y[9], y[10], y[11]);
+    out.w = pack4_e4m3(y[12], y[13], y[14], y[15]);
+    // a byte with all seven low bits set is a NaN code: (b & 0x7f) + 1 carries into bit 7
+    const uint32_t m7 = 0x7f7f7f7fu, one = 0x01010101u;
+    const uint32_t nan_bits = (((out.x & m7) + one) | ((out.y & m7) + one) | ((out.z & m7) + one) |
+                               ((out.w & m7) + one)) & 0x80808080u;
+    need_slow = nan_bits != 0;
+  }
+  if (need_slow) {
+    // the reference's expression, literally
+    float y[kVec];
+#pragma unroll
+    for (int i = 0; i < kVec; ++i)
+      y[i] = fminf(fmaxf(__fdiv_rn(data.get(i), scale), fp8_min), fp8_max);
+    out.x = pack4_e4m3(y[0], y[1], y[2], y[3]);
+    out.y = pack4_e4m3(y[4], y[5], y[6], y[7]);
+    out.z = pack4_e4m3(y[8], y[9], y[10], y[11]);
+    out.w = pack4_e4m3(y[12], y[13], y[14], y[15]);
+  }
+  return out;
 }
 
 // FUSE_SILU: x is [M, 2K] (gate | up); the row to quantise is silu(gate) * up, computed in fp32 and
@@ -168,52 +238,7 @@ quant_group_kernel(const T* __restrict__ x, const int32_t* __restrict__ src_rows
 
     float scale = __fdiv_rn(amax, fp8_max);
     if constexpr (UE8M0) scale = exp2f(ceilf(log2f(fmaxf(scale, 1e-10f))));
-    const bool std_range = (fp8_max == 448.0f) && (fp8_min == -448.0f);
-    bool fast = !IEEE_DIV && std_range;
-    if (fast) {
-      const uint32_t bits = __float_as_uint(scale);
-      // all-ones significand or Inf/NaN scale: leave the fast form
-      fast = ((bits & 0x007fffffu) != 0x007fffffu) && ((bits & 0x7f800000u) != 0x7f800000u);
-    }
-    uint4 out;
-    bool need_slow = !fast;
-    if (fast) {
-      // Correctly rounded x/scale from the correctly rounded reciprocal (Markstein): q0 = x*r,
-      // t = fma(q0, scale, -x) = -(x - q0*scale) exactly, q = fma(-t, r, q0).  Written with t = -rem so
-      // that a zero x keeps its sign through both fmas (-0 stays -0, +0 stays +0), as x/scale does.
-      // |q| <= 448*(1 + 2^-23): the saturating conversion clamps that, so no explicit clamp is needed;
-      // only a NaN input must become fp8_min (fmaxf(NaN, lo) = lo in the reference): NaN survives the
-      // arithmetic and converts to code 0x7f / 0xff, which is detected on the packed codes below.
-      const float r = __frcp_rn(scale);
-      float y[kVec];
-#pragma unroll
-      for (int i = 0; i < kVec; ++i) {
-        const float v = data[p].get(i);
-        const float q0 = __fmul_rn(v, r);
-        const float t = __fmaf_rn(q0, scale, -v);
-        y[i] = __fmaf_rn(-t, r, q0);
-      }
-      out.x = pack4_e4m3(y[0], y[1], y[2], y[3]);
-      out.y = pack4_e4m3(y[4], y[5], y[6], y[7]);
-      out.z = pack4_e4m3(y[8], y[9], y[10], y[11]);
-      out.w = pack4_e4m3(y[12], y[13], y[14], y[15]);
-      // a byte with all seven low bits set is a NaN code: (b & 0x7f) + 1 carries into bit 7
-      const uint32_t m7 = 0x7f7f7f7fu, one = 0x01010101u;
-      const uint32_t nan_bits = (((out.x & m7) + one) | ((out.y & m7) + one) | ((out.z & m7) + one) |
-                                 ((out.w & m7) + one)) & 0x80808080u;
-      need_slow = nan_bits != 0;
-    }
-    if (need_slow) {
-      // the reference's expression, literally
-      float y[kVec];
-#pragma unroll
-      for (int i = 0; i < kVec; ++i)
-        y[i] = fminf(fmaxf(__fdiv_rn(data[p].get(i), scale), fp8_min), fp8_max);
-      out.x = pack4_e4m3(y[0], y[1], y[2], y[3]);
-      out.y = pack4_e4m3(y[4], y[5], y[6], y[7]);
-      out.z = pack4_e4m3(y[8], y[9], y[10], y[11]);
-      out.w = pack4_e4m3(y[12], y[13], y[14], y[15]);
-    }
+    const uint4 out = quantise_vec16<T, IEEE_DIV>(data[p], scale, fp8_min, fp8_max);
     if (col_ok && row < M) *reinterpret_cast<uint4*>(q + row * K + col) = out;
     if ((slot % TPG) == 0) s_tile[(p * ROWS_PER_PASS + row_in_pass) * GPT + slot / TPG] = scale;
   }
@@ -253,6 +278,106 @@ quant_group_kernel(const T* __restrict__ x, const int32_t* __restrict__ src_rows
       g = idx % GPT;
     }
     if (r0 + r < M && g0 + g < G) s[(r0 + r) * s_stride_row + (g0 + g) * s_stride_grp] = s_tile[r * GPT + g];
+  }
+}
+
+// ------------------------------------------------------------------------------------------ RMSNorm -> quant
+// One block per row: y = T((x * rsqrt(mean(x^2) + eps)) * w), optionally after x += residual (the sum is kept in
+// fp32 for the norm and written back rounded, as the reference's fused_add_rmsnorm does), then the 128-group
+// quantisation of y -- the arithmetic of RMSNorm.forward_native
+// (python/sglang/srt/layers/layernorm.py:135-171) followed by sglang_per_token_group_quant_fp8.  The row stays in
+// registers between the three phases (sum of squares, normalise, quantise), so HBM sees one read of x (and of the
+// residual) and one write of the codes (and of y when the caller wants it).  WITH_Q = false is the plain norm.
+constexpr int kNormMaxVecs = 4;   // 16-element vectors per thread: rows up to 256 * 4 * 16 = 16384 elements
+
+template <typename T, bool WITH_Q, bool UE8M0, int NV, bool HAS_RES>
+__global__ void __launch_bounds__(kThreads, NV <= 2 ? (HAS_RES ? 4 : 5) : 2) rmsnorm_quant_kernel(const T* __restrict__ x, T* __restrict__ residual,
+                                                                    const T* __restrict__ weight, T* __restrict__ y,
+                                                                    uint8_t* __restrict__ q, float* __restrict__ s, int64_t M,
+                                                                    int64_t K, int64_t s_stride_row, int64_t s_stride_grp,
+                                                                    float norm_eps, float eps, float fp8_min,
+                                                                    float fp8_max) {
+  __shared__ float red[kThreads / 32];
+  const int tid = threadIdx.x;
+  const int64_t row = blockIdx.x;
+  const int nvec = static_cast<int>(K / kVec);
+  // The row is held PACKED (8 registers per 16 elements; with a residual both addends) and unpacked again in each
+  // phase: few registers per thread, so that several blocks share an SM and enough loads are in flight.
+  Vec16<T> d[NV];
+  [[maybe_unused]] Vec16<T> r[HAS_RES ? NV : 1];
+  constexpr bool has_res = HAS_RES;
+  float sumsq = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int v = tid + i * kThreads;
+    if (v < nvec) {
+      d[i].load(x + row * K + static_cast<int64_t>(v) * kVec);
+      if constexpr (HAS_RES) {
+        r[i].load(residual + row * K + static_cast<int64_t>(v) * kVec);
+        float f[kVec];
+#pragma unroll
+        for (int e = 0; e < kVec; ++e) {
+          f[e] = d[i].get(e) + r[i].get(e);
+          sumsq = fmaf(f[e], f[e], sumsq);
+        }
+        Vec16<T> o;
+        o.from_floats(f);
+        o.store(residual + row * K + static_cast<int64_t>(v) * kVec);
+      } else {
+#pragma unroll
+        for (int e = 0; e < kVec; ++e) sumsq = fmaf(d[i].get(e), d[i].get(e), sumsq);
+      }
+    }
+  }
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) sumsq += __shfl_xor_sync(0xffffffffu, sumsq, off);
+  if ((tid & 31) == 0) red[tid >> 5] = sumsq;
+  __syncthreads();
+  float total = 0.f;
+#pragma unroll
+  for (int w = 0; w < kThreads / 32; ++w) total += red[w];   // same order in every thread
+  const float rinv = rsqrtf(total / static_cast<float>(K) + norm_eps);
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int v = tid + i * kThreads;
+    // K % 128 == 0: the eight lanes of a group are inside the row together or not at all
+    [[maybe_unused]] const unsigned lanes = __ballot_sync(0xffffffffu, v < nvec);
+    if (v < nvec) {
+      Vec16<T> w;
+      w.load_cached(weight + static_cast<int64_t>(v) * kVec);
+      float f[kVec];
+#pragma unroll
+      for (int e = 0; e < kVec; ++e) {
+        float xe = d[i].get(e);
+        if constexpr (HAS_RES) xe += r[i].get(e);                              // the same fp32 sum as in phase one
+        f[e] = __fmul_rn(__fmul_rn(xe, rinv), w.get(e));
+      }
+      Vec16<T> o;
+      o.from_floats(f);                                          // y in T, exactly what a separate norm kernel stores
+      if (y) o.store(y + row * K + static_cast<int64_t>(v) * kVec);
+      if constexpr (WITH_Q) {
+        // a 128-group is eight consecutive vectors = eight consecutive lanes
+        float amax = eps;
+#pragma unroll
+        for (int e = 0; e < kVec; ++e) amax = fmaxf(amax, fabsf(o.get(e)));
+#pragma unroll
+        for (int off = 4; off >= 1; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(lanes, amax, off));
+        float scale = __fdiv_rn(amax, fp8_max);
+        if constexpr (UE8M0) scale = exp2f(ceilf(log2f(fmaxf(scale, 1e-10f))));
+        const uint4 codes = quantise_vec16<T, false>(o, scale, fp8_min, fp8_max);
+        *reinterpret_cast<uint4*>(q + row * K + static_cast<int64_t>(v) * kVec) = codes;
+        if ((v & 7) == 0) {
+          const int g = v >> 3;
+          if constexpr (UE8M0) {
+            // one byte of the packed word of (row, g / 4); the four groups of a word are written by four threads
+            reinterpret_cast<uint8_t*>(s)[(static_cast<int64_t>(g >> 2) * s_stride_grp + row) * 4 + (g & 3)] =
+                static_cast<uint8_t>(static_cast<int>(log2f(scale)) + 127);
+          } else {
+            s[row * s_stride_row + g * s_stride_grp] = scale;
+          }
+        }
+      }
+    }
   }
 }
 
@@ -451,4 +576,71 @@ extern "C" int b200_gather_per_token_group_quant_fp8(const void* x, int x_dtype,
     default: return B200_ERR_BAD_DTYPE;
   }
 #undef B200_GQ
+}
+
+// RMSNorm (optionally fused with the residual add) with or without the 128-group FP8 quantisation of its output,
+// one pass.  x [M, K] (bf16 / fp16), weight [K]; residual [M, K] or NULL: x + residual is normalised and written back
+// to residual; y [M, K] or NULL: the normalised row in x's type; q / s: codes and scales as in
+// b200_per_token_group_quant_fp8 (scale_ue8m0 != 0: the packed layout, s_stride_grp = stride between words), or
+// both NULL for the norm alone.  K % 128 == 0 and K <= 16384.
+extern "C" int b200_rmsnorm_per_token_group_quant_fp8(const void* x, int x_dtype, void* residual, const void* weight,
+                                                      float norm_eps, void* y, void* q, void* s, int64_t M, int64_t K,
+                                                      int64_t s_stride_row, int64_t s_stride_grp, int scale_ue8m0,
+                                                      float eps, float fp8_min, float fp8_max, void* stream) {
+  using namespace b200;
+  if (M < 0 || K <= 0) return B200_ERR_BAD_SHAPE;
+  if (K % 128 != 0) return B200_ERR_BAD_SHAPE;
+  if (K > static_cast<int64_t>(kThreads) * kNormMaxVecs * kVec) return B200_ERR_TOO_LARGE;
+  if (M == 0) return B200_OK;
+  if (M > 0x7fffffffLL) return B200_ERR_TOO_LARGE;
+  if (!x || !weight) return B200_ERR_NULL_PTR;
+  const bool with_q = q != nullptr;
+  if (with_q != (s != nullptr)) return B200_ERR_NULL_PTR;
+  if (!with_q && !y) return B200_ERR_NULL_PTR;
+  if (!aligned16(x) || !aligned16(weight) || (residual && !aligned16(residual)) || (y && !aligned16(y)) ||
+      (q && !aligned16(q)))
+    return B200_ERR_MISALIGNED;
+  if (with_q) {
+    if (scale_ue8m0) {
+      if (s_stride_grp < M) return B200_ERR_BAD_STRIDE;
+    } else if (s_stride_row < 0 || s_stride_grp < 0 || (s_stride_row == 0 && M > 1) || (s_stride_grp == 0 && K / 128 > 1)) {
+      return B200_ERR_BAD_STRIDE;
+    }
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const dim3 grid(static_cast<unsigned>(M));
+#define B200_NORM_GO(T, NV, WQ, UE, RES)                                                                              \
+  rmsnorm_quant_kernel<T, WQ, UE, NV, RES><<<grid, kThreads, 0, st>>>(                                                \
+      static_cast<const T*>(x), static_cast<T*>(residual), static_cast<const T*>(weight), static_cast<T*>(y),         \
+      static_cast<uint8_t*>(q), static_cast<float*>(s), M, K, s_stride_row, s_stride_grp, norm_eps, eps, fp8_min,     \
+      fp8_max)
+#define B200_NORM_NV(T, NV)                                       \
+  do {                                                            \
+    if (residual) {                                               \
+      if (!with_q) B200_NORM_GO(T, NV, false, false, true);       \
+      else if (scale_ue8m0) B200_NORM_GO(T, NV, true, true, true); \
+      else B200_NORM_GO(T, NV, true, false, true);                \
+    } else {                                                      \
+      if (!with_q) B200_NORM_GO(T, NV, false, false, false);      \
+      else if (scale_ue8m0) B200_NORM_GO(T, NV, true, true, false); \
+      else B200_NORM_GO(T, NV, true, false, false);               \
+    }                                                             \
+  } while (0)
+  // vectors per thread: rows up to 4096 / 8192 / 16384 elements
+#define B200_NORM(T)                                              \
+  do {                                                            \
+    if (K <= kThreads * kVec) B200_NORM_NV(T, 1);                 \
+    else if (K <= 2 * kThreads * kVec) B200_NORM_NV(T, 2);        \
+    else B200_NORM_NV(T, 4);                                      \
+  } while (0)
+  switch (x_dtype) {
+    case B200_DT_BF16: B200_NORM(__nv_bfloat16); break;
+    case B200_DT_F16: B200_NORM(__half); break;
+    default: return B200_ERR_BAD_DTYPE;
+  }
+#undef B200_NORM_NV
+#undef B200_NORM_GO
+#undef B200_NORM
+  B200_CUDA_TRY(cudaGetLastError());
+  return B200_OK;
 }

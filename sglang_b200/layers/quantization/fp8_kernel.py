@@ -8,7 +8,7 @@ python/sglang/srt/layers/quantization/fp8_kernel.py in the reference:
 """
 from __future__ import annotations
 
-from typing import List, Tuple
+from typing import List, Optional, Tuple
 
 import torch
 
@@ -115,6 +115,58 @@ def gather_per_token_group_quant_fp8(x: torch.Tensor, src_rows: torch.Tensor, gr
                 torch.cuda.current_stream(x.device).cuda_stream)
         _lib.check("gather_per_token_group_quant_fp8", rc)
     return x_q, x_s
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, residual: Optional[torch.Tensor] = None):
+    """RMSNorm.forward_native's arithmetic (python/sglang/srt/layers/layernorm.py:135-171) in one kernel: returns the
+    normalised tensor; with `residual`, x + residual is normalised and `residual` is overwritten with the sum."""
+    _, y, _, _ = _rmsnorm_launch(x, weight, eps, residual, want_y=True, want_q=False)
+    return y
+
+
+def rmsnorm_per_token_group_quant_fp8(x: torch.Tensor, weight: torch.Tensor, norm_eps: float = 1e-6,
+                                      residual: Optional[torch.Tensor] = None, group_size: int = 128,
+                                      eps: float = 1e-10, column_major_scales: bool = False,
+                                      scale_tma_aligned: bool = False, scale_ue8m0: bool = False,
+                                      return_normed: bool = False):
+    """RMSNorm (optionally with the residual add) and the group quantisation of its output in one pass: bit-identical
+    to rmsnorm(...) followed by sglang_per_token_group_quant_fp8(...), without writing and re-reading the normalised
+    activations.  Returns (codes, scales) or (codes, scales, normed) with return_normed."""
+    assert group_size == 128, "the fused form is built for 128-wide groups"
+    _, y, q, s = _rmsnorm_launch(x, weight, norm_eps, residual, want_y=return_normed, want_q=True, eps=eps,
+                                 column_major_scales=column_major_scales, scale_tma_aligned=scale_tma_aligned,
+                                 scale_ue8m0=scale_ue8m0)
+    return (q, s, y) if return_normed else (q, s)
+
+
+def _rmsnorm_launch(x, weight, norm_eps, residual, want_y, want_q, eps=1e-10, column_major_scales=False,
+                    scale_tma_aligned=False, scale_ue8m0=False):
+    assert x.is_contiguous() and x.dtype in (torch.bfloat16, torch.float16)
+    K = x.shape[-1]
+    assert weight.shape == (K,) and weight.dtype == x.dtype and weight.is_contiguous()
+    assert K % 128 == 0 and K <= 16384
+    if residual is not None:
+        assert residual.shape == x.shape and residual.dtype == x.dtype and residual.is_contiguous()
+    M = x.numel() // K
+    y = torch.empty_like(x) if want_y else None
+    q = s = None
+    ssr = ssg = 0
+    if want_q:
+        q = torch.empty(x.shape, device=x.device, dtype=fp8_dtype)
+        s = create_per_token_group_quant_fp8_output_scale((M, K) if scale_ue8m0 else x.shape, x.device, 128,
+                                                          column_major_scales, scale_tma_aligned, scale_ue8m0)
+        s2 = s if s.dim() == 2 else s.reshape(M, K // 128)
+        ssr, ssg = s2.stride(0), s2.stride(1)
+    if M > 0:
+        dt = {torch.float16: _lib.DT_F16, torch.bfloat16: _lib.DT_BF16}[x.dtype]
+        with torch.cuda.device(x.device):
+            rc = _lib.lib().b200_rmsnorm_per_token_group_quant_fp8(
+                x.data_ptr(), dt, residual.data_ptr() if residual is not None else None, weight.data_ptr(),
+                float(norm_eps), y.data_ptr() if y is not None else None, q.data_ptr() if q is not None else None,
+                s.data_ptr() if s is not None else None, M, K, ssr, ssg, 1 if scale_ue8m0 else 0, eps, fp8_min, fp8_max,
+                torch.cuda.current_stream(x.device).cuda_stream)
+        _lib.check("rmsnorm_per_token_group_quant_fp8", rc)
+    return residual, y, q, s
 
 
 def per_token_group_quant_fp8(x: torch.Tensor, group_size: int, eps: float = 1e-10,

@@ -18,8 +18,9 @@ Sources executed (paths inside the reference checkout):
   test/srt/quant/test_fp8_kernel.py         TestFP8Base._make_A / _make_B (known-answer generators)
   python/sglang/test/test_block_fp8_deep_gemm_blackwell.py   ceil_to_ue8m0, per_token_group_quant_mxfp8,
                                             per_block_quant_mxfp8 (power-of-two scales)
+  python/sglang/srt/layers/layernorm.py     RMSNorm.forward_native (producer of the linear's input)
 
-Usage:  python tests/golden/make_golden.py --reference <reference checkout> [--only ue8m0]
+Usage:  python tests/golden/make_golden.py --reference <reference checkout> [--only ue8m0|rmsnorm]
 """
 from __future__ import annotations
 
@@ -84,7 +85,34 @@ def make_ue8m0(reference: str):
                         x32=_np(x32), x32q=_np(x32q), x32s=_np(x32s), w=_np(w), wq=_np(wq), ws=_np(ws))
 
 
+def make_rmsnorm(reference: str):
+    """RMSNorm.forward_native (python/sglang/srt/layers/layernorm.py:135-171), executed as written with a stand-in
+    `self` that carries the four attributes the method reads."""
+    from types import SimpleNamespace
+    from typing import Union
+    ns = {"torch": torch, "Optional": Optional, "Tuple": Tuple, "Union": Union}
+    _extract(os.path.join(reference, "python/sglang/srt/layers/layernorm.py"), ["forward_native"], ns,
+             inside_class="RMSNorm")
+    out = {}
+    for name, dtype in (("bf16", torch.bfloat16), ("f16", torch.float16)):
+        torch.manual_seed(11)
+        x = (torch.randn(7, 512) * 2.0).to(dtype)
+        r = torch.randn(7, 512).to(dtype)
+        w = (1.0 + 0.1 * torch.randn(512)).to(dtype)
+        me = SimpleNamespace(hidden_size=512, variance_size_override=None, variance_epsilon=1e-6, weight=w)
+        y = ns["forward_native"](me, x.clone())
+        y2, r2 = ns["forward_native"](me, x.clone(), r.clone())
+        out.update({f"{name}_x": _np(x), f"{name}_r": _np(r), f"{name}_w": _np(w), f"{name}_y": _np(y),
+                    f"{name}_y_res": _np(y2), f"{name}_r_out": _np(r2)})
+    np.savez_compressed(os.path.join(HERE, "rmsnorm_native.npz"), **out)
+
+
 def main(reference: str, only: str = ""):
+    if only in ("", "rmsnorm"):
+        make_rmsnorm(reference)
+        if only:
+            print("golden vectors written to", HERE)
+            return
     if only in ("", "ue8m0"):
         make_ue8m0(reference)
         if only:
@@ -170,6 +198,6 @@ def main(reference: str, only: str = ""):
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of the reference checkout")
-    ap.add_argument("--only", default="", choices=["", "ue8m0"], help="write just this group of vectors")
+    ap.add_argument("--only", default="", choices=["", "ue8m0", "rmsnorm"], help="write just this group of vectors")
     a = ap.parse_args()
     main(a.reference, a.only)

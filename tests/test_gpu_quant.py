@@ -218,3 +218,56 @@ def test_ue8m0_argument_errors():
     with pytest.raises(RuntimeError):      # row-major int32
         sgl_per_token_group_quant_fp8(x, q, torch.zeros(8, 2, device="cuda", dtype=torch.int32)[:, :1], 128, 1e-10,
                                       -448.0, 448.0, True)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("with_residual", [False, True])
+@pytest.mark.parametrize("M,K", [(1, 128), (19, 1024), (64, 7168), (5, 16384), (300, 8192)])
+def test_rmsnorm_alone_against_the_oracle(M, K, with_residual, dtype):
+    """The norm kernel against RMSNorm.forward_native's arithmetic (the oracle, pinned to the reference's method by
+    tests/golden/rmsnorm_native.npz).  The only freedom is the order of the fp32 sum of squares (and rsqrt's last
+    bit): an element may differ by one unit in the last place of the 16-bit type; the residual sum must be exact."""
+    from sglang_b200.layers.quantization.fp8_kernel import rmsnorm
+    g = torch.Generator().manual_seed(M + K)
+    x = (torch.randn(M, K, generator=g) * 2).to(dtype)
+    w = (1.0 + 0.1 * torch.randn(K, generator=g)).to(dtype)
+    r = torch.randn(M, K, generator=g).to(dtype) if with_residual else None
+    if with_residual:
+        y_ref, r_ref = O.rmsnorm_native(x, w, 1e-6, r)
+        r_dev = r.cuda()
+        y = rmsnorm(x.cuda(), w.cuda(), 1e-6, residual=r_dev).cpu()
+        assert same_bits(r_dev.cpu(), r_ref)
+    else:
+        y_ref = O.rmsnorm_native(x, w, 1e-6)
+        y = rmsnorm(x.cuda(), w.cuda(), 1e-6).cpu()
+    ulp = 2.0 ** (-7 if dtype == torch.bfloat16 else -10)
+    diff = (y.float() - y_ref.float()).abs()
+    assert (diff <= ulp * y_ref.float().abs() + 1e-30).all()
+    assert (diff == 0).float().mean() > 0.99
+
+
+@pytest.mark.parametrize("layout", ["row", "col_tma", "ue8m0"])
+@pytest.mark.parametrize("with_residual", [False, True])
+@pytest.mark.parametrize("M,K", [(1, 128), (37, 1024), (64, 7168), (130, 2048)])
+def test_rmsnorm_quant_fused_equals_the_two_kernel_sequence(M, K, with_residual, layout):
+    """One pass == norm kernel, then the quant kernel: codes, scales, normalised rows and residual, bit for bit."""
+    from sglang_b200.layers.quantization.fp8_kernel import (rmsnorm, rmsnorm_per_token_group_quant_fp8,
+                                                            sglang_per_token_group_quant_fp8)
+    g = torch.Generator().manual_seed(M * 3 + K)
+    x = O.gen_activation(M, K, seed=M, outlier_frac=1e-3).cuda()
+    w = (1.0 + 0.1 * torch.randn(K, generator=g)).to(torch.bfloat16).cuda()
+    r0 = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda() if with_residual else None
+    kw = {"row": {}, "col_tma": dict(column_major_scales=True, scale_tma_aligned=True),
+          "ue8m0": dict(column_major_scales=True, scale_tma_aligned=True, scale_ue8m0=True)}[layout]
+    r1 = r0.clone() if with_residual else None
+    y = rmsnorm(x, w, 1e-6, residual=r1)
+    q_ref, s_ref = sglang_per_token_group_quant_fp8(y, 128, **kw)
+    r2 = r0.clone() if with_residual else None
+    q, s, y2 = rmsnorm_per_token_group_quant_fp8(x, w, 1e-6, residual=r2, return_normed=True, **kw)
+    assert same_bits(y2.cpu(), y.cpu())
+    assert same_bits(q.cpu(), q_ref.cpu()) and torch.equal(s.cpu(), s_ref.cpu())
+    assert s.stride() == s_ref.stride()
+    if with_residual:
+        assert same_bits(r2.cpu(), r1.cpu())
+    q3, s3 = rmsnorm_per_token_group_quant_fp8(x, w, 1e-6, residual=r0.clone() if with_residual else None, **kw)
+    assert same_bits(q3.cpu(), q_ref.cpu()) and torch.equal(s3.cpu(), s_ref.cpu())

@@ -41,6 +41,16 @@ def test_quant_ue8m0_matches_reference_functions():
     assert same_bits(wq, as_fp8(g["wq"])) and same_bits(ws, t(g["ws"]))
 
 
+def test_rmsnorm_matches_reference_forward_native():
+    """RMSNorm.forward_native executed by make_golden.py --only rmsnorm vs the oracle's restatement: same bits."""
+    g = load_golden("rmsnorm_native.npz")
+    for name, conv in (("bf16", as_bf16), ("f16", as_f16)):
+        x, r, w = conv(g[f"{name}_x"]), conv(g[f"{name}_r"]), conv(g[f"{name}_w"])
+        assert same_bits(O.rmsnorm_native(x, w, 1e-6), conv(g[f"{name}_y"]))
+        y2, r2 = O.rmsnorm_native(x, w, 1e-6, r)
+        assert same_bits(y2, conv(g[f"{name}_y_res"])) and same_bits(r2, conv(g[f"{name}_r_out"]))
+
+
 def test_quant_known_answer():
     """test/srt/quant/test_fp8_kernel.py:90-100: scales equal, <1e-4 of codes differ."""
     g = load_golden("known_answer.npz")
