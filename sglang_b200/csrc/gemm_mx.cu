@@ -868,7 +868,12 @@ extern "C" int b200_fp8_blockwise_scaled_mm_pow2(const void* a, int64_t lda, con
   if (g_force_block_n == 240) return launch_mx_dtype<240, 1>(a, lda, b, ldb, p, st);
   if (g_force_block_n == 2240) return launch_mx_dtype<240, 2>(a, lda, b, ldb, p, st);
   if (M >= 1024 && K >= 12288) return launch_mx_dtype<240, 2>(a, lda, b, ldb, p, st);
-  if (M >= 512 && N >= 4096) return launch_mx_pair_dtype(a, lda, b, ldb, p, st);
+  if (M >= 512 && N >= 4096) {
+    // a cluster launch can be refused where a plain one is not (no pair of SMs free, a tool that does not support
+    // clusters): then the one-CTA form runs instead
+    if (launch_mx_pair_dtype(a, lda, b, ldb, p, st) == B200_OK) return B200_OK;
+    (void)cudaGetLastError();
+  }
   return launch_mx_dtype<256, 1>(a, lda, b, ldb, p, st);
 }
 
