@@ -577,8 +577,9 @@ def gpu_comparator(dev, steps=10):
     from oracle import build_ref_cuda as R
     from sglang_b200.layers.quantization.fp8_kernel import sglang_per_token_group_quant_fp8
     from sglang_b200.sgl_kernel import fp8_blockwise_scaled_mm
-    out = {"built_from": "sgl-kernel/csrc/gemm/fp8_blockwise_gemm_kernel.cu, per_token_group_quant_8bit.cu "
-                         "(CUTLASS headers of the flashinfer package, not the commit the reference pins)"}
+    out = {"built_from": "sgl-kernel/csrc/gemm/fp8_blockwise_gemm_kernel.cu, per_token_group_quant_8bit.cu, "
+                         "csrc/moe/fp8_blockwise_moe_kernel.cu (CUTLASS headers of the flashinfer package, not the "
+                         "commit the reference pins)"}
     have = {}
     for fam in ("quant", "gemm"):
         try:
@@ -644,6 +645,69 @@ def gpu_comparator(dev, steps=10):
                          "ours_tflops": 2.0 * m * n * k / (t_us * 1e-6) / 1e12,
                          "reference_tflops": 2.0 * m * n * k / (t_ref * 1e-6) / 1e12}
             del ws
+    try:
+        have_moe = R.load("moe")
+    except Exception as e:  # noqa: BLE001
+        have_moe = False
+        out["moe_load_error"] = str(e)[:200]
+    if have_moe:
+        # the two expert GEMMs of config 4 (256 experts, 4096 tokens, top-8) on the reference's CUTLASS grouped kernel
+        # (sgl-kernel/csrc/moe/fp8_blockwise_moe_kernel.cu), on this library's fp32-scale grouped kernel (same inputs,
+        # outputs compared) and on its block-scaling grouped kernel (power-of-two scales)
+        from sglang_b200.layers.quantization.deep_gemm_wrapper import grouped_gemm_pow2
+        from sglang_b200.layers.quantization.fp8_kernel import silu_and_mul_per_token_group_quant_fp8
+        from sglang_b200.sgl_kernel import (fp8_blockwise_scaled_grouped_mm, prepare_moe_input, shuffle_packed_scales,
+                                            shuffle_rows)
+        E, H, I, topk, m = 256, 7168, 2048, 8, 4096
+        w13, w2, w13s, w2s = moe_weights(dev, list(range(E)), 5000)
+        a, tw, ti = moe_routing(dev, m, E=E)
+        i32, i64 = dict(dtype=torch.int32, device=dev), dict(dtype=torch.int64, device=dev)
+        eo, ps1, ps2 = torch.empty(E + 1, **i32), torch.empty((E, 3), **i32), torch.empty((E, 3), **i32)
+        a_map, c_map = torch.zeros(m * topk, **i32), torch.empty(m * topk, **i32)
+        prepare_moe_input(ti, eo, ps1, ps2, a_map, c_map, E, I, H)
+        a_q, a_s = sglang_per_token_group_quant_fp8(a, 128)
+        rq, rs = shuffle_rows(a_q, a_map, (m * topk, H)), shuffle_rows(a_s, a_map, (m * topk, H // 128))
+        a_qp, a_sp = sglang_per_token_group_quant_fp8(a, 128, column_major_scales=True, scale_tma_aligned=True,
+                                                      scale_ue8m0=True)
+        rqp, rsp = shuffle_rows(a_qp, a_map, (m * topk, H)), shuffle_packed_scales(a_sp, a_map)
+        w13p, w2p = torch.exp2(torch.ceil(torch.log2(w13s))), torch.exp2(torch.ceil(torch.log2(w2s)))
+        ptrs = [torch.empty(E, **i64) for _ in range(5)]
+        lay = [torch.empty((E, 5), **i32) for _ in range(2)]
+        wsp = torch.empty(90000, dtype=torch.uint8, device=dev)
+        c1r, c1 = (torch.zeros((m * topk, 2 * I), dtype=torch.bfloat16, device=dev) for _ in range(2))
+        c2r, c2 = (torch.zeros((m * topk, H), dtype=torch.bfloat16, device=dev) for _ in range(2))
+
+        def our_mm(c, x, xs_, w, wsc, ps):
+            fp8_blockwise_scaled_grouped_mm(c, None, None, None, None, None, x, w.transpose(1, 2), xs_,
+                                            wsc.transpose(1, 2), None, None, None, None, None, ps, eo[:-1], None)
+        st1 = (torch.full((E,), H, **i64), torch.full((E,), 2 * I, **i64))
+        st2 = (torch.full((E,), I, **i64), torch.full((E,), H, **i64))
+
+        def ref1():
+            ops.fp8_blockwise_scaled_grouped_mm(c1r, *ptrs, rq, w13.transpose(1, 2), rs, w13s.transpose(1, 2), st1[0], st1[0],
+                                                st1[1], lay[0], lay[1], ps1, eo[:-1], wsp)
+        ref1()
+        our_mm(c1, rq, rs, w13, w13s, ps1)
+        iq, is_ = silu_and_mul_per_token_group_quant_fp8(c1, 128)
+        iqp, isp = silu_and_mul_per_token_group_quant_fp8(c1, 128, scale_ue8m0=True)
+
+        def ref2():
+            ops.fp8_blockwise_scaled_grouped_mm(c2r, *ptrs, iq, w2.transpose(1, 2), is_, w2s.transpose(1, 2), st2[0], st2[0],
+                                                st2[1], lay[0], lay[1], ps2, eo[:-1], wsp)
+        ref2()
+        our_mm(c2, iq, is_, w2, w2s, ps2)
+        torch.cuda.synchronize()
+        for name, fr, fo, fp, cr, co in (
+                ("moe_gemm1_E256_T4096", ref1, lambda: our_mm(c1, rq, rs, w13, w13s, ps1),
+                 lambda: grouped_gemm_pow2(rqp, rsp, w13, w13p, c1, eo[:-1], ps1[:, 0]), c1r, c1),
+                ("moe_gemm2_E256_T4096", ref2, lambda: our_mm(c2, iq, is_, w2, w2s, ps2),
+                 lambda: grouped_gemm_pow2(iqp, isp, w2, w2p, c2, eo[:-1], ps1[:, 0]), c2r, c2)):
+            err = rel_l2(co, cr)
+            t_ref, t_us, t_p2 = graph_us(fr), graph_us(fo), graph_us(fp)
+            out[name] = {"reference_us": t_ref, "ours_us": t_us, "speedup": t_ref / t_us, "rel_l2_between": err,
+                         "ours_power_of_two_scales_us": t_p2, "speedup_power_of_two_scales": t_ref / t_p2}
+        del w13, w2, w13s, w2s, w13p, w2p
+        torch.cuda.empty_cache()
     return out
 
 
