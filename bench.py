@@ -566,6 +566,26 @@ def moe_config4_ep(dev, world, rank, steps=5):
            "bitwise_equal_to_single_gpu_on_rank0_tokens": bool(int(flag.item()))}
     if stages:
         res["stages_ms_rank0"] = stages
+    # the same layer on the block-scaling path: power-of-two weight scales (the drawn ones rounded up), activations
+    # dispatched with packed exponent words
+    w13s.copy_(torch.exp2(torch.ceil(torch.log2(w13s))))
+    w2s.copy_(torch.exp2(torch.ceil(torch.log2(w2s))))
+    moe2 = ExpertParallelBlockFp8MoE(w13, w2, w13s, w2s, scale_ue8m0=True)
+    ms2 = []
+    for _ in range(2):
+        moe2(x, tw, ti)
+    for _ in range(steps):
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        moe2(x, tw, ti)
+        b.record()
+        torch.cuda.synchronize()
+        ms2.append(a.elapsed_time(b))
+    moe2.check()
+    t2 = torch.tensor([sorted(ms2)[len(ms2) // 2]], device=dev)
+    dist.all_reduce(t2, op=dist.ReduceOp.MAX)
+    res["ue8m0_path_ms"] = float(t2.item())
     return res, bool(int(flag.item()))
 
 

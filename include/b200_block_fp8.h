@@ -99,6 +99,15 @@ int b200_silu_mul_per_token_group_quant_fp8(const void* x, int x_dtype, void* q,
                                             float fp8_max, void* stream);
 
 /*
+ * b200_per_token_group_quant_fp8_ue8m0 with caller-chosen word strides: word (r, w) at
+ * s_packed[r * s_stride_row + w * s_stride_pack].  s_stride_pack = 1 keeps a token's words together (the scale row
+ * an expert-parallel dispatch copies per token).
+ */
+int b200_per_token_group_quant_fp8_ue8m0_strided(const void* x, int x_dtype, void* q, uint32_t* s_packed, int64_t M,
+                                                 int64_t K, int64_t s_stride_row, int64_t s_stride_pack, float eps,
+                                                 float fp8_min, float fp8_max, void* stream);
+
+/*
  * The same fusion with power-of-two scales in the packed layout of b200_per_token_group_quant_fp8_ue8m0: the input
  * of the second expert GEMM on the block-scaling path.  Bit-identical to b200_silu_and_mul followed by
  * b200_per_token_group_quant_fp8_ue8m0.  Replaces silu_and_mul + sglang_per_token_group_quant_fp8(scale_ue8m0=True)
@@ -444,7 +453,10 @@ int b200_allreduce_max_blocks(void);
  * b200_ep_dispatch: for every (token, choice) slot f = token*topk + j with expert e = topk_ids[f] >= 0, the
  *   token's row (q [num_tokens, hidden] e4m3, s [num_tokens, hidden/128] fp32 row-major) is stored into
  *   rank e / experts_per_rank's receive region for this source, at the slot's position among this source's
- *   rows for that rank (stable in f), together with (e % experts_per_rank, f).  Rows beyond `capacity` for one
+ *   rows for that rank (stable in f), together with (e % experts_per_rank, f).  A token's scales are
+ *   scale_words_per_row consecutive 32-bit words of s (0 = hidden/128 fp32 scales; a multiple of 4, at most
+ *   hidden/128: e.g. the packed power-of-two exponents with the words of a token contiguous and padded to four
+ *   words); the receive region then holds rows of that many words.  Rows beyond `capacity` for one
  *   destination are dropped and *status becomes 31.  The call ends with a flag barrier between the ranks
  *   (flag words [flag_base_words, + world_size) of the signal pads), so kernels enqueued after it on the same
  *   stream see every peer's rows.  scratch_pos [num_tokens*topk] int32, scratch_counts [8] int32,
@@ -460,11 +472,11 @@ int b200_allreduce_max_blocks(void);
  */
 int64_t b200_ep_buffer_bytes(int world_size, int capacity, int hidden, int max_slots, int out_elem_bytes,
                              int64_t* layout_offsets_5);
-int b200_ep_dispatch(const void* q, const float* s, const int32_t* topk_ids, int64_t num_tokens, int topk, int hidden,
-                     int experts_per_rank, void* const* peer_buffers, void* const* peer_signal_pads,
-                     const int64_t* layout_offsets_5, int capacity, int rank, int world_size, int64_t flag_base_words,
-                     int* status, int32_t* scratch_pos, int32_t* scratch_counts, unsigned int* scratch_counter,
-                     void* stream);
+int b200_ep_dispatch(const void* q, const void* s, int scale_words_per_row, const int32_t* topk_ids, int64_t num_tokens,
+                     int topk, int hidden, int experts_per_rank, void* const* peer_buffers,
+                     void* const* peer_signal_pads, const int64_t* layout_offsets_5, int capacity, int rank,
+                     int world_size, int64_t flag_base_words, int* status, int32_t* scratch_pos, int32_t* scratch_counts,
+                     unsigned int* scratch_counter, void* stream);
 int b200_ep_received_expert_ids(const void* local_buffer, const int64_t* layout_offsets_5, int capacity, int hidden,
                                 int world_size, int32_t* ids_out, void* stream);
 int b200_ep_combine(const void* rows, const int32_t* row_of, int dtype, int hidden, void* const* peer_buffers,

@@ -64,6 +64,8 @@ _SIGNATURES = {
     "b200_rmsnorm_per_token_group_quant_fp8": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
                                                        c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_float,
                                                        c_float, c_float, c_void_p]),
+    "b200_per_token_group_quant_fp8_ue8m0_strided": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                                                             c_int64, c_float, c_float, c_float, c_void_p]),
     "b200_gemm_device_status": (c_int, [ctypes.POINTER(c_int)]),
     "b200_gemm_poll_status": (c_int, [ctypes.POINTER(c_int)]),
     "b200_fp8_blockwise_scaled_grouped_mm": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64,
@@ -93,7 +95,7 @@ _SIGNATURES = {
     "b200_allreduce_flag_words": (c_int, [c_int]),
     "b200_allreduce_max_blocks": (c_int, []),
     "b200_ep_buffer_bytes": (c_int64, [c_int, c_int, c_int, c_int, c_int, c_void_p]),
-    "b200_ep_dispatch": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+    "b200_ep_dispatch": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                  c_int, c_int, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "b200_ep_received_expert_ids": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "b200_ep_combine": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,

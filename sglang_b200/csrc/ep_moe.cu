@@ -244,8 +244,8 @@ extern "C" int64_t b200_ep_buffer_bytes(int world_size, int capacity, int hidden
   return off;
 }
 
-extern "C" int b200_ep_dispatch(const void* q, const float* s, const int32_t* topk_ids, int64_t num_tokens, int topk,
-                                int hidden, int experts_per_rank, void* const* peer_buffers,
+extern "C" int b200_ep_dispatch(const void* q, const void* s, int scale_words_per_row, const int32_t* topk_ids,
+                                int64_t num_tokens, int topk, int hidden, int experts_per_rank, void* const* peer_buffers,
                                 void* const* peer_signal_pads, const int64_t* layout_offsets_5, int capacity, int rank,
                                 int world_size, int64_t flag_base_words, int* status, int32_t* scratch_pos,
                                 int32_t* scratch_counts, unsigned int* scratch_counter, void* stream) {
@@ -255,9 +255,13 @@ extern "C" int b200_ep_dispatch(const void* q, const float* s, const int32_t* to
   const int64_t n_slots = num_tokens * topk;
   if (n_slots > 0x7fffff00LL) return B200_ERR_TOO_LARGE;
   if (!aligned16(q) || !aligned16(s)) return B200_ERR_MISALIGNED;
+  // a token's scales are `scale_words_per_row` 32-bit words (0 = one fp32 per 128 codes; 16-byte multiples, and no
+  // more than the region holds: hidden / 128 words per row)
+  const int G = scale_words_per_row > 0 ? scale_words_per_row : hidden / 128;
+  if (G % 4 != 0 || G > hidden / 128) return B200_ERR_BAD_SHAPE;
   EpParams p;
   int rc = fill_params(&p, peer_buffers, peer_signal_pads, rank, world_size, flag_base_words, status, layout_offsets_5,
-                       capacity, hidden, hidden / 128);
+                       capacity, hidden, G);
   if (rc != B200_OK) return rc;
   rc = require_sm100();
   if (rc != B200_OK) return rc;
@@ -270,7 +274,8 @@ extern "C" int b200_ep_dispatch(const void* q, const float* s, const int32_t* to
   const int cap_blocks = 4 * sm_count();
   if (blocks > cap_blocks) blocks = cap_blocks;
   if (blocks < 1) blocks = 1;
-  ep_push_kernel<<<static_cast<int>(blocks), 32 * warps, 0, st>>>(static_cast<const uint8_t*>(q), s, topk_ids, scratch_pos,
+  ep_push_kernel<<<static_cast<int>(blocks), 32 * warps, 0, st>>>(static_cast<const uint8_t*>(q),
+                                                                 static_cast<const float*>(s), topk_ids, scratch_pos,
                                                                  static_cast<int>(n_slots), topk, experts_per_rank,
                                                                  scratch_counter, p);
   B200_CUDA_TRY(cudaGetLastError());

@@ -174,8 +174,10 @@ __device__ __forceinline__ uint4 quantise_vec16(const Vec16<T>& data, float scal
 // UE8M0: the scale is rounded up to a power of two, exp2f(ceilf(log2f(max(amax/448, 1e-10)))), and
 // stored as its biased exponent byte, four k-groups per int32, column-major: the byte of (row r,
 // group g) lives at byte ((g/4) * s_stride_grp + r) * 4 + g%4 of s
-// (sgl-kernel/csrc/gemm/per_token_group_quant_8bit.cu:54-61,86-97).  s_stride_row is unused (rows are
-// contiguous).  The tile writes whole words; groups past K/GROUP inside the last word are zero bytes.
+// (sgl-kernel/csrc/gemm/per_token_group_quant_8bit.cu:54-61,86-97; rows are
+// contiguous; s_stride_row = 1 there).  A caller may ask for other word strides (rows of words contiguous: what an
+// expert-parallel dispatch sends per token).  The tile writes whole words; groups past K/GROUP inside the last word
+// are zero bytes.
 template <typename T, int GROUP, int PASSES, bool IEEE_DIV, bool FUSE_SILU = false, bool UE8M0 = false>
 __global__ void __launch_bounds__(kThreads, (PASSES >= 8 || sizeof(T) == 4) ? 2 : 4)   // 4 blocks/SM: <= 64 registers
 quant_group_kernel(const T* __restrict__ x, const int32_t* __restrict__ src_rows, int64_t x_rows, uint8_t* __restrict__ q,
@@ -262,7 +264,7 @@ quant_group_kernel(const T* __restrict__ x, const int32_t* __restrict__ src_rows
             word |= byte << (8 * b);
           }
         }
-        sp[(g0 / 4 + w) * s_stride_grp + (r0 + r)] = word;
+        sp[(g0 / 4 + w) * s_stride_grp + (r0 + r) * s_stride_row] = word;
       }
     }
     return;
@@ -643,4 +645,33 @@ extern "C" int b200_rmsnorm_per_token_group_quant_fp8(const void* x, int x_dtype
 #undef B200_NORM
   B200_CUDA_TRY(cudaGetLastError());
   return B200_OK;
+}
+
+// The power-of-two quantisation with caller-chosen word strides: word (r, w) at s_packed[r * s_stride_row +
+// w * s_stride_pack].  s_stride_row = 1 is b200_per_token_group_quant_fp8_ue8m0; s_stride_pack = 1 with
+// s_stride_row >= ceil(K / 512) keeps a token's words together (one contiguous scale row per token, which is what the
+// expert-parallel dispatch copies).
+extern "C" int b200_per_token_group_quant_fp8_ue8m0_strided(const void* x, int x_dtype, void* q, uint32_t* s_packed,
+                                                            int64_t M, int64_t K, int64_t s_stride_row,
+                                                            int64_t s_stride_pack, float eps, float fp8_min,
+                                                            float fp8_max, void* stream) {
+  using namespace b200;
+  if (M < 0 || K < 0) return B200_ERR_BAD_SHAPE;
+  if (K % 128 != 0) return B200_ERR_BAD_SHAPE;
+  if (M == 0 || K == 0) return B200_OK;
+  if (!x || !q || !s_packed) return B200_ERR_NULL_PTR;
+  if (!aligned16(x) || !aligned16(q)) return B200_ERR_MISALIGNED;
+  if (s_stride_row <= 0 || s_stride_pack <= 0) return B200_ERR_BAD_STRIDE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  float* s = reinterpret_cast<float*>(s_packed);
+  switch (x_dtype) {
+    case B200_DT_BF16:
+      return launch_group<__nv_bfloat16, 128, false, false, true>(x, q, s, M, K, s_stride_row, s_stride_pack, eps, fp8_min, fp8_max, st);
+    case B200_DT_F16:
+      return launch_group<__half, 128, false, false, true>(x, q, s, M, K, s_stride_row, s_stride_pack, eps, fp8_min, fp8_max, st);
+    case B200_DT_F32:
+      return launch_group<float, 128, false, false, true>(x, q, s, M, K, s_stride_row, s_stride_pack, eps, fp8_min, fp8_max, st);
+    default:
+      return B200_ERR_BAD_DTYPE;
+  }
 }

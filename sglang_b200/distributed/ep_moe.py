@@ -85,7 +85,7 @@ class _NvlinkExchange:
         R = self.world * self.capacity
         off = [int(v) for v in self.layout]
         self.recv_q = self.buf[off[0]:off[0] + R * hidden].view(torch.float8_e4m3fn).view(R, hidden)
-        self.recv_s = self.buf[off[1]:off[1] + R * (hidden // 128) * 4].view(torch.float32).view(R, hidden // 128)
+        self.recv_s_bytes = self.buf[off[1]:off[1] + R * (hidden // 128) * 4]
         self.back = self.buf[off[4]:off[4] + self.max_slots * hidden * esz].view(out_dtype).view(self.max_slots, hidden)
         self.ids = torch.empty(R, dtype=torch.int32, device=device)
         self.identity = torch.arange(self.max_slots, dtype=torch.int32, device=device)
@@ -94,17 +94,24 @@ class _NvlinkExchange:
         self.hdl.barrier()   # every rank's buffer and flags are zero before the first kernel touches them
 
     def dispatch(self, q, s, topk_ids, experts_per_rank):
+        """s [m, W]: one contiguous row of W 32-bit scale words per token -- fp32 scales (W = hidden / 128) or packed
+        power-of-two exponents (int32, W a multiple of 4).  Returns the receive regions; the scale region is viewed
+        with s's type and width."""
         m = q.shape[0]
+        assert s.dim() == 2 and s.is_contiguous() and s.element_size() == 4 and s.shape[0] == m
+        W = s.shape[1]
         st = torch.cuda.current_stream(self.device).cuda_stream
         rc = self.lib.lib().b200_ep_dispatch(
-            q.data_ptr(), s.data_ptr(), topk_ids.data_ptr(), m, self.topk, self.hidden, experts_per_rank,
+            q.data_ptr(), s.data_ptr(), W, topk_ids.data_ptr(), m, self.topk, self.hidden, experts_per_rank,
             self.peer_ptrs, self.signal_ptrs, self.layout, self.capacity, self.rank, self.world, 0,
             self.status.data_ptr(), self.pos.data_ptr(), self.counts.data_ptr(), self.counter.data_ptr(), st)
         self.lib.check("b200_ep_dispatch", rc)
         rc = self.lib.lib().b200_ep_received_expert_ids(self.buf.data_ptr(), self.layout, self.capacity, self.hidden,
                                                         self.world, self.ids.data_ptr(), st)
         self.lib.check("b200_ep_received_expert_ids", rc)
-        return self.recv_q, self.recv_s, self.ids
+        R = self.world * self.capacity
+        recv_s = self.recv_s_bytes[:R * W * 4].view(s.dtype).view(R, W)
+        return self.recv_q, recv_s, self.ids
 
     def combine(self, rows, row_of):
         dt = {torch.float16: self.lib.DT_F16, torch.bfloat16: self.lib.DT_BF16}[rows.dtype]
@@ -127,12 +134,17 @@ class ExpertParallelBlockFp8MoE:
     that to one rank drops the excess and `check()` raises; the default 2.0 is about twenty standard deviations
     above the mean for uniformly random routing of a few thousand rows.
     max_tokens (nvlink): bound on the tokens per rank and call the exchange buffer is sized for (default: the
-    first call's count; a larger later call re-allocates, which is a collective: all ranks must do it together)."""
+    first call's count; a larger later call re-allocates, which is a collective: all ranks must do it together).
+    scale_ue8m0 (nvlink): the block-scaling path -- activations quantised to power-of-two scales, dispatched with
+    their packed exponent words, expert GEMMs on the block-scaling MMA; the weights' block scales must be powers of
+    two (requant_weight_ue8m0).  Bitwise equal to fused_experts_block_fp8_ue8m0 on one GPU."""
 
     def __init__(self, w13, w2, w13_scale, w2_scale, group=None, quant_fn: Callable = _default_quant,
                  local_fn: Callable = _default_local, weighted_sum_fn: Callable = _default_weighted_sum,
-                 backend: str = "auto", capacity_factor: float = 2.0, max_tokens: Optional[int] = None):
+                 backend: str = "auto", capacity_factor: float = 2.0, max_tokens: Optional[int] = None,
+                 scale_ue8m0: bool = False):
         self.w13, self.w2, self.w13_scale, self.w2_scale = w13, w2, w13_scale, w2_scale
+        self.scale_ue8m0 = bool(scale_ue8m0)
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -145,6 +157,8 @@ class ExpertParallelBlockFp8MoE:
             raise ValueError(f"unknown backend {backend!r}")
         if backend == "nvlink" and not (self.world > 1 and w13.is_cuda and default_fns):
             raise ValueError("the nvlink backend needs CUDA ranks (world size > 1) and the default compute functions")
+        if self.scale_ue8m0 and backend != "nvlink":
+            raise ValueError("power-of-two scales (scale_ue8m0) are built for the nvlink backend")
         self.backend = backend
         self.capacity_factor = float(capacity_factor)
         self.max_tokens = max_tokens
@@ -164,11 +178,21 @@ class ExpertParallelBlockFp8MoE:
         m, H = x.shape
         topk = topk_ids.shape[1]
         xc = self._exchange(m, topk, H, x.dtype, x.device)
-        q, s = self._quant(x)                                            # quantise once per token
         ids = topk_ids.to(torch.int32).contiguous()
-        recv_q, recv_s, recv_ids = xc.dispatch(q, s.contiguous(), ids, self.e_local)
-        c2, row_of = grouped_experts_prequantized(recv_q, recv_s, recv_ids, self.w13, self.w2, self.w13_scale,
-                                                  self.w2_scale, x.dtype, return_sorted=True)
+        if self.scale_ue8m0:
+            # block-scaling path: power-of-two activation scales travel as packed exponent words (a quarter of the
+            # fp32 scale bytes), weights carry power-of-two block scales
+            from ..layers.moe.cutlass_moe import grouped_experts_prequantized_ue8m0
+            from ..layers.quantization.fp8_kernel import per_token_group_quant_fp8_ue8m0_rows
+            q, s = per_token_group_quant_fp8_ue8m0_rows(x)
+            recv_q, recv_s, recv_ids = xc.dispatch(q, s, ids, self.e_local)
+            c2, row_of = grouped_experts_prequantized_ue8m0(recv_q, recv_s, recv_ids, self.w13, self.w2, self.w13_scale,
+                                                            self.w2_scale, x.dtype, return_sorted=True)
+        else:
+            q, s = self._quant(x)                                        # quantise once per token
+            recv_q, recv_s, recv_ids = xc.dispatch(q, s.contiguous(), ids, self.e_local)
+            c2, row_of = grouped_experts_prequantized(recv_q, recv_s, recv_ids, self.w13, self.w2, self.w13_scale,
+                                                      self.w2_scale, x.dtype, return_sorted=True)
         back = xc.combine(c2, row_of)
         return self._wsum(back[:m * topk], xc.identity[:m * topk], topk_weights.to(x.dtype).contiguous(), m)
 

@@ -174,3 +174,32 @@ def grouped_experts_prequantized(a_q, a_scale, expert_ids, w13, w2, w13_scale, w
     out = torch.empty((R, k), device=device, dtype=out_dtype)
     apply_shuffle_mul_sum(c2, out, c_map, None)     # topk = 1: pure un-permute back to input order
     return out
+
+
+def grouped_experts_prequantized_ue8m0(a_q, a_words, expert_ids, w13, w2, w13_scale, w2_scale,
+                                       out_dtype=torch.bfloat16, return_sorted: bool = False):
+    """grouped_experts_prequantized on the block-scaling path: a_q [R, k] e4m3, a_words [R, W] int32 -- each row's
+    packed power-of-two exponents, contiguous per row (per_token_group_quant_fp8_ue8m0_rows) -- expert_ids [R] int32
+    (< 0 = skip); weights with power-of-two block scales."""
+    R, k = a_q.shape
+    E, n = w13.shape[0], w2.shape[2]
+    device = a_q.device
+    i32 = dict(dtype=torch.int32, device=device)
+    ids = expert_ids.to(torch.int32).reshape(R, 1).contiguous()
+    expert_offsets = torch.empty(E + 1, **i32)
+    ps1, ps2 = torch.empty((E, 3), **i32), torch.empty((E, 3), **i32)
+    a_map, c_map = torch.zeros(R, **i32), torch.empty(R, **i32)
+    prepare_moe_input(ids, expert_offsets, ps1, ps2, a_map, c_map, E, n, k)
+    rep_q = shuffle_rows(a_q, a_map, (R, k))
+    rep_w = shuffle_rows(a_words.contiguous(), a_map, (R, a_words.shape[1]))       # rows of words: a plain row gather
+    rows = ps1[:, 0]
+    c1 = torch.empty((R, 2 * n), device=device, dtype=out_dtype)
+    grouped_gemm_pow2(rep_q, rep_w, w13, w13_scale, c1, expert_offsets[:-1], rows)
+    inter_q, inter_s = silu_and_mul_per_token_group_quant_fp8(c1, 128, scale_ue8m0=True)
+    c2 = torch.empty((R, k), device=device, dtype=out_dtype)
+    grouped_gemm_pow2(inter_q, inter_s, w2, w2_scale, c2, expert_offsets[:-1], rows)
+    if return_sorted:
+        return c2, c_map
+    out = torch.empty((R, k), device=device, dtype=out_dtype)
+    apply_shuffle_mul_sum(c2, out, c_map, None)
+    return out

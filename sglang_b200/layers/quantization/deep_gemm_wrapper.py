@@ -48,6 +48,7 @@ def grouped_gemm_pow2(a: torch.Tensor, sa_packed: torch.Tensor, w: torch.Tensor,
     assert Kw == K and K % 128 == 0 and N % 128 == 0
     assert a.dtype == fp8_dtype and w.dtype == fp8_dtype and a.is_contiguous() and w.is_contiguous()
     assert sa_packed.dtype == torch.int32 and ws.dtype == torch.float32 and ws.shape == (E, N // 128, K // 128)
+    assert sa_packed.shape[-1] >= (K // 128 + 3) // 4, "one packed word per four k-blocks"
     assert out.shape == (R, N) and out.stride(1) == 1 and out.dtype in (torch.bfloat16, torch.float16, torch.float32)
     assert problem_offsets.dtype == torch.int32 and problem_rows.dtype == torch.int32
     assert problem_offsets.is_contiguous() and problem_rows.dim() == 1

@@ -56,6 +56,26 @@ def sglang_per_token_group_quant_fp8(x: torch.Tensor, group_size: int, eps: floa
     return x_q, x_s
 
 
+def per_token_group_quant_fp8_ue8m0_rows(x: torch.Tensor, eps: float = 1e-10) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The power-of-two quantisation (same codes and exponent bytes as sglang_per_token_group_quant_fp8 with
+    scale_ue8m0=True) with every token's packed words CONTIGUOUS: scales int32 [M, W], W = ceil(K / 512) rounded up to
+    four words (16 bytes), padding words zero.  One scale row per token is what the expert-parallel dispatch copies;
+    the grouped block-scaling GEMM takes the layout through its strides."""
+    assert x.dim() == 2 and x.is_contiguous() and x.shape[1] % 128 == 0
+    M, K = x.shape
+    W = ((K // 128 + 3) // 4 + 3) // 4 * 4
+    x_q = torch.empty_like(x, dtype=fp8_dtype)
+    x_s = torch.zeros((M, W), dtype=torch.int32, device=x.device)
+    if M > 0:
+        dt = {torch.float32: _lib.DT_F32, torch.float16: _lib.DT_F16, torch.bfloat16: _lib.DT_BF16}[x.dtype]
+        with torch.cuda.device(x.device):
+            rc = _lib.lib().b200_per_token_group_quant_fp8_ue8m0_strided(
+                x.data_ptr(), dt, x_q.data_ptr(), x_s.data_ptr(), M, K, W, 1, eps, fp8_min, fp8_max,
+                torch.cuda.current_stream(x.device).cuda_stream)
+        _lib.check("per_token_group_quant_fp8_ue8m0_rows", rc)
+    return x_q, x_s
+
+
 def silu_and_mul_per_token_group_quant_fp8(x: torch.Tensor, group_size: int = 128, eps: float = 1e-10,
                                            column_major_scales: bool = False, scale_tma_aligned: bool = False,
                                            scale_ue8m0: bool = False):

@@ -321,3 +321,45 @@ def test_fused_experts_power_of_two_scales_full_size_256_experts_4096_tokens():
         _status_ok()
     finally:
         torch.backends.cuda.matmul.allow_tf32 = old_tf32
+
+
+@pytest.mark.parametrize("M,K", [(1, 128), (37, 1024), (64, 7168), (130, 2048)])
+def test_packed_exponents_with_contiguous_rows(M, K):
+    """per_token_group_quant_fp8_ue8m0_rows: the codes and exponent bytes of the column-major packed form, one
+    contiguous (padded) row of words per token."""
+    from sglang_b200.layers.quantization.fp8_kernel import (per_token_group_quant_fp8_ue8m0_rows,
+                                                            sglang_per_token_group_quant_fp8)
+    x = O.gen_activation(M, K, seed=M + K, outlier_frac=1e-3).cuda()
+    q, s = sglang_per_token_group_quant_fp8(x, 128, column_major_scales=True, scale_tma_aligned=True, scale_ue8m0=True)
+    q2, s2 = per_token_group_quant_fp8_ue8m0_rows(x)
+    W = s.shape[1]
+    assert s2.is_contiguous() and s2.shape[1] % 4 == 0 and s2.shape[1] >= W
+    assert same_bits(q2.cpu(), q.cpu()) and torch.equal(s2[:, :W].cpu(), s.cpu()) and (s2[:, W:] == 0).all()
+
+
+def test_prequantized_rows_on_the_block_scaling_path_equal_the_fused_layer():
+    """What an expert-parallel rank runs on received rows (codes + contiguous exponent words + local expert ids, some
+    rows empty) against the single-GPU layer on the same routing: same bits, row by row."""
+    from sglang_b200.layers.moe.cutlass_moe import fused_experts_block_fp8_ue8m0, grouped_experts_prequantized_ue8m0
+    from sglang_b200.layers.quantization.fp8_kernel import per_token_group_quant_fp8_ue8m0_rows
+    E, H, I, m = 8, 512, 256, 70
+    w13, w13s = _make_experts(E, 2 * I, H, seed=21)
+    w2, w2s = _make_experts(E, H, I, seed=22)
+    w13, w13s, w2, w2s = w13.cuda(), w13s.cuda(), w2.cuda(), w2s.cuda()
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(m, H, generator=g).to(torch.bfloat16).cuda()
+    ids = torch.randint(0, E, (m, 1), generator=g, dtype=torch.int32).cuda()
+    ones = torch.ones(m, 1, device="cuda")
+    ref = fused_experts_block_fp8_ue8m0(x, w13, w2, w13s, w2s, ones, ids)            # top-1, weight 1: the expert output
+    q, words = per_token_group_quant_fp8_ue8m0_rows(x)
+    # interleave empty rows (id -1), as a receive region with spare capacity has them
+    R = 2 * m
+    q_pad = torch.zeros(R, H, dtype=torch.uint8, device="cuda")
+    q_pad[::2] = q.view(torch.uint8)
+    w_pad = torch.zeros(R, words.shape[1], dtype=torch.int32, device="cuda")
+    w_pad[::2] = words
+    id_pad = torch.full((R,), -1, dtype=torch.int32, device="cuda")
+    id_pad[::2] = ids.flatten()
+    out = grouped_experts_prequantized_ue8m0(q_pad.view(FP8), w_pad, id_pad, w13, w2, w13s, w2s, torch.bfloat16)
+    assert same_bits(out[::2].cpu(), ref.cpu())
+    _status_ok()

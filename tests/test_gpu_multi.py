@@ -85,6 +85,24 @@ def _ep_worker(rank, world, port, q):
         torch.cuda.synchronize()
         moe.check()
         results["all_to_rank0"] = bool(torch.equal(torch.cat(parts, 0), ref0))
+        # the block-scaling path: power-of-two weight scales, activations dispatched with packed exponent words
+        from sglang_b200.layers.moe.cutlass_moe import fused_experts_block_fp8_ue8m0
+        g2 = torch.Generator().manual_seed(33)
+        p13q, p13s, p2q, p2s = [], [], [], []
+        for _ in range(E):
+            a_, b_ = O.per_block_quant_mxfp8(torch.randn(2 * I, H, generator=g2) * 0.05); p13q.append(a_); p13s.append(b_)
+            a_, b_ = O.per_block_quant_mxfp8(torch.randn(H, I, generator=g2) * 0.05); p2q.append(a_); p2s.append(b_)
+        p13q, p13s, p2q, p2s = [torch.stack(v).cuda() for v in (p13q, p13s, p2q, p2s)]
+        refp = fused_experts_block_fp8_ue8m0(x, p13q, p2q, p13s, p2s, w, ids)
+        moe = ExpertParallelBlockFp8MoE(p13q[sl].contiguous(), p2q[sl].contiguous(), p13s[sl].contiguous(),
+                                        p2s[sl].contiguous(), backend="nvlink", scale_ue8m0=True)
+        for it in range(2):
+            y = moe(x[rows].contiguous(), w[rows].contiguous(), ids[rows].contiguous())
+            parts = [torch.empty_like(y) for _ in range(world)]
+            dist.all_gather(parts, y)
+            torch.cuda.synchronize()
+            moe.check()
+            results[f"nvlink_ue8m0_{it}"] = bool(torch.equal(torch.cat(parts, 0), refp))
         if rank == 0:
             q.put(results)
     finally:
