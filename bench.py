@@ -786,6 +786,22 @@ def run_gpu_arm(args):
         from sglang_b200.distributed.custom_all_reduce import SymmetricAllReduce
         ar = SymmetricAllReduce(max(M_TOKENS, 8192) * 8192 * 2)
         ar_forms_us = ar.autotune(M_TOKENS * HIDDEN * 2)       # multicast or peer pointers: whichever is faster here
+        # NCCL's all-reduce of the same bytes, for comparison only (it is not used in this configuration)
+        t_nccl = torch.zeros((M_TOKENS, HIDDEN), dtype=torch.bfloat16, device=dev)
+        for _ in range(3):
+            dist.all_reduce(t_nccl)
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0_, e1_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0_.record()
+        for _ in range(10):
+            dist.all_reduce(t_nccl)
+        e1_.record()
+        torch.cuda.synchronize()
+        tn_ = torch.tensor([e0_.elapsed_time(e1_) / 10 * 1e3], device=dev)
+        dist.all_reduce(tn_, op=dist.ReduceOp.MAX)
+        ar_forms_us["nccl_for_comparison"] = float(tn_.item())
+        del t_nccl
     col = ColumnParallelBlockFp8Linear(w1q, w1s)
     row = RowParallelBlockFp8Linear(w2q, w2s, all_reduce=ar)
     g = torch.Generator(device=dev).manual_seed(7)           # x is replicated: same seed on all ranks
@@ -846,7 +862,7 @@ def run_gpu_arm(args):
         # and the all-reduce runs in its multicast form beside them; with none the two kernels compete for the SMs.
         cands = [(args.tp_chunks, 0)] if args.tp_chunks else [(1, 0), (2, 0), (4, 0)]
         if not args.tp_chunks and ar is not None and ar.has_multicast:
-            cands += [(2, 16), (4, 16), (8, 16)]
+            cands += [(2, 16), (4, 16), (8, 16), (2, 8), (4, 8)]
         best = None
         for c, r in cands:
             row.overlap_chunks, row.reserve_sms = c, r
