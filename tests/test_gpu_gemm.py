@@ -520,3 +520,18 @@ def test_tail_split_large_m(M, N, K):
     if s.value > 1:
         differing_rows = int((out != plain).any(dim=1).sum())
         assert differing_rows <= 128 * 74, differing_rows   # only tail tiles (at most half a wave) may differ at all
+
+
+def test_sm_limit_changes_the_grid_not_the_result():
+    """b200_set_sm_limit: the persistent kernels run on fewer SMs (what a row-parallel linear does to leave SMs to
+    its all-reduce); same bits, and the previous limit comes back from the call."""
+    from sglang_b200.sgl_kernel.gemm import set_sm_limit
+    a, b, sa, sb = _rand_problem(700, 1280, 2048, seed=5)
+    full = _run_sgl(a, b, sa, sb).cpu()
+    assert set_sm_limit(100) == 0
+    try:
+        limited = _run_sgl(a, b, sa, sb).cpu()
+        _status_ok()
+    finally:
+        assert set_sm_limit(0) == 100
+    assert same_bits(limited, full)
