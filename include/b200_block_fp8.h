@@ -260,6 +260,27 @@ int b200_fp8_blockwise_scaled_grouped_mm_pow2(
     int num_weight_experts, int64_t N, int64_t K, void* stream);
 
 /*
+ * Expert GEMM 1 of the block-scaling path with the activation and the NEXT GEMM's quantisation in its epilogue:
+ *   codes, exponents = quantise_pow2( SiLU(x W_gate^T) * (x W_up^T) )     (128-wide groups, packed words)
+ * b holds 2 * N rows per weight slice (gate rows first), N = intermediate size; problems as in
+ * b200_fp8_blockwise_scaled_grouped_mm_pow2.  The accumulator is rounded to mid_dtype (bf16 / fp16) before the
+ * activation and the product after it, as the unfused kernels store them: the result equals
+ * b200_fp8_blockwise_scaled_grouped_mm_pow2 followed by b200_silu_mul_per_token_group_quant_fp8_ue8m0 bit for bit,
+ * and the [rows, 2N] intermediate never reaches HBM.  out_q [total_rows, N] e4m3 (leading dimension ldq bytes);
+ * out_s: word (row, w) at out_s[w * out_s_stride_pack + row] (pass zeroed memory: bytes of absent groups are not
+ * written).  N % 128 == 0, K % 128 == 0.
+ * Replaces: grouped GEMM + silu_and_mul + sglang_per_token_group_quant_fp8 at
+ * python/sglang/srt/layers/moe/cutlass_moe.py:171-194 / ep_moe/layer.py:603-628 -- the "GEMM epilogue that emits
+ * e4m3 and scales" form of the fusion.
+ */
+int b200_fp8_blockwise_scaled_grouped_mm_pow2_silu_quant(
+    const void* a, int64_t lda, int64_t total_rows, const void* b, int64_t ldb, const uint32_t* sa_packed,
+    int64_t sa_stride_m, int64_t sa_stride_pack, int64_t sa_stride_problem, const float* sb_pow2, int64_t sb_stride_e,
+    int64_t sb_stride_n, int64_t sb_stride_g, void* out_q, int64_t ldq, uint32_t* out_s, int64_t out_s_stride_pack,
+    int mid_dtype, const int32_t* problem_offsets, const int32_t* problem_rows, int64_t problem_rows_stride,
+    const int32_t* problem_experts, int num_problems, int num_weight_experts, int64_t N, int64_t K, void* stream);
+
+/*
  * Grouped (per-expert) block-scaled FP8 GEMM: for every expert e,
  *   out[off_e : off_e + m_e, :] = blockscaled( a[off_e : off_e + m_e, :], b[e] )   (same math as above)
  * with off_e = expert_offsets[e], m_e = problem_sizes[3*e] read ON THE DEVICE (no host sync).

@@ -56,6 +56,10 @@ _SIGNATURES = {
                                                           c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64,
                                                           c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int64,
                                                           c_void_p, c_int, c_int, c_int64, c_int64, c_void_p]),
+    "b200_fp8_blockwise_scaled_grouped_mm_pow2_silu_quant": (c_int, [
+        c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int64,
+        c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int,
+        c_int64, c_int64, c_void_p]),
     "b200_silu_mul_per_token_group_quant_fp8_ue8m0": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64,
                                                               c_int64, c_float, c_float, c_float, c_void_p]),
     "b200_gather_per_token_group_quant_fp8": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_int64,

@@ -34,6 +34,7 @@ constexpr int BM = 128, BK = 128;
 constexpr int kSfSlots = 3;                             // scale-factor ring: one slot serves four k-blocks
 constexpr int kSfaBytes = 512, kSfbBytes = 1024;       // one 512-byte tile per 128 rows of A, two for the (up to 256) columns of B
 constexpr int kThreadsMx = 256;
+constexpr int kThreadsMxSilu = 384;   // the fused-activation form: four more epilogue warps (warps 8-11)
 constexpr int kGroupMMx = 32;
 
 // Tile shapes (rows x columns per CTA) and their tensor-memory maps:
@@ -79,6 +80,12 @@ struct MxParams {
   // contiguous layout), or per problem by the row inside it at sa + i * sa_stride_problem (its masked layout)
   int64_t sa_stride_problem;
   int num_problems, num_weight_experts;
+  // SiLU*mul + power-of-two quantisation in the epilogue (grouped form, expert GEMM 1): N is the number of OUTPUT
+  // columns (the intermediate size I); weight slice e holds 2 * N rows, gate rows first; `out` receives e4m3 codes
+  // [rows, N] (leading dimension ldo bytes) and out_s the packed exponent words (word (row, w) at
+  // out_s[w * out_s_stride_pack + row]).
+  uint32_t* out_s;
+  int64_t out_s_stride_pack;
 };
 
 constexpr int kMaxProblems = 2048;
@@ -168,10 +175,16 @@ __device__ __forceinline__ MxTile mx_get_tile(int tile, const MxParams& p, int m
   return t;
 }
 
-template <int BN, int MSUB, bool GROUPED, typename OutT>
-__global__ void __launch_bounds__(kThreadsMx, 1)
+template <int BN, int MSUB, bool GROUPED, typename OutT, bool SILU_Q = false>
+__global__ void __launch_bounds__((SILU_Q || (BN == 256 && MSUB == 1)) ? kThreadsMxSilu : kThreadsMx, 1)
 gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const MxParams p) {
   using C = MxCfg<BN, MSUB>;
+  static_assert(!SILU_Q || (GROUPED && BN == 256 && MSUB == 1), "the fused activation epilogue is built for the grouped 128 x 256 tile");
+  // SILU_Q: a tile is 128 rows x (128 gate columns | the 128 up columns of the same outputs); n-blocks count
+  // 128 OUTPUT columns
+  constexpr int kOutN = SILU_Q ? 128 : BN;
+  // the 128 x 256 tile runs with eight epilogue warps (warps 0-3 and 8-11: two per row quadrant, 128 columns each)
+  constexpr bool kWide8 = (BN == 256 && MSUB == 1);
   constexpr int kStagesMx = C::kStages;
   constexpr int kABytesMx = C::kABytes;
   constexpr int kSfBytes = C::kSfBytes;
@@ -193,12 +206,14 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int m_blocks = (p.M + kTileM - 1) / kTileM;
-  const int n_blocks = (p.N + BN - 1) / BN;
+  const int n_blocks = (p.N + kOutN - 1) / kOutN;
   const int nkb = (p.K + BK - 1) / BK;
   __shared__ int tile_start[GROUPED ? kMaxProblems + 1 : 1];
+  __shared__ float amax_x[SILU_Q ? 2 : 1][2][SILU_Q ? BM : 1];   // fused-activation epilogue: maxima of the two column halves
+  __shared__ uint64_t xbar[4];                                    // ... and where the two warps of a row quadrant meet
   if constexpr (GROUPED) {
     // row tiles per problem (none for an empty problem or one whose weight slice does not exist) ...
-    for (int i = threadIdx.x; i < p.num_problems; i += kThreadsMx) {
+    for (int i = threadIdx.x; i < p.num_problems; i += blockDim.x) {
       const int rows = __ldg(p.rows + static_cast<int64_t>(i) * p.rows_stride);
       const int e = p.experts ? __ldg(p.experts + i) : i;
       tile_start[i + 1] = (rows > 0 && e >= 0 && e < p.num_weight_experts) ? (min(rows, p.M) + kTileM - 1) / kTileM : 0;
@@ -234,8 +249,9 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&acc_full[i], 1);
-      mbar_init(&acc_empty[i], 4);
+      mbar_init(&acc_empty[i], kWide8 ? 8 : 4);
     }
+    for (int i = 0; i < 4; ++i) mbar_init(&xbar[i], 2);
     fence_mbar_init();
     fence_proxy_async_smem();
   }
@@ -259,14 +275,21 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
       const MxTile t = mx_get_tile<GROUPED, kTileM>(tile, p, m_blocks, n_blocks, tile_start);
-      const int w_row0 = t.e_w * p.N + t.n_blk * BN;
+      // SILU_Q: the weight map's box is 128 rows; the gate rows and the up rows of the tile's 128 outputs land in
+      // the two halves of the stage
+      const int w_row0 = SILU_Q ? t.e_w * 2 * p.N + t.n_blk * 128 : t.e_w * p.N + t.n_blk * BN;
       for (int kb = 0; kb < nkb; ++kb) {
         ok = mbar_wait_warp(&empty_bar[stage], phase ^ 1u, p.status, 41);
         if (!ok) break;
         if (elect_one()) {
           mbar_expect_tx(&full_bar[stage], C::kStageBytes);
           tma_load_2d(smem_a + stage * kABytesMx, &map_a, &full_bar[stage], kb * BK, t.row0);
-          tma_load_2d(smem_b + stage * C::kBBytes, &map_b, &full_bar[stage], kb * BK, w_row0);
+          if constexpr (SILU_Q) {
+            tma_load_2d(smem_b + stage * C::kBBytes, &map_b, &full_bar[stage], kb * BK, w_row0);
+            tma_load_2d(smem_b + stage * C::kBBytes + 128 * BK, &map_b, &full_bar[stage], kb * BK, w_row0 + p.N);
+          } else {
+            tma_load_2d(smem_b + stage * C::kBBytes, &map_b, &full_bar[stage], kb * BK, w_row0);
+          }
         }
         __syncwarp();
         if (++stage == kStagesMx) { stage = 0; phase ^= 1u; }
@@ -360,6 +383,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const MxTile t = mx_get_tile<GROUPED, kTileM>(tile, p, m_blocks, n_blocks, tile_start);
       const int row0 = t.row0, n_blk = t.n_blk, row_end = t.row0 + t.valid;
       const float* sb_e = p.sb + (GROUPED ? static_cast<int64_t>(t.e_w) * p.sb_stride_e : 0);
+      [[maybe_unused]] const int up_blocks0 = p.N >> 7;     // SILU_Q: first scale block of the up rows
       for (int kb0 = 0; kb0 < nkb; kb0 += 4) {
         uint32_t w[4 * MSUB];
 #pragma unroll
@@ -372,7 +396,8 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int i = 0; i < 8; ++i) {
           // column (i / 4) * 128 + (i % 4) * 32 + lane of the tile
           const int col = min(n_blk * BN + (i >> 2) * 128 + (i & 3) * 32 + lane, p.N - 1);
-          const float* sp = sb_e + static_cast<int64_t>(col >> 7) * p.sb_stride_n;
+          const int wblock = SILU_Q ? ((i >> 2) ? up_blocks0 + n_blk : n_blk) : (col >> 7);
+          const float* sp = sb_e + static_cast<int64_t>(wblock) * p.sb_stride_n;
           uint32_t word = 0;
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
@@ -396,11 +421,12 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
     }
     __syncwarp();
-  } else if (warp < 4) {
+  } else if (warp < 4 || (kWide8 && warp >= 8)) {
     // ------------------------------------------------------------------ epilogue
     OutT* out = static_cast<OutT*>(p.out);
     const bool vec_ok = (p.ldo % (16 / (int)sizeof(OutT)) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15u) == 0);
-    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    [[maybe_unused]] uint32_t xpar = 0;
     int acc = 0;
     uint32_t acc_phase[2] = {0, 0};
     bool ok = true;
@@ -411,11 +437,140 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       ok = mbar_wait(&acc_full[acc], acc_phase[acc], p.status, 46);
       if (!ok) break;
       tc_fence_after();
-      constexpr int kChunks = BN / 16;
+      if constexpr (SILU_Q) {
+        // gate = columns [0, 128), up = [128, 256) of the accumulator: round both to OutT (what GEMM 1 would have
+        // stored), SiLU(gate) * up in fp32, round to OutT (what the activation kernel stores), then the power-of-two
+        // quantisation of the row's 128 values -- the arithmetic of the unfused sequence, value for value.
+        // Two warps share a row quadrant: warps 0-3 take outputs [0, 64), warps 8-11 outputs [64, 128); the halves'
+        // maxima meet in shared memory.  The accumulator goes back to the MMA warp as soon as both have read it, and
+        // the arithmetic runs under the next tile's MMAs.
+        const int quad = warp & 3, half = warp >> 3;
+        const int row_in_tile = quad * 32 + lane;
+        const int m = t.row0 + row_in_tile;
+        const uint32_t taddr = tmem_base + lane_addr + static_cast<uint32_t>(acc) * C::kAccStride + half * 64;
+        // phase one: the accumulator's values rounded to OutT and packed (64 registers), then the accumulator goes
+        // back; phase two: the arithmetic, from registers
+        uint32_t gp[32], up[32];
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          float g[16], u[16];
+          tmem_ld16(taddr + ch * 16, g);
+          tmem_ld16(taddr + 128 + ch * 16, u);
+          tmem_ld_wait();
+#pragma unroll
+          for (int c = 0; c < 16; c += 2) {
+            gp[ch * 8 + c / 2] = pack2(out, g[c], g[c + 1]);
+            up[ch * 8 + c / 2] = pack2(out, u[c], u[c + 1]);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        auto lo_of = [](uint32_t w) { OutT v; *reinterpret_cast<uint16_t*>(&v) = static_cast<uint16_t>(w & 0xffffu); return static_cast<float>(v); };
+        auto hi_of = [](uint32_t w) { OutT v; *reinterpret_cast<uint16_t*>(&v) = static_cast<uint16_t>(w >> 16); return static_cast<float>(v); };
+        uint32_t y[32];                       // 64 activations in OutT, packed in pairs
+        float amax = 1e-10f;                  // eps of the quantiser
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float g0 = lo_of(gp[i]), g1 = hi_of(gp[i]);
+          const float f0 = (g0 / (1.0f + __expf(-g0))) * lo_of(up[i]);
+          const float f1 = (g1 / (1.0f + __expf(-g1))) * hi_of(up[i]);
+          y[i] = pack2(out, f0, f1);
+          amax = fmaxf(amax, fmaxf(fabsf(lo_of(y[i])), fabsf(hi_of(y[i]))));
+        }
+        // exchange through shared memory, double-buffered by tile parity; the two warps of a quadrant meet at an
+        // mbarrier (bounded wait, like every other wait of the kernel)
+        amax_x[xpar][half][row_in_tile] = amax;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&xbar[quad]);
+        ok = mbar_wait(&xbar[quad], xpar, p.status, 47);
+        if (!ok) break;
+        amax = fmaxf(amax, amax_x[xpar][half ^ 1][row_in_tile]);
+        xpar ^= 1u;
+        const float scale = exp2f(ceilf(log2f(fmaxf(__fdiv_rn(amax, 448.0f), 1e-10f))));
+        const float rinv = __frcp_rn(scale);          // exact: the scale is a power of two
+        if (m < m_end) {
+          uint8_t* qrow = reinterpret_cast<uint8_t*>(p.out) + static_cast<int64_t>(m) * p.ldo + n_blk * 128 + half * 64;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint32_t w4[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              float q4[4];
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                const uint32_t packed = y[v * 8 + j * 2 + e];
+                OutT lo, hi;
+                *reinterpret_cast<uint16_t*>(&lo) = static_cast<uint16_t>(packed & 0xffffu);
+                *reinterpret_cast<uint16_t*>(&hi) = static_cast<uint16_t>(packed >> 16);
+                q4[2 * e] = fminf(fmaxf(static_cast<float>(lo) * rinv, -448.0f), 448.0f);
+                q4[2 * e + 1] = fminf(fmaxf(static_cast<float>(hi) * rinv, -448.0f), 448.0f);
+              }
+              const uint32_t c01 = __nv_cvt_float2_to_fp8x2(make_float2(q4[0], q4[1]), __NV_SATFINITE, __NV_E4M3);
+              const uint32_t c23 = __nv_cvt_float2_to_fp8x2(make_float2(q4[2], q4[3]), __NV_SATFINITE, __NV_E4M3);
+              w4[j] = c01 | (c23 << 16);
+            }
+            *reinterpret_cast<uint4*>(qrow + v * 16) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+          }
+          if (half == 0)
+            reinterpret_cast<uint8_t*>(p.out_s)[(static_cast<int64_t>(n_blk >> 2) * p.out_s_stride_pack + m) * 4 + (n_blk & 3)] =
+                static_cast<uint8_t>(static_cast<int>(log2f(scale)) + 127);
+        }
+        acc_phase[acc] ^= 1u;
+        if (C::kNumAcc == 2) acc ^= 1;
+        continue;
+      }
+      if constexpr (kWide8 && sizeof(OutT) == 2) {
+        // 16-bit output: each warp reads its 32 rows x 128 columns out of tensor memory, rounds and packs them into
+        // 64 registers, hands the accumulator back at once and only then stores -- the stores (32 rows per
+        // instruction, 16 bytes each) run under the next tile's MMAs.
+        const int half = warp >> 3;
+        const int m = t.row0 + (warp & 3) * 32 + lane;
+        const uint32_t taddr = tmem_base + lane_addr + static_cast<uint32_t>(acc) * C::kAccStride + half * 128;
+        uint32_t pk[64];
+#pragma unroll
+        for (int ch = 0; ch < 8; ch += 2) {
+          float v[32];
+          tmem_ld16(taddr + ch * 16, *reinterpret_cast<float(*)[16]>(v));
+          tmem_ld16(taddr + (ch + 1) * 16, *reinterpret_cast<float(*)[16]>(v + 16));
+          tmem_ld_wait();
+#pragma unroll
+          for (int c = 0; c < 32; c += 2) pk[ch * 8 + c / 2] = pack2(out, v[c], v[c + 1]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        const int n0 = n_blk * BN + half * 128;
+        if (m < m_end && n0 < p.N) {
+          OutT* dst = out + static_cast<int64_t>(m) * p.ldo + n0;
+          const int valid = min(p.N - n0, 128);
+          if (vec_ok && valid == 128) {
+#pragma unroll
+            for (int c = 0; c < 16; ++c)
+              reinterpret_cast<uint4*>(dst)[c] = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+          } else {
+#pragma unroll
+            for (int c = 0; c < 64; ++c) {
+              OutT lo, hi;
+              *reinterpret_cast<uint16_t*>(&lo) = static_cast<uint16_t>(pk[c] & 0xffffu);
+              *reinterpret_cast<uint16_t*>(&hi) = static_cast<uint16_t>(pk[c] >> 16);
+              if (2 * c < valid) dst[2 * c] = lo;
+              if (2 * c + 1 < valid) dst[2 * c + 1] = hi;
+            }
+          }
+        }
+        acc_phase[acc] ^= 1u;
+        if (C::kNumAcc == 2) acc ^= 1;
+        continue;
+      }
+      // (fp32 output, and the 240-wide tiles: chunk by chunk, the accumulator is handed back after the last load)
+      constexpr int kChunks = (kWide8 ? 128 : BN) / 16;
+      [[maybe_unused]] const int col_half = kWide8 ? (warp >> 3) : 0;
 #pragma unroll 1
       for (int h = 0; h < MSUB; ++h) {
-        const int m = t.row0 + h * BM + warp * 32 + lane;
-        const uint32_t taddr = tmem_base + lane_addr + static_cast<uint32_t>(MSUB == 2 ? h : acc) * C::kAccStride;
+        const int m = t.row0 + h * BM + (warp & 3) * 32 + lane;
+        const uint32_t taddr = tmem_base + lane_addr + static_cast<uint32_t>(MSUB == 2 ? h : acc) * C::kAccStride +
+                               col_half * 128;
 #pragma unroll 1
         for (int ch = 0; ch < kChunks; ch += 2) {
           float v[32];
@@ -427,7 +582,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[acc]);
           }
-          const int n0 = n_blk * BN + ch * 16;
+          const int n0 = n_blk * BN + col_half * 128 + ch * 16;
           const int width = (ch + 1 < kChunks) ? 32 : 16;
           if (m < m_end && n0 < p.N)
             store_row<32>(out + static_cast<int64_t>(m) * p.ldo + n0, v, min(p.N - n0, width), vec_ok && width == 32);
@@ -464,7 +619,7 @@ int launch_mx(const CUtensorMap& ma, const CUtensorMap& mb, const MxParams& p, c
   const long long m_tiles = (p.M + BM * MSUB - 1) / (BM * MSUB) + (GROUPED ? p.num_problems : 0);
   const long long tiles = m_tiles * ((p.N + BN - 1) / BN);
   const int grid = tiles < sm_count() ? static_cast<int>(tiles) : sm_count();
-  kern<<<grid, kThreadsMx, C::kSmem, stream>>>(ma, mb, p);
+  kern<<<grid, (BN == 256 && MSUB == 1) ? kThreadsMxSilu : kThreadsMx, C::kSmem, stream>>>(ma, mb, p);
   B200_CUDA_TRY(cudaGetLastError());
   return B200_OK;
 }
@@ -483,6 +638,30 @@ int launch_mx_dtype(const void* a, int64_t lda, const void* b, int64_t ldb, cons
   }
 }
 
+
+template <typename OutT>
+int launch_mx_silu(const void* a, int64_t lda, const void* b, int64_t ldb, const MxParams& p, cudaStream_t stream) {
+  using C = MxCfg<256, 1>;
+  CUtensorMap ma, mb;
+  int rc = make_map_u8_2d(&ma, a, p.M, p.K, lda, BM);
+  if (rc != B200_OK) return rc;
+  rc = make_map_u8_2d(&mb, b, static_cast<int64_t>(2) * p.N * p.num_weight_experts, p.K, ldb, 128);
+  if (rc != B200_OK) return rc;
+  auto kern = gemm_mx_kernel<256, 1, true, OutT, true>;   // 12 warps
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  B200_CUDA_TRY(cudaGetDevice(&dev));
+  if (!attr_set[dev & 63]) {
+    B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem));
+    attr_set[dev & 63] = true;
+  }
+  const long long m_tiles = (p.M + BM - 1) / BM + p.num_problems;
+  const long long tiles = m_tiles * ((p.N + 127) / 128);
+  const int grid = tiles < sm_count() ? static_cast<int>(tiles) : sm_count();
+  kern<<<grid, kThreadsMxSilu, C::kSmem, stream>>>(ma, mb, p);
+  B200_CUDA_TRY(cudaGetLastError());
+  return B200_OK;
+}
 
 // ============================================================================================ CTA-pair form
 // Two CTAs of a cluster work on one 256 x 256 tile (tcgen05 cta_group::2): each CTA loads its own 128 rows of A
@@ -555,7 +734,7 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
 }
 
 template <typename OutT>
-__global__ void __launch_bounds__(kThreadsMx, 1)
+__global__ void __launch_bounds__(kThreadsMxSilu, 1)
 gemm_mx_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const MxParams p) {
   constexpr int kTileM = 2 * BM, kTileN = 256;
@@ -595,7 +774,7 @@ gemm_mx_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       mbar_init(&sf_empty[i], 1);
     }
     mbar_init(acc_full, 1);
-    mbar_init(acc_empty, 8);         // four epilogue warps in each CTA
+    mbar_init(acc_empty, 16);        // eight epilogue warps in each CTA
     fence_mbar_init();
     fence_proxy_async_smem();
   }
@@ -726,11 +905,13 @@ gemm_mx_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
     }
     __syncwarp();
-  } else if (warp < 4) {
-    // ------------------------------------------------------------------ epilogue (each CTA, its own 128 rows)
+  } else if (warp < 4 || warp >= 8) {
+    // ------------------------------------------------------------------ epilogue (each CTA, its own 128 rows; warps
+    // 0-3 take columns [0, 128) of their row quadrant, warps 8-11 columns [128, 256))
     OutT* out = static_cast<OutT*>(p.out);
     const bool vec_ok = (p.ldo % (16 / (int)sizeof(OutT)) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15u) == 0);
-    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const int half = warp >> 3;
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int tile = pair_id; ok && tile < num_tiles; tile += num_pairs) {
@@ -739,22 +920,58 @@ gemm_mx_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       ok = mbar_wait(acc_full, acc_phase, p.status, 56);
       if (!ok) break;
       tc_fence_after();
-      const int m = m_blk * kTileM + static_cast<int>(rank) * BM + warp * 32 + lane;
-      const uint32_t taddr = tmem_base + lane_addr;
-      constexpr int kChunks = kTileN / 16;
-#pragma unroll 1
-      for (int ch = 0; ch < kChunks; ch += 2) {
-        float v[32];
-        tmem_ld16(taddr + ch * 16, *reinterpret_cast<float(*)[16]>(v));
-        tmem_ld16(taddr + (ch + 1) * 16, *reinterpret_cast<float(*)[16]>(v + 16));
-        tmem_ld_wait();
-        if (ch + 2 >= kChunks) {
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(acc_empty, 0);
+      const int m = m_blk * kTileM + static_cast<int>(rank) * BM + (warp & 3) * 32 + lane;
+      const uint32_t taddr = tmem_base + lane_addr + half * 128;
+      const int n_half = n_blk * kTileN + half * 128;
+      if constexpr (sizeof(OutT) == 2) {
+        // 16-bit output: read, round and pack the warp's 128 columns (64 registers), hand the accumulator back, then
+        // store -- the stores run under the next tile's MMAs
+        uint32_t pk[64];
+#pragma unroll
+        for (int ch = 0; ch < 8; ch += 2) {
+          float v[32];
+          tmem_ld16(taddr + ch * 16, *reinterpret_cast<float(*)[16]>(v));
+          tmem_ld16(taddr + (ch + 1) * 16, *reinterpret_cast<float(*)[16]>(v + 16));
+          tmem_ld_wait();
+#pragma unroll
+          for (int c = 0; c < 32; c += 2) pk[ch * 8 + c / 2] = pack2(out, v[c], v[c + 1]);
         }
-        const int n0 = n_blk * kTileN + ch * 16;
-        if (m < p.M && n0 < p.N) store_row<32>(out + static_cast<int64_t>(m) * p.ldo + n0, v, min(p.N - n0, 32), vec_ok);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(acc_empty, 0);
+        if (m < p.M && n_half < p.N) {
+          OutT* dst = out + static_cast<int64_t>(m) * p.ldo + n_half;
+          const int valid = min(p.N - n_half, 128);
+          if (vec_ok && valid == 128) {
+#pragma unroll
+            for (int c = 0; c < 16; ++c)
+              reinterpret_cast<uint4*>(dst)[c] = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+          } else {
+#pragma unroll
+            for (int c = 0; c < 64; ++c) {
+              OutT lo, hi;
+              *reinterpret_cast<uint16_t*>(&lo) = static_cast<uint16_t>(pk[c] & 0xffffu);
+              *reinterpret_cast<uint16_t*>(&hi) = static_cast<uint16_t>(pk[c] >> 16);
+              if (2 * c < valid) dst[2 * c] = lo;
+              if (2 * c + 1 < valid) dst[2 * c + 1] = hi;
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int ch = 0; ch < 8; ch += 2) {
+          float v[32];
+          tmem_ld16(taddr + ch * 16, *reinterpret_cast<float(*)[16]>(v));
+          tmem_ld16(taddr + (ch + 1) * 16, *reinterpret_cast<float(*)[16]>(v + 16));
+          tmem_ld_wait();
+          if (ch + 2 >= 8) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(acc_empty, 0);
+          }
+          const int n0 = n_half + ch * 16;
+          if (m < p.M && n0 < p.N) store_row<32>(out + static_cast<int64_t>(m) * p.ldo + n0, v, min(p.N - n0, 32), vec_ok);
+        }
       }
       acc_phase ^= 1u;
     }
@@ -784,7 +1001,7 @@ int launch_mx_pair(const CUtensorMap& ma, const CUtensorMap& mb, const MxParams&
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
-  cfg.blockDim = dim3(kThreadsMx);
+  cfg.blockDim = dim3(kThreadsMxSilu);
   cfg.dynamicSmemBytes = kPairSmem;
   cfg.stream = stream;
   cfg.attrs = attr;
@@ -851,13 +1068,14 @@ extern "C" int b200_fp8_blockwise_scaled_mm_pow2(const void* a, int64_t lda, con
   p.out_dtype = out_dtype;
   p.offsets = nullptr; p.rows = nullptr; p.experts = nullptr;
   p.rows_stride = 0; p.sb_stride_e = 0; p.sa_stride_problem = -1; p.num_problems = 0; p.num_weight_experts = 1;
+  p.out_s = nullptr; p.out_s_stride_pack = 0;
   p.status = gemm_status_ptr();
   if (!p.status) return B200_ERR_CUDA;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // Tile choice.  Measured (us; 1024 / 4096 x 36864 x 7168, then 1024 / 4096 / 16384 x 7168 x 18432):
-  //   128 x 256, one CTA        252 / 873    171 / 541 / 1793
-  //   256 x 240, one CTA        261 / 876    136 / 543 / 1640
-  //   256 x 256 on a CTA pair   226 / 848    172 / 566 / 1973
+  // Tile choice.  Measured (us; 1024 / 4096 / 16384 x 36864 x 7168, then 1024 / 4096 / 16384 x 7168 x 18432):
+  //   128 x 256, one CTA        245 / 857 / 3358    179 / 496 / 1770
+  //   256 x 240, one CTA        261 / 883 / 3881    142 / 482 / 1649
+  //   256 x 256 on a CTA pair   228 / 858 / 3587    151 / 511 / 2053
   // (128 x 240 with two accumulators: 940 on the second shape, never ahead.)  Long K favours the two-half tile
   // (fewer, longer tiles amortise its unoverlapped read-out), wide N with K up to 8192 the CTA pair (half the
   // operand bytes per SM).  With every SM issuing MMAs back to back and nothing else the chip settles at 1.5 GHz
@@ -868,7 +1086,7 @@ extern "C" int b200_fp8_blockwise_scaled_mm_pow2(const void* a, int64_t lda, con
   if (g_force_block_n == 240) return launch_mx_dtype<240, 1>(a, lda, b, ldb, p, st);
   if (g_force_block_n == 2240) return launch_mx_dtype<240, 2>(a, lda, b, ldb, p, st);
   if (M >= 1024 && K >= 12288) return launch_mx_dtype<240, 2>(a, lda, b, ldb, p, st);
-  if (M >= 512 && N >= 4096) {
+  if (M >= 512 && M < 4096 && N >= 4096) {
     // a cluster launch can be refused where a plain one is not (no pair of SMs free, a tool that does not support
     // clusters): then the one-CTA form runs instead
     if (launch_mx_pair_dtype(a, lda, b, ldb, p, st) == B200_OK) return B200_OK;
@@ -915,6 +1133,7 @@ extern "C" int b200_fp8_blockwise_scaled_grouped_mm_pow2(
   p.offsets = problem_offsets; p.rows = problem_rows; p.experts = problem_experts;
   p.rows_stride = problem_rows_stride; p.sb_stride_e = sb_stride_e; p.sa_stride_problem = sa_stride_problem;
   p.num_problems = num_problems; p.num_weight_experts = num_weight_experts;
+  p.out_s = nullptr; p.out_s_stride_pack = 0;
   p.status = gemm_status_ptr();
   if (!p.status) return B200_ERR_CUDA;
   // Tile width.  128 x 256 with one accumulator is the default; the test hook reaches the narrower tiles with two
@@ -922,4 +1141,55 @@ extern "C" int b200_fp8_blockwise_scaled_grouped_mm_pow2(
   if (g_force_block_n == 9240) return launch_mx_dtype<240, 1, true>(a, lda, b, ldb, p, static_cast<cudaStream_t>(stream));
   if (g_force_block_n == 9192) return launch_mx_dtype<192, 1, true>(a, lda, b, ldb, p, static_cast<cudaStream_t>(stream));
   return launch_mx_dtype<256, 1, true>(a, lda, b, ldb, p, static_cast<cudaStream_t>(stream));
+}
+
+// Expert GEMM 1 with the activation and the next GEMM's quantisation in its epilogue: for every problem,
+//   q, s = quantise_pow2( SiLU(x W_gate^T) * (x W_up^T) )       (128-wide groups, packed exponent words)
+// where W = b holds, per weight slice, 2 * N rows (gate rows first) and N is the intermediate size.  The accumulator
+// is rounded to `mid_dtype` (bf16 / fp16) before the activation and the product after it, exactly as the unfused
+// sequence stores them, so codes and exponents equal b200_fp8_blockwise_scaled_grouped_mm_pow2 followed by
+// b200_silu_mul_per_token_group_quant_fp8_ue8m0 bit for bit -- without the [rows, 2N] intermediate ever reaching HBM.
+// out_q [total_rows, N] e4m3 (leading dimension ldq bytes); out_s packed words, word (row, w) at
+// out_s[w * out_s_stride_pack + row], bytes of groups past N / 128 untouched (pass a zeroed tensor).
+// Replaces: the SiLU*mul + quant pass between the two expert GEMMs (python/sglang/srt/layers/moe/cutlass_moe.py:191-194;
+// ep_moe/layer.py:606-628) together with the GEMM before it.
+extern "C" int b200_fp8_blockwise_scaled_grouped_mm_pow2_silu_quant(
+    const void* a, int64_t lda, int64_t total_rows, const void* b, int64_t ldb, const uint32_t* sa_packed,
+    int64_t sa_stride_m, int64_t sa_stride_pack, int64_t sa_stride_problem, const float* sb_pow2, int64_t sb_stride_e,
+    int64_t sb_stride_n, int64_t sb_stride_g, void* out_q, int64_t ldq, uint32_t* out_s, int64_t out_s_stride_pack,
+    int mid_dtype, const int32_t* problem_offsets, const int32_t* problem_rows, int64_t problem_rows_stride,
+    const int32_t* problem_experts, int num_problems, int num_weight_experts, int64_t N, int64_t K, void* stream) {
+  using namespace b200;
+  if (total_rows < 0 || N < 0 || K <= 0 || num_problems < 0 || num_weight_experts <= 0) return B200_ERR_BAD_SHAPE;
+  if (total_rows == 0 || N == 0 || num_problems == 0) return B200_OK;
+  if (num_problems > kMaxProblems) return B200_ERR_TOO_LARGE;
+  if (total_rows > 0x7fffff00LL || K > 0x7fffff00LL || 2 * N * num_weight_experts > 0x7fffff00LL) return B200_ERR_TOO_LARGE;
+  if (!a || !b || !sa_packed || !sb_pow2 || !out_q || !out_s || !problem_offsets || !problem_rows) return B200_ERR_NULL_PTR;
+  if (mid_dtype != B200_DT_BF16 && mid_dtype != B200_DT_F16) return B200_ERR_BAD_DTYPE;
+  if (lda < K || ldb < K || ldq < N || out_s_stride_pack < total_rows) return B200_ERR_BAD_STRIDE;
+  if ((lda % 16) != 0 || (ldb % 16) != 0 || (ldq % 16) != 0 || !aligned16(a) || !aligned16(b) || !aligned16(out_q))
+    return B200_ERR_MISALIGNED;
+  if (sa_stride_m < 0 || sa_stride_pack < 0 || sb_stride_e < 0 || sb_stride_n < 0 || sb_stride_g < 0 ||
+      problem_rows_stride < 0)
+    return B200_ERR_BAD_STRIDE;
+  if (K % 128 != 0) return B200_ERR_BAD_SHAPE;
+  if (N % 128 != 0) return B200_ERR_UNSUPPORTED;
+  int rc = require_sm100();
+  if (rc != B200_OK) return rc;
+  if (gemm_sticky_status() != 0) return B200_ERR_DEVICE_TIMEOUT;
+  MxParams p;
+  p.sa = sa_packed; p.sb = sb_pow2; p.out = out_q;
+  p.sa_stride_m = sa_stride_m; p.sa_stride_pack = sa_stride_pack;
+  p.sb_stride_n = sb_stride_n; p.sb_stride_g = sb_stride_g; p.ldo = ldq;
+  p.M = static_cast<int>(total_rows); p.N = static_cast<int>(N); p.K = static_cast<int>(K);
+  p.out_dtype = mid_dtype;
+  p.offsets = problem_offsets; p.rows = problem_rows; p.experts = problem_experts;
+  p.rows_stride = problem_rows_stride; p.sb_stride_e = sb_stride_e; p.sa_stride_problem = sa_stride_problem;
+  p.num_problems = num_problems; p.num_weight_experts = num_weight_experts;
+  p.out_s = out_s; p.out_s_stride_pack = out_s_stride_pack;
+  p.status = gemm_status_ptr();
+  if (!p.status) return B200_ERR_CUDA;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return mid_dtype == B200_DT_BF16 ? launch_mx_silu<__nv_bfloat16>(a, lda, b, ldb, p, st)
+                                    : launch_mx_silu<__half>(a, lda, b, ldb, p, st);
 }

@@ -13,7 +13,7 @@ import torch
 
 from ...sgl_kernel import (apply_shuffle_mul_sum, fp8_blockwise_scaled_grouped_mm, prepare_moe_input,
                            shuffle_packed_scales, shuffle_rows, silu_and_mul)
-from ..quantization.deep_gemm_wrapper import grouped_gemm_pow2
+from ..quantization.deep_gemm_wrapper import grouped_gemm_pow2, grouped_gemm_pow2_silu_quant
 from ..quantization.fp8_kernel import sglang_per_token_group_quant_fp8, silu_and_mul_per_token_group_quant_fp8
 
 
@@ -106,13 +106,15 @@ def fused_experts_block_fp8(a, w13, w2, w13_scale, w2_scale, topk_weights, topk_
                                      w2_scale.transpose(1, 2), topk_weights, topk_ids)
 
 
-def fused_experts_block_fp8_ue8m0(a, w13, w2, w13_scale, w2_scale, topk_weights, topk_ids):
+def fused_experts_block_fp8_ue8m0(a, w13, w2, w13_scale, w2_scale, topk_weights, topk_ids,
+                                  fuse_activation: bool = True):
     """The fused expert layer on the tensor core's block-scaling path: activations quantised to power-of-two
     scales, weights w13 [E, 2n, k] / w2 [E, k, n] e4m3 with POWER-OF-TWO fp32 block scales [E, 2n/128, k/128] /
     [E, k/128, n/128] (requant_weight_ue8m0 at load time).  The reference's counterpart is its DeepGEMM expert path
     with UE8M0 scales (python/sglang/srt/layers/moe/ep_moe/layer.py:540-640: scatter -> contiguous grouped GEMM ->
     SiLU*mul -> quant -> grouped GEMM -> weighted gather); here every expert's rows are packed without padding and
-    the schedule reads offsets and counts on the device."""
+    the schedule reads offsets and counts on the device.  fuse_activation: SiLU*mul and the second quantisation run in
+    the first GEMM's epilogue (same bits as the separate kernels)."""
     assert topk_weights.shape == topk_ids.shape
     assert a.dtype in (torch.half, torch.bfloat16) and a.dim() == 2 and a.is_contiguous()
     E, n2, k = w13.shape
@@ -134,9 +136,14 @@ def fused_experts_block_fp8_ue8m0(a, w13, w2, w13_scale, w2_scale, topk_weights,
     rep_q = shuffle_rows(a_q, a_map, (m * topk, k))
     rep_s = shuffle_packed_scales(a_s, a_map)
     rows = ps1[:, 0]
-    c1 = torch.empty((m * topk, 2 * n), device=device, dtype=a.dtype)
-    grouped_gemm_pow2(rep_q, rep_s, w13, w13_scale, c1, expert_offsets[:-1], rows)
-    inter_q, inter_s = silu_and_mul_per_token_group_quant_fp8(c1, 128, scale_ue8m0=True)
+    if fuse_activation:
+        # GEMM 1 with SiLU*mul and GEMM 2's quantisation in its epilogue: the [rows, 2n] intermediate stays on chip
+        inter_q, inter_s = grouped_gemm_pow2_silu_quant(rep_q, rep_s, w13, w13_scale, expert_offsets[:-1], rows,
+                                                        mid_dtype=a.dtype)
+    else:
+        c1 = torch.empty((m * topk, 2 * n), device=device, dtype=a.dtype)
+        grouped_gemm_pow2(rep_q, rep_s, w13, w13_scale, c1, expert_offsets[:-1], rows)
+        inter_q, inter_s = silu_and_mul_per_token_group_quant_fp8(c1, 128, scale_ue8m0=True)
     c2 = torch.empty((m * topk, k), device=device, dtype=a.dtype)
     grouped_gemm_pow2(inter_q, inter_s, w2, w2_scale, c2, expert_offsets[:-1], rows)
     result = torch.empty((m, k), device=device, dtype=a.dtype)
@@ -193,9 +200,8 @@ def grouped_experts_prequantized_ue8m0(a_q, a_words, expert_ids, w13, w2, w13_sc
     rep_q = shuffle_rows(a_q, a_map, (R, k))
     rep_w = shuffle_rows(a_words.contiguous(), a_map, (R, a_words.shape[1]))       # rows of words: a plain row gather
     rows = ps1[:, 0]
-    c1 = torch.empty((R, 2 * n), device=device, dtype=out_dtype)
-    grouped_gemm_pow2(rep_q, rep_w, w13, w13_scale, c1, expert_offsets[:-1], rows)
-    inter_q, inter_s = silu_and_mul_per_token_group_quant_fp8(c1, 128, scale_ue8m0=True)
+    inter_q, inter_s = grouped_gemm_pow2_silu_quant(rep_q, rep_w, w13, w13_scale, expert_offsets[:-1], rows,
+                                                    mid_dtype=out_dtype)
     c2 = torch.empty((R, k), device=device, dtype=out_dtype)
     grouped_gemm_pow2(inter_q, inter_s, w2, w2_scale, c2, expert_offsets[:-1], rows)
     if return_sorted:

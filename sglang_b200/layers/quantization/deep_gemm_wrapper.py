@@ -70,6 +70,39 @@ def grouped_gemm_pow2(a: torch.Tensor, sa_packed: torch.Tensor, w: torch.Tensor,
     return out
 
 
+def grouped_gemm_pow2_silu_quant(a: torch.Tensor, sa_packed: torch.Tensor, w13: torch.Tensor, w13s: torch.Tensor,
+                                 problem_offsets: torch.Tensor, problem_rows: torch.Tensor,
+                                 problem_experts: Optional[torch.Tensor] = None, mid_dtype: torch.dtype = torch.bfloat16,
+                                 sa_stride_problem: int = -1):
+    """Expert GEMM 1 with SiLU*mul and the next GEMM's power-of-two quantisation in its epilogue.  a [R, K] e4m3,
+    w13 [E, 2n, K] (gate rows first), w13s [E, 2n/128, K/128] fp32 powers of two.  Returns (codes [R, n] e4m3, packed
+    exponents int32 [R, ceil(n/512)], rows contiguous) -- the bits of grouped_gemm_pow2 into a `mid_dtype` tensor
+    followed by silu_and_mul_per_token_group_quant_fp8(..., scale_ue8m0=True)."""
+    from .fp8_kernel import create_per_token_group_quant_fp8_output_scale
+    R, K = a.shape
+    E, n2, Kw = w13.shape
+    n = n2 // 2
+    assert Kw == K and K % 128 == 0 and n % 128 == 0 and n2 == 2 * n
+    assert a.dtype == fp8_dtype and w13.dtype == fp8_dtype and a.is_contiguous() and w13.is_contiguous()
+    assert sa_packed.dtype == torch.int32 and w13s.dtype == torch.float32 and w13s.shape == (E, n2 // 128, K // 128)
+    assert problem_offsets.dtype == torch.int32 and problem_rows.dtype == torch.int32 and problem_rows.dim() == 1
+    P = problem_offsets.numel()
+    q = torch.empty((R, n), dtype=fp8_dtype, device=a.device)
+    s = create_per_token_group_quant_fp8_output_scale((R, n), a.device, 128, True, True, True)     # zero-filled
+    if R == 0 or P == 0:
+        return q, s
+    dt = {torch.float16: _lib.DT_F16, torch.bfloat16: _lib.DT_BF16}[mid_dtype]
+    with torch.cuda.device(a.device):
+        rc = _lib.lib().b200_fp8_blockwise_scaled_grouped_mm_pow2_silu_quant(
+            a.data_ptr(), K, R, w13.data_ptr(), K, sa_packed.data_ptr(), sa_packed.stride(-2), sa_packed.stride(-1),
+            sa_stride_problem, w13s.data_ptr(), w13s.stride(0), w13s.stride(1), w13s.stride(2), q.data_ptr(), n,
+            s.data_ptr(), s.stride(1), dt, problem_offsets.data_ptr(), problem_rows.data_ptr(), problem_rows.stride(0),
+            problem_experts.data_ptr() if problem_experts is not None else None, P, E, n, K,
+            torch.cuda.current_stream(a.device).cuda_stream)
+    _lib.check("grouped_gemm_pow2_silu_quant", rc)
+    return q, s
+
+
 def gemm_nt_f8f8bf16(lhs: Tuple[torch.Tensor, torch.Tensor], rhs: Tuple[torch.Tensor, torch.Tensor],
                      out: torch.Tensor) -> None:
     """out[M, N] = lhs[M, K] @ rhs[N, K].T (entrypoint.py:78-93)."""

@@ -363,3 +363,57 @@ def test_prequantized_rows_on_the_block_scaling_path_equal_the_fused_layer():
     out = grouped_experts_prequantized_ue8m0(q_pad.view(FP8), w_pad, id_pad, w13, w2, w13s, w2s, torch.bfloat16)
     assert same_bits(out[::2].cpu(), ref.cpu())
     _status_ok()
+
+
+@pytest.mark.parametrize("mid_dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("sizes,I,K", [([5], 128, 128), ([0, 1, 127, 128, 129, 300, 0, 64], 256, 1024),
+                                       ([130] * 12, 640, 512), ([256, 3, 200], 2048, 7168)])
+def test_gemm_epilogue_that_emits_codes_and_exponents(sizes, I, K, mid_dtype):
+    """Expert GEMM 1 with SiLU*mul and the next quantisation in its epilogue against the three-kernel sequence
+    (grouped GEMM into a 16-bit tensor, SiLU*mul + power-of-two quantisation): codes and exponent bytes of every owned
+    row bit for bit; rows outside every problem untouched."""
+    from sglang_b200.layers.quantization.deep_gemm_wrapper import grouped_gemm_pow2, grouped_gemm_pow2_silu_quant
+    from sglang_b200.layers.quantization.fp8_kernel import (sglang_per_token_group_quant_fp8,
+                                                            silu_and_mul_per_token_group_quant_fp8)
+    E = len(sizes)
+    wq, ws = _make_experts(E, 2 * I, K, seed=I + K)
+    gap = 3
+    offsets, R = [], 0
+    for sz in sizes:
+        offsets.append(R)
+        R += sz + gap
+    x = _rows(R, K, seed=R + 1)
+    q, sp = sglang_per_token_group_quant_fp8(x.cuda(), 128, column_major_scales=True, scale_tma_aligned=True,
+                                             scale_ue8m0=True)
+    d = dict(dtype=torch.int32, device="cuda")
+    off_t = torch.tensor(offsets, **d)
+    rows_t = torch.tensor(sizes, **d)
+    c1 = torch.zeros((R, 2 * I), dtype=mid_dtype, device="cuda")
+    grouped_gemm_pow2(q, sp, wq.cuda(), ws.cuda(), c1, off_t, rows_t)
+    q_ref, s_ref = silu_and_mul_per_token_group_quant_fp8(c1, 128, scale_ue8m0=True)
+    q_f, s_f = grouped_gemm_pow2_silu_quant(q, sp, wq.cuda(), ws.cuda(), off_t, rows_t, mid_dtype=mid_dtype)
+    _status_ok()
+    assert s_f.shape == s_ref.shape and s_f.stride() == s_ref.stride()
+    owned = torch.zeros(R, dtype=torch.bool)
+    for o, sz in zip(offsets, sizes):
+        owned[o:o + sz] = True
+    assert owned.any()
+    assert torch.equal(q_f.view(torch.uint8).cpu()[owned], q_ref.view(torch.uint8).cpu()[owned])
+    assert torch.equal(s_f.cpu()[owned], s_ref.cpu()[owned])
+    assert (s_f.cpu()[~owned] == 0).all(), "an exponent of a row outside every problem was written"
+
+
+def test_fused_experts_with_and_without_the_activation_in_the_epilogue():
+    from sglang_b200.layers.moe.cutlass_moe import fused_experts_block_fp8_ue8m0
+    E, H, I, m, topk = 32, 1024, 512, 600, 4
+    w13, w13s = _make_experts(E, 2 * I, H, seed=E)
+    w2, w2s = _make_experts(E, H, I, seed=E + 1)
+    w13, w13s, w2, w2s = w13.cuda(), w13s.cuda(), w2.cuda(), w2s.cuda()
+    g = torch.Generator().manual_seed(m)
+    x = torch.randn(m, H, generator=g).to(torch.bfloat16).cuda()
+    tw, ti = O.fused_topk_native(torch.randn(m, E, generator=g), topk)
+    tw, ti = tw.cuda(), ti.to(torch.int32).cuda()
+    a = fused_experts_block_fp8_ue8m0(x, w13, w2, w13s, w2s, tw, ti, fuse_activation=True)
+    b = fused_experts_block_fp8_ue8m0(x, w13, w2, w13s, w2s, tw, ti, fuse_activation=False)
+    assert same_bits(a, b)
+    _status_ok()
