@@ -426,7 +426,8 @@ int b200_topk_softmax(const void* gating_output, int dtype, int64_t row_stride, 
  * the calling process; 0 = all.  Returns the previous value.  A row-parallel linear that overlaps the all-reduce of
  * one row chunk with the GEMM of the next leaves a few SMs to the all-reduce kernel this way (the reference reaches
  * the same end with deep_gemm.set_num_sms, python/sglang/srt/layers/quantization/deep_gemm_wrapper/entrypoint.py:100-110).
- * The value is read when a kernel is launched (or captured into a graph).
+ * The value is read when a kernel is launched (or captured into a graph).  One setting per process, not synchronised:
+ * a caller that launches from several threads sets it once, or serialises the launches it brackets with it.
  */
 int b200_set_sm_limit(int sms);
 
