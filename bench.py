@@ -862,7 +862,7 @@ def run_gpu_arm(args):
         # and the all-reduce runs in its multicast form beside them; with none the two kernels compete for the SMs.
         cands = [(args.tp_chunks, 0)] if args.tp_chunks else [(1, 0), (2, 0), (4, 0)]
         if not args.tp_chunks and ar is not None and ar.has_multicast:
-            cands += [(2, 16), (4, 16), (8, 16), (2, 8), (4, 8)]
+            cands += [(2, 16), (4, 16), (8, 16), (2, 8), (4, 8), (2, 4)]
         best = None
         for c, r in cands:
             row.overlap_chunks, row.reserve_sms = c, r
