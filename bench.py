@@ -415,6 +415,29 @@ def ue8m0_mlp(dev, ceiling, steps=10):
            "rel_l2_vs_fp32_promotion_kernel_on_the_same_codes": err}
     if ceiling:
         out["frac_of_fp8_ceiling"] = gemm_tf / ceiling
+    # the same two projections as a CHAIN (down consumes SiLU(gate) * up of gate_up's output): with the activation and
+    # the second quantisation in gate_up's epilogue, and as separate kernels; the two produce the same bits
+    from sglang_b200.layers.quantization.deep_gemm_wrapper import gate_up_silu_quant_pow2
+    from sglang_b200.layers.quantization.fp8_kernel import silu_and_mul_per_token_group_quant_fp8
+
+    def chain_fused():
+        q_, s_ = sglang_per_token_group_quant_fp8(x, 128, column_major_scales=True, scale_tma_aligned=True, scale_ue8m0=True)
+        hq, hs = gate_up_silu_quant_pow2(q_, s_, w1q, w1s)
+        return w8a8_block_fp8_matmul_deepgemm(hq, w2q, hs, w2s, [128, 128], torch.bfloat16, weight_scale_ue8m0=True)
+
+    def chain_separate():
+        q_, s_ = sglang_per_token_group_quant_fp8(x, 128, column_major_scales=True, scale_tma_aligned=True, scale_ue8m0=True)
+        c1 = w8a8_block_fp8_matmul_deepgemm(q_, w1q, s_, w1s, [128, 128], torch.bfloat16, weight_scale_ue8m0=True)
+        hq, hs = silu_and_mul_per_token_group_quant_fp8(c1, 128, scale_ue8m0=True)
+        return w8a8_block_fp8_matmul_deepgemm(hq, w2q, hs, w2s, [128, 128], torch.bfloat16, weight_scale_ue8m0=True)
+    same = bool(torch.equal(chain_fused(), chain_separate()))
+    ms_f, g_ = time_graph(chain_fused, steps, torch.cuda.synchronize)
+    g_.reset()
+    ms_s, g_ = time_graph(chain_separate, steps, torch.cuda.synchronize)
+    g_.reset()
+    out["mlp_chain"] = {"what": "quant -> gate_up -> SiLU*mul -> quant -> down as one dependent chain (4096 tokens)",
+                        "fused_epilogue_ms": ms_f, "separate_kernels_ms": ms_s, "same_bits": same,
+                        "tflops_fused": FLOPS_PER_STEP / (ms_f * 1e-3) / 1e12}
     del w1q, w1s, w2q, w2s
     torch.cuda.empty_cache()
     return out

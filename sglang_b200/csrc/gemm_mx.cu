@@ -139,9 +139,9 @@ __device__ __forceinline__ void mx_tile_coords(int tile, int m_blocks, int n_blo
   n_blk = in_group / rows;
 }
 
-// Dense: groups of 32 row blocks x all column blocks.  Grouped: the row tiles of all problems laid end to end
-// (prefix table `tile_start`, built once per CTA), column blocks fastest, so the one or two row tiles of an expert
-// run at the same time on neighbouring SMs and its weights are fetched from HBM once.  Offsets and counts come from
+// Dense: groups of 32 row blocks x all column blocks.  Grouped: the problems laid end to end (prefix table
+// `tile_start` of row tiles, built once per CTA); inside a problem the column blocks are outermost, so the row tiles
+// that share a weight block run at the same time on neighbouring SMs and the block is fetched from HBM once.  Offsets and counts come from
 // device memory and are clamped into the row range: a table that does not match the buffers cannot send a load or a
 // store out of bounds.
 template <bool GROUPED, int TILE_M>
@@ -156,14 +156,18 @@ __device__ __forceinline__ MxTile mx_get_tile(int tile, const MxParams& p, int m
     t.e_w = 0;
     t.sa_base = 0;
   } else {
-    const int vt = tile / n_blocks;
-    t.n_blk = tile - vt * n_blocks;
-    int lo = 0, hi = p.num_problems;            // last problem whose first tile is <= vt
+    // tiles of a problem: column blocks outermost, its row tiles innermost -- the row tiles of one column block run
+    // side by side and share the weight block (one expert with a few thousand rows behaves like the dense kernel:
+    // its activations stay in L2 and every weight block comes from HBM once)
+    int lo = 0, hi = p.num_problems;            // last problem whose first tile is <= tile
     while (hi - lo > 1) {
       const int mid = (lo + hi) >> 1;
-      if (tile_start[mid] <= vt) lo = mid; else hi = mid;
+      if (tile_start[mid] * n_blocks <= tile) lo = mid; else hi = mid;
     }
-    const int sub = vt - tile_start[lo];
+    const int local = tile - tile_start[lo] * n_blocks;
+    const int row_tiles = max(tile_start[lo + 1] - tile_start[lo], 1);
+    t.n_blk = local / row_tiles;
+    const int sub = local - t.n_blk * row_tiles;
     const int rows = __ldg(p.rows + static_cast<int64_t>(lo) * p.rows_stride);
     const int off = __ldg(p.offsets + lo);
     t.row0 = min(max(off + sub * TILE_M, 0), p.M - 1);

@@ -103,6 +103,21 @@ def grouped_gemm_pow2_silu_quant(a: torch.Tensor, sa_packed: torch.Tensor, w13: 
     return q, s
 
 
+def gate_up_silu_quant_pow2(a: torch.Tensor, sa_packed: torch.Tensor, w_gate_up: torch.Tensor, ws: torch.Tensor,
+                            mid_dtype: torch.dtype = torch.bfloat16):
+    """Dense MLP, first half, on the block-scaling path: a [M, K] e4m3 with packed exponents, w_gate_up [2n, K]
+    (gate rows first: the merged gate_up weight of the reference's MergedColumnParallelLinear,
+    python/sglang/srt/layers/linear.py:415-520), ws [2n/128, K/128] fp32 powers of two.  One kernel computes the
+    projection, SiLU(gate) * up and the quantisation for the down projection; returns (codes [M, n], packed exponents).
+    Same bits as the GEMM into a `mid_dtype` tensor followed by silu_and_mul_per_token_group_quant_fp8."""
+    M = a.shape[0]
+    dev = a.device
+    offsets = torch.zeros(1, dtype=torch.int32, device=dev)
+    rows = torch.full((1,), M, dtype=torch.int32, device=dev)
+    return grouped_gemm_pow2_silu_quant(a, sa_packed, w_gate_up.unsqueeze(0), ws.unsqueeze(0), offsets, rows,
+                                        mid_dtype=mid_dtype)
+
+
 def gemm_nt_f8f8bf16(lhs: Tuple[torch.Tensor, torch.Tensor], rhs: Tuple[torch.Tensor, torch.Tensor],
                      out: torch.Tensor) -> None:
     """out[M, N] = lhs[M, K] @ rhs[N, K].T (entrypoint.py:78-93)."""

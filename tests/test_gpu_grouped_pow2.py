@@ -417,3 +417,22 @@ def test_fused_experts_with_and_without_the_activation_in_the_epilogue():
     b = fused_experts_block_fp8_ue8m0(x, w13, w2, w13s, w2s, tw, ti, fuse_activation=False)
     assert same_bits(a, b)
     _status_ok()
+
+
+def test_dense_gate_up_with_the_activation_in_the_epilogue():
+    """The dense MLP's gate_up projection + SiLU*mul + quantisation in one kernel against the three-kernel chain, and
+    the chain's end (down projection) against the oracle."""
+    from sglang_b200.layers.quantization.deep_gemm_wrapper import gate_up_silu_quant_pow2
+    from sglang_b200.layers.quantization.fp8_kernel import (sglang_per_token_group_quant_fp8,
+                                                            silu_and_mul_per_token_group_quant_fp8,
+                                                            w8a8_block_fp8_matmul_deepgemm)
+    M, K, I = 300, 1024, 768
+    wq, ws = _make_experts(1, 2 * I, K, seed=77)
+    wq, ws = wq[0].cuda(), ws[0].cuda()
+    x = _rows(M, K, seed=78).cuda()
+    q, sp = sglang_per_token_group_quant_fp8(x, 128, column_major_scales=True, scale_tma_aligned=True, scale_ue8m0=True)
+    c1 = w8a8_block_fp8_matmul_deepgemm(q, wq, sp, ws, [128, 128], torch.bfloat16, weight_scale_ue8m0=True)
+    q_ref, s_ref = silu_and_mul_per_token_group_quant_fp8(c1, 128, scale_ue8m0=True)
+    q_f, s_f = gate_up_silu_quant_pow2(q, sp, wq, ws)
+    _status_ok()
+    assert same_bits(q_f.cpu(), q_ref.cpu()) and torch.equal(s_f.cpu(), s_ref.cpu())
