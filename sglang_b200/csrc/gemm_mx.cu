@@ -317,6 +317,11 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc) * C::kAccStride;
+      // two-half tile of a problem with at most 128 rows left: the second half's MMAs are not issued
+      int nh = MSUB;
+      if constexpr (GROUPED && MSUB == 2)
+        nh = mx_get_tile<GROUPED, kTileM>(tile, p, m_blocks, n_blocks, tile_start).valid > BM ? 2 : 1;
+      const int hl = nh - 1;
       for (int kb = 0; kb < nkb; ++kb) {
         if (!next_ready) {
           ok = mbar_wait(&full_bar[stage], phase, p.status, 43);
@@ -348,6 +353,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < 4 * MSUB - 1; ++i) {
             const int k = i / MSUB, h = i % MSUB;      // K step, 128-row half
+            if (h >= nh || (k == 3 && h == hl)) continue;
             umma_mx(d_tmem + h * C::kAccStride, a_desc + static_cast<uint64_t>(2 * k + h * ((BM * BK) >> 4)),
                     b_desc + static_cast<uint64_t>(2 * k), idesc, tmem_base + C::kSfaCol + 4 * h, tmem_base + C::kSfbCol,
                     (kb > 0 || k > 0) ? 1u : 0u);
@@ -357,7 +363,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         next_ready = mbar_try_wait(&full_bar[nstage], nphase, 1);
         next_ready = __all_sync(0xffffffffu, next_ready);
         if (elected) {
-          constexpr int h = MSUB - 1;
+          const int h = hl;
           umma_mx(d_tmem + h * C::kAccStride, a_desc + static_cast<uint64_t>(6 + h * ((BM * BK) >> 4)), b_desc + 6, idesc,
                   tmem_base + C::kSfaCol + 4 * h, tmem_base + C::kSfbCol, 1u);
           umma_commit(&empty_bar[stage]);
@@ -570,8 +576,9 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       // (fp32 output, and the 240-wide tiles: chunk by chunk, the accumulator is handed back after the last load)
       constexpr int kChunks = (kWide8 ? 128 : BN) / 16;
       [[maybe_unused]] const int col_half = kWide8 ? (warp >> 3) : 0;
+      const int nh = (MSUB == 2 && t.valid <= BM) ? 1 : MSUB;   // halves that hold rows of the problem
 #pragma unroll 1
-      for (int h = 0; h < MSUB; ++h) {
+      for (int h = 0; h < nh; ++h) {
         const int m = t.row0 + h * BM + (warp & 3) * 32 + lane;
         const uint32_t taddr = tmem_base + lane_addr + static_cast<uint32_t>(MSUB == 2 ? h : acc) * C::kAccStride +
                                col_half * 128;
@@ -581,7 +588,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           tmem_ld16(taddr + ch * 16, *reinterpret_cast<float(*)[16]>(v));
           if (ch + 1 < kChunks) tmem_ld16(taddr + (ch + 1) * 16, *reinterpret_cast<float(*)[16]>(v + 16));
           tmem_ld_wait();
-          if (h == MSUB - 1 && ch + 2 >= kChunks) {
+          if (h == nh - 1 && ch + 2 >= kChunks) {
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[acc]);
@@ -1144,6 +1151,7 @@ extern "C" int b200_fp8_blockwise_scaled_grouped_mm_pow2(
   // accumulators (a tile's read-out overlaps the next tile's MMAs): 9240 -> 128 x 240, 9192 -> 128 x 192.
   if (g_force_block_n == 9240) return launch_mx_dtype<240, 1, true>(a, lda, b, ldb, p, static_cast<cudaStream_t>(stream));
   if (g_force_block_n == 9192) return launch_mx_dtype<192, 1, true>(a, lda, b, ldb, p, static_cast<cudaStream_t>(stream));
+  if (g_force_block_n == 9480) return launch_mx_dtype<240, 2, true>(a, lda, b, ldb, p, static_cast<cudaStream_t>(stream));
   return launch_mx_dtype<256, 1, true>(a, lda, b, ldb, p, static_cast<cudaStream_t>(stream));
 }
 

@@ -104,7 +104,7 @@ def _rows(R, K, seed):
     return x
 
 
-@pytest.mark.parametrize("tile_hook", [0, 9240, 9192])      # 128 x 256 (default), 128 x 240, 128 x 192 tiles
+@pytest.mark.parametrize("tile_hook", [0, 9240, 9192, 9480])      # 128 x 256 (default), 128 x 240, 128 x 192, 256 x 240 tiles
 @pytest.mark.parametrize("sizes,N,K", [([5], 256, 128), ([0, 1, 127, 128, 129, 300, 0, 64], 512, 1024),
                                        ([130] * 20, 1152, 640), ([256, 3, 700], 4096, 7168)])
 def test_grouped_block_scaling_gemm_problem_table(sizes, N, K, tile_hook):
