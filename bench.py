@@ -354,12 +354,21 @@ def quant_config2(dev, pk, steps=20):
     g_.reset()
     ms_p, g_ = time_graph(lambda: [pair() for _ in range(6)], steps, torch.cuda.synchronize)
     g_.reset()
+    # the same operator with its int8 destination
+    from sglang_b200.layers.quantization.int8_kernel import sglang_per_token_group_quant_int8
+
+    def int8():
+        it[0] += 1
+        return sglang_per_token_group_quant_int8(xs[it[0] % 3], 128)
+    ms_i, g_ = time_graph(lambda: [int8() for _ in range(6)], steps, torch.cuda.synchronize)
+    g_.reset()
     return {"bound": "hbm", "kernel": "quant_group_kernel<bf16,128> on [16384,7168] (config 2), graph replay, 3 rotating "
                                       "inputs (705 MB)", "us": ms * 1e3, "achieved": gbs, "peak": pk["hbm_gbs"],
             "unit": "GB/s", "frac": gbs / pk["hbm_gbs"], "frac_of_nominal_8000": gbs / NOMINAL_HBM_GBS,
             "algorithmic_bytes_per_launch": nbytes,
             "rmsnorm_quant_fused_us": ms_f / 6 * 1e3, "rmsnorm_then_quant_us": ms_p / 6 * 1e3,
-            "rmsnorm_quant_fused_gbs": nbytes / (ms_f / 6 * 1e-3) / 1e9}
+            "rmsnorm_quant_fused_gbs": nbytes / (ms_f / 6 * 1e-3) / 1e9,
+            "int8_destination_us": ms_i / 6 * 1e3, "int8_destination_gbs": nbytes / (ms_i / 6 * 1e-3) / 1e9}
 
 
 def fp8_ceiling(dev, steps=20):

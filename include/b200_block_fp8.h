@@ -63,6 +63,20 @@ int b200_per_token_group_quant_fp8(const void* x, int x_dtype, void* q, float* s
                                    int64_t s_stride_row, int64_t s_stride_grp,
                                    float eps, float fp8_min, float fp8_max, void* stream);
 
+/*
+ * Per-token-group INT8 quantisation: the same operator with an int8 destination.
+ * Replaces: sgl_per_token_group_quant_int8 (sgl-kernel/csrc/gemm/per_token_group_quant_8bit.cu:219-228; the
+ *   DST_DTYPE = int8_t launch at :206-207), called by sglang_per_token_group_quant_int8
+ *   (python/sglang/srt/layers/quantization/int8_kernel.py:185-209).
+ * Same layout arguments as above; q holds int8 codes.
+ * Arithmetic (bit-exact with the reference kernel): amax = max(eps, max|float(x)|); scale = amax / int8_max (IEEE);
+ * code = (int8) trunc(min(max(float(x)/scale, int8_min), int8_max)).
+ */
+int b200_per_token_group_quant_int8(const void* x, int x_dtype, void* q, float* s,
+                                    int64_t M, int64_t K, int64_t group_size,
+                                    int64_t s_stride_row, int64_t s_stride_grp,
+                                    float eps, float int8_min, float int8_max, void* stream);
+
 /* Same contract; divides with the IEEE division instruction sequence per element instead of
  * the reciprocal + exact-residual form.  Used by the tests to cross-check the fast form.
  * No counterpart in the reference. */

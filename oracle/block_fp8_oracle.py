@@ -72,6 +72,28 @@ def quant_group_fp8_cuda_semantics(
     return q, s
 
 
+def quant_group_int8_cuda_semantics(
+    x: torch.Tensor, group_size: int = 128, eps: float = 1e-10, int8_min: float = -128.0, int8_max: float = 127.0,
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The same kernel with an int8 destination (per_token_group_quant_8bit.cu:79-111 with DST_DTYPE = int8_t,
+    launched at :206-207; entry sgl_per_token_group_quant_int8 :219-228).
+
+    amax = max(eps, max|float(x)|);  s = amax / int8_max (IEEE fp32);
+    q    = (int8) trunc(fminf(fmaxf(float(x) / s, int8_min), int8_max))   -- the C++ cast truncates toward zero.
+    NaN elements become int8_min, as in the FP8 form.  Returns (int8 codes [.., K], fp32 scales [.., K/group]).
+    """
+    assert x.shape[-1] % group_size == 0
+    xf = x.detach().to("cpu").to(torch.float32).reshape(-1, group_size)
+    absx = torch.nan_to_num(xf.abs(), nan=0.0, posinf=float("inf"))
+    amax = torch.clamp(absx.amax(dim=-1, keepdim=True), min=torch.tensor(eps, dtype=torch.float32))
+    s = amax / torch.tensor(int8_max, dtype=torch.float32)
+    y = xf / s
+    y = torch.where(torch.isnan(y), torch.full_like(y, int8_min), y)
+    y = y.clamp(min=int8_min, max=int8_max)
+    q = torch.trunc(y).to(torch.int8).reshape(x.shape)
+    return q, s.reshape(x.shape[:-1] + (x.shape[-1] // group_size,))
+
+
 def native_per_token_group_quant_fp8(x, group_size, eps=1e-10, dtype=FP8):
     """Torch twin from the reference tests (test_block_fp8.py:24-49).
 

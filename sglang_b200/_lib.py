@@ -31,6 +31,8 @@ _SIGNATURES = {
     "b200_set_sm_limit": (c_int, [c_int]),
     "b200_per_token_group_quant_fp8": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                                c_int64, c_int64, c_float, c_float, c_float, c_void_p]),
+    "b200_per_token_group_quant_int8": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                                                c_int64, c_int64, c_float, c_float, c_float, c_void_p]),
     "b200_per_token_group_quant_fp8_ieee_div": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64,
                                                         c_int64, c_int64, c_int64, c_float, c_float, c_float,
                                                         c_void_p]),

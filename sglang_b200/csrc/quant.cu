@@ -168,6 +168,39 @@ __device__ __forceinline__ uint4 quantise_vec16(const Vec16<T>& data, float scal
   return out;
 }
 
+// int8 destination (per_token_group_quant_8bit.cu:110-111 with DST_DTYPE = int8_t, :206-207): the clamped quotient is
+// converted by truncation toward zero, as the C++ cast does.  Same quotient as above (correctly rounded; the literal
+// division where the reciprocal form is not exact); the clamp is explicit here, and fmaxf turns a NaN into q_min.
+template <typename T>
+__device__ __forceinline__ uint4 quantise_vec16_int8(const Vec16<T>& data, float scale, float q_min, float q_max) {
+  const uint32_t bits = __float_as_uint(scale);
+  const bool fast = ((bits & 0x007fffffu) != 0x007fffffu) && ((bits & 0x7f800000u) != 0x7f800000u);
+  const float r = __frcp_rn(scale);
+  uint32_t w[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    int c[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float v = data.get(4 * j + e);
+      float q;
+      if (fast) {
+        const float q0 = __fmul_rn(v, r);
+        const float t = __fmaf_rn(q0, scale, -v);
+        q = __fmaf_rn(-t, r, q0);
+      } else {
+        q = __fdiv_rn(v, scale);
+      }
+      c[e] = __float2int_rz(fminf(fmaxf(q, q_min), q_max));
+    }
+    // four ints -> four saturated int8 in one word (byte e = c[e])
+    uint32_t hi;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(c[3]), "r"(c[2]));
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(w[j]) : "r"(c[1]), "r"(c[0]), "r"(hi));
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
 // FUSE_SILU: x is [M, 2K] (gate | up); the row to quantise is silu(gate) * up, computed in fp32 and
 // rounded to T exactly as the separate silu_and_mul kernel stores it, so codes and scales equal the
 // two-kernel sequence bit for bit while the [M, K] intermediate never touches HBM.
@@ -178,7 +211,7 @@ __device__ __forceinline__ uint4 quantise_vec16(const Vec16<T>& data, float scal
 // contiguous; s_stride_row = 1 there).  A caller may ask for other word strides (rows of words contiguous: what an
 // expert-parallel dispatch sends per token).  The tile writes whole words; groups past K/GROUP inside the last word
 // are zero bytes.
-template <typename T, int GROUP, int PASSES, bool IEEE_DIV, bool FUSE_SILU = false, bool UE8M0 = false>
+template <typename T, int GROUP, int PASSES, bool IEEE_DIV, bool FUSE_SILU = false, bool UE8M0 = false, bool INT8 = false>
 __global__ void __launch_bounds__(kThreads, (PASSES >= 8 || sizeof(T) == 4) ? 2 : 4)   // 4 blocks/SM: <= 64 registers
 quant_group_kernel(const T* __restrict__ x, const int32_t* __restrict__ src_rows, int64_t x_rows, uint8_t* __restrict__ q,
                    float* __restrict__ s, int64_t M, int64_t K,
@@ -240,7 +273,9 @@ quant_group_kernel(const T* __restrict__ x, const int32_t* __restrict__ src_rows
 
     float scale = __fdiv_rn(amax, fp8_max);
     if constexpr (UE8M0) scale = exp2f(ceilf(log2f(fmaxf(scale, 1e-10f))));
-    const uint4 out = quantise_vec16<T, IEEE_DIV>(data[p], scale, fp8_min, fp8_max);
+    uint4 out;
+    if constexpr (INT8) out = quantise_vec16_int8<T>(data[p], scale, fp8_min, fp8_max);
+    else out = quantise_vec16<T, IEEE_DIV>(data[p], scale, fp8_min, fp8_max);
     if (col_ok && row < M) *reinterpret_cast<uint4*>(q + row * K + col) = out;
     if ((slot % TPG) == 0) s_tile[(p * ROWS_PER_PASS + row_in_pass) * GPT + slot / TPG] = scale;
   }
@@ -383,7 +418,7 @@ __global__ void __launch_bounds__(kThreads, NV <= 2 ? (HAS_RES ? 4 : 5) : 2) rms
   }
 }
 
-template <typename T, int GROUP, bool IEEE_DIV, bool FUSE_SILU = false, bool UE8M0 = false>
+template <typename T, int GROUP, bool IEEE_DIV, bool FUSE_SILU = false, bool UE8M0 = false, bool INT8 = false>
 int launch_group(const void* x, void* q, float* s, int64_t M, int64_t K, int64_t ssr, int64_t ssg, float eps,
                  float fmin_, float fmax_, cudaStream_t stream, const int32_t* src_rows = nullptr, int64_t x_rows = 0) {
   const int tiles_k = static_cast<int>((K + kTileW - 1) / kTileW);
@@ -401,7 +436,7 @@ int launch_group(const void* x, void* q, float* s, int64_t M, int64_t K, int64_t
   const T* xp = static_cast<const T*>(x);
   uint8_t* qp = static_cast<uint8_t*>(q);
 #define B200_LAUNCH_Q(P)                                                                                       \
-  quant_group_kernel<T, GROUP, P, IEEE_DIV, FUSE_SILU, UE8M0><<<grid, kThreads, 0, stream>>>(xp, src_rows, x_rows, qp, s, M, K, ssr, ssg, eps, fmin_, \
+  quant_group_kernel<T, GROUP, P, IEEE_DIV, FUSE_SILU, UE8M0, INT8><<<grid, kThreads, 0, stream>>>(xp, src_rows, x_rows, qp, s, M, K, ssr, ssg, eps, fmin_, \
                                                                            fmax_, tiles_k)
   switch (passes) {
     case 8:
@@ -416,19 +451,19 @@ int launch_group(const void* x, void* q, float* s, int64_t M, int64_t K, int64_t
   return B200_OK;
 }
 
-template <typename T, bool IEEE_DIV>
+template <typename T, bool IEEE_DIV, bool INT8 = false>
 int dispatch_group(int64_t group, const void* x, void* q, float* s, int64_t M, int64_t K, int64_t ssr, int64_t ssg,
                    float eps, float fmin_, float fmax_, cudaStream_t st) {
   switch (group) {
-    case 64: return launch_group<T, 64, IEEE_DIV>(x, q, s, M, K, ssr, ssg, eps, fmin_, fmax_, st);
-    case 128: return launch_group<T, 128, IEEE_DIV>(x, q, s, M, K, ssr, ssg, eps, fmin_, fmax_, st);
-    case 256: return launch_group<T, 256, IEEE_DIV>(x, q, s, M, K, ssr, ssg, eps, fmin_, fmax_, st);
-    case 512: return launch_group<T, 512, IEEE_DIV>(x, q, s, M, K, ssr, ssg, eps, fmin_, fmax_, st);
+    case 64: return launch_group<T, 64, IEEE_DIV, false, false, INT8>(x, q, s, M, K, ssr, ssg, eps, fmin_, fmax_, st);
+    case 128: return launch_group<T, 128, IEEE_DIV, false, false, INT8>(x, q, s, M, K, ssr, ssg, eps, fmin_, fmax_, st);
+    case 256: return launch_group<T, 256, IEEE_DIV, false, false, INT8>(x, q, s, M, K, ssr, ssg, eps, fmin_, fmax_, st);
+    case 512: return launch_group<T, 512, IEEE_DIV, false, false, INT8>(x, q, s, M, K, ssr, ssg, eps, fmin_, fmax_, st);
     default: return B200_ERR_UNSUPPORTED;
   }
 }
 
-template <bool IEEE_DIV>
+template <bool IEEE_DIV, bool INT8 = false>
 int quant_entry(const void* x, int x_dtype, void* q, float* s, int64_t M, int64_t K, int64_t group, int64_t ssr,
                 int64_t ssg, float eps, float fmin_, float fmax_, void* stream) {
   if (M < 0 || K < 0 || group <= 0) return B200_ERR_BAD_SHAPE;
@@ -440,11 +475,11 @@ int quant_entry(const void* x, int x_dtype, void* q, float* s, int64_t M, int64_
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (x_dtype) {
     case B200_DT_BF16:
-      return dispatch_group<__nv_bfloat16, IEEE_DIV>(group, x, q, s, M, K, ssr, ssg, eps, fmin_, fmax_, st);
+      return dispatch_group<__nv_bfloat16, IEEE_DIV, INT8>(group, x, q, s, M, K, ssr, ssg, eps, fmin_, fmax_, st);
     case B200_DT_F16:
-      return dispatch_group<__half, IEEE_DIV>(group, x, q, s, M, K, ssr, ssg, eps, fmin_, fmax_, st);
+      return dispatch_group<__half, IEEE_DIV, INT8>(group, x, q, s, M, K, ssr, ssg, eps, fmin_, fmax_, st);
     case B200_DT_F32:
-      return dispatch_group<float, IEEE_DIV>(group, x, q, s, M, K, ssr, ssg, eps, fmin_, fmax_, st);
+      return dispatch_group<float, IEEE_DIV, INT8>(group, x, q, s, M, K, ssr, ssg, eps, fmin_, fmax_, st);
     default:
       return B200_ERR_BAD_DTYPE;
   }
@@ -458,6 +493,13 @@ extern "C" int b200_per_token_group_quant_fp8(const void* x, int x_dtype, void* 
                                               float eps, float fp8_min, float fp8_max, void* stream) {
   return b200::quant_entry<false>(x, x_dtype, q, s, M, K, group_size, s_stride_row, s_stride_grp, eps, fp8_min,
                                   fp8_max, stream);
+}
+
+extern "C" int b200_per_token_group_quant_int8(const void* x, int x_dtype, void* q, float* s, int64_t M, int64_t K,
+                                               int64_t group_size, int64_t s_stride_row, int64_t s_stride_grp,
+                                               float eps, float int8_min, float int8_max, void* stream) {
+  return b200::quant_entry<false, true>(x, x_dtype, q, s, M, K, group_size, s_stride_row, s_stride_grp, eps, int8_min,
+                                        int8_max, stream);
 }
 
 extern "C" int b200_per_token_group_quant_fp8_ieee_div(const void* x, int x_dtype, void* q, float* s, int64_t M,

@@ -1,13 +1,13 @@
 """Drop-in for the block-FP8 subset of the reference's `sgl_kernel` package.
 
 Importing this module registers the operators under torch.ops.sgl_kernel with the reference's
-schemas verbatim (sgl-kernel/csrc/common_extension.cc:111-119,165-179,192-207), implemented for the
+schemas verbatim (sgl-kernel/csrc/common_extension.cc:111-124,165-179,192-207), implemented for the
 CUDA dispatch key by the B200 C-ABI library, and exposes the same-named Python wrappers
 (sgl-kernel/python/sgl_kernel/{gemm,moe}.py).
 """
 import torch
 
-from .gemm import fp8_blockwise_scaled_mm, sgl_per_token_group_quant_fp8
+from .gemm import fp8_blockwise_scaled_mm, sgl_per_token_group_quant_fp8, sgl_per_token_group_quant_int8
 from .moe import (apply_shuffle_mul_sum, fp8_blockwise_scaled_grouped_mm, prepare_moe_input, shuffle_rows,
                   shuffle_rows_into, shuffle_packed_scales, silu_and_mul, topk_softmax, moe_fused_gate,
                   moe_align_block_size)
@@ -18,6 +18,9 @@ _SCHEMAS = {
     "sgl_per_token_group_quant_fp8":
         "(Tensor input, Tensor output_q, Tensor output_s, int group_size, float eps, float fp8_min, "
         "float fp8_max, bool scale_ue8m0) -> ()",
+    "sgl_per_token_group_quant_int8":
+        "(Tensor input, Tensor output_q, Tensor output_s, int group_size, float eps, float int8_min, "
+        "float int8_max) -> ()",
     "fp8_blockwise_scaled_grouped_mm":
         "(Tensor output, Tensor a_ptrs, Tensor b_ptrs, Tensor out_ptrs, Tensor a_scales_ptrs, Tensor b_scales_ptrs, "
         "Tensor a, Tensor b, Tensor scales_a, Tensor scales_b, Tensor stride_a, Tensor stride_b, Tensor stride_c, "
@@ -61,6 +64,7 @@ def _moe_fused_gate_meta(input, bias, num_expert_group, topk_group, topk, num_fu
 _IMPLS = {
     "fp8_blockwise_scaled_mm": fp8_blockwise_scaled_mm,
     "sgl_per_token_group_quant_fp8": sgl_per_token_group_quant_fp8,
+    "sgl_per_token_group_quant_int8": sgl_per_token_group_quant_int8,
     "fp8_blockwise_scaled_grouped_mm": fp8_blockwise_scaled_grouped_mm,
     "prepare_moe_input": _prepare_moe_input_op,
     "shuffle_rows": shuffle_rows_into,
@@ -107,6 +111,6 @@ def register_torch_ops() -> None:
 
 register_torch_ops()
 
-__all__ = ["fp8_blockwise_scaled_mm", "sgl_per_token_group_quant_fp8", "fp8_blockwise_scaled_grouped_mm",
+__all__ = ["fp8_blockwise_scaled_mm", "sgl_per_token_group_quant_fp8", "sgl_per_token_group_quant_int8", "fp8_blockwise_scaled_grouped_mm",
            "prepare_moe_input", "shuffle_rows", "shuffle_packed_scales", "apply_shuffle_mul_sum", "silu_and_mul", "topk_softmax",
            "moe_fused_gate", "moe_align_block_size", "register_torch_ops"]

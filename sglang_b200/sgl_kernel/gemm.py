@@ -4,6 +4,7 @@ B200 C-ABI library.
 Mirrors (names, argument order, layouts, error behaviour):
   sgl_kernel.fp8_blockwise_scaled_mm          sgl-kernel/python/sgl_kernel/gemm.py:24-31
   sgl_kernel.sgl_per_token_group_quant_fp8    sgl-kernel/python/sgl_kernel/gemm.py:100-112
+  sgl_kernel.sgl_per_token_group_quant_int8   sgl-kernel/python/sgl_kernel/gemm.py:115-126
 and the argument checks of the C++ entry points they dispatch to
 (sgl-kernel/csrc/gemm/fp8_blockwise_gemm_kernel.cu:351-383,
  sgl-kernel/csrc/gemm/per_token_group_quant_8bit.cu:125-131,153-156).
@@ -121,8 +122,7 @@ def sgl_per_token_group_quant_fp8(
     _check(input.numel() % group_size == 0, "input.numel() % group_size != 0")
     _check(output_s.dim() == 2, "output_s.dim() != 2")
     _check(input.dtype in _DT, "input must be float32, float16 or bfloat16")
-    if output_q.dtype != FP8:
-        raise NotImplementedError("only float8_e4m3fn codes are built (the int8 variant belongs to the INT8 path)")
+    _check(output_q.dtype == FP8, "output_q must be float8_e4m3fn (int8 codes: sgl_per_token_group_quant_int8)")
     K = input.shape[-1]
     _check(K % group_size == 0, "the last dimension of input must be divisible by group_size")
     M = input.numel() // K
@@ -153,6 +153,42 @@ def sgl_per_token_group_quant_fp8(
             M, K, group_size, output_s.stride(0), output_s.stride(1),
             float(eps), float(fp8_min), float(fp8_max), _stream_ptr(input.device))
     _lib.check("sgl_per_token_group_quant_fp8", rc)
+
+
+def sgl_per_token_group_quant_int8(
+    input: torch.Tensor,
+    output_q: torch.Tensor,
+    output_s: torch.Tensor,
+    group_size: int,
+    eps: float,
+    int8_min: float,
+    int8_max: float,
+) -> None:
+    """In place: int8 codes into `output_q`, fp32 scales (amax / int8_max) into `output_s`; the clamped quotient is
+    truncated toward zero (sgl-kernel/python/sgl_kernel/gemm.py:115-126;
+    sgl-kernel/csrc/gemm/per_token_group_quant_8bit.cu:110-111,206-207,219-228).  `output_s` is a 2-D view
+    [rows, K/group], row- or column-major as for the FP8 operator."""
+    _check(input.is_cuda, "input must be a CUDA tensor")
+    _check(input.is_contiguous(), "input must be contiguous")
+    _check(output_q.is_cuda, "output_q must be a CUDA tensor")
+    _check(output_q.is_contiguous(), "output_q must be contiguous")
+    _check(output_q.dtype == torch.int8, "output_q must be int8")
+    _check(input.numel() % group_size == 0, "input.numel() % group_size != 0")
+    _check(output_s.dim() == 2, "output_s.dim() != 2")
+    _check(output_s.dtype == torch.float32, "output_s must be float32")
+    _check(input.dtype in _DT, "input must be float32, float16 or bfloat16")
+    K = input.shape[-1]
+    _check(K % group_size == 0, "the last dimension of input must be divisible by group_size")
+    M = input.numel() // K
+    if M == 0:
+        return
+    _check(output_s.shape[0] == M and output_s.shape[1] == K // group_size, "output_s shape mismatch")
+    with torch.cuda.device(input.device):
+        rc = _lib.lib().b200_per_token_group_quant_int8(
+            input.data_ptr(), _DT[input.dtype], output_q.data_ptr(), output_s.data_ptr(),
+            M, K, group_size, output_s.stride(0), output_s.stride(1),
+            float(eps), float(int8_min), float(int8_max), _stream_ptr(input.device))
+    _lib.check("sgl_per_token_group_quant_int8", rc)
 
 
 def fp8_blockwise_scaled_mm(

@@ -19,8 +19,9 @@ Sources executed (paths inside the reference checkout):
   python/sglang/test/test_block_fp8_deep_gemm_blackwell.py   ceil_to_ue8m0, per_token_group_quant_mxfp8,
                                             per_block_quant_mxfp8 (power-of-two scales)
   python/sglang/srt/layers/layernorm.py     RMSNorm.forward_native (producer of the linear's input)
+  test/srt/quant/test_block_int8.py         native_per_token_group_quant_int8 (int8 destination of the quantiser)
 
-Usage:  python tests/golden/make_golden.py --reference <reference checkout> [--only ue8m0|rmsnorm]
+Usage:  python tests/golden/make_golden.py --reference <reference checkout> [--only ue8m0|rmsnorm|int8]
 """
 from __future__ import annotations
 
@@ -107,7 +108,27 @@ def make_rmsnorm(reference: str):
     np.savez_compressed(os.path.join(HERE, "rmsnorm_native.npz"), **out)
 
 
+def make_int8(reference: str):
+    """native_per_token_group_quant_int8 (test/srt/quant/test_block_int8.py:13-35), executed as written."""
+    ns = {"torch": torch}
+    _extract(os.path.join(reference, "test/srt/quant/test_block_int8.py"), ["native_per_token_group_quant_int8"], ns)
+    out = {}
+    for name, dtype in (("bf16", torch.bfloat16), ("f16", torch.float16), ("f32", torch.float32)):
+        torch.manual_seed(13)
+        x = (torch.randn(19, 512) * torch.where(torch.rand(19, 512) < 1e-2, 50.0, 1.0)).to(dtype)
+        for group in (64, 128):
+            q, s = ns["native_per_token_group_quant_int8"](x, group)
+            out.update({f"{name}_g{group}_q": q.numpy(), f"{name}_g{group}_s": s.numpy()})
+        out[f"{name}_x"] = _np(x)
+    np.savez_compressed(os.path.join(HERE, "quant_int8_native.npz"), **out)
+
+
 def main(reference: str, only: str = ""):
+    if only in ("", "int8"):
+        make_int8(reference)
+        if only:
+            print("golden vectors written to", HERE)
+            return
     if only in ("", "rmsnorm"):
         make_rmsnorm(reference)
         if only:
@@ -198,6 +219,6 @@ def main(reference: str, only: str = ""):
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of the reference checkout")
-    ap.add_argument("--only", default="", choices=["", "ue8m0", "rmsnorm"], help="write just this group of vectors")
+    ap.add_argument("--only", default="", choices=["", "ue8m0", "rmsnorm", "int8"], help="write just this group of vectors")
     a = ap.parse_args()
     main(a.reference, a.only)

@@ -57,6 +57,10 @@ def test_argument_checks_return_before_any_device_work(lib):
     assert q(None, 2, one, one, 4, 256, 128, 2, 1, 1e-10, -448.0, 448.0, None) == -1
     assert q(P(8), 2, one, one, 4, 256, 128, 2, 1, 1e-10, -448.0, 448.0, None) == -5
     assert q(one, 2, one, one, 0, 256, 128, 2, 1, 1e-10, -448.0, 448.0, None) == 0       # M == 0: no-op
+    q8 = lib.b200_per_token_group_quant_int8
+    assert q8(one, 2, one, one, 4, 100, 128, 1, 1, 1e-10, -128.0, 127.0, None) == -3
+    assert q8(one, 2, one, one, 4, 192, 96, 2, 1, 1e-10, -128.0, 127.0, None) == -6
+    assert q8(None, 2, one, one, 4, 256, 128, 2, 1, 1e-10, -128.0, 127.0, None) == -1
     # GEMM: shapes, strides, alignment, dtype
     mm = lib.b200_fp8_blockwise_scaled_mm
     assert mm(one, 256, one, 256, one, 1, 4, one, 2, 1, one, 128, 2, -1, 128, 256, None) == -3
@@ -126,6 +130,7 @@ def test_operator_schemas_and_shape_functions():
     schema = str(ops.fp8_blockwise_scaled_mm.default._schema)
     assert "Tensor mat_a, Tensor mat_b, Tensor scales_a, Tensor scales_b, ScalarType out_dtype" in schema
     assert "bool scale_ue8m0" in str(ops.sgl_per_token_group_quant_fp8.default._schema)
+    assert "float int8_min, float int8_max" in str(ops.sgl_per_token_group_quant_int8.default._schema)
     assert "Tensor? blockscale_offsets" in str(ops.prepare_moe_input.default._schema)
     assert "Tensor gating_output, bool renormalize" in str(ops.topk_softmax.default._schema)
     fp8 = torch.float8_e4m3fn

@@ -271,3 +271,67 @@ def test_rmsnorm_quant_fused_equals_the_two_kernel_sequence(M, K, with_residual,
         assert same_bits(r2.cpu(), r1.cpu())
     q3, s3 = rmsnorm_per_token_group_quant_fp8(x, w, 1e-6, residual=r0.clone() if with_residual else None, **kw)
     assert same_bits(q3.cpu(), q_ref.cpu()) and torch.equal(s3.cpu(), s_ref.cpu())
+
+
+# ------------------------------------------------------------------------------------------ int8 destination
+def _check_int8(x, group=128, column_major=False):
+    from sglang_b200.sgl_kernel import sgl_per_token_group_quant_int8
+    xd = x.cuda()
+    M, K = x.shape
+    q = torch.empty(M, K, dtype=torch.int8, device="cuda")
+    s = (torch.empty(K // group, M, device="cuda").t() if column_major else torch.empty(M, K // group, device="cuda"))
+    sgl_per_token_group_quant_int8(xd, q, s, group, 1e-10, -128, 127)
+    q_ref, s_ref = O.quant_group_int8_cuda_semantics(x, group)
+    assert torch.equal(q.cpu(), q_ref), f"{(q.cpu() != q_ref).sum().item()} codes differ of {q_ref.numel()}"
+    assert same_bits(s.cpu().contiguous(), s_ref)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("group", [64, 128, 256, 512])
+@pytest.mark.parametrize("shape", [(1, 512), (7, 512), (83, 4096), (33, 5120), (2048, 7168)])
+def test_int8_destination_bit_exact(shape, group, dtype):
+    """The reference's own grid for the int8 form (sgl-kernel/tests/test_per_token_group_quant_8bit.py:268-276):
+    codes (truncated toward zero) and scales against the oracle, both scale layouts."""
+    g = torch.Generator().manual_seed(shape[0] * 31 + group)
+    x = (torch.randn(shape, generator=g) * torch.where(torch.rand(shape, generator=g) < 1e-3, 100.0, 1.0)).to(dtype)
+    _check_int8(x, group)
+    _check_int8(x, group, column_major=True)
+
+
+def test_int8_destination_golden_and_special_values():
+    from sglang_b200.layers.quantization.int8_kernel import sglang_per_token_group_quant_int8
+    g = load_golden("quant_int8_native.npz")
+    x = as_bf16(g["bf16_x"])
+    q, s = sglang_per_token_group_quant_int8(x.cuda(), 128)
+    assert torch.equal(q.cpu(), torch.from_numpy(g["bf16_g128_q"]))
+    assert same_bits(s.cpu(), t(g["bf16_g128_s"]).reshape(s.shape))
+    x = torch.zeros(8, 256, dtype=torch.bfloat16)
+    x[1, 5] = float("nan"); x[1, 7] = 3.0
+    x[2, 0] = float("inf"); x[2, 1] = 1.0
+    x[3, :128] = 1e-30
+    x[4, 3] = -65280.0; x[4, 4] = 2.0 ** -120
+    x[5, 130] = -0.0
+    x[6, :] = torch.finfo(torch.bfloat16).max
+    x[7, ::2] = 0.999; x[7, 1] = 127.0          # quotients just below an integer: truncation, not rounding
+    _check_int8(x)
+    # a scale whose significand is all ones takes the literal division
+    xf = torch.randn(64, 256).clamp(-1.0, 1.0)
+    xf[:, 0] = float(np.float32(127.0) * np.frombuffer(np.uint32(0x3fffffff).tobytes(), dtype=np.float32)[0])
+    _check_int8(xf)
+    empty_q, empty_s = sglang_per_token_group_quant_int8(torch.empty(0, 256, dtype=torch.bfloat16, device="cuda"), 128)
+    assert empty_q.shape == (0, 256) and empty_s.shape == (0, 2)
+
+
+def test_int8_destination_full_size_property():
+    """The benchmark's quantisation size (16384 x 7168): dequantised codes lie within one step below the input in
+    magnitude (truncation never rounds away from zero), and every group's largest code is 127 or -- where
+    amax / (amax / 127) rounds just below 127 -- 126."""
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn(16384, 7168, generator=g, device="cuda").to(torch.bfloat16)
+    from sglang_b200.layers.quantization.int8_kernel import sglang_per_token_group_quant_int8
+    q, s = sglang_per_token_group_quant_int8(x, 128)
+    xf = x.float().view(16384, 56, 128)
+    deq = q.float().view(16384, 56, 128) * s.unsqueeze(-1)
+    assert bool((deq.abs() <= xf.abs() * (1 + 1e-6)).all())
+    assert bool(((xf - deq).abs() <= s.unsqueeze(-1) * (1 + 1e-6)).all())
+    assert bool((q.view(16384, 56, 128).to(torch.int16).abs().amax(dim=-1) >= 126).all())

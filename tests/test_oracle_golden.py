@@ -51,6 +51,19 @@ def test_rmsnorm_matches_reference_forward_native():
         assert same_bits(y2, conv(g[f"{name}_y_res"])) and same_bits(r2, conv(g[f"{name}_r_out"]))
 
 
+def test_int8_quant_matches_reference_native():
+    """native_per_token_group_quant_int8 (test/srt/quant/test_block_int8.py:13-35) executed by
+    make_golden.py --only int8 vs the oracle's restatement of the CUDA kernel's int8 destination: same codes, same
+    scales (no all-zero group in these inputs, the one case where the torch twin clamps eps in the input type)."""
+    g = load_golden("quant_int8_native.npz")
+    for name, conv in (("bf16", as_bf16), ("f16", as_f16), ("f32", t)):
+        x = conv(g[f"{name}_x"])
+        for group in (64, 128):
+            q, s = O.quant_group_int8_cuda_semantics(x, group)
+            assert torch.equal(q, torch.from_numpy(g[f"{name}_g{group}_q"]))
+            assert same_bits(s, t(g[f"{name}_g{group}_s"]).reshape(s.shape))
+
+
 def test_quant_known_answer():
     """test/srt/quant/test_fp8_kernel.py:90-100: scales equal, <1e-4 of codes differ."""
     g = load_golden("known_answer.npz")
