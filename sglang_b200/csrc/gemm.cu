@@ -624,6 +624,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cu
   const long long split_from = p.split_k == 1 ? dense_tiles : p.tail_first;
   const long long tiles = GROUPED ? static_cast<long long>(m_blocks + p.num_experts) * n_blocks
                                   : split_from + (dense_tiles - split_from) * p.split_k;
+  if (tiles > 0x7fffffffLL) return B200_ERR_TOO_LARGE;   // the kernels count tiles in 32 bits
   const int grid = tiles < sm_count() ? static_cast<int>(tiles) : sm_count();
   kern<<<grid, C::kThreads, C::kSmemBytes, stream>>>(ma, mb, p);
   B200_CUDA_TRY(cudaGetLastError());

@@ -638,6 +638,7 @@ int launch_mx(const CUtensorMap& ma, const CUtensorMap& mb, const MxParams& p, c
   // grouped: the tile count lives on the device; row tiles <= ceil(rows / tile) + problems bounds the grid
   const long long m_tiles = (p.M + BM * MSUB - 1) / (BM * MSUB) + (GROUPED ? p.num_problems : 0);
   const long long tiles = m_tiles * ((p.N + BN - 1) / BN);
+  if (tiles > 0x7fffffffLL) return B200_ERR_TOO_LARGE;   // the kernels count tiles in 32 bits
   const int grid = tiles < sm_count() ? static_cast<int>(tiles) : sm_count();
   kern<<<grid, (BN == 256 && MSUB == 1) ? kThreadsMxSilu : kThreadsMx, C::kSmem, stream>>>(ma, mb, p);
   B200_CUDA_TRY(cudaGetLastError());
@@ -677,6 +678,7 @@ int launch_mx_silu(const void* a, int64_t lda, const void* b, int64_t ldb, const
   }
   const long long m_tiles = (p.M + BM - 1) / BM + p.num_problems;
   const long long tiles = m_tiles * ((p.N + 127) / 128);
+  if (tiles > 0x7fffffffLL) return B200_ERR_TOO_LARGE;   // the kernels count tiles in 32 bits
   const int grid = tiles < sm_count() ? static_cast<int>(tiles) : sm_count();
   kern<<<grid, kThreadsMxSilu, C::kSmem, stream>>>(ma, mb, p);
   B200_CUDA_TRY(cudaGetLastError());

@@ -487,6 +487,7 @@ int launch_swap(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& 
   const long long n_tiles = (p.N + BLOCK_W - 1) / BLOCK_W;
   // grouped: the tile count lives on the device; token tiles <= ceil(rows/TN) + experts bounds the grid
   const long long tiles = GROUPED ? (m_tiles + p.num_experts) * n_tiles : m_tiles * n_tiles * p.split_k;
+  if (tiles > 0x7fffffffLL) return B200_ERR_TOO_LARGE;   // the kernels count tiles in 32 bits
   const int grid = tiles < sm_count() ? static_cast<int>(tiles) : sm_count();
   kern<<<grid, C::kThreads, C::kSmemBytes, stream>>>(mw, mx, p);
   B200_CUDA_TRY(cudaGetLastError());
